@@ -1,0 +1,239 @@
+/*
+ * kvcache_b200.h — C ABI of the B200 (sm_100a) retrieval-sparse decode attention library.
+ *
+ * One shared library, plain pointers and sizes, no C++ or torch types. Every entry point
+ *   - takes DEVICE pointers unless a parameter says "host",
+ *   - takes the CUDA device ordinal and the stream (a cudaStream_t passed as void*),
+ *   - validates shapes, strides and alignment on the host and returns a kvb_status
+ *     BEFORE anything is launched when they are wrong,
+ *   - never allocates, never frees, never synchronises the device, never throws
+ *     (the one exception, kvb_device_status, says so).
+ *
+ * Tensor naming: B batch, Hq query heads, Hkv KV heads, G = Hq / Hkv, D head dim (128),
+ * T cached ("history") tokens, C partial channels (even, <= 128), k top-k, S length of a
+ * final index list. "bf16" is the 16-bit brain float; rows are contiguous along D.
+ *
+ * Reference interfaces these entry points stand in for (paths inside littlexi001/kv_cache):
+ *   QCK  = ymluo/projects/qwen3_top2_head_limit3_ppl/src/qabs_cuda_kernels.py
+ *   EVAL = ymluo/projects/qwen3_top2_head_limit3_ppl/src/evaluate_qwen3_top2_head_limit3_ppl.py
+ */
+#ifndef KVCACHE_B200_H
+#define KVCACHE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum kvb_status {
+  KVB_OK = 0,
+  KVB_BAD_SHAPE = 1,          /* a dimension is zero/negative/unsupported                */
+  KVB_BAD_ALIGN = 2,          /* a pointer or stride breaks the alignment rule stated     */
+  KVB_BAD_DEVICE = 3,         /* device ordinal out of range or cudaSetDevice failed      */
+  KVB_WORKSPACE_TOO_SMALL = 4,
+  KVB_TIMEOUT = 5,            /* a bounded device-side wait gave up (see kvb_device_status)*/
+  KVB_CUDA_ERROR = 6,         /* a CUDA runtime call or a launch returned an error        */
+  KVB_BAD_ARG = 7             /* null pointer where one is required, bad flag, ...        */
+} kvb_status;
+
+/* Library version (major*10000 + minor*100 + patch) and a static string for a status. */
+int kvb_version(void);
+const char* kvb_status_string(int status);
+
+/* Reads and clears the sticky per-device status word that kernels set when a bounded wait
+ * (mbarrier / pipeline) runs out. SYNCHRONISES the device; meant for health checks and
+ * tests, never for the hot path. *out_status receives a kvb_status. */
+int kvb_device_status(int device, int* out_status);
+
+/* ---------------------------------------------------------------------------------------
+ * Stage 1 — quantize / pack K to int4 over C chosen channels, per-token symmetric scale.
+ *
+ * No counterpart in the reference (its K stays bf16); the closest structure is the
+ * incrementally appended side copy of K, EVAL:2018-2042 (SparQMeanState.key_dim_major).
+ *
+ *   key          bf16 [B,Hkv,T,D] view: element strides key_sb/key_sh/key_st, D contiguous;
+ *                the pointer and all strides must be multiples of 8 elements (16 bytes).
+ *   channel_idx  int32 [Hkv,C], ascending per head, each in [0,D).
+ *   packed       uint8 cache [B,Hkv,cap,C/2]; byte strides packed_sb/packed_sh; token
+ *                stride is C/2. Byte j of a token: low nibble = code of channel_idx[2j],
+ *                high nibble = code of channel_idx[2j+1], two's complement, in [-7,7].
+ *   scale        fp32 cache [B,Hkv,cap]; element strides scale_sb/scale_sh.
+ *   t_dst        first destination token in the caches (rows t_dst .. t_dst+T-1 are written).
+ * scale = max(absmax, 2^-24) / 7 (IEEE division), code = clamp(rint(x / scale), -7, 7).
+ * kvb_quantize_append is the T == 1 form used once per decode step.
+ * ------------------------------------------------------------------------------------- */
+int kvb_quantize_pack(const void* key, int64_t key_sb, int64_t key_sh, int64_t key_st,
+                      const int32_t* channel_idx,
+                      uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                      float* scale, int64_t scale_sb, int64_t scale_sh,
+                      int B, int Hkv, int T, int D, int C, int64_t t_dst,
+                      int device, void* stream);
+
+int kvb_quantize_append(const void* key_row, int64_t key_sb, int64_t key_sh,
+                        const int32_t* channel_idx,
+                        uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                        float* scale, int64_t scale_sb, int64_t scale_sh,
+                        int B, int Hkv, int D, int C, int64_t t_dst,
+                        int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Stage 2 — decode scoring: one query token per sequence against all T packed keys.
+ *
+ * Stands in for partial_scores / partial_scores_dim_major (QCK:654-665; kernels QCK:63-158;
+ * torch form EVAL:4443-4446) with the channel list as an input like dim_indices there, but
+ * computed exactly in integers on the int4 cache:
+ *   qcode[b,h,c] = clamp(rint(q[b,h,ch[h/G][c]] / qscale[b,h]), -127, 127),
+ *   qscale = max(absmax_c, 2^-24) / 127,
+ *   acc[b,h,t]  = sum_c qcode * code                       (int32, exact)
+ *   deq[b,h,t]  = (float(acc) * scale[b,h/G,t]) * qscale[b,h]   (two rounded fp32 products)
+ *   gmax[b,g,t] = max over the G heads of group g of deq, with -0 stored as +0.
+ *
+ *   query     bf16 [B,Hq,D], element strides q_sb/q_sh, D contiguous.
+ *   packed/scale/channel_idx as in stage 1. For the streaming fast path (C in {32,64,128},
+ *   G in {1,2,4,8}) packed must be 16-byte aligned with 16-byte-multiple strides and scale
+ *   16-byte aligned with strides that are multiples of 4 elements; other even C <= 128 and
+ *   other G <= 16 take a slower generic kernel.
+ *   gmax_out  fp32 [B,Hkv,T] or NULL; acc_out int32 [B,Hq,T] or NULL; deq_out fp32 [B,Hq,T]
+ *   or NULL — all dense. At least one must be given.
+ *   hist_out  uint32 [B*Hkv, 4096] or NULL: when given (and gmax_out is given) the kernel
+ *   ADDS the histogram of the top 12 bits of the order-preserving key of gmax into it
+ *   (the caller zeroes it); kvb_select_topk can then skip its own histogram pass.
+ * ------------------------------------------------------------------------------------- */
+int kvb_score_decode(const void* query, int64_t q_sb, int64_t q_sh,
+                     const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                     const float* scale, int64_t scale_sb, int64_t scale_sh,
+                     const int32_t* channel_idx,
+                     int B, int Hq, int Hkv, int T, int D, int C,
+                     float* gmax_out, int32_t* acc_out, float* deq_out,
+                     uint32_t* hist_out,
+                     int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Stage 3 — top-k select per row, order (score descending, index ascending).
+ *
+ * Stands in for the torch.topk candidate selection of the reference (EVAL:4448, count rule
+ * EVAL:4423) with the tie-break pinned: among equal scores the lower index wins, and the
+ * output is ordered by (score desc, index asc). -0 and +0 compare equal.
+ *
+ *   scores    fp32 [R,T] rows (row_stride elements apart), no NaN.
+ *   payload   int32 [R,T] (same row stride) or NULL. With NULL the index of column t is
+ *             t + idx_offset; otherwise it is payload[r,t] (used to merge per-rank candidate
+ *             lists that carry global token ids). Indices must be unique within a row and
+ *             fit in int32.
+ *   k         requested count; kk = min(k, T) entries are produced per row. k <= 16384.
+ *   out_idx32 int32 [R,kk] or NULL; out_idx64 int64 [R,kk] or NULL; out_scores fp32 [R,kk]
+ *             or NULL (dense, row stride kk).
+ *   hist_in   uint32 [R,4096] histogram already produced by kvb_score_decode, or NULL.
+ *   workspace >= kvb_select_topk_workspace_bytes(R, T, k) bytes, 256-byte aligned.
+ * ------------------------------------------------------------------------------------- */
+size_t kvb_select_topk_workspace_bytes(int R, int T, int k);
+
+int kvb_select_topk(const float* scores, int64_t row_stride, const int32_t* payload,
+                    int R, int T, int k, int64_t idx_offset,
+                    int32_t* out_idx32, int64_t* out_idx64, float* out_scores,
+                    const uint32_t* hist_in,
+                    void* workspace, size_t workspace_bytes,
+                    int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Final index list — selected || sink || recent || self with protected ranges invalidated.
+ * Restates _qabs_final_indices_from_selected (EVAL:2938-2982); with append_protected != 0,
+ * _qabs_final_indices_append_protected (EVAL:2985-3022), which keeps the selected entries
+ * valid even inside the protected ranges.
+ *
+ *   sel_idx     int32 [R,kk] selected history indices; sel_valid uint8 [R,kk] or NULL (all valid)
+ *   out_idx     int32 [R,S], out_valid uint8 [R,S] with
+ *               S = kvb_final_index_count(kk, history_count, sink, recent, keep_self).
+ * ------------------------------------------------------------------------------------- */
+int kvb_final_index_count(int kk, int history_count, int protect_sink, int protect_recent,
+                          int keep_self);
+
+int kvb_build_final_indices(const int32_t* sel_idx, const uint8_t* sel_valid, int R, int kk,
+                            int history_count, int key_count,
+                            int protect_sink, int protect_recent, int keep_self,
+                            int append_protected,
+                            int32_t* out_idx, uint8_t* out_valid,
+                            int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Stage 4 — exact attention over gathered rows (split over the list, log-sum-exp merge).
+ *
+ * Stands in for final_attention (QCK:694-705, kernel QCK:335-419) and the torch form
+ * _qabs_attention_from_final_indices (EVAL:4612-4647); like the Triton kernels of the
+ * reference it reads UN-repeated K/V (kv_head = head / G,
+ * run_longrange_book_index_sparse_eval.py:879).
+ *
+ *   query    bf16 [B,Hq,D] (strides q_sb/q_sh); key/value bf16 [B,Hkv,Tk,D] views with
+ *            element strides *_sb/*_sh/*_st, D = 128 contiguous, all multiples of 8.
+ *   indices  [B,Hi,S] with Hi == Hkv (one list per KV head, shared by its G query heads) or
+ *            Hi == Hq (one list per query head, the reference layout); int32, or int64 when
+ *            idx_is_i64 != 0; dense.
+ *   valid    uint8 [B,Hi,S] or NULL (all valid). Entries that are invalid or outside
+ *            [0,Tk) get weight zero (QCK:366-367).
+ *   mask     fp32 additive mask rows [B,Tk] (element stride mask_sb) or NULL
+ *            (the torch form adds mask[b, 0, 0, idx], EVAL:4637-4641).
+ *   out      bf16 [B,1,Hq,D] dense, or NULL.
+ *   out_partial fp32 [B,Hq,D+2] or NULL: un-normalised accumulator scaled to the row
+ *            maximum m, then m, then l = sum exp(s - m) — what a sequence shard contributes
+ *            (kvb_lse_merge combines shards). A row with no valid entry gives zeros in out
+ *            (QCK:388,404) and (0, -inf, 0) in out_partial.
+ *   workspace >= kvb_sparse_attend_workspace_bytes(B, Hq, Hi, S), 256-byte aligned.
+ * ------------------------------------------------------------------------------------- */
+size_t kvb_sparse_attend_workspace_bytes(int B, int Hq, int Hi, int S);
+
+int kvb_sparse_attend(const void* query, int64_t q_sb, int64_t q_sh,
+                      const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+                      const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st,
+                      const void* indices, int idx_is_i64, const uint8_t* valid,
+                      const float* mask, int64_t mask_sb,
+                      int B, int Hq, int Hkv, int Hi, int Tk, int D, int S,
+                      float scaling,
+                      void* out, float* out_partial,
+                      void* workspace, size_t workspace_bytes,
+                      int device, void* stream);
+
+/* Combine N shard partials [N,B,Hq,D+2] (layout of out_partial above) into bf16 [B,1,Hq,D]:
+ * o = sum_r e^{m_r-m} o_r / sum_r e^{m_r-m} l_r, shards with l == 0 ignored. No reference
+ * counterpart (the reference has no sequence sharding). */
+int kvb_lse_merge(const float* partials, int N, int B, int Hq, int D, void* out,
+                  int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused decode step for one layer: quantize-append of the new K row, score, select,
+ * final index list, attend — all enqueued on `stream`, nothing else touched.
+ * Equivalent to the sequence _qabs_candidate_attention_forward runs (EVAL:4400-4502) with the
+ * int4 scorer in place of its fp32 partial score and the group-max select in place of its
+ * per-head torch.topk. `key`/`value` hold key_count = history+1 rows (the last row is the
+ * token being decoded, EVAL:4421-4425); the packed cache holds rows [0, history) on entry
+ * and, when append_self != 0, row `history` on return.
+ * ------------------------------------------------------------------------------------- */
+typedef struct kvb_decode_step_params {
+  const void* query;  int64_t q_sb, q_sh;                 /* bf16 [B,Hq,D]            */
+  const void* key;    int64_t k_sb, k_sh, k_st;           /* bf16 [B,Hkv,key_count,D] */
+  const void* value;  int64_t v_sb, v_sh, v_st;
+  uint8_t* packed;    int64_t packed_sb, packed_sh;       /* int4 cache               */
+  float* scale;       int64_t scale_sb, scale_sh;
+  const int32_t* channel_idx;                             /* int32 [Hkv,C]            */
+  const float* mask;  int64_t mask_sb;                    /* fp32 [B,key_count] or NULL */
+  int B, Hq, Hkv, D, C;
+  int history_count;                                      /* T; key_count = T + 1     */
+  int top_k;
+  int protect_sink, protect_recent, keep_self, append_protected;
+  int append_self;
+  float scaling;
+  void* out;                                              /* bf16 [B,1,Hq,D]          */
+  int32_t* sel_idx_out;                                   /* int32 [B,Hkv,kk] or NULL */
+  void* workspace; size_t workspace_bytes;
+} kvb_decode_step_params;
+
+size_t kvb_decode_step_workspace_bytes(int B, int Hq, int Hkv, int history_count, int top_k,
+                                       int protect_sink, int protect_recent, int keep_self);
+
+int kvb_decode_step(const kvb_decode_step_params* p, int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVCACHE_B200_H */

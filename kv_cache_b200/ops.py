@@ -1,0 +1,403 @@
+"""The four operators of the retrieval-sparse decode path on torch CUDA tensors.
+
+Layouts follow the reference (paths inside littlexi001/kv_cache,
+EVAL = ymluo/projects/qwen3_top2_head_limit3_ppl/src/evaluate_qwen3_top2_head_limit3_ppl.py,
+QCK = .../src/qabs_cuda_kernels.py):
+
+* ``key`` / ``value``  bf16 ``[B, Hkv, T, D]`` as the HF cache holds them (NOT repeated to query
+  heads, unlike EVAL:6248-6251); views with arbitrary batch/head/token strides are accepted.
+* ``query``            bf16 ``[B, Hq, D]`` (``[B, Hq, 1, D]`` is accepted and squeezed, EVAL:4424).
+* scores               ``[B, H, T]`` (QCK:654-665), indices int64 ``[B, H, S]`` + bool valid
+  (QCK:694-705), attention output ``[B, 1, Hq, D]`` (EVAL:4502).
+
+Every function launches on the current torch stream of the tensors' device and calls the C-ABI
+library; there is no eager/torch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _native
+from ._native import DecodeStepParams, check
+
+HIST_BINS = 4096
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _dev(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise RuntimeError("kv_cache_b200 operators need CUDA tensors; there is no CPU path")
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _rows_contiguous(t: torch.Tensor) -> torch.Tensor:
+    """[.., T, D] with contiguous D and 16-byte aligned strides, copying only when needed (QCK:595-599)."""
+    ok = t.stride(-1) == 1 and all(s % 8 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
+    return t if ok else t.contiguous()
+
+
+def _query3(query: torch.Tensor) -> torch.Tensor:
+    if query.dim() == 4:
+        if query.shape[2] != 1:
+            raise RuntimeError("decode operators take one query token per sequence")
+        query = query[:, :, 0, :]
+    if query.dim() != 3:
+        raise RuntimeError("query must have shape [batch, heads, dim]")
+    return _rows_contiguous(query)
+
+
+# ------------------------------------------------------------------------------------------
+# channel choice (host-side policy; an input to every kernel, like dim_indices in QCK:659-665)
+# ------------------------------------------------------------------------------------------
+
+def choose_channels(key: torch.Tensor, num_channels: int) -> torch.Tensor:
+    """Per KV head, the ``num_channels`` head-dim channels with the largest mean |K| over (B, T);
+    ties go to the lower channel; returned ascending as int32 ``[Hkv, C]``."""
+    mean_abs = key.float().abs().mean(dim=(0, 2))                       # [Hkv, D]
+    order = torch.sort(mean_abs, dim=-1, descending=True, stable=True).indices[:, :num_channels]
+    return torch.sort(order, dim=-1).values.to(torch.int32).contiguous()
+
+
+# ------------------------------------------------------------------------------------------
+# stage 1: quantize / pack
+# ------------------------------------------------------------------------------------------
+
+def alloc_side_cache(batch: int, kv_heads: int, capacity: int, num_channels: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """int4 side cache for ``capacity`` tokens: packed uint8 ``[B,Hkv,cap,C/2]`` and fp32 scale
+    ``[B,Hkv,cap]``; capacity is rounded up to 256 tokens so every row start is 16-byte aligned."""
+    cap = (int(capacity) + 255) // 256 * 256
+    packed = torch.empty((batch, kv_heads, cap, num_channels // 2), dtype=torch.uint8, device=device)
+    scale = torch.empty((batch, kv_heads, cap), dtype=torch.float32, device=device)
+    return packed, scale
+
+
+def _check_side_cache(packed: torch.Tensor, scale: torch.Tensor, C_: int) -> None:
+    if packed.dtype != torch.uint8 or scale.dtype != torch.float32:
+        raise RuntimeError("packed must be uint8 and scale float32")
+    if packed.dim() != 4 or scale.dim() != 3 or packed.shape[-1] * 2 != C_:
+        raise RuntimeError("side cache shapes must be [B,Hkv,cap,C/2] and [B,Hkv,cap]")
+    if packed.stride(3) != 1 or packed.stride(2) != C_ // 2 or scale.stride(2) != 1:
+        raise RuntimeError("side cache token rows must be dense")
+
+
+def quantize(key: torch.Tensor, channel_idx: torch.Tensor,
+             out: Optional[tuple[torch.Tensor, torch.Tensor]] = None, t_dst: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """int4 codes (two per byte) of ``key[..., channel_idx]`` with one fp32 scale per token.
+
+    Returns ``(packed[B,Hkv,T,C/2], scale[B,Hkv,T])`` views of a freshly allocated side cache, or
+    writes rows ``t_dst .. t_dst+T`` of the cache given in ``out`` and returns it."""
+    if key.dtype != torch.bfloat16 or key.dim() != 4:
+        raise RuntimeError("key must be bf16 [B,Hkv,T,D]")
+    B, Hkv, T, D = key.shape
+    C_ = int(channel_idx.shape[-1])
+    key = _rows_contiguous(key)
+    channel_idx = channel_idx.to(device=key.device, dtype=torch.int32).contiguous()
+    if out is None:
+        packed, scale = alloc_side_cache(B, Hkv, t_dst + T, C_, key.device)
+    else:
+        packed, scale = out
+    _check_side_cache(packed, scale, C_)
+    if packed.shape[2] < t_dst + T:
+        raise RuntimeError("side cache too small")
+    check(_native.lib().kvb_quantize_pack(
+        key.data_ptr(), key.stride(0), key.stride(1), key.stride(2), channel_idx.data_ptr(),
+        packed.data_ptr(), packed.stride(0), packed.stride(1),
+        scale.data_ptr(), scale.stride(0), scale.stride(1),
+        B, Hkv, T, D, C_, t_dst, _dev(key), _stream(key.device)), "kvb_quantize_pack")
+    if out is None:
+        return packed[:, :, : t_dst + T], scale[:, :, : t_dst + T]
+    return packed, scale
+
+
+def quantize_append(key_row: torch.Tensor, channel_idx: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
+                    t_dst: int) -> None:
+    """Quantizes the single new row ``key_row[B,Hkv,1,D]`` into row ``t_dst`` of the side cache."""
+    if key_row.dim() == 4:
+        key_row = key_row[:, :, 0, :]
+    key_row = _rows_contiguous(key_row)
+    B, Hkv, D = key_row.shape
+    C_ = int(channel_idx.shape[-1])
+    _check_side_cache(packed, scale, C_)
+    check(_native.lib().kvb_quantize_append(
+        key_row.data_ptr(), key_row.stride(0), key_row.stride(1), channel_idx.data_ptr(),
+        packed.data_ptr(), packed.stride(0), packed.stride(1),
+        scale.data_ptr(), scale.stride(0), scale.stride(1),
+        B, Hkv, D, C_, t_dst, _dev(key_row), _stream(key_row.device)), "kvb_quantize_append")
+
+
+def unpack_codes(packed: torch.Tensor) -> torch.Tensor:
+    """int8 codes ``[..., C]`` of a packed tensor ``[..., C/2]`` (helper for inspection and tests)."""
+    lo = (packed << 4).view(torch.int8) >> 4
+    hi = packed.view(torch.int8) >> 4
+    return torch.stack((lo, hi), dim=-1).flatten(-2)
+
+
+# ------------------------------------------------------------------------------------------
+# stage 2: score
+# ------------------------------------------------------------------------------------------
+
+@dataclass
+class ScoreResult:
+    acc: Optional[torch.Tensor]    # int32 [B,Hq,T] exact partial dot products
+    deq: Optional[torch.Tensor]    # fp32  [B,Hq,T] dequantised scores
+    gmax: Optional[torch.Tensor]   # fp32  [B,Hkv,T] max over each GQA group
+    hist: Optional[torch.Tensor]   # uint32-as-int32 [B*Hkv,4096] histogram of gmax keys
+
+
+def score(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
+          history_count: Optional[int] = None, *, want_acc: bool = True, want_deq: bool = True,
+          want_gmax: bool = True, want_hist: bool = False) -> ScoreResult:
+    """Exact int32 partial QK of one query token against the first ``history_count`` packed keys."""
+    query = _query3(query)
+    if query.dtype != torch.bfloat16:
+        raise RuntimeError("query must be bf16")
+    B, Hq, D = query.shape
+    Hkv = packed.shape[1]
+    C_ = int(channel_idx.shape[-1])
+    _check_side_cache(packed, scale, C_)
+    T = packed.shape[2] if history_count is None else int(history_count)
+    if T > packed.shape[2]:
+        raise RuntimeError("history_count exceeds the side cache")
+    dev = query.device
+    acc = torch.empty((B, Hq, T), dtype=torch.int32, device=dev) if want_acc else None
+    deq = torch.empty((B, Hq, T), dtype=torch.float32, device=dev) if want_deq else None
+    gmax = torch.empty((B, Hkv, T), dtype=torch.float32, device=dev) if (want_gmax or want_hist) else None
+    hist = torch.zeros((B * Hkv, HIST_BINS), dtype=torch.int32, device=dev) if want_hist else None
+    channel_idx = channel_idx.to(device=dev, dtype=torch.int32).contiguous()
+    check(_native.lib().kvb_score_decode(
+        query.data_ptr(), query.stride(0), query.stride(1),
+        packed.data_ptr(), packed.stride(0), packed.stride(1),
+        scale.data_ptr(), scale.stride(0), scale.stride(1), channel_idx.data_ptr(),
+        B, Hq, Hkv, T, D, C_, _ptr(gmax), _ptr(acc), _ptr(deq), _ptr(hist),
+        _dev(query), _stream(dev)), "kvb_score_decode")
+    return ScoreResult(acc, deq, gmax, hist)
+
+
+# ------------------------------------------------------------------------------------------
+# stage 3: select
+# ------------------------------------------------------------------------------------------
+
+def select(scores: torch.Tensor, k: int, *, payload: Optional[torch.Tensor] = None, idx_offset: int = 0,
+           hist: Optional[torch.Tensor] = None, return_scores: bool = False,
+           index_dtype: torch.dtype = torch.int64):
+    """Top-``k`` columns of every row of ``scores[..., T]`` ordered by (score desc, index asc).
+
+    Returns indices ``[..., min(k,T)]`` (and the scores when asked). ``payload`` (int32, same
+    shape as scores) replaces the column number as the index that is returned and tie-broken."""
+    if scores.dtype != torch.float32:
+        raise RuntimeError("scores must be float32")
+    lead = scores.shape[:-1]
+    T = scores.shape[-1]
+    s2 = scores.reshape(-1, T)
+    if s2.stride(-1) != 1:
+        s2 = s2.contiguous()
+    R = s2.shape[0]
+    kk = min(int(k), T)
+    dev = scores.device
+    p2 = None
+    if payload is not None:
+        p2 = payload.reshape(-1, T).to(torch.int32)
+        if p2.stride() != s2.stride():
+            p2 = p2.contiguous()
+            s2 = s2.contiguous()
+    lib = _native.lib()
+    ws_bytes = lib.kvb_select_topk_workspace_bytes(R, T, kk)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    out32 = torch.empty((R, kk), dtype=torch.int32, device=dev) if index_dtype == torch.int32 else None
+    out64 = torch.empty((R, kk), dtype=torch.int64, device=dev) if index_dtype == torch.int64 else None
+    if out32 is None and out64 is None:
+        raise RuntimeError("index_dtype must be torch.int32 or torch.int64")
+    outs = torch.empty((R, kk), dtype=torch.float32, device=dev) if return_scores else None
+    check(lib.kvb_select_topk(
+        s2.data_ptr(), s2.stride(0), _ptr(p2), R, T, int(k), int(idx_offset),
+        _ptr(out32), _ptr(out64), _ptr(outs), _ptr(hist), ws.data_ptr(), ws_bytes,
+        _dev(scores), _stream(dev)), "kvb_select_topk")
+    idx = (out32 if out32 is not None else out64).reshape(*lead, kk)
+    if return_scores:
+        return idx, outs.reshape(*lead, kk)
+    return idx
+
+
+# ------------------------------------------------------------------------------------------
+# final index list (EVAL:2938-3022)
+# ------------------------------------------------------------------------------------------
+
+def build_final_indices(selected: torch.Tensor, selected_valid: Optional[torch.Tensor], history_count: int,
+                        key_count: int, protect_sink: int = 0, protect_recent: int = 0, keep_self: bool = True,
+                        append_protected: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """``selected ‖ sink ‖ recent ‖ self`` as int32 ``[..., S]`` with a bool validity mask."""
+    lead = selected.shape[:-1]
+    kk = selected.shape[-1]
+    sel = selected.reshape(-1, kk).to(torch.int32).contiguous()
+    sv = None if selected_valid is None else selected_valid.reshape(-1, kk).to(torch.uint8).contiguous()
+    R = sel.shape[0]
+    lib = _native.lib()
+    S = lib.kvb_final_index_count(kk, history_count, protect_sink, protect_recent, int(keep_self))
+    dev = selected.device
+    out_idx = torch.empty((R, S), dtype=torch.int32, device=dev)
+    out_valid = torch.empty((R, S), dtype=torch.uint8, device=dev)
+    check(lib.kvb_build_final_indices(
+        sel.data_ptr(), _ptr(sv), R, kk, history_count, key_count, protect_sink, protect_recent,
+        int(keep_self), int(append_protected), out_idx.data_ptr(), out_valid.data_ptr(),
+        _dev(selected), _stream(dev)), "kvb_build_final_indices")
+    return out_idx.reshape(*lead, S), out_valid.reshape(*lead, S).bool()
+
+
+# ------------------------------------------------------------------------------------------
+# stage 4: sparse attention
+# ------------------------------------------------------------------------------------------
+
+def _mask_rows(attention_mask: Optional[torch.Tensor], B: int, Tk: int) -> Optional[torch.Tensor]:
+    """HF additive mask ``[B,1,Tq,Tk']`` -> fp32 rows ``[B,Tk]`` of its first query row (EVAL:4637-4641)."""
+    if attention_mask is None:
+        return None
+    m = attention_mask
+    if m.dim() == 4:
+        if m.shape[1] != 1:
+            raise RuntimeError("per-head attention masks are not supported")
+        m = m[:, 0, 0, :Tk]
+    elif m.dim() == 2:
+        m = m[:, :Tk]
+    else:
+        raise RuntimeError("attention_mask must be [B,1,Tq,Tk] or [B,Tk]")
+    if m.shape[0] == 1 and B != 1:
+        m = m.expand(B, -1)
+    return m.to(torch.float32).contiguous()
+
+
+def sparse_attend(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, indices: torch.Tensor,
+                  valid: Optional[torch.Tensor] = None, scaling: Optional[float] = None,
+                  attention_mask: Optional[torch.Tensor] = None, return_partial: bool = False):
+    """Exact softmax attention of one query token over ``key/value[..., indices, :]``.
+
+    ``indices`` is ``[B,Hkv,S]`` (one list per KV head, shared by its query heads) or ``[B,Hq,S]``
+    (the layout of QCK:694-705), int32 or int64. Returns bf16 ``[B,1,Hq,D]``; with
+    ``return_partial`` returns fp32 ``[B,Hq,D+2]`` = (un-normalised output, max, sum) instead."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    if key.dim() != 4 or value.shape != key.shape:
+        raise RuntimeError("key/value must be [B,Hkv,Tk,D] of equal shape")
+    if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16 or query.dtype != torch.bfloat16:
+        raise RuntimeError("query/key/value must be bf16")
+    Hkv, Tk = key.shape[1], key.shape[2]
+    key = _rows_contiguous(key)
+    value = _rows_contiguous(value)
+    if indices.dim() != 3 or indices.shape[0] != B:
+        raise RuntimeError("indices must be [B,H,S]")
+    Hi, S = indices.shape[1], indices.shape[2]
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("indices must be int32 or int64")
+    indices = indices.contiguous()
+    v8 = None if valid is None else valid.to(torch.uint8).contiguous()
+    if scaling is None:
+        scaling = float(D) ** -0.5
+    dev = query.device
+    mask = _mask_rows(attention_mask, B, Tk)
+    lib = _native.lib()
+    ws_bytes = lib.kvb_sparse_attend_workspace_bytes(B, Hq, Hi, S)
+    if ws_bytes == 0:
+        raise RuntimeError("kvb_sparse_attend: unsupported shape")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    out = None if return_partial else torch.empty((B, 1, Hq, D), dtype=torch.bfloat16, device=dev)
+    part = torch.empty((B, Hq, D + 2), dtype=torch.float32, device=dev) if return_partial else None
+    check(lib.kvb_sparse_attend(
+        query.data_ptr(), query.stride(0), query.stride(1),
+        key.data_ptr(), key.stride(0), key.stride(1), key.stride(2),
+        value.data_ptr(), value.stride(0), value.stride(1), value.stride(2),
+        indices.data_ptr(), int(indices.dtype == torch.int64), _ptr(v8),
+        _ptr(mask), 0 if mask is None else mask.stride(0),
+        B, Hq, Hkv, Hi, Tk, D, S, float(scaling), _ptr(out), _ptr(part), ws.data_ptr(), ws_bytes,
+        _dev(query), _stream(dev)), "kvb_sparse_attend")
+    return part if return_partial else out
+
+
+def lse_merge(partials: torch.Tensor) -> torch.Tensor:
+    """Combines shard partials fp32 ``[N,B,Hq,D+2]`` into bf16 ``[B,1,Hq,D]``."""
+    N, B, Hq, PW = partials.shape
+    partials = partials.contiguous()
+    out = torch.empty((B, 1, Hq, PW - 2), dtype=torch.bfloat16, device=partials.device)
+    check(_native.lib().kvb_lse_merge(partials.data_ptr(), N, B, Hq, PW - 2, out.data_ptr(),
+                                      _dev(partials), _stream(partials.device)), "kvb_lse_merge")
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# fused decode step
+# ------------------------------------------------------------------------------------------
+
+class DecodeStep:
+    """One layer's decode step (append, score, select, final list, attend) through
+    ``kvb_decode_step`` with a workspace that is allocated once and reused."""
+
+    def __init__(self, top_k: int, protect_sink: int = 0, protect_recent: int = 0, keep_self: bool = True,
+                 append_protected: bool = False, append_self: bool = True):
+        self.top_k = int(top_k)
+        self.protect_sink = int(protect_sink)
+        self.protect_recent = int(protect_recent)
+        self.keep_self = bool(keep_self)
+        self.append_protected = bool(append_protected)
+        self.append_self = bool(append_self)
+        self._ws: Optional[torch.Tensor] = None
+
+    def workspace(self, B: int, Hq: int, Hkv: int, history_count: int, device) -> torch.Tensor:
+        need = _native.lib().kvb_decode_step_workspace_bytes(
+            B, Hq, Hkv, history_count, self.top_k, self.protect_sink, self.protect_recent, int(self.keep_self))
+        if self._ws is None or self._ws.numel() < need or self._ws.device != torch.device(device):
+            # headroom so that a growing history does not reallocate every step
+            self._ws = torch.empty(int(need * 1.25) + 4096, dtype=torch.uint8, device=device)
+        return self._ws
+
+    def __call__(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, packed: torch.Tensor,
+                 scale: torch.Tensor, channel_idx: torch.Tensor, scaling: Optional[float] = None,
+                 attention_mask: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 selected_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``key``/``value`` hold history+1 rows (the last is the token being decoded); the side
+        cache holds the history rows. Returns bf16 ``[B,1,Hq,D]``."""
+        query = _query3(query)
+        B, Hq, D = query.shape
+        Hkv, key_count = key.shape[1], key.shape[2]
+        T = key_count - 1
+        if T < 1:
+            raise RuntimeError("the fused step needs at least one history token")
+        C_ = int(channel_idx.shape[-1])
+        _check_side_cache(packed, scale, C_)
+        if self.append_self and packed.shape[2] < key_count:
+            raise RuntimeError("side cache has no room for the appended row")
+        key = _rows_contiguous(key)
+        value = _rows_contiguous(value)
+        dev = query.device
+        ws = self.workspace(B, Hq, Hkv, T, dev)
+        if out is None:
+            out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16, device=dev)
+        mask = _mask_rows(attention_mask, B, key_count)
+        p = DecodeStepParams()
+        p.query, p.q_sb, p.q_sh = query.data_ptr(), query.stride(0), query.stride(1)
+        p.key, p.k_sb, p.k_sh, p.k_st = key.data_ptr(), key.stride(0), key.stride(1), key.stride(2)
+        p.value, p.v_sb, p.v_sh, p.v_st = value.data_ptr(), value.stride(0), value.stride(1), value.stride(2)
+        p.packed, p.packed_sb, p.packed_sh = packed.data_ptr(), packed.stride(0), packed.stride(1)
+        p.scale, p.scale_sb, p.scale_sh = scale.data_ptr(), scale.stride(0), scale.stride(1)
+        p.channel_idx = channel_idx.data_ptr()
+        p.mask, p.mask_sb = (_ptr(mask), 0 if mask is None else mask.stride(0))
+        p.B, p.Hq, p.Hkv, p.D, p.C = B, Hq, Hkv, D, C_
+        p.history_count = T
+        p.top_k = self.top_k
+        p.protect_sink, p.protect_recent = self.protect_sink, self.protect_recent
+        p.keep_self, p.append_protected = int(self.keep_self), int(self.append_protected)
+        p.append_self = int(self.append_self)
+        p.scaling = float(D) ** -0.5 if scaling is None else float(scaling)
+        p.out = out.data_ptr()
+        p.sel_idx_out = _ptr(selected_out)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        check(_native.lib().kvb_decode_step(C.byref(p), _dev(query), _stream(dev)), "kvb_decode_step")
+        return out

@@ -1,0 +1,305 @@
+"""CPU oracle for the retrieval-sparse decode attention path — TEST INFRASTRUCTURE ONLY.
+
+Nothing in the product imports this file; tests, the smoke check and the CPU-baseline leg of
+the benchmark use it as the checker. It is written with torch CPU ops (and a little numpy).
+
+Two kinds of functions live here.
+
+(1) Restatements of code that exists in the reference (littlexi001/kv_cache); each cites the
+    lines it follows. These are pinned by the golden vectors in tests/golden/ that were produced
+    by importing the reference itself (tests/golden/make_reference_golden.py):
+      EVAL = ymluo/projects/qwen3_top2_head_limit3_ppl/src/evaluate_qwen3_top2_head_limit3_ppl.py
+      QCK  = ymluo/projects/qwen3_top2_head_limit3_ppl/src/qabs_cuda_kernels.py
+(2) The int4 stages the reference does not have (quantize/pack, integer scoring, GQA-group
+    max, tie-broken top-k, block scoring, shard merge). PARITY UNPINNED for these: no reference
+    code, test or golden vector exists; the semantics below are this project's own pinned
+    specification, stated once here and implemented independently by the CUDA kernels.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+TWO_M24 = 2.0 ** -24
+
+
+# ==========================================================================================
+# (2) int4 path — project specification (parity unpinned by the reference)
+# ==========================================================================================
+
+def choose_channels(key: torch.Tensor, num_channels: int) -> torch.Tensor:
+    """Per KV head the C channels with the largest mean |K| over (B, T); ties -> lower channel;
+    ascending int32 [Hkv, C]."""
+    mean_abs = key.float().abs().mean(dim=(0, 2))
+    order = torch.sort(mean_abs, dim=-1, descending=True, stable=True).indices[:, :num_channels]
+    return torch.sort(order, dim=-1).values.to(torch.int32)
+
+
+def _div(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """IEEE fp32 division, done by numpy so that no library rewrites x / c as x * (1 / c)."""
+    return torch.from_numpy(np.divide(a.numpy().astype(np.float32), b.numpy().astype(np.float32), dtype=np.float32))
+
+
+def quantize_pack(key: torch.Tensor, channel_idx: torch.Tensor):
+    """key bf16 [B,Hkv,T,D], channel_idx [Hkv,C] -> codes int8 [B,Hkv,T,C] in [-7,7],
+    packed uint8 [B,Hkv,T,C/2] (byte j: low nibble = code 2j, high nibble = code 2j+1, two's
+    complement), scale fp32 [B,Hkv,T] = max(absmax, 2^-24) / 7 (IEEE), code = clamp(round_half_even(x / scale))."""
+    B, Hkv, T, D = key.shape
+    C = channel_idx.shape[-1]
+    idx = channel_idx.long()[None, :, None, :].expand(B, Hkv, T, C)
+    ksel = torch.gather(key.float(), -1, idx)
+    absmax = ksel.abs().amax(-1)
+    scale = _div(absmax.clamp_min(TWO_M24), torch.full_like(absmax, 7.0))
+    codes = torch.round(_div(ksel, scale[..., None].expand_as(ksel))).clamp(-7, 7).to(torch.int8)
+    u = codes.to(torch.int16) & 0xF
+    packed = (u[..., 0::2] | (u[..., 1::2] << 4)).to(torch.uint8)
+    return codes, packed, scale
+
+
+def unpack(packed: torch.Tensor) -> torch.Tensor:
+    """uint8 [..., C/2] -> int8 codes [..., C]."""
+    p = packed.to(torch.int16)
+    lo = p & 0xF
+    hi = (p >> 4) & 0xF
+    lo = torch.where(lo >= 8, lo - 16, lo)
+    hi = torch.where(hi >= 8, hi - 16, hi)
+    return torch.stack((lo, hi), dim=-1).flatten(-2).to(torch.int8)
+
+
+def quantize_query(query: torch.Tensor, channel_idx: torch.Tensor):
+    """query bf16 [B,Hq,D] -> qcode int8 [B,Hq,C] in [-127,127], qscale fp32 [B,Hq] =
+    max(absmax, 2^-24) / 127, over the channels of the head's KV head."""
+    B, Hq, D = query.shape
+    Hkv, C = channel_idx.shape
+    G = Hq // Hkv
+    idx = channel_idx.long().repeat_interleave(G, dim=0)[None].expand(B, Hq, C)
+    qsel = torch.gather(query.float(), -1, idx)
+    absmax = qsel.abs().amax(-1)
+    qscale = _div(absmax.clamp_min(TWO_M24), torch.full_like(absmax, 127.0))
+    qcode = torch.round(_div(qsel, qscale[..., None].expand_as(qsel))).clamp(-127, 127).to(torch.int8)
+    return qcode, qscale
+
+
+def score(qcode: torch.Tensor, qscale: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor):
+    """acc int32 [B,Hq,T] = sum_c qcode*code (exact); deq = (float(acc) * scale[b,h/G,t]) * qscale[b,h]
+    with two separately rounded fp32 products in this order; gmax [B,Hkv,T] = max over the group,
+    -0 folded into +0."""
+    B, Hq, C = qcode.shape
+    Hkv, T = codes.shape[1], codes.shape[2]
+    G = Hq // Hkv
+    # exact: |acc| <= 128 * 127 * 7 < 2^24, so an fp32 (or fp64) matmul of small integers is exact
+    qf = qcode.to(torch.float64).view(B, Hkv, G, C)
+    cf = codes.to(torch.float64)                                   # [B,Hkv,T,C]
+    acc = torch.einsum("bgqc,bgtc->bgqt", qf, cf).round().to(torch.int32).reshape(B, Hq, T)
+    ks = scale.repeat_interleave(G, dim=1)                         # [B,Hq,T]
+    deq = (acc.to(torch.float32) * ks) * qscale[..., None]
+    gmax = deq.view(B, Hkv, G, T).amax(dim=2) + 0.0
+    return acc, deq, gmax
+
+
+def select(gmax: torch.Tensor, k: int, index: Optional[torch.Tensor] = None):
+    """Per row: order (score desc, index asc), first min(k, T). Stable descending sort, never
+    torch.topk (which leaves the order of ties unspecified). With ``index`` (same shape as gmax,
+    unique per row) the tie-break and the returned ids use it instead of the column number."""
+    T = gmax.shape[-1]
+    kk = min(k, T)
+    g = gmax + 0.0
+    if index is None:
+        order = torch.sort(g, dim=-1, descending=True, stable=True).indices[..., :kk]
+        return order, torch.gather(g, -1, order)
+    # sort by index ascending first, then stable by score descending
+    by_idx = torch.sort(index, dim=-1, stable=True).indices
+    g1 = torch.gather(g, -1, by_idx)
+    o2 = torch.sort(g1, dim=-1, descending=True, stable=True).indices[..., :kk]
+    pos = torch.gather(by_idx, -1, o2)
+    return torch.gather(index, -1, pos), torch.gather(g, -1, pos)
+
+
+def attend_fp32(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, indices: torch.Tensor,
+                valid: Optional[torch.Tensor], scaling: float, mask_rows: Optional[torch.Tensor] = None):
+    """fp32-accumulate form of the sparse attention on UN-repeated K/V: query [B,Hq,D] bf16,
+    key/value [B,Hkv,Tk,D] bf16, indices [B,Hkv|Hq,S]. Returns (out fp32 [B,1,Hq,D], m, l)."""
+    B, Hq, D = query.shape
+    Hkv, Tk = key.shape[1], key.shape[2]
+    G = Hq // Hkv
+    Hi = indices.shape[1]
+    idx = indices.long()
+    if valid is None:
+        valid = torch.ones_like(idx, dtype=torch.bool)
+    ok = valid.bool() & (idx >= 0) & (idx < Tk)
+    idx = idx.clamp(0, Tk - 1)
+    if Hi == Hkv:
+        idx = idx.repeat_interleave(G, dim=1)
+        ok = ok.repeat_interleave(G, dim=1)
+    kr = key.repeat_interleave(G, dim=1).float()
+    vr = value.repeat_interleave(G, dim=1).float()
+    gi = idx[..., None].expand(-1, -1, -1, D)
+    ks = torch.gather(kr, 2, gi)
+    vs = torch.gather(vr, 2, gi)
+    s = torch.einsum("bhd,bhsd->bhs", query.float(), ks) * scaling
+    if mask_rows is not None:
+        s = s + torch.gather(mask_rows.float()[:, None, :].expand(-1, Hq, -1), -1, idx)
+    s = s.masked_fill(~ok, float("-inf"))
+    m = s.amax(-1)
+    mu = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    p = torch.exp(s - mu[..., None])
+    p = torch.where(ok, p, torch.zeros_like(p))
+    l = p.sum(-1)
+    o = torch.einsum("bhs,bhsd->bhd", p, vs)
+    out = torch.where(l[..., None] > 0, o / l.clamp_min(1e-30)[..., None], torch.zeros_like(o))
+    return out[:, None, :, :], m, l
+
+
+def decode_step(query, key, value, channel_idx, top_k, *, protect_sink=0, protect_recent=0, keep_self=True,
+                append_protected=False, scaling=None):
+    """The whole int4 path on CPU for key/value holding history+1 rows. Returns a dict."""
+    B, Hq, D = query.shape
+    Tk = key.shape[2]
+    T = Tk - 1
+    scaling = D ** -0.5 if scaling is None else scaling
+    codes, packed, kscale = quantize_pack(key[:, :, :T], channel_idx)
+    qcode, qscale = quantize_query(query, channel_idx)
+    acc, deq, gmax = score(qcode, qscale, codes, kscale)
+    sel, sel_scores = select(gmax, top_k)
+    fidx, fvalid = final_indices_from_selected(sel, torch.ones_like(sel, dtype=torch.bool), T, Tk, keep_self,
+                                               protect_sink, protect_recent, append_protected)
+    out, m, l = attend_fp32(query, key, value, fidx, fvalid, scaling)
+    return dict(codes=codes, packed=packed, kscale=kscale, qcode=qcode, qscale=qscale, acc=acc, deq=deq, gmax=gmax,
+                selected=sel, selected_scores=sel_scores, final_indices=fidx, final_valid=fvalid, out=out, m=m, l=l)
+
+
+def merge_shards(cand_scores: torch.Tensor, cand_idx: torch.Tensor, k: int):
+    """Global top-k from per-shard candidate lists [N,R,kk] (scores, global ids): concatenated
+    along the shard axis and selected with the same (score desc, id asc) rule."""
+    N, R, kk = cand_scores.shape
+    s = cand_scores.permute(1, 0, 2).reshape(R, N * kk)
+    i = cand_idx.permute(1, 0, 2).reshape(R, N * kk)
+    return select(s, k, index=i)
+
+
+def lse_merge(partials: torch.Tensor) -> torch.Tensor:
+    """partials fp32 [N,B,Hq,D+2] = (o scaled to m, m, l) -> fp32 [B,1,Hq,D]."""
+    o, m, l = partials[..., :-2], partials[..., -2], partials[..., -1]
+    m = torch.where(l > 0, m, torch.full_like(m, float("-inf")))
+    M = m.amax(0)
+    Mu = torch.where(torch.isinf(M), torch.zeros_like(M), M)
+    w = torch.where(l > 0, torch.exp(m - Mu[None]), torch.zeros_like(m))
+    L = (l * w).sum(0)
+    O = (o * w[..., None]).sum(0)
+    out = torch.where(L[..., None] > 0, O / L.clamp_min(1e-30)[..., None], torch.zeros_like(O))
+    return out[:, None, :, :]
+
+
+# ==========================================================================================
+# (1) restatements of reference code (pinned by tests/golden/reference_*.npz)
+# ==========================================================================================
+
+def final_indices_from_selected(selected: torch.Tensor, selected_valid: torch.Tensor, history_count: int,
+                                key_count: int, always_keep_self: bool, protect_sink: int, protect_recent: int,
+                                append_protected: bool = False):
+    """EVAL:2938-2982 (_qabs_final_indices_from_selected) and, with append_protected,
+    EVAL:2985-3022 (_qabs_final_indices_append_protected): selected || sink || recent || self.
+    The reference reads the protect counts from module globals; here they are arguments."""
+    lead = selected.shape[:-1]
+    sel = selected.long()
+    valid = selected_valid.clone()
+    sink_end = min(protect_sink, history_count) if protect_sink > 0 else 0
+    idx_parts, valid_parts = [sel], None
+    recent_from = None
+    if append_protected:
+        if protect_recent > 0:
+            rs = max(max(0, history_count - protect_recent), sink_end)
+            if rs < history_count:
+                recent_from = rs
+    else:
+        recent_start = history_count
+        if protect_recent > 0:
+            recent_start = max(0, history_count - protect_recent)
+            valid &= ~((sel >= recent_start) & (sel < history_count))
+        if sink_end > 0:
+            valid &= sel >= sink_end
+        if protect_recent > 0 and recent_start < history_count:
+            rs = max(recent_start, sink_end)
+            if rs < history_count:
+                recent_from = rs
+    valid_parts = [valid]
+    if sink_end > 0:
+        part = torch.arange(sink_end, dtype=torch.long).expand(*lead, -1)
+        idx_parts.append(part)
+        valid_parts.append(torch.ones_like(part, dtype=torch.bool))
+    if recent_from is not None:
+        part = torch.arange(recent_from, history_count, dtype=torch.long).expand(*lead, -1)
+        idx_parts.append(part)
+        valid_parts.append(torch.ones_like(part, dtype=torch.bool))
+    if always_keep_self:
+        part = torch.full((*lead, 1), key_count - 1, dtype=torch.long)
+        idx_parts.append(part)
+        valid_parts.append(torch.ones_like(part, dtype=torch.bool))
+    return torch.cat(idx_parts, dim=-1), torch.cat(valid_parts, dim=-1)
+
+
+def attention_from_final_indices(query_states, key_states, value_states, attention_mask, final_indices, final_valid,
+                                 scaling):
+    """EVAL:4612-4647 (_qabs_attention_from_final_indices), torch branch: K/V already repeated to
+    the query heads, bf16 matmul, fp32 softmax cast to the input dtype, weighted sum in the input
+    dtype. query [B,H,1,D]; returns [B,1,H,D]."""
+    _, head_count, _, head_dim = query_states.shape
+    key_count = key_states.shape[-2]
+    gather = final_indices[:, :, :, None].expand(-1, -1, -1, head_dim)
+    sel_k = torch.gather(key_states, 2, gather)
+    sel_v = torch.gather(value_states, 2, gather)
+    scores = torch.matmul(query_states[:, :, 0:1, :], sel_k.transpose(2, 3)).squeeze(2) * scaling
+    if attention_mask is not None:
+        mask_row = attention_mask[:, :, 0, :key_count]
+        if mask_row.shape[1] == 1 and head_count != 1:
+            mask_row = mask_row.expand(-1, head_count, -1)
+        scores = scores + torch.gather(mask_row, -1, final_indices)
+    scores = scores.masked_fill(~final_valid, torch.finfo(scores.dtype).min)
+    weights = F.softmax(scores, dim=-1, dtype=torch.float32).to(query_states.dtype)
+    out = torch.sum(weights[:, :, :, None] * sel_v, dim=2)
+    return out[:, None, :, :].contiguous()
+
+
+def qabs_partial_scores(q_raw: torch.Tensor, k_history: torch.Tensor, dim_count: int):
+    """EVAL:4428 + EVAL:4443-4446: per (b, head) the dim_count channels with the largest |q|, then
+    fp32 sum over those channels of q * K. q_raw [B,H,D], k_history [B,H,T,D]. Returns
+    (scores fp32 [B,H,T], channel indices [B,H,dim_count])."""
+    T = k_history.shape[2]
+    qdim = torch.topk(q_raw.float().abs(), k=dim_count, dim=-1, largest=True).indices
+    q_sel = torch.gather(q_raw.float(), -1, qdim)
+    k_idx = qdim[:, :, None, :].expand(-1, -1, T, -1)
+    k_sel = torch.gather(k_history.float(), -1, k_idx)
+    return (k_sel * q_sel[:, :, None, :]).sum(-1), qdim
+
+
+def candidate_count(candidate_fraction: float, history_count: int) -> int:
+    """EVAL:4423: min(T, max(1, ceil(fraction * T)))."""
+    return min(history_count, max(1, math.ceil(candidate_fraction * history_count)))
+
+
+def qabs_candidate_attention(query_states, key_states, value_states, attention_mask, scaling, dim_count,
+                             candidate_fraction, always_keep_self=True, protect_sink=0, protect_recent=0):
+    """EVAL:4400-4502 (_qabs_candidate_attention_forward, torch branches) preceded by the K/V
+    repeat of the dispatcher (EVAL:6248-6251): the reference's own CPU path for one decode step.
+    query [B,Hq,1,D], key/value [B,Hkv,Tk,D] -> [B,1,Hq,D]."""
+    if key_states.shape[1] != query_states.shape[1]:
+        rep = query_states.shape[1] // key_states.shape[1]
+        key_states = key_states.repeat_interleave(rep, dim=1)
+        value_states = value_states.repeat_interleave(rep, dim=1)
+    head_dim = query_states.shape[-1]
+    key_count = key_states.shape[-2]
+    if key_count <= 1:
+        return value_states[:, :, -1:, :].transpose(1, 2).contiguous()
+    history = key_count - 1
+    d_s = min(max(1, dim_count), head_dim)
+    requested = candidate_count(candidate_fraction, history)
+    q_raw = query_states[:, :, 0, :]
+    partial, _ = qabs_partial_scores(q_raw, key_states[:, :, :history, :], d_s)
+    _, cand = torch.topk(partial, k=requested, dim=-1, largest=True)
+    fidx, fvalid = final_indices_from_selected(cand, torch.ones_like(cand, dtype=torch.bool), history, key_count,
+                                               always_keep_self, protect_sink, protect_recent)
+    return attention_from_final_indices(query_states, key_states, value_states, attention_mask, fidx, fvalid, scaling)

@@ -1,0 +1,57 @@
+"""The C-ABI library builds for sm_100a, loads without a GPU, and exports every symbol that
+include/kvcache_b200.h declares (no compute calls here)."""
+import ctypes
+import re
+from pathlib import Path
+
+from kv_cache_b200 import _native, build
+
+HEADER = Path(__file__).resolve().parents[1] / "include" / "kvcache_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(kvb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_symbols()
+    for must in ("kvb_quantize_pack", "kvb_quantize_append", "kvb_score_decode", "kvb_select_topk",
+                 "kvb_sparse_attend", "kvb_decode_step", "kvb_select_topk_workspace_bytes",
+                 "kvb_sparse_attend_workspace_bytes"):
+        assert must in names
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    path = build.build()
+    assert path.exists()
+    handle = ctypes.CDLL(str(path))
+    for name in declared_symbols():
+        assert hasattr(handle, name), f"{name} is declared in the header but not exported"
+
+
+def test_python_binding_covers_every_declared_symbol():
+    assert sorted(_native.SIGNATURES) == declared_symbols()
+    lib = _native.lib()
+    assert lib.kvb_version() >= 100
+    assert lib.kvb_status_string(0) == b"ok"
+    assert lib.kvb_status_string(4) == b"workspace too small"
+
+
+def test_size_queries_need_no_gpu():
+    lib = _native.lib()
+    assert lib.kvb_final_index_count(2048, 131072, 0, 0, 1) == 2049
+    assert lib.kvb_final_index_count(16, 100, 4, 5, 1) == 16 + 4 + 5 + 1
+    assert lib.kvb_final_index_count(16, 100, 200, 0, 0) == 16 + 100
+    assert lib.kvb_select_topk_workspace_bytes(128, 131072, 2048) > 128 * 8192 * 8
+    assert lib.kvb_sparse_attend_workspace_bytes(16, 32, 8, 2049) > 0
+    assert lib.kvb_sparse_attend_workspace_bytes(16, 32, 5, 2049) == 0
+    assert lib.kvb_decode_step_workspace_bytes(16, 32, 8, 131072, 2048, 0, 0, 1) > 16 * 8 * 131072 * 4
+
+
+def test_bad_arguments_are_rejected_before_any_launch():
+    lib = _native.lib()
+    # null pointers / impossible shapes return a status without touching a device
+    assert lib.kvb_quantize_pack(None, 0, 0, 0, None, None, 0, 0, None, 0, 0, 1, 1, 1, 128, 32, 0, 0, None) == 7
+    assert lib.kvb_select_topk(None, 0, None, 1, 1, 1, 0, None, None, None, None, None, 0, 0, None) == 7
+    assert lib.kvb_lse_merge(None, 1, 1, 1, 128, None, 0, None) == 7

@@ -1,0 +1,61 @@
+"""The fused per-layer step against the oracle chain: selected ids bit-exact, output in tolerance,
+side cache extended by the decoded token."""
+import pytest
+import torch
+
+from kv_cache_b200 import ops
+from oracle import oracle
+from tests.gpu_util import cpu, make_case
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2e-2, 1e-2
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,T,C,k,sink,recent", [
+    (1, 16, 8, 4096, 32, 256, 0, 0),        # config 0 shapes
+    (2, 8, 2, 1000, 64, 64, 0, 0),
+    (2, 8, 2, 1000, 64, 64, 10, 10),
+    (2, 4, 4, 300, 32, 512, 3, 2),          # k > T
+    (1, 8, 1, 70, 128, 16, 0, 0),
+])
+def test_step_matches_oracle(cuda_device, B, Hq, Hkv, T, C, k, sink, recent):
+    w, q, key, value = make_case(cuda_device, batch=B, q_heads=Hq, kv_heads=Hkv, context=T, channels=C, seed=B + T)
+    ch = ops.choose_channels(key[:, :, :T], C)
+    packed, scale = ops.alloc_side_cache(B, Hkv, T + 1, C, cuda_device)
+    ops.quantize(key[:, :, :T], ch, out=(packed, scale))
+    step = ops.DecodeStep(k, protect_sink=sink, protect_recent=recent)
+    sel = torch.empty((B, Hkv, min(k, T)), dtype=torch.int32, device=cuda_device)
+    out = step(q, key, value, packed, scale, ch, selected_out=sel)
+    r = oracle.decode_step(*cpu(q, key, value, ch), k, protect_sink=sink, protect_recent=recent)
+    assert torch.equal(sel.cpu().long(), r["selected"])
+    torch.testing.assert_close(out.float().cpu(), r["out"], rtol=RTOL, atol=ATOL)
+    # the decoded token's row joined the int4 cache
+    _, packed_o, scale_o = oracle.quantize_pack(key.cpu(), ch.cpu())
+    assert torch.equal(packed[:, :, :T + 1].cpu(), packed_o)
+    assert torch.equal(scale[:, :, :T + 1].cpu(), scale_o)
+    # running it again (now stale workspace contents) gives the same answer
+    out2 = step(q, key, value, packed, scale, ch)
+    assert torch.equal(out, out2)
+
+
+def test_step_equals_operator_chain(cuda_device):
+    w, q, key, value = make_case(cuda_device, batch=2, q_heads=8, kv_heads=2, context=5000, channels=64)
+    T = 5000
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    packed, scale = ops.alloc_side_cache(2, 2, T + 1, 64, cuda_device)
+    ops.quantize(key[:, :, :T], ch, out=(packed, scale))
+    r = ops.score(q, packed, scale, ch, T)
+    sel = ops.select(r.gmax, 128)
+    fidx, fvalid = ops.build_final_indices(sel, None, T, T + 1, 4, 4, True)
+    chain = ops.sparse_attend(q, key, value, fidx, fvalid)
+    fused = ops.DecodeStep(128, 4, 4)(q, key, value, packed, scale, ch)
+    assert torch.equal(chain, fused)
+
+
+def test_device_status_is_clean(cuda_device):
+    import ctypes
+    from kv_cache_b200 import _native
+
+    st = ctypes.c_int(-1)
+    assert _native.lib().kvb_device_status(0, ctypes.byref(st)) == 0
+    assert st.value == 0

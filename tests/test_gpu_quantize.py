@@ -1,0 +1,56 @@
+"""Stage 1 parity: int4 codes, packed bytes and scales bit-exact against the oracle."""
+import pytest
+import torch
+
+from kv_cache_b200 import ops
+from oracle import oracle
+from tests.gpu_util import cpu, make_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("C", [16, 32, 64, 128, 34, 6])
+@pytest.mark.parametrize("T", [1, 15, 16, 17, 257, 1000])
+def test_quantize_bit_exact(cuda_device, C, T):
+    w, q, key, _ = make_case(cuda_device, context=T, channels=C)
+    hist = key[:, :, :T]
+    ch = ops.choose_channels(hist, C)
+    packed, scale = ops.quantize(hist, ch)
+    codes_o, packed_o, scale_o = oracle.quantize_pack(*cpu(hist, ch))
+    assert torch.equal(ch.cpu(), oracle.choose_channels(hist.cpu(), C))
+    assert torch.equal(packed.cpu(), packed_o)
+    assert torch.equal(scale.cpu().view(torch.int32), scale_o.view(torch.int32))
+    assert torch.equal(ops.unpack_codes(packed).cpu(), codes_o)
+
+
+def test_quantize_strided_view_and_append(cuda_device):
+    """A sliced key (the HF cache hands out [:, :, :T] views) and the one-row append."""
+    w, q, key, _ = make_case(cuda_device, context=300, channels=64)
+    T = 300
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    packed, scale = ops.alloc_side_cache(w.batch, w.kv_heads, T + 1, 64, cuda_device)
+    packed.fill_(0xAB)
+    scale.fill_(-1.0)
+    ops.quantize(key[:, :, :T], ch, out=(packed, scale))          # non-contiguous batch/head strides
+    ops.quantize_append(key[:, :, T:T + 1], ch, packed, scale, T)
+    _, packed_o, scale_o = oracle.quantize_pack(key.cpu(), ch.cpu())
+    assert torch.equal(packed[:, :, :T + 1].cpu(), packed_o)
+    assert torch.equal(scale[:, :, :T + 1].cpu(), scale_o)
+    # nothing beyond the written rows was touched
+    assert (packed[:, :, T + 1:] == 0xAB).all() and (scale[:, :, T + 1:] == -1.0).all()
+
+
+def test_quantize_edge_values(cuda_device):
+    """All-zero rows, a single huge outlier, exact .5 rounding ties."""
+    T, D, C = 8, 128, 32
+    key = torch.zeros(1, 1, T, D, dtype=torch.bfloat16, device=cuda_device)
+    key[0, 0, 1, :32] = 1.0
+    key[0, 0, 2, 0] = 3.0e38
+    key[0, 0, 2, 1] = 1.0
+    key[0, 0, 3, :32] = torch.tensor([7.0, 3.5, 2.5, 1.5, 0.5, -0.5, -1.5, -2.5] * 4, dtype=torch.bfloat16)
+    key[0, 0, 4, 5] = -1.0e-30
+    ch = torch.arange(C, dtype=torch.int32, device=cuda_device)[None]
+    packed, scale = ops.quantize(key, ch)
+    _, packed_o, scale_o = oracle.quantize_pack(key.cpu(), ch.cpu())
+    assert torch.equal(packed.cpu(), packed_o)
+    assert torch.equal(scale.cpu(), scale_o)
