@@ -64,7 +64,11 @@ def _query3(query: torch.Tensor) -> torch.Tensor:
 def choose_channels(key: torch.Tensor, num_channels: int) -> torch.Tensor:
     """Per KV head, the ``num_channels`` head-dim channels with the largest mean |K| over (B, T);
     ties go to the lower channel; returned ascending as int32 ``[Hkv, C]``."""
-    mean_abs = key.float().abs().mean(dim=(0, 2))                       # [Hkv, D]
+    T = key.shape[2]
+    total = torch.zeros((key.shape[1], key.shape[3]), dtype=torch.float64, device=key.device)
+    for t0 in range(0, T, 16384):                                       # bounded fp32 temporaries
+        total += key[:, :, t0:t0 + 16384].float().abs().sum(dim=(0, 2), dtype=torch.float64)
+    mean_abs = total / max(1, key.shape[0] * T)                         # [Hkv, D]
     order = torch.sort(mean_abs, dim=-1, descending=True, stable=True).indices[:, :num_channels]
     return torch.sort(order, dim=-1).values.to(torch.int32).contiguous()
 

