@@ -307,12 +307,17 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the workload's batch (smaller device footprint for profiler captures)")
     args = ap.parse_args()
 
     from kv_cache_b200 import inputs
 
     name = args.workload or ("c2" if args.gpus == 1 else "c4")
     w = inputs.WORKLOADS[name]
+    if args.batch:
+        import dataclasses
+        w = dataclasses.replace(w, batch=args.batch, name=f"{w.name}_batch{args.batch}")
     if args.impl == "reference":
         run_reference_arm(args, w)
         return

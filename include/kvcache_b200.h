@@ -111,11 +111,13 @@ int kvb_score_decode(const void* query, int64_t q_sb, int64_t q_sh,
                      int device, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * Stage 3 — top-k select per row, order (score descending, index ascending).
+ * Stage 3 — exact top-k select per row; among equal scores the lower index wins.
  *
  * Stands in for the torch.topk candidate selection of the reference (EVAL:4448, count rule
- * EVAL:4423) with the tie-break pinned: among equal scores the lower index wins, and the
- * output is ordered by (score desc, index asc). -0 and +0 compare equal.
+ * EVAL:4423) with the tie-break pinned, so the selected SET is unique. -0 and +0 compare
+ * equal. The kk winners are written in one of two pinned orders:
+ *   order 0: (score descending, index ascending) — the order torch.topk(sorted=True) aims at;
+ *   order 1: index ascending — cheaper to produce and friendlier to the K/V gather that follows.
  *
  *   scores    fp32 [R,T] rows (row_stride elements apart), no NaN.
  *   payload   int32 [R,T] (same row stride) or NULL. With NULL the index of column t is
@@ -131,7 +133,7 @@ int kvb_score_decode(const void* query, int64_t q_sb, int64_t q_sh,
 size_t kvb_select_topk_workspace_bytes(int R, int T, int k);
 
 int kvb_select_topk(const float* scores, int64_t row_stride, const int32_t* payload,
-                    int R, int T, int k, int64_t idx_offset,
+                    int R, int T, int k, int64_t idx_offset, int order,
                     int32_t* out_idx32, int64_t* out_idx64, float* out_scores,
                     const uint32_t* hist_in,
                     void* workspace, size_t workspace_bytes,

@@ -60,7 +60,7 @@ SIGNATURES = {
     "kvb_score_decode": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
                               _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _p]),
     "kvb_select_topk_workspace_bytes": (_sz, [_i, _i, _i]),
-    "kvb_select_topk": (_i, [_p, _i64, _p, _i, _i, _i, _i64, _p, _p, _p, _p, _p, _sz, _i, _p]),
+    "kvb_select_topk": (_i, [_p, _i64, _p, _i, _i, _i, _i64, _i, _p, _p, _p, _p, _p, _sz, _i, _p]),
     "kvb_final_index_count": (_i, [_i, _i, _i, _i, _i]),
     "kvb_build_final_indices": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p]),
     "kvb_sparse_attend_workspace_bytes": (_sz, [_i, _i, _i, _i]),

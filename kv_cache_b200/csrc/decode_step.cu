@@ -5,10 +5,12 @@
 
 namespace kvb {
 
+// Workspace of the fused step. The regions that must start at zero (attention split counters,
+// select candidate counters, histogram) are adjacent so ONE memset per step clears them.
 struct StepLayout {
   int R, kk, S;
-  size_t off_gmax, off_hist, off_sel, off_fidx, off_fvalid, off_selws, off_attws;
-  size_t selws_bytes, attws_bytes, bytes;
+  size_t off_attcnt, off_selws, off_attpart, off_gmax, off_sel, off_fidx, off_fvalid;
+  size_t zero_bytes, selws_bytes, bytes;
 };
 
 static StepLayout step_layout(int B, int Hq, int Hkv, int T, int k, int sink, int recent, int keep_self) {
@@ -16,35 +18,39 @@ static StepLayout step_layout(int B, int Hq, int Hkv, int T, int k, int sink, in
   L.R = B * Hkv;
   L.kk = k < T ? k : T;
   L.S = kvb_final_index_count(L.kk, T, sink, recent, keep_self);
+  const SelectWorkspace sw = select_carve(nullptr, L.R, L.kk > 0 ? L.kk : 1);
+  const AttendPlan ap = attend_plan(B, Hq, Hkv, L.S > 0 ? L.S : 1);
   size_t off = 0;
-  L.off_gmax = off;   off += round_up(sizeof(float) * (size_t)L.R * (size_t)T, 256);
-  L.off_hist = off;   off += round_up(sizeof(uint32_t) * (size_t)L.R * 4096, 256);
-  L.off_sel = off;    off += round_up(sizeof(int32_t) * (size_t)L.R * (size_t)(L.kk > 0 ? L.kk : 1), 256);
-  L.off_fidx = off;   off += round_up(sizeof(int32_t) * (size_t)L.R * (size_t)(L.S > 0 ? L.S : 1), 256);
-  L.off_fvalid = off; off += round_up((size_t)L.R * (size_t)(L.S > 0 ? L.S : 1), 256);
-  L.selws_bytes = T > 0 ? kvb_select_topk_workspace_bytes(L.R, T, L.kk) : 0;
-  L.off_selws = off;  off += round_up(L.selws_bytes, 256);
-  L.attws_bytes = L.S > 0 ? kvb_sparse_attend_workspace_bytes(B, Hq, Hkv, L.S) : 0;
-  L.off_attws = off;  off += round_up(L.attws_bytes, 256);
+  L.off_attcnt = off;  off += ap.counter_bytes;
+  L.off_selws = off;   off += round_up(sw.bytes, 256);
+  L.selws_bytes = sw.bytes;
+  L.zero_bytes = ap.counter_bytes + sw.zero_bytes;       // attention counters + select counters + histogram
+  L.off_attpart = off; off += ap.partial_bytes;
+  L.off_gmax = off;    off += round_up(sizeof(float) * (size_t)L.R * (size_t)T, 256);
+  L.off_sel = off;     off += round_up(sizeof(int32_t) * (size_t)L.R * (size_t)(L.kk > 0 ? L.kk : 1), 256);
+  L.off_fidx = off;    off += round_up(sizeof(int32_t) * (size_t)L.R * (size_t)(L.S > 0 ? L.S : 1), 256);
+  L.off_fvalid = off;  off += round_up((size_t)L.R * (size_t)(L.S > 0 ? L.S : 1), 256);
   L.bytes = off;
   return L;
 }
 
 }  // namespace kvb
 
-extern "C" __attribute__((visibility("default"))) size_t kvb_decode_step_workspace_bytes(int B, int Hq, int Hkv, int history_count, int top_k,
-                                                  int protect_sink, int protect_recent, int keep_self) {
+extern "C" __attribute__((visibility("default"))) size_t kvb_decode_step_workspace_bytes(
+    int B, int Hq, int Hkv, int history_count, int top_k, int protect_sink, int protect_recent, int keep_self) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || history_count < 0 || top_k <= 0 || (Hq % Hkv)) return 0;
   return kvb::step_layout(B, Hq, Hkv, history_count, top_k, protect_sink, protect_recent, keep_self).bytes;
 }
 
-extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_decode_step_params* p, int device, void* stream) {
+extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_decode_step_params* p, int device,
+                                                                      void* stream) {
   using namespace kvb;
   if (!p || !p->query || !p->key || !p->value || !p->packed || !p->scale || !p->channel_idx || !p->out ||
       !p->workspace)
     return KVB_BAD_ARG;
   if (p->B <= 0 || p->Hq <= 0 || p->Hkv <= 0 || (p->Hq % p->Hkv) || p->history_count <= 0 || p->top_k <= 0)
     return KVB_BAD_SHAPE;
+  if (p->top_k > SEL_MAX_K && p->history_count > SEL_MAX_K) return KVB_BAD_SHAPE;
   if (!aligned_to(p->workspace, 256)) return KVB_BAD_ALIGN;
   const int T = p->history_count;
   const StepLayout L = step_layout(p->B, p->Hq, p->Hkv, T, p->top_k, p->protect_sink, p->protect_recent,
@@ -52,8 +58,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   if (p->workspace_bytes < L.bytes) return KVB_WORKSPACE_TOO_SMALL;
   if (L.S <= 0) return KVB_BAD_SHAPE;
   uint8_t* ws = reinterpret_cast<uint8_t*>(p->workspace);
+  uint32_t* attcnt = reinterpret_cast<uint32_t*>(ws + L.off_attcnt);
+  void* selws = ws + L.off_selws;
+  const SelectWorkspace sw = select_carve(selws, L.R, L.kk);
+  float* attpart = reinterpret_cast<float*>(ws + L.off_attpart);
   float* gmax = reinterpret_cast<float*>(ws + L.off_gmax);
-  uint32_t* hist = reinterpret_cast<uint32_t*>(ws + L.off_hist);
   int32_t* sel = p->sel_idx_out ? p->sel_idx_out : reinterpret_cast<int32_t*>(ws + L.off_sel);
   int32_t* fidx = reinterpret_cast<int32_t*>(ws + L.off_fidx);
   uint8_t* fvalid = ws + L.off_fvalid;
@@ -63,21 +72,22 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   {
     DeviceGuard guard(device);
     if (!guard.ok) return KVB_BAD_DEVICE;
-    KVB_CHECK_CUDA(cudaMemsetAsync(hist, 0, sizeof(uint32_t) * (size_t)L.R * 4096, st));
+    KVB_CHECK_CUDA(cudaMemsetAsync(ws + L.off_attcnt, 0, L.zero_bytes, st));
   }
   rc = kvb_score_decode(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
-                        p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, gmax, nullptr, nullptr, hist,
-                        device, stream);
+                        p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, gmax, nullptr, nullptr,
+                        sw.hist, device, stream);
   if (rc != KVB_OK) return rc;
-  rc = kvb_select_topk(gmax, T, nullptr, L.R, T, p->top_k, 0, sel, nullptr, nullptr, hist, ws + L.off_selws,
-                       L.selws_bytes, device, stream);
+  // ascending-index order: the set is what matters to the attention, and it is the cheapest to emit
+  rc = select_run(gmax, T, nullptr, L.R, T, p->top_k, 0, /*order=*/1, sel, nullptr, nullptr, nullptr,
+                  /*hist_in_workspace=*/true, /*zeroed=*/true, selws, L.selws_bytes, device, st);
   if (rc != KVB_OK) return rc;
   rc = kvb_build_final_indices(sel, nullptr, L.R, L.kk, T, T + 1, p->protect_sink, p->protect_recent, p->keep_self,
                                p->append_protected, fidx, fvalid, device, stream);
   if (rc != KVB_OK) return rc;
-  rc = kvb_sparse_attend(p->query, p->q_sb, p->q_sh, p->key, p->k_sb, p->k_sh, p->k_st, p->value, p->v_sb, p->v_sh,
-                         p->v_st, fidx, 0, fvalid, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D,
-                         L.S, p->scaling, p->out, nullptr, ws + L.off_attws, L.attws_bytes, device, stream);
+  rc = attend_run(p->query, p->q_sb, p->q_sh, p->key, p->k_sb, p->k_sh, p->k_st, p->value, p->v_sb, p->v_sh, p->v_st,
+                  fidx, 0, fvalid, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D, L.S, p->scaling,
+                  p->out, nullptr, attcnt, attpart, /*counters_zeroed=*/true, device, st);
   if (rc != KVB_OK) return rc;
   if (p->append_self) {
     // Row T of key (the token being decoded) joins the int4 cache for the following steps.

@@ -1,15 +1,18 @@
-// Stage 3: exact top-k per row with the order (score descending, index ascending).
+// Stage 3: exact top-k per row; ties between equal scores go to the lower index.
 //
 // Every element becomes a unique 64-bit composite  (order-preserving key of the score) << 32 |
 // (0xFFFFFFFF - index), so "larger composite" is exactly "better score, then lower index" and
 // ties need no special case. Selection is an MSB-first radix select on the composite:
 //   1. a 4096-bin histogram of the top 12 bits (taken from the scorer when it already made one),
-//   2. every CTA finds the bin b* holding the k-th element and appends all elements of bins
-//      >= b* to a per-row candidate list (a few thousand entries for Gaussian-like scores),
-//   3. one CTA per row sorts the candidates in shared memory (bitonic, descending) and writes
-//      the first k.
-// When a row has more than CAP candidates after step 1 (heavy ties, e.g. constant scores) the
-// last kernel refines the prefix with further 11-bit passes over the row itself until the
+//   2. one small CTA per row finds the bin b* that holds the k-th element,
+//   3. a streaming pass appends all elements of bins >= b* to a per-row candidate list (a few
+//      thousand entries for Gaussian-like scores; one atomic per CTA),
+//   4. one CTA per row loads the candidates into shared memory, finishes the radix select there
+//      (11 bits per pass) to get the exact k-th composite, and writes the k winners either
+//      ordered by (score desc, index asc) — bitonic sort — or by ascending index — a bitmap in
+//      shared memory read out in order, which is what the gather of the attention stage likes.
+// When a row has more than CAP candidates after step 2 (heavy ties, e.g. constant scores) the
+// last kernel first refines the prefix with 11-bit passes over the row itself until the
 // candidate set fits; that path is slower but exact for any input.
 #include "common.cuh"
 
@@ -35,6 +38,9 @@ struct SelectParams {
   uint32_t* cand_count;       // [R]
   int cap;
   int tokens_per_cta;         // scan kernels: tokens per CTA along a row
+  uint4* thresholds;          // [R] (bin, above, in-bin, unused)
+  int order_by_index;         // 0: (score desc, index asc); 1: ascending index
+  int use_bitmap;             // order_by_index served by the shared-memory bitmap
 };
 
 __device__ __forceinline__ uint64_t make_composite(float score, uint32_t idx) {
@@ -103,6 +109,37 @@ __device__ __forceinline__ void find_threshold(const uint32_t* hist, int nbins, 
   __syncthreads();
 }
 
+// Exclusive prefix sum of one value per thread over the CTA; also returns the total.
+// s_warp needs NT/32 + 1 words. Ends with a barrier.
+template <int NT>
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s_warp, uint32_t& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t incl = v;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t n = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += n;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = lane < NT / 32 ? s_warp[lane] : 0u;
+    uint32_t wi = w;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, wi, off);
+      if (lane >= off) wi += n;
+    }
+    if (lane < NT / 32) s_warp[lane] = wi - w;
+    if (lane == 31) s_warp[NT / 32] = wi;
+  }
+  __syncthreads();
+  const uint32_t res = s_warp[warp] + incl - v;
+  total = s_warp[NT / 32];
+  __syncthreads();
+  return res;
+}
+
 // Histogram of the top 12 key bits of every row (only when the scorer did not produce one).
 __global__ void __launch_bounds__(SEL_SCAN_THREADS) select_hist_kernel(SelectParams p, uint32_t* hist_out) {
   __shared__ uint32_t s_hist[SEL_HIST_BINS];
@@ -123,42 +160,78 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS) select_hist_kernel(SelectPar
   }
 }
 
-// Appends every element whose top-12-bit bin is >= the threshold bin to the row's candidate list
-// (skipped for rows whose candidate set would not fit; the final kernel handles those).
-__global__ void __launch_bounds__(SEL_SCAN_THREADS) select_collect_kernel(SelectParams p) {
+// One CTA per row: the bin that holds the k-th element, the count above it and inside it.
+__global__ void __launch_bounds__(SEL_SCAN_THREADS) select_threshold_kernel(SelectParams p) {
   __shared__ uint32_t s_tmp[SEL_SCAN_THREADS + 40];
-  const int row = blockIdx.y;
+  const int row = blockIdx.x;
   uint32_t bin, above, inb;
   find_threshold<SEL_SCAN_THREADS>(p.hist + (int64_t)row * SEL_HIST_BINS, SEL_HIST_BINS, (uint32_t)p.kk, s_tmp, bin,
                                    above, inb);
-  if (above + inb > (uint32_t)p.cap) return;
+  if (threadIdx.x == 0) p.thresholds[row] = make_uint4(bin, above, inb, 0u);
+}
+
+// Appends every element whose top-12-bit bin is >= the threshold bin to the row's candidate list
+// (skipped for rows whose candidate set would not fit; the final kernel handles those).
+// Each thread holds SEL_TOK_PER_THREAD elements in registers; the CTA reserves its output range
+// with ONE atomic and writes its candidates in token order.
+constexpr int SEL_TOK_PER_THREAD = 16;
+constexpr int SEL_TOK_PER_CTA = SEL_TOK_PER_THREAD * SEL_SCAN_THREADS;   // 4096
+
+template <bool VEC>
+__global__ void __launch_bounds__(SEL_SCAN_THREADS) select_collect_kernel(SelectParams p) {
+  __shared__ uint32_t s_warp[SEL_SCAN_THREADS / 32 + 2];
+  __shared__ uint32_t s_base;
+  const int row = blockIdx.y;
+  const uint4 thr = p.thresholds[row];
+  if (thr.y + thr.z > (uint32_t)p.cap) return;
+  const uint32_t bin = thr.x;
   const float* src = p.scores + (int64_t)row * p.row_stride;
-  uint64_t* cand = p.cand + (int64_t)row * p.cap;
-  uint32_t* count = p.cand_count + row;
-  const int lane = threadIdx.x & 31;
-  const int64_t t0 = (int64_t)blockIdx.x * p.tokens_per_cta;
-  int64_t t1 = t0 + p.tokens_per_cta;
-  if (t1 > p.T) t1 = p.T;
-  // warp-uniform trip count so the ballots below see the whole warp
-  for (int64_t tb = t0 + (threadIdx.x & ~31); tb < t1; tb += SEL_SCAN_THREADS) {
-    const int64_t t = tb + lane;
-    bool take = false;
-    uint32_t key = 0;
-    if (t < t1) {
-      key = float_to_key(src[t]);
-      take = (key >> (32 - SEL_HIST_BITS)) >= bin;
-    }
-    const uint32_t m = __ballot_sync(0xffffffffu, take);
-    if (m) {
-      uint32_t base = 0;
-      const int leader = __ffs(m) - 1;
-      if (lane == leader) base = atomicAdd(count, (uint32_t)__popc(m));
-      base = __shfl_sync(0xffffffffu, base, leader);
-      if (take) {
-        const uint32_t pos = base + (uint32_t)__popc(m & ((1u << lane) - 1u));
-        if (pos < (uint32_t)p.cap)
-          cand[pos] = ((uint64_t)key << 32) | (uint64_t)(0xFFFFFFFFu - element_index(p, row, t));
+  const int64_t t0 = (int64_t)blockIdx.x * SEL_TOK_PER_CTA;
+  const int tid = threadIdx.x;
+
+  float v[SEL_TOK_PER_THREAD];
+  if (VEC) {
+#pragma unroll
+    for (int j = 0; j < SEL_TOK_PER_THREAD / 4; ++j) {
+      const int64_t t = t0 + j * (SEL_SCAN_THREADS * 4) + tid * 4;
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t + 3 < p.T) {
+        x = __ldcg(reinterpret_cast<const float4*>(src + t));
+      } else {
+        if (t < p.T) x.x = src[t];
+        if (t + 1 < p.T) x.y = src[t + 1];
+        if (t + 2 < p.T) x.z = src[t + 2];
       }
+      v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < SEL_TOK_PER_THREAD / 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t t = t0 + j * (SEL_SCAN_THREADS * 4) + tid * 4 + i;
+        v[4 * j + i] = t < p.T ? src[t] : 0.0f;
+      }
+  }
+  uint32_t takemask = 0;
+#pragma unroll
+  for (int e = 0; e < SEL_TOK_PER_THREAD; ++e) {
+    const int64_t t = t0 + (e >> 2) * (SEL_SCAN_THREADS * 4) + tid * 4 + (e & 3);
+    if (t < p.T && (float_to_key(v[e]) >> (32 - SEL_HIST_BITS)) >= bin) takemask |= 1u << e;
+  }
+  uint32_t total;
+  const uint32_t off = block_exclusive_scan<SEL_SCAN_THREADS>((uint32_t)__popc(takemask), s_warp, total);
+  if (total == 0) return;
+  if (tid == 0) s_base = atomicAdd(p.cand_count + row, total);
+  __syncthreads();
+  uint64_t* cand = p.cand + (int64_t)row * p.cap;
+  uint32_t pos = s_base + off;
+#pragma unroll
+  for (int e = 0; e < SEL_TOK_PER_THREAD; ++e) {
+    if (takemask & (1u << e)) {
+      const int64_t t = t0 + (e >> 2) * (SEL_SCAN_THREADS * 4) + tid * 4 + (e & 3);
+      if (pos < (uint32_t)p.cap) cand[pos] = make_composite(v[e], element_index(p, row, t));
+      ++pos;
     }
   }
 }
@@ -180,35 +253,34 @@ __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
   }
 }
 
-// One CTA per row: take the prepared candidates (or refine the prefix over the row itself when
-// they did not fit), sort, write the first kk.
+// One CTA per row: candidates -> exact k-th composite -> the k winners in the requested order.
 __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectParams p) {
   extern __shared__ __align__(16) uint8_t sel_smem[];
   uint64_t* s_cand = reinterpret_cast<uint64_t*>(sel_smem);                     // [cap]
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(sel_smem + (size_t)p.cap * 8);  // [2048]
   uint32_t* s_tmp = s_hist + 2048;                                              // [NT + 40]
-  uint32_t* s_count = s_tmp + SEL_FINAL_THREADS + 40;                           // [1]
+  uint32_t* s_count = s_tmp + SEL_FINAL_THREADS + 40;                           // [4]
+  uint32_t* s_bitmap = s_count + 4;                                             // [ceil(T/32)] when use_bitmap
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
   const float* src = p.scores + (int64_t)row * p.row_stride;
 
-  uint32_t bin, above, inb;
-  find_threshold<SEL_FINAL_THREADS>(p.hist + (int64_t)row * SEL_HIST_BINS, SEL_HIST_BINS, (uint32_t)p.kk, s_tmp, bin,
-                                    above, inb);
-  int n;   // number of candidates placed in s_cand
-  if (above + inb <= (uint32_t)p.cap) {
-    n = (int)(above + inb);
+  const uint4 thr = p.thresholds[row];
+  uint64_t prefix = thr.x;                              // top `fixed` bits of the k-th composite so far
+  int fixed = SEL_HIST_BITS;
+  uint32_t need = (uint32_t)p.kk - thr.y;               // still to take from inside the prefix
+  uint32_t in_prefix = thr.z;
+  int n;                                                // candidates in s_cand: all with composite >= prefix
+  if (thr.y + thr.z <= (uint32_t)p.cap) {
+    n = (int)(thr.y + thr.z);
     const uint32_t have = p.cand_count[row];
-    if ((uint32_t)n > have) n = (int)have;             // cannot happen; keeps reads in bounds
+    if ((uint32_t)n > have) n = (int)have;              // cannot happen; keeps reads in bounds
     const uint64_t* cand = p.cand + (int64_t)row * p.cap;
-    for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = cand[i];
+    for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
+    __syncthreads();
   } else {
-    // Refinement: prefix = the bits fixed so far (top `fixed` bits of the composite).
-    uint64_t prefix = bin;
-    int fixed = SEL_HIST_BITS;
-    uint32_t need = (uint32_t)p.kk - above;            // still to take from inside the prefix
-    uint32_t in_prefix = inb;
+    // Too many candidates share the threshold bin: refine over the row itself until they fit.
     while ((uint32_t)p.kk - need + in_prefix > (uint32_t)p.cap && fixed < 64) {
       const int width = (64 - fixed) >= 11 ? 11 : (64 - fixed);
       const int shift = 64 - fixed - width;
@@ -227,13 +299,12 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
       prefix = (prefix << width) | d;
       fixed += width;
     }
-    // Collect everything at or above the prefix: (kk - need) sure ones + in_prefix <= cap.
     if (tid == 0) *s_count = 0;
     __syncthreads();
     const int sh = 64 - fixed;
     for (int64_t t = tid; t < p.T; t += SEL_FINAL_THREADS) {
       const uint64_t c = make_composite(src[t], element_index(p, row, t));
-      const bool take = (sh >= 64) ? true : ((c >> sh) >= prefix);
+      const bool take = (sh == 0) ? (c >= prefix) : ((c >> sh) >= prefix);
       if (take) {
         const uint32_t pos = atomicAdd(s_count, 1u);
         if (pos < (uint32_t)p.cap) s_cand[pos] = c;
@@ -243,14 +314,87 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     n = (int)*s_count;
     if (n > p.cap) n = p.cap;
   }
-  int n2 = 1;
+
+  // Finish the radix select inside shared memory: stop when exactly `need` elements carry the prefix.
+  while (in_prefix > need && fixed < 64) {
+    const int width = (64 - fixed) >= 11 ? 11 : (64 - fixed);
+    const int shift = 64 - fixed - width;
+    const int nb = 1 << width;
+    for (int i = tid; i < nb; i += SEL_FINAL_THREADS) s_hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
+      const uint64_t c = s_cand[i];
+      if ((c >> (64 - fixed)) == prefix) atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
+    }
+    __syncthreads();
+    uint32_t d, ab, in;
+    find_threshold<SEL_FINAL_THREADS>(s_hist, nb, need, s_tmp, d, ab, in);
+    need -= ab;
+    in_prefix = in;
+    prefix = (prefix << width) | d;
+    fixed += width;
+  }
+  const uint64_t kth = fixed >= 64 ? prefix : (prefix << (64 - fixed));   // the winners: composite >= kth
+
+  if (p.use_bitmap) {
+    // Ascending-index output: one bit per token of the row, read out in order.
+    const int words = (p.T + 31) >> 5;
+    for (int i = tid; i < words; i += SEL_FINAL_THREADS) s_bitmap[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
+      const uint64_t c = s_cand[i];
+      if (c >= kth) {
+        const uint32_t local = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - (uint32_t)p.idx_offset;
+        atomicOr(&s_bitmap[local >> 5], 1u << (local & 31));
+      }
+    }
+    __syncthreads();
+    const int per = (words + SEL_FINAL_THREADS - 1) / SEL_FINAL_THREADS;
+    const int w0 = tid * per;
+    uint32_t cnt = 0;
+    for (int j = 0; j < per; ++j)
+      if (w0 + j < words) cnt += (uint32_t)__popc(s_bitmap[w0 + j]);
+    uint32_t total;
+    uint32_t pos = block_exclusive_scan<SEL_FINAL_THREADS>(cnt, s_tmp, total);
+    for (int j = 0; j < per; ++j) {
+      if (w0 + j >= words) break;
+      uint32_t bits = s_bitmap[w0 + j];
+      while (bits) {
+        const int bit = __ffs(bits) - 1;
+        bits &= bits - 1;
+        const uint32_t local = (uint32_t)(w0 + j) * 32u + (uint32_t)bit;
+        if (pos < (uint32_t)p.kk) {
+          const int64_t o = (int64_t)row * p.kk + pos;
+          const uint32_t idx = local + (uint32_t)p.idx_offset;
+          if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
+          if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
+          if (p.out_scores) {
+            float sv = src[local];
+            if (sv == 0.0f) sv = 0.0f;
+            p.out_scores[o] = sv;
+          }
+        }
+        ++pos;
+      }
+    }
+    return;
+  }
+
+  // Sorted output: losers become 0 (below every real composite); with order_by_index the key is
+  // re-built so that a descending sort yields ascending indices.
+  for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
+    const uint64_t c = s_cand[i];
+    if (c < kth) s_cand[i] = 0;
+    else if (p.order_by_index) s_cand[i] = ((c & 0xFFFFFFFFull) << 32) | (c >> 32);
+  }
+  int n2 = 2;
   while (n2 < n) n2 <<= 1;
-  if (n2 < 2) n2 = 2;
-  for (int i = n + tid; i < n2; i += SEL_FINAL_THREADS) s_cand[i] = 0;   // below every real composite
+  for (int i = n + tid; i < n2; i += SEL_FINAL_THREADS) s_cand[i] = 0;
   __syncthreads();
   bitonic_sort_desc<SEL_FINAL_THREADS>(s_cand, n2);
   for (int i = tid; i < p.kk; i += SEL_FINAL_THREADS) {
-    const uint64_t c = s_cand[i];
+    uint64_t c = s_cand[i];
+    if (p.order_by_index) c = ((c & 0xFFFFFFFFull) << 32) | (c >> 32);
     const uint32_t idx = 0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull);
     const int64_t o = (int64_t)row * p.kk + i;
     if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
@@ -266,10 +410,15 @@ static int select_cap(int k) {
   return c;
 }
 
+constexpr size_t SEL_FINAL_FIXED_SMEM = sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 40 + 4);
+constexpr size_t SEL_SMEM_LIMIT = 227 * 1024;
+
 struct SelectWorkspace {
-  uint32_t* hist;
-  uint64_t* cand;
-  uint32_t* count;
+  uint32_t* count;     // [R]      } zeroed per call, contiguous
+  uint32_t* hist;      // [R,4096] }
+  uint4* thresholds;   // [R]
+  uint64_t* cand;      // [R,cap]
+  size_t zero_bytes;   // count + hist
   size_t bytes;
 };
 
@@ -281,10 +430,84 @@ static SelectWorkspace select_carve(void* base, int R, int k) {
   off += round_up(sizeof(uint32_t) * (size_t)R, 256);
   w.hist = reinterpret_cast<uint32_t*>(ptr + off);
   off += round_up(sizeof(uint32_t) * (size_t)R * SEL_HIST_BINS, 256);
+  w.zero_bytes = off;
+  w.thresholds = reinterpret_cast<uint4*>(ptr + off);
+  off += round_up(sizeof(uint4) * (size_t)R, 256);
   w.cand = reinterpret_cast<uint64_t*>(ptr + off);
   off += round_up(sizeof(uint64_t) * (size_t)R * select_cap(k), 256);
   w.bytes = off;
   return w;
+}
+
+// Shared by kvb_select_topk and the fused step. `zeroed` tells that the caller already cleared
+// the first zero_bytes of the workspace (count + histogram) on this stream.
+static int select_run(const float* scores, int64_t row_stride, const int32_t* payload, int R, int T, int k,
+                      int64_t idx_offset, int order, int32_t* out_idx32, int64_t* out_idx64, float* out_scores,
+                      const uint32_t* hist_in, bool hist_in_workspace, bool zeroed, void* workspace,
+                      size_t workspace_bytes, int device, cudaStream_t st) {
+  if (!scores || !workspace) return KVB_BAD_ARG;
+  if (!out_idx32 && !out_idx64 && !out_scores) return KVB_BAD_ARG;
+  if (R <= 0 || T <= 0 || k <= 0 || R > 65535) return KVB_BAD_SHAPE;
+  if (order != 0 && order != 1) return KVB_BAD_ARG;
+  const int kk = k < T ? k : T;
+  if (kk > SEL_MAX_K) return KVB_BAD_SHAPE;
+  if (row_stride < T) return KVB_BAD_SHAPE;
+  if (!payload && (idx_offset < 0 || idx_offset + T > 0x7fffffffLL)) return KVB_BAD_SHAPE;
+  if (!aligned_to(workspace, 256) || !aligned_to(scores, 4)) return KVB_BAD_ALIGN;
+  SelectWorkspace w = select_carve(workspace, R, kk);
+  if (workspace_bytes < w.bytes) return KVB_WORKSPACE_TOO_SMALL;
+  DeviceGuard guard(device);
+  if (!guard.ok) return KVB_BAD_DEVICE;
+
+  SelectParams p;
+  p.scores = scores; p.row_stride = row_stride; p.payload = payload;
+  p.R = R; p.T = T; p.k = k; p.kk = kk; p.idx_offset = idx_offset;
+  p.out_idx32 = out_idx32; p.out_idx64 = out_idx64; p.out_scores = out_scores;
+  p.cand = w.cand; p.cand_count = w.count; p.cap = select_cap(kk);
+  p.thresholds = w.thresholds;
+  p.order_by_index = order;
+  const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
+  size_t smem = (size_t)p.cap * 8 + SEL_FINAL_FIXED_SMEM;
+  p.use_bitmap = (order == 1 && !payload && smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
+  if (p.use_bitmap) smem += bitmap_bytes;
+
+  if (hist_in_workspace) {
+    p.hist = w.hist;
+    if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(w.count, 0, sizeof(uint32_t) * (size_t)R, st));
+  } else if (hist_in) {
+    p.hist = hist_in;
+    if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(w.count, 0, sizeof(uint32_t) * (size_t)R, st));
+  } else {
+    if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(workspace, 0, w.zero_bytes, st));
+    p.hist = w.hist;
+    int splits = ceil_div(sm_count(device) * 8, R);
+    const int max_splits = ceil_div(T, 2048);
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    int tokens_per_cta = ceil_div(ceil_div(T, splits), 32) * 32;
+    splits = ceil_div(T, tokens_per_cta);
+    p.tokens_per_cta = tokens_per_cta;
+    select_hist_kernel<<<dim3(splits, R), SEL_SCAN_THREADS, 0, st>>>(p, w.hist);
+    KVB_CHECK_CUDA(cudaGetLastError());
+  }
+  p.tokens_per_cta = SEL_TOK_PER_CTA;
+  select_threshold_kernel<<<R, SEL_SCAN_THREADS, 0, st>>>(p);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  const dim3 cgrid(ceil_div(T, SEL_TOK_PER_CTA), R);
+  const bool vec = aligned_to(scores, 16) && (row_stride % 4) == 0;
+  if (vec) select_collect_kernel<true><<<cgrid, SEL_SCAN_THREADS, 0, st>>>(p);
+  else select_collect_kernel<false><<<cgrid, SEL_SCAN_THREADS, 0, st>>>(p);
+  KVB_CHECK_CUDA(cudaGetLastError());
+
+  static bool attr_done[64] = {false};
+  if (device < 64 && !attr_done[device]) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)SEL_SMEM_LIMIT));
+    attr_done[device] = true;
+  }
+  select_final_kernel<<<R, SEL_FINAL_THREADS, smem, st>>>(p);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  return KVB_OK;
 }
 
 }  // namespace kvb
@@ -296,61 +519,11 @@ extern "C" __attribute__((visibility("default"))) size_t kvb_select_topk_workspa
   return kvb::select_carve(nullptr, R, k).bytes;
 }
 
-extern "C" __attribute__((visibility("default"))) int kvb_select_topk(const float* scores, int64_t row_stride, const int32_t* payload, int R, int T, int k,
-                               int64_t idx_offset, int32_t* out_idx32, int64_t* out_idx64, float* out_scores,
-                               const uint32_t* hist_in, void* workspace, size_t workspace_bytes, int device,
-                               void* stream) {
-  using namespace kvb;
-  if (!scores || !workspace) return KVB_BAD_ARG;
-  if (!out_idx32 && !out_idx64 && !out_scores) return KVB_BAD_ARG;
-  if (R <= 0 || T <= 0 || k <= 0 || R > 65535) return KVB_BAD_SHAPE;
-  const int kk = k < T ? k : T;
-  if (kk > SEL_MAX_K) return KVB_BAD_SHAPE;
-  if (row_stride < T) return KVB_BAD_SHAPE;
-  if (!payload && (idx_offset < 0 || idx_offset + T > 0x7fffffffLL)) return KVB_BAD_SHAPE;
-  if (!aligned_to(workspace, 256) || !aligned_to(scores, 4)) return KVB_BAD_ALIGN;
-  SelectWorkspace w = select_carve(workspace, R, kk);
-  if (workspace_bytes < w.bytes) return KVB_WORKSPACE_TOO_SMALL;
-  DeviceGuard guard(device);
-  if (!guard.ok) return KVB_BAD_DEVICE;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-
-  SelectParams p;
-  p.scores = scores; p.row_stride = row_stride; p.payload = payload;
-  p.R = R; p.T = T; p.k = k; p.kk = kk; p.idx_offset = idx_offset;
-  p.out_idx32 = out_idx32; p.out_idx64 = out_idx64; p.out_scores = out_scores;
-  p.cand = w.cand; p.cand_count = w.count; p.cap = select_cap(kk);
-
-  // CTAs along a row: aim at ~8 CTAs per SM in total, at least 2048 tokens each.
-  int splits = ceil_div(sm_count(device) * 8, R);
-  const int max_splits = ceil_div(T, 2048);
-  if (splits > max_splits) splits = max_splits;
-  if (splits < 1) splits = 1;
-  int tokens_per_cta = ceil_div(T, splits);
-  tokens_per_cta = ceil_div(tokens_per_cta, 32) * 32;
-  splits = ceil_div(T, tokens_per_cta);
-  p.tokens_per_cta = tokens_per_cta;
-
-  KVB_CHECK_CUDA(cudaMemsetAsync(w.count, 0, sizeof(uint32_t) * (size_t)R, st));
-  if (hist_in) {
-    p.hist = hist_in;
-  } else {
-    KVB_CHECK_CUDA(cudaMemsetAsync(w.hist, 0, sizeof(uint32_t) * (size_t)R * SEL_HIST_BINS, st));
-    p.hist = w.hist;
-    select_hist_kernel<<<dim3(splits, R), SEL_SCAN_THREADS, 0, st>>>(p, w.hist);
-    KVB_CHECK_CUDA(cudaGetLastError());
-  }
-  select_collect_kernel<<<dim3(splits, R), SEL_SCAN_THREADS, 0, st>>>(p);
-  KVB_CHECK_CUDA(cudaGetLastError());
-
-  const size_t smem = (size_t)p.cap * 8 + sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 40 + 4);
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)((size_t)SEL_MAX_K * 8 + sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 44))));
-    attr_done[device] = true;
-  }
-  select_final_kernel<<<R, SEL_FINAL_THREADS, smem, st>>>(p);
-  KVB_CHECK_CUDA(cudaGetLastError());
-  return KVB_OK;
+extern "C" __attribute__((visibility("default"))) int kvb_select_topk(
+    const float* scores, int64_t row_stride, const int32_t* payload, int R, int T, int k, int64_t idx_offset,
+    int order, int32_t* out_idx32, int64_t* out_idx64, float* out_scores, const uint32_t* hist_in, void* workspace,
+    size_t workspace_bytes, int device, void* stream) {
+  return kvb::select_run(scores, row_stride, payload, R, T, k, idx_offset, order, out_idx32, out_idx64, out_scores,
+                         hist_in, /*hist_in_workspace=*/false, /*zeroed=*/false, workspace, workspace_bytes, device,
+                         reinterpret_cast<cudaStream_t>(stream));
 }

@@ -399,14 +399,17 @@ extern "C" __attribute__((visibility("default"))) size_t kvb_sparse_attend_works
   return kvb::attend_plan(B, Hq, Hi, S).bytes;
 }
 
-extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb,
-                                 int64_t k_sh, int64_t k_st, const void* value, int64_t v_sb, int64_t v_sh,
-                                 int64_t v_st, const void* indices, int idx_is_i64, const uint8_t* valid,
-                                 const float* mask, int64_t mask_sb, int B, int Hq, int Hkv, int Hi, int Tk, int D,
-                                 int S, float scaling, void* out, float* out_partial, void* workspace,
-                                 size_t workspace_bytes, int device, void* stream) {
-  using namespace kvb;
-  if (!query || !key || !value || !indices || !workspace) return KVB_BAD_ARG;
+namespace kvb {
+
+// Shared by kvb_sparse_attend and the fused step. `counters_zeroed` tells that the caller already
+// cleared ws_counter on this stream.
+static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh,
+                      int64_t k_st, const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st,
+                      const void* indices, int idx_is_i64, const uint8_t* valid, const float* mask, int64_t mask_sb,
+                      int B, int Hq, int Hkv, int Hi, int Tk, int D, int S, float scaling, void* out,
+                      float* out_partial, uint32_t* ws_counter, float* ws_partial, bool counters_zeroed, int device,
+                      cudaStream_t st) {
+  if (!query || !key || !value || !indices || !ws_counter || !ws_partial) return KVB_BAD_ARG;
   if (!out && !out_partial) return KVB_BAD_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hi <= 0 || Tk <= 0 || S <= 0) return KVB_BAD_SHAPE;
   if (D != AT_D || (Hq % Hkv) || (Hi != Hkv && Hi != Hq)) return KVB_BAD_SHAPE;
@@ -416,13 +419,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(const vo
   if (!aligned_to(query, 16) || !aligned_to(key, 16) || !aligned_to(value, 16)) return KVB_BAD_ALIGN;
   if ((q_sb % 8) || (q_sh % 8) || (k_sb % 8) || (k_sh % 8) || (k_st % 8) || (v_sb % 8) || (v_sh % 8) || (v_st % 8))
     return KVB_BAD_ALIGN;
-  if (!aligned_to(indices, idx_is_i64 ? 8 : 4) || !aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
+  if (!aligned_to(indices, idx_is_i64 ? 8 : 4) || !aligned_to(ws_partial, 16)) return KVB_BAD_ALIGN;
   if (out && !aligned_to(out, 2)) return KVB_BAD_ALIGN;
   const AttendPlan plan = attend_plan(B, Hq, Hi, S);
-  if (workspace_bytes < plan.bytes) return KVB_WORKSPACE_TOO_SMALL;
   DeviceGuard guard(device);
   if (!guard.ok) return KVB_BAD_DEVICE;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
   AttendParams p;
   p.query = reinterpret_cast<const __nv_bfloat16*>(query); p.q_sb = q_sb; p.q_sh = q_sh;
@@ -434,17 +435,37 @@ extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(const vo
   p.scaling = scaling;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.out_partial = out_partial;
-  p.ws_counter = reinterpret_cast<uint32_t*>(workspace);
-  p.ws_partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes);
+  p.ws_counter = ws_counter;
+  p.ws_partial = ws_partial;
   p.nsplit = plan.nsplit; p.tiles_per_cta = plan.tiles_per_cta;
 
-  KVB_CHECK_CUDA(cudaMemsetAsync(p.ws_counter, 0, sizeof(uint32_t) * (size_t)B * Hi, st));
+  if (!counters_zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(p.ws_counter, 0, sizeof(uint32_t) * (size_t)B * Hi, st));
   switch (GG) {
     case 1: return attend_launch<1>(p, device, st);
     case 2: return attend_launch<2>(p, device, st);
     case 4: return attend_launch<4>(p, device, st);
     default: return attend_launch<8>(p, device, st);
   }
+}
+
+}  // namespace kvb
+
+extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(
+    const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+    const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st, const void* indices, int idx_is_i64,
+    const uint8_t* valid, const float* mask, int64_t mask_sb, int B, int Hq, int Hkv, int Hi, int Tk, int D, int S,
+    float scaling, void* out, float* out_partial, void* workspace, size_t workspace_bytes, int device, void* stream) {
+  using namespace kvb;
+  if (!workspace) return KVB_BAD_ARG;
+  if (B <= 0 || Hq <= 0 || Hi <= 0 || S <= 0 || (Hq % Hi)) return KVB_BAD_SHAPE;
+  if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
+  const AttendPlan plan = attend_plan(B, Hq, Hi, S);
+  if (workspace_bytes < plan.bytes) return KVB_WORKSPACE_TOO_SMALL;
+  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, indices, idx_is_i64, valid,
+                    mask, mask_sb, B, Hq, Hkv, Hi, Tk, D, S, scaling, out, out_partial,
+                    reinterpret_cast<uint32_t*>(workspace),
+                    reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes),
+                    /*counters_zeroed=*/false, device, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" __attribute__((visibility("default"))) int kvb_lse_merge(const float* partials, int N, int B, int Hq, int D, void* out, int device,

@@ -194,11 +194,14 @@ def score(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channe
 
 def select(scores: torch.Tensor, k: int, *, payload: Optional[torch.Tensor] = None, idx_offset: int = 0,
            hist: Optional[torch.Tensor] = None, return_scores: bool = False,
-           index_dtype: torch.dtype = torch.int64):
-    """Top-``k`` columns of every row of ``scores[..., T]`` ordered by (score desc, index asc).
+           index_dtype: torch.dtype = torch.int64, order: str = "score"):
+    """Exact top-``k`` columns of every row of ``scores[..., T]``; equal scores go to the lower index.
 
+    ``order="score"`` returns them by (score desc, index asc), ``order="index"`` by ascending index.
     Returns indices ``[..., min(k,T)]`` (and the scores when asked). ``payload`` (int32, same
     shape as scores) replaces the column number as the index that is returned and tie-broken."""
+    if order not in ("score", "index"):
+        raise RuntimeError("order must be 'score' or 'index'")
     if scores.dtype != torch.float32:
         raise RuntimeError("scores must be float32")
     lead = scores.shape[:-1]
@@ -224,7 +227,7 @@ def select(scores: torch.Tensor, k: int, *, payload: Optional[torch.Tensor] = No
         raise RuntimeError("index_dtype must be torch.int32 or torch.int64")
     outs = torch.empty((R, kk), dtype=torch.float32, device=dev) if return_scores else None
     check(lib.kvb_select_topk(
-        s2.data_ptr(), s2.stride(0), _ptr(p2), R, T, int(k), int(idx_offset),
+        s2.data_ptr(), s2.stride(0), _ptr(p2), R, T, int(k), int(idx_offset), int(order == "index"),
         _ptr(out32), _ptr(out64), _ptr(outs), _ptr(hist), ws.data_ptr(), ws_bytes,
         _dev(scores), _stream(dev)), "kvb_select_topk")
     idx = (out32 if out32 is not None else out64).reshape(*lead, kk)

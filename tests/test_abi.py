@@ -53,5 +53,5 @@ def test_bad_arguments_are_rejected_before_any_launch():
     lib = _native.lib()
     # null pointers / impossible shapes return a status without touching a device
     assert lib.kvb_quantize_pack(None, 0, 0, 0, None, None, 0, 0, None, 0, 0, 1, 1, 1, 128, 32, 0, 0, None) == 7
-    assert lib.kvb_select_topk(None, 0, None, 1, 1, 1, 0, None, None, None, None, None, 0, 0, None) == 7
+    assert lib.kvb_select_topk(None, 0, None, 1, 1, 1, 0, 0, None, None, None, None, None, 0, 0, None) == 7
     assert lib.kvb_lse_merge(None, 1, 1, 1, 128, None, 0, None) == 7

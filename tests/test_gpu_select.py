@@ -19,9 +19,15 @@ def _check(scores, k, payload=None, idx_offset=0):
         assert got_i.dtype == dt
         assert torch.equal(got_i.cpu().long(), want_i)
         assert torch.equal(got_s.cpu(), want_s)
+    # the same set written by ascending index (bitmap path, or the sort path with a payload)
+    asc_i, order = torch.sort(want_i, dim=-1)
+    got_i, got_s = ops.select(scores, k, payload=payload, idx_offset=idx_offset, return_scores=True, order="index")
+    assert torch.equal(got_i.cpu(), asc_i)
+    assert torch.equal(got_s.cpu(), torch.gather(want_s, -1, order))
 
 
-@pytest.mark.parametrize("T,k", [(1, 1), (5, 8), (63, 7), (64, 64), (65, 3), (257, 100), (4096, 256), (100000, 2048)])
+@pytest.mark.parametrize("T,k", [(1, 1), (5, 8), (63, 7), (64, 64), (65, 3), (257, 100), (4096, 256), (4097, 4097),
+                                 (100000, 2048), (1048576, 4096), (1500000, 300)])
 def test_gaussian_scores(cuda_device, T, k):
     g = torch.Generator(device=cuda_device).manual_seed(T * 31 + k)
     _check(torch.randn(3, T, generator=g, device=cuda_device), k)
