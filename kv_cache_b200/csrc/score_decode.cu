@@ -3,17 +3,16 @@
 // HBM-bound: every packed token (C/2 bytes) and its fp32 scale is read exactly once. The stream
 // is staged through shared memory by the TMA engine (1-D cp.async.bulk + mbarrier), one private
 // stage ring per warp so no CTA-wide barrier sits in the loop. Nibbles are widened to int8*16 with
-// one shift and two masks per 32-bit word, accumulated exactly in int32 with dp4a against the
-// int8 query codes of all G heads of the KV head, combined across the C/32 lanes that share a
-// token with warp shuffles, dequantised with two rounded fp32 products and reduced to the
-// group maximum in registers. Only the group maximum (4 bytes per token per KV head) is written.
+// one shift and two masks per 32-bit word and multiplied exactly in int32 against the int8 query
+// codes of all G heads of the KV head (int8 tensor-core tiles in the streaming kernel, plain
+// integer arithmetic in the generic one), dequantised with two rounded fp32 products and reduced
+// to the group maximum in registers. Only the group maximum (4 bytes per token per KV head) is
+// written, plus an optional histogram of its sort keys for the selector.
 #include "common.cuh"
 
 namespace kvb {
 
-constexpr int SC_WARPS = 4;
-constexpr int SC_THREADS = SC_WARPS * 32;
-constexpr int SC_TILE_PACKED_BYTES = 4096;       // packed bytes per warp tile, whatever C is
+constexpr int SC_THREADS = 128;                  // generic kernel
 constexpr int SC_HIST_BITS = 12;
 constexpr int SC_HIST_BINS = 1 << SC_HIST_BITS;
 constexpr int SC_MAX_C = 128;
@@ -104,28 +103,59 @@ __device__ __forceinline__ void score_token_plain(const ScoreParams& p, int G, i
   if (s_hist) atomicAdd(&s_hist[float_to_key(best) >> (32 - SC_HIST_BITS)], 1u);
 }
 
-// Streaming kernel. C in {32,64,128}; LPT = C/32 lanes share one token (16 bytes each).
-// NS = stages of each warp's ring. Persistent: CTA c owns the contiguous unit range
-// [c*U/grid, (c+1)*U/grid) of the flattened (row, tile) space.
+// int8 tensor-core tile: D[16x8] (int32) += A[16x32] (int8, row) * B[32x8] (int8, col).
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Streaming kernel. C in {32,64,128}, G in {1,2,4,8}.
+//
+// A warp owns a ring of NS stages; each stage holds TW tokens (packed bytes + scales) brought in
+// by two bulk copies. The integer dot products of 16 tokens x 32 channels x 8 columns run as one
+// m16n8k32 int8 MMA: a lane (g = lane/4, t = lane%4) reads C/8 contiguous bytes of the tokens in
+// rows g and g+8, widens each packed word into "low nibbles * 16" and "high nibbles * 16" (three
+// integer ops) and uses them directly as A fragments; the query codes sit in the B fragment in
+// the matching channel order. With G < 8 heads the 8 columns are shared by 8/G token tiles
+// (tile j's heads go to columns [jG, jG+G)), so one accumulator covers 128/G tokens densely and
+// every lane dequantises exactly four (token, head) values.
+// Persistent: CTA c owns the contiguous unit range [c*U/grid, (c+1)*U/grid) of the flattened
+// (row, tile) space.
+template <int C, int G>
+struct ScoreCfg {
+  static constexpr int WARPS = 8;
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr int KS = C / 32;                     // k-steps of 32 channels; also packed words per lane-token
+  static constexpr int TPA = 8 / G;                     // 16-token tiles that share one accumulator
+  static constexpr int ITER_TOKENS = 16 * TPA;          // tokens per accumulator
+  static constexpr int TW = ITER_TOKENS > 64 ? ITER_TOKENS : 64;   // tokens per stage
+  static constexpr int IT = TW / ITER_TOKENS;
+  static constexpr int TOKEN_BYTES = C / 2;
+  static constexpr int PACKED_BYTES = TW * TOKEN_BYTES;
+  static constexpr int STAGE_BYTES = PACKED_BYTES + TW * 4;
+};
+
 template <int C, int G, int NS, bool HIST>
-__global__ void __launch_bounds__(SC_THREADS) score_decode_stream_kernel(ScoreParams p) {
-  constexpr int LPT = C / 32;
-  constexpr int TW = SC_TILE_PACKED_BYTES / (C / 2);    // tokens per warp tile: 256 / 128 / 64
-  constexpr int IT = TW / 32;                           // 32-token iterations per tile
-  constexpr int STAGE_BYTES = SC_TILE_PACKED_BYTES + TW * 4;
-  constexpr int TOK_PER_LOAD = 32 / LPT;
+__global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_stream_kernel(ScoreParams p) {
+  using Cfg = ScoreCfg<C, G>;
+  constexpr int KS = Cfg::KS, TPA = Cfg::TPA, TW = Cfg::TW, IT = Cfg::IT;
+  constexpr int WARPS = Cfg::WARPS, THREADS = Cfg::THREADS;
+  constexpr int STAGE_BYTES = Cfg::STAGE_BYTES, PACKED_BYTES = Cfg::PACKED_BYTES, TOKEN_BYTES = Cfg::TOKEN_BYTES;
 
   extern __shared__ __align__(128) uint8_t smem_raw[];
   // layout: [warps][NS][STAGE_BYTES] | bars [warps][NS] | qv | qscale | qcode | hist
   uint8_t* s_stage = smem_raw;
-  uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + SC_WARPS * NS * STAGE_BYTES);
-  float* s_qv = reinterpret_cast<float*>(s_bar + SC_WARPS * NS);
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + WARPS * NS * STAGE_BYTES);
+  float* s_qv = reinterpret_cast<float*>(s_bar + WARPS * NS);
   float* s_qscale = s_qv + G * C;
   int8_t* s_qcode = reinterpret_cast<int8_t*>(s_qscale + SC_MAX_G);
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_qcode + G * C);   // G*C is a multiple of 32
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int hq = lane % LPT;                 // which 16-byte quarter/half of a token this lane reads
+  const int g = lane >> 2, t4 = lane & 3;
   uint8_t* my_stage = s_stage + warp * NS * STAGE_BYTES;
   uint64_t* my_bar = s_bar + warp * NS;
 
@@ -135,7 +165,7 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_stream_kernel(ScorePa
     fence_mbar_init();
   }
   if (HIST) {
-    for (int i = tid; i < SC_HIST_BINS; i += SC_THREADS) s_hist[i] = 0;
+    for (int i = tid; i < SC_HIST_BINS; i += THREADS) s_hist[i] = 0;
   }
   fence_proxy_async_smem();
   __syncthreads();
@@ -147,6 +177,13 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_stream_kernel(ScorePa
   uint32_t ring = 0;        // tiles this warp has consumed so far (stage = ring % NS, parity = ring / NS & 1)
   bool dead = false;        // a bounded wait gave up: skip all further streaming work
 
+  // Which accumulator column pair this lane reads back: columns 2*t4, 2*t4+1.
+  //   G >= 2: both columns belong to tile jt = 2*t4 / G, heads h0 = 2*t4 % G and h0 + 1.
+  //   G == 1: column c is tile c, head 0.
+  constexpr int HV = G >= 2 ? 2 : 1;                     // distinct heads among the lane's two columns
+  const int jt = (2 * t4) / G;
+  const int h0 = (2 * t4) % G;
+
   int64_t u = u_begin;
   while (u < u_end) {
     const int row = (int)(u / p.units_per_row);
@@ -154,47 +191,52 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_stream_kernel(ScorePa
     int64_t row_end_u = (int64_t)(row + 1) * p.units_per_row;
     const int ub = (int)((row_end_u < u_end ? row_end_u : u_end) - (int64_t)row * p.units_per_row);
     u += (ub - ua);
-    const int b = row / p.Hkv, g = row - b * p.Hkv;
+    const int b = row / p.Hkv, kvh = row - b * p.Hkv;
 
-    quantize_query_group<SC_THREADS>(p, b, g, G, s_qv, s_qcode, s_qscale);
+    quantize_query_group<THREADS>(p, b, kvh, G, s_qv, s_qcode, s_qscale);
 
-    // Per-lane query words: word w of this lane's 16-byte piece holds channels
-    // 32*hq + 8*w + {0,2,4,6} in its low nibbles and + {1,3,5,7} in its high nibbles.
-    int qlo[G][4], qhi[G][4];
-    float qs[G];
+    // B fragments. Lane t4 owns packed bytes [KS*4*t4, KS*4*(t4+1)) of every token; k-step s uses
+    // packed word s: its low nibbles are channels 2*(KS*4*t4 + 4*s + i), its high nibbles the odd
+    // neighbours. Column n = g carries head g - j*G in the variant for tile j, zero elsewhere.
+    uint32_t bq[TPA][KS][2];
 #pragma unroll
-    for (int hd = 0; hd < G; ++hd) {
-      qs[hd] = s_qscale[hd];
+    for (int j = 0; j < TPA; ++j) {
+      const bool mine = (g / G) == j;
+      const int hd = g % G;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int s = 0; s < KS; ++s) {
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int c = 32 * hq + 8 * w + 2 * i;
+          const int c = 2 * (KS * 4 * t4 + 4 * s + i);
           lo |= (uint32_t)(uint8_t)s_qcode[hd * C + c] << (8 * i);
           hi |= (uint32_t)(uint8_t)s_qcode[hd * C + c + 1] << (8 * i);
         }
-        qlo[hd][w] = (int)lo;
-        qhi[hd][w] = (int)hi;
+        bq[j][s][0] = mine ? lo : 0u;
+        bq[j][s][1] = mine ? hi : 0u;
       }
     }
+    // The accumulator holds 16 * dot; fold the 1/16 into the (power-of-two exact) query scale.
+    float qs16[HV];
+#pragma unroll
+    for (int v = 0; v < HV; ++v) qs16[v] = s_qscale[(h0 + v) % G] * 0.0625f;
 
-    const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)g * p.packed_sh;
-    const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)g * p.scale_sh;
+    const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)kvh * p.packed_sh;
+    const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)kvh * p.scale_sh;
     float* gmax_row = p.gmax_out ? p.gmax_out + (int64_t)row * p.T : nullptr;
 
-    // Full tiles of this segment: [ta, tb); warp w takes ta + w, ta + w + SC_WARPS, ...
+    // Full tiles of this segment: [ta, tb); warp w takes ta + w, ta + w + WARPS, ...
     const int ta = ua;
     const int tb = ub < p.full_tiles ? ub : p.full_tiles;
-    const int nmy = (tb - ta - warp + SC_WARPS - 1) / SC_WARPS;   // <= 0 when none
+    const int nmy = (tb - ta - warp + WARPS - 1) / WARPS;   // <= 0 when none
 
     auto issue = [&](int j, uint32_t slot) {
       // lane 0 only: tile j of this warp into ring slot `slot`
-      const int64_t t0 = (int64_t)(ta + warp + j * SC_WARPS) * TW;
+      const int64_t t0 = (int64_t)(ta + warp + j * WARPS) * TW;
       uint8_t* dst = my_stage + (slot % NS) * STAGE_BYTES;
       mbar_arrive_expect_tx(&my_bar[slot % NS], STAGE_BYTES);
-      bulk_g2s_evict_first(dst, packed_row + t0 * (C / 2), SC_TILE_PACKED_BYTES, &my_bar[slot % NS], policy);
-      bulk_g2s_evict_first(dst + SC_TILE_PACKED_BYTES, scale_row + t0, TW * 4, &my_bar[slot % NS], policy);
+      bulk_g2s_evict_first(dst, packed_row + t0 * TOKEN_BYTES, PACKED_BYTES, &my_bar[slot % NS], policy);
+      bulk_g2s_evict_first(dst + PACKED_BYTES, scale_row + t0, TW * 4, &my_bar[slot % NS], policy);
     };
 
     if (!dead && nmy > 0) {
@@ -208,78 +250,105 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_stream_kernel(ScorePa
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { dead = true; break; }
         const uint8_t* st = my_stage + (slot % NS) * STAGE_BYTES;
-        const uint4* sp = reinterpret_cast<const uint4*>(st);
-        const float* ssc = reinterpret_cast<const float*>(st + SC_TILE_PACKED_BYTES);
-        const int64_t t0 = (int64_t)(ta + warp + j * SC_WARPS) * TW;
+        const float* ssc = reinterpret_cast<const float*>(st + PACKED_BYTES);
+        const int64_t t0 = (int64_t)(ta + warp + j * WARPS) * TW;
 
-#pragma unroll 1
+#pragma unroll
         for (int it = 0; it < IT; ++it) {
-          int part[LPT][G];
+          int acc[4] = {0, 0, 0, 0};
 #pragma unroll
-          for (int ld = 0; ld < LPT; ++ld) {
-            const uint4 v = sp[it * 32 * LPT + ld * 32 + lane];
-            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+          for (int tj = 0; tj < TPA; ++tj) {
+            // rows g and g+8 of token tile tj: KS packed words each, from this lane's byte range
+            const uint8_t* r0 = st + (size_t)(it * Cfg::ITER_TOKENS + tj * 16 + g) * TOKEN_BYTES + KS * 4 * t4;
+            const uint8_t* r1 = r0 + 8 * TOKEN_BYTES;
+            uint32_t w0[KS], w1[KS];
+            if constexpr (KS == 1) {
+              w0[0] = *reinterpret_cast<const uint32_t*>(r0);
+              w1[0] = *reinterpret_cast<const uint32_t*>(r1);
+            } else if constexpr (KS == 2) {
+              const uint2 x0 = *reinterpret_cast<const uint2*>(r0);
+              const uint2 x1 = *reinterpret_cast<const uint2*>(r1);
+              w0[0] = x0.x; w0[1] = x0.y; w1[0] = x1.x; w1[1] = x1.y;
+            } else {
+              const uint4 x0 = *reinterpret_cast<const uint4*>(r0);
+              const uint4 x1 = *reinterpret_cast<const uint4*>(r1);
+              w0[0] = x0.x; w0[1] = x0.y; w0[2] = x0.z; w0[3] = x0.w;
+              w1[0] = x1.x; w1[1] = x1.y; w1[2] = x1.z; w1[3] = x1.w;
+            }
 #pragma unroll
-            for (int hd = 0; hd < G; ++hd) part[ld][hd] = 0;
+            for (int s = 0; s < KS; ++s) {
+              const uint32_t a0 = (w0[s] << 4) & 0xF0F0F0F0u;   // int8 lanes = 16 * low-nibble codes, row g
+              const uint32_t a1 = (w1[s] << 4) & 0xF0F0F0F0u;   // row g+8
+              const uint32_t a2 = w0[s] & 0xF0F0F0F0u;          // 16 * high-nibble codes, row g
+              const uint32_t a3 = w1[s] & 0xF0F0F0F0u;
+              mma_s8_16832(acc, a0, a1, a2, a3, bq[tj][s][0], bq[tj][s][1]);
+            }
+          }
+          // acc[0], acc[1]: row g, columns 2*t4, 2*t4+1; acc[2], acc[3]: row g+8, same columns.
+          // value v of the lane: row (v>>1 ? g+8 : g), column 2*t4 + (v&1).
+          float d[4];
+          int tl[4];                                        // token (inside the stage) of each value
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const int lo = (int)((wv[w] << 4) & 0xF0F0F0F0u);   // int8 lanes = 16 * low-nibble code
-              const int hi = (int)(wv[w] & 0xF0F0F0F0u);          // int8 lanes = 16 * high-nibble code
+          for (int v = 0; v < 4; ++v) {
+            const int col = v & 1;
+            const int tile = G >= 2 ? jt : (2 * t4 + col);
+            tl[v] = it * Cfg::ITER_TOKENS + tile * 16 + g + ((v >> 1) ? 8 : 0);
+            const float f = __int_as_float(acc[v] + 0x4B400000) - 12582912.0f;   // exact int -> float, |acc| < 2^22
+            d[v] = __fmul_rn(__fmul_rn(f, ssc[tl[v]]), qs16[G >= 2 ? col : 0]);
+          }
+          if (p.acc_out || p.deq_out) {
 #pragma unroll
-              for (int hd = 0; hd < G; ++hd) {
-                part[ld][hd] = __dp4a(lo, qlo[hd][w], part[ld][hd]);
-                part[ld][hd] = __dp4a(hi, qhi[hd][w], part[ld][hd]);
+            for (int v = 0; v < 4; ++v) {
+              const int hd = G >= 2 ? (h0 + (v & 1)) : 0;
+              const int64_t o = ((int64_t)b * p.Hq + (int64_t)kvh * G + hd) * p.T + t0 + tl[v];
+              if (p.acc_out) p.acc_out[o] = acc[v] >> 4;
+              if (p.deq_out) p.deq_out[o] = d[v];
+            }
+          }
+          // Group maximum per token, then every lane finishes NOUT tokens of its own.
+          if constexpr (G >= 2) {
+            float m0 = fmaxf(d[0], d[1]);                   // row g
+            float m1 = fmaxf(d[2], d[3]);                   // row g+8
+            if constexpr (G >= 4) {
+              m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+              m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+            }
+            if constexpr (G >= 8) {
+              m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+              m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+            }
+            if constexpr (G == 2) {
+              // the lane alone holds both heads of its two tokens
+              if (m0 == 0.0f) m0 = 0.0f;
+              if (m1 == 0.0f) m1 = 0.0f;
+              if (gmax_row) { gmax_row[t0 + tl[0]] = m0; gmax_row[t0 + tl[2]] = m1; }
+              if (HIST) {
+                atomicAdd(&s_hist[float_to_key(m0) >> (32 - SC_HIST_BITS)], 1u);
+                atomicAdd(&s_hist[float_to_key(m1) >> (32 - SC_HIST_BITS)], 1u);
+              }
+            } else {
+              // G == 4: lanes (t4, t4^1) share two tokens -> even lane finishes row g, odd lane row g+8.
+              // G == 8: the quad shares two tokens -> lane t4 == 0 finishes row g, t4 == 1 row g+8.
+              const bool second = (t4 & 1) != 0;
+              float m = second ? m1 : m0;
+              const int tok = second ? tl[2] : tl[0];
+              const bool writer = (G == 4) ? true : (t4 < 2);
+              if (m == 0.0f) m = 0.0f;
+              if (writer) {
+                if (gmax_row) gmax_row[t0 + tok] = m;
+                if (HIST) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
               }
             }
-          }
-          // Transposing reduction over the LPT lanes of a token: afterwards lane with
-          // hq == ld owns the complete sum of the token read by load ld.
-          int mine[G];
-          if constexpr (LPT == 1) {
-#pragma unroll
-            for (int hd = 0; hd < G; ++hd) mine[hd] = part[0][hd];
-          } else if constexpr (LPT == 2) {
-#pragma unroll
-            for (int hd = 0; hd < G; ++hd) {
-              const int send = hq ? part[0][hd] : part[LPT - 1][hd];
-              const int keep = hq ? part[LPT - 1][hd] : part[0][hd];
-              mine[hd] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
-            }
           } else {
-            const int hb = (hq >> 1) & 1, lb = hq & 1;
+            // G == 1: four tokens per lane, no reduction
 #pragma unroll
-            for (int hd = 0; hd < G; ++hd) {
-              // step 1 (partner lane ^ 2): keep loads {0,1} when hb == 0, {2,3} when hb == 1
-              const int s0 = hb ? part[0][hd] : part[LPT - 2][hd];
-              const int s1 = hb ? part[1][hd] : part[LPT - 1][hd];
-              const int k0 = hb ? part[LPT - 2][hd] : part[0][hd];
-              const int k1 = hb ? part[LPT - 1][hd] : part[1][hd];
-              const int r0 = k0 + __shfl_xor_sync(0xffffffffu, s0, 2);
-              const int r1 = k1 + __shfl_xor_sync(0xffffffffu, s1, 2);
-              // step 2 (partner lane ^ 1): keep r0 when lb == 0, r1 when lb == 1
-              const int send = lb ? r0 : r1;
-              const int keep = lb ? r1 : r0;
-              mine[hd] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+            for (int v = 0; v < 4; ++v) {
+              float m = d[v];
+              if (m == 0.0f) m = 0.0f;
+              if (gmax_row) gmax_row[t0 + tl[v]] = m;
+              if (HIST) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
             }
           }
-          const int tl = it * 32 + hq * TOK_PER_LOAD + lane / LPT;    // token inside the tile
-          const float ks = ssc[tl];
-          const int64_t t = t0 + tl;
-          float best = -INFINITY;
-#pragma unroll
-          for (int hd = 0; hd < G; ++hd) {
-            const int a = mine[hd] >> 4;                               // exact: the sum is 16 * acc
-            const float d = __fmul_rn(__fmul_rn((float)a, ks), qs[hd]);
-            best = fmaxf(best, d);
-            if (p.acc_out || p.deq_out) {
-              const int64_t o = ((int64_t)b * p.Hq + (int64_t)g * G + hd) * p.T + t;
-              if (p.acc_out) p.acc_out[o] = a;
-              if (p.deq_out) p.deq_out[o] = d;
-            }
-          }
-          if (best == 0.0f) best = 0.0f;                               // -0 -> +0
-          if (gmax_row) gmax_row[t] = best;
-          if (HIST) atomicAdd(&s_hist[float_to_key(best) >> (32 - SC_HIST_BITS)], 1u);
         }
 
         __syncwarp();
@@ -294,14 +363,14 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_stream_kernel(ScorePa
     // Ragged tail of the row (fewer than TW tokens), owned by the segment that holds the tail unit.
     if (ub > p.full_tiles) {
       const int64_t tail0 = (int64_t)p.full_tiles * TW;
-      for (int64_t t = tail0 + tid; t < p.T; t += SC_THREADS)
-        score_token_plain<G>(p, G, row, b, g, t, s_qcode, s_qscale, HIST ? s_hist : nullptr);
+      for (int64_t t = tail0 + tid; t < p.T; t += THREADS)
+        score_token_plain<G>(p, G, row, b, kvh, t, s_qcode, s_qscale, HIST ? s_hist : nullptr);
     }
 
     if (HIST) {
       __syncthreads();
       uint32_t* gh = p.hist_out + (int64_t)row * SC_HIST_BINS;
-      for (int i = tid; i < SC_HIST_BINS; i += SC_THREADS) {
+      for (int i = tid; i < SC_HIST_BINS; i += THREADS) {
         const uint32_t c = s_hist[i];
         if (c) {
           atomicAdd(&gh[i], c);
@@ -340,20 +409,19 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_generic_kernel(ScoreP
 
 template <int C, int G, int NS, bool HIST>
 static size_t score_stream_smem_bytes() {
-  constexpr int TW = SC_TILE_PACKED_BYTES / (C / 2);
-  constexpr int STAGE_BYTES = SC_TILE_PACKED_BYTES + TW * 4;
-  size_t s = (size_t)SC_WARPS * NS * STAGE_BYTES + sizeof(uint64_t) * SC_WARPS * NS + sizeof(float) * G * C +
-             sizeof(float) * SC_MAX_G + (size_t)G * C;
+  using Cfg = ScoreCfg<C, G>;
+  size_t s = (size_t)Cfg::WARPS * NS * Cfg::STAGE_BYTES + sizeof(uint64_t) * Cfg::WARPS * NS +
+             sizeof(float) * G * C + sizeof(float) * SC_MAX_G + (size_t)G * C;
   if (HIST) s += sizeof(uint32_t) * SC_HIST_BINS;
   return s;
 }
 
 template <int C, int G, int NS, bool HIST>
 static int score_stream_launch(const ScoreParams& p0, int device, cudaStream_t st) {
+  using Cfg = ScoreCfg<C, G>;
   ScoreParams p = p0;
-  constexpr int TW = SC_TILE_PACKED_BYTES / (C / 2);
-  p.full_tiles = p.T / TW;
-  p.units_per_row = p.full_tiles + ((p.T % TW) ? 1 : 0);
+  p.full_tiles = p.T / Cfg::TW;
+  p.units_per_row = p.full_tiles + ((p.T % Cfg::TW) ? 1 : 0);
   p.total_units = (int64_t)p.B * p.Hkv * p.units_per_row;
   const size_t smem = score_stream_smem_bytes<C, G, NS, HIST>();
   auto kern = score_decode_stream_kernel<C, G, NS, HIST>;
@@ -364,24 +432,31 @@ static int score_stream_launch(const ScoreParams& p0, int device, cudaStream_t s
   }
   int per_sm = (int)((227 * 1024) / (smem + 1024));
   if (per_sm < 1) per_sm = 1;
-  if (per_sm > 4) per_sm = 4;
+  if (per_sm > 2) per_sm = 2;
   int64_t grid = (int64_t)sm_count(device) * per_sm;
-  if (grid > p.total_units) grid = p.total_units;
+  const int64_t max_ctas = (p.total_units + 1) / 2;        // at least two units per CTA
+  if (grid > max_ctas) grid = max_ctas;
   if (grid < 1) grid = 1;
-  kern<<<(unsigned)grid, SC_THREADS, smem, st>>>(p);
+  kern<<<(unsigned)grid, Cfg::THREADS, smem, st>>>(p);
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
 }
 
+// Stages per warp ring so that two 8-warp CTAs (plus the histogram) fit one SM's shared memory.
+template <int C, int G>
+constexpr int score_stages() {
+  constexpr int budget = 96 * 1024 - 20 * 1024;
+  constexpr int per_stage = ScoreCfg<C, G>::WARPS * ScoreCfg<C, G>::STAGE_BYTES;
+  return budget / per_stage >= 4 ? 4 : (budget / per_stage >= 2 ? budget / per_stage : 2);
+}
+
 template <int C, bool HIST>
 static int score_stream_dispatch_g(const ScoreParams& p, int device, cudaStream_t st) {
-  // 3 stages when the histogram shares the CTA's shared memory, else 4.
-  constexpr int NS = HIST ? 3 : 4;
   switch (p.G) {
-    case 1: return score_stream_launch<C, 1, NS, HIST>(p, device, st);
-    case 2: return score_stream_launch<C, 2, NS, HIST>(p, device, st);
-    case 4: return score_stream_launch<C, 4, NS, HIST>(p, device, st);
-    case 8: return score_stream_launch<C, 8, NS, HIST>(p, device, st);
+    case 1: return score_stream_launch<C, 1, score_stages<C, 1>(), HIST>(p, device, st);
+    case 2: return score_stream_launch<C, 2, score_stages<C, 2>(), HIST>(p, device, st);
+    case 4: return score_stream_launch<C, 4, score_stages<C, 4>(), HIST>(p, device, st);
+    case 8: return score_stream_launch<C, 8, score_stages<C, 8>(), HIST>(p, device, st);
     default: return -1;
   }
 }

@@ -51,64 +51,6 @@ __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row
   return p.payload ? (uint32_t)p.payload[(int64_t)row * p.row_stride + t] : (uint32_t)(t + p.idx_offset);
 }
 
-// Whole-CTA search of a histogram from its TOP bin downwards: finds the bin d whose cumulative
-// count (bins > d, then bin d) first reaches `need` (1 <= need <= total). Results, identical in
-// every thread: bin d, count of elements in bins above d, count in bin d.
-// `hist` may live in global or shared memory. s_tmp needs NT + 40 words. Ends with a barrier.
-template <int NT>
-__device__ __forceinline__ void find_threshold(const uint32_t* hist, int nbins, uint32_t need, uint32_t* s_tmp,
-                                               uint32_t& bin_out, uint32_t& above_out, uint32_t& in_out) {
-  const int tid = threadIdx.x;
-  const int per = (nbins + NT - 1) / NT;              // bins per thread, taken from the top
-  // thread i owns reversed bins [i*per, (i+1)*per): reversed bin r <-> bin nbins-1-r
-  uint32_t sum = 0;
-  for (int j = 0; j < per; ++j) {
-    const int r = tid * per + j;
-    if (r < nbins) sum += hist[nbins - 1 - r];
-  }
-  s_tmp[tid] = sum;
-  __syncthreads();
-  uint32_t* s_res = s_tmp + NT + 32;
-  if (tid < 32) {
-    constexpr int CH = NT / 32;                       // chunk sums per lane
-    uint32_t lane_sum = 0;
-    for (int j = 0; j < CH; ++j) lane_sum += s_tmp[tid * CH + j];
-    uint32_t incl = lane_sum;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
-      if (tid >= off) incl += v;
-    }
-    const uint32_t excl = incl - lane_sum;
-    if (excl < need && need <= incl) {
-      // the crossing lies inside this lane's chunks
-      uint32_t cum = excl;
-      int chunk = tid * CH;
-      for (int j = 0; j < CH; ++j) {
-        const uint32_t c = s_tmp[tid * CH + j];
-        if (cum + c >= need) { chunk = tid * CH + j; break; }
-        cum += c;
-      }
-      uint32_t bin = 0, inb = 0;
-      for (int j = 0; j < per; ++j) {
-        const int r = chunk * per + j;
-        if (r >= nbins) break;
-        const uint32_t c = hist[nbins - 1 - r];
-        if (cum + c >= need) { bin = (uint32_t)(nbins - 1 - r); inb = c; break; }
-        cum += c;
-      }
-      s_res[0] = bin;
-      s_res[1] = cum;
-      s_res[2] = inb;
-    }
-  }
-  __syncthreads();
-  bin_out = s_res[0];
-  above_out = s_res[1];
-  in_out = s_res[2];
-  __syncthreads();
-}
-
 // Exclusive prefix sum of one value per thread over the CTA; also returns the total.
 // s_warp needs NT/32 + 1 words. Ends with a barrier.
 template <int NT>
@@ -140,6 +82,54 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s
   return res;
 }
 
+// Whole-CTA search of a histogram from its TOP bin downwards: finds the bin d whose cumulative
+// count (bins > d, then bin d) first reaches `need` (1 <= need <= total). Results, identical in
+// every thread: bin d, count of elements in bins above d, count in bin d.
+// `hist` may live in global or shared memory. s_tmp needs 80 words. Ends with a barrier.
+template <int NT>
+__device__ __forceinline__ void find_threshold(const uint32_t* hist, int nbins, uint32_t need, uint32_t* s_tmp,
+                                               uint32_t& bin_out, uint32_t& above_out, uint32_t& in_out) {
+  constexpr int MAXPER = SEL_HIST_BINS / 256;         // largest bins-per-thread ever asked for (NT >= 256)
+  const int tid = threadIdx.x;
+  const int per = (nbins + NT - 1) / NT;              // bins per thread, taken from the top
+  // thread i owns reversed bins [i*per, (i+1)*per): reversed bin r <-> bin nbins-1-r
+  uint32_t local[MAXPER];
+  uint32_t sum = 0;
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) {
+    const int r = tid * per + j;
+    local[j] = (j < per && r < nbins) ? hist[nbins - 1 - r] : 0u;
+    sum += local[j];
+  }
+  uint32_t total;
+  const uint32_t excl = block_exclusive_scan<NT>(sum, s_tmp, total);
+  uint32_t* s_res = s_tmp + 64;
+  if (excl < need && need <= excl + sum) {
+    uint32_t cum = excl, bin = 0, inb = 0;
+    bool found = false;
+#pragma unroll
+    for (int j = 0; j < MAXPER; ++j) {
+      if (!found) {
+        if (cum + local[j] >= need) {
+          bin = (uint32_t)(nbins - 1 - (tid * per + j));
+          inb = local[j];
+          found = true;
+        } else {
+          cum += local[j];
+        }
+      }
+    }
+    s_res[0] = bin;
+    s_res[1] = cum;
+    s_res[2] = inb;
+  }
+  __syncthreads();
+  bin_out = s_res[0];
+  above_out = s_res[1];
+  in_out = s_res[2];
+  __syncthreads();
+}
+
 // Histogram of the top 12 key bits of every row (only when the scorer did not produce one).
 __global__ void __launch_bounds__(SEL_SCAN_THREADS) select_hist_kernel(SelectParams p, uint32_t* hist_out) {
   __shared__ uint32_t s_hist[SEL_HIST_BINS];
@@ -162,7 +152,7 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS) select_hist_kernel(SelectPar
 
 // One CTA per row: the bin that holds the k-th element, the count above it and inside it.
 __global__ void __launch_bounds__(SEL_SCAN_THREADS) select_threshold_kernel(SelectParams p) {
-  __shared__ uint32_t s_tmp[SEL_SCAN_THREADS + 40];
+  __shared__ uint32_t s_tmp[80];
   const int row = blockIdx.x;
   uint32_t bin, above, inb;
   find_threshold<SEL_SCAN_THREADS>(p.hist + (int64_t)row * SEL_HIST_BINS, SEL_HIST_BINS, (uint32_t)p.kk, s_tmp, bin,
@@ -178,13 +168,10 @@ constexpr int SEL_TOK_PER_THREAD = 16;
 constexpr int SEL_TOK_PER_CTA = SEL_TOK_PER_THREAD * SEL_SCAN_THREADS;   // 4096
 
 template <bool VEC>
-__global__ void __launch_bounds__(SEL_SCAN_THREADS) select_collect_kernel(SelectParams p) {
+__global__ void __launch_bounds__(SEL_SCAN_THREADS, 8) select_collect_kernel(SelectParams p) {
   __shared__ uint32_t s_warp[SEL_SCAN_THREADS / 32 + 2];
   __shared__ uint32_t s_base;
   const int row = blockIdx.y;
-  const uint4 thr = p.thresholds[row];
-  if (thr.y + thr.z > (uint32_t)p.cap) return;
-  const uint32_t bin = thr.x;
   const float* src = p.scores + (int64_t)row * p.row_stride;
   const int64_t t0 = (int64_t)blockIdx.x * SEL_TOK_PER_CTA;
   const int tid = threadIdx.x;
@@ -213,6 +200,10 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS) select_collect_kernel(Select
         v[4 * j + i] = t < p.T ? src[t] : 0.0f;
       }
   }
+  // the row's threshold is read after the element loads were issued, so both latencies overlap
+  const uint4 thr = __ldcg(p.thresholds + row);
+  if (thr.y + thr.z > (uint32_t)p.cap) return;
+  const uint32_t bin = thr.x;
   uint32_t takemask = 0;
 #pragma unroll
   for (int e = 0; e < SEL_TOK_PER_THREAD; ++e) {
@@ -258,7 +249,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   extern __shared__ __align__(16) uint8_t sel_smem[];
   uint64_t* s_cand = reinterpret_cast<uint64_t*>(sel_smem);                     // [cap]
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(sel_smem + (size_t)p.cap * 8);  // [2048]
-  uint32_t* s_tmp = s_hist + 2048;                                              // [NT + 40]
+  uint32_t* s_tmp = s_hist + 2048;                                              // [NT + 40] (80 used)
   uint32_t* s_count = s_tmp + SEL_FINAL_THREADS + 40;                           // [4]
   uint32_t* s_bitmap = s_count + 4;                                             // [ceil(T/32)] when use_bitmap
 

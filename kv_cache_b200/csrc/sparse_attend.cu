@@ -21,7 +21,7 @@ constexpr int AT_STAGE_BYTES = 2 * AT_TILE_BYTES;        // K then V
 constexpr int AT_MAX_TILES_PER_CTA = 32;
 constexpr int AT_MAX_ROWS_PER_CTA = AT_MAX_TILES_PER_CTA * AT_TILE;
 constexpr int AT_S_PITCH = 40;              // floats per score row
-constexpr int AT_TARGET_CTAS = 1184;        // ~ 148 SMs x 4 resident x 2 waves
+constexpr int AT_TARGET_CTAS = 444;         // one wave: 148 SMs x 3 resident CTAs (shared memory bound)
 
 struct AttendParams {
   const __nv_bfloat16* query; int64_t q_sb, q_sh;
@@ -364,10 +364,12 @@ static AttendPlan attend_plan(int B, int Hq, int Hi, int S) {
   const int R = B * Hi;
   const int GG = Hq / Hi;
   const int ntiles = ceil_div(S, AT_TILE);
-  int want_splits = ceil_div(AT_TARGET_CTAS, R);
+  // As many chunks per list as fit in ONE wave of resident CTAs: long chunks keep the 3-stage
+  // gather pipeline full and make the final merge short.
+  int want_splits = AT_TARGET_CTAS / R;
   if (want_splits < 1) want_splits = 1;
   int tpc = ceil_div(ntiles, want_splits);
-  if (tpc < 2) tpc = ntiles < 2 ? 1 : 2;
+  if (tpc < 1) tpc = 1;
   if (tpc > AT_MAX_TILES_PER_CTA) tpc = AT_MAX_TILES_PER_CTA;
   a.tiles_per_cta = tpc;
   a.nsplit = ceil_div(ntiles, tpc);
