@@ -9,7 +9,7 @@ namespace kvb {
 // select candidate counters, histogram) are adjacent so ONE memset per step clears them.
 struct StepLayout {
   int R, kk, S;
-  size_t off_attcnt, off_selws, off_attpart, off_gmax, off_sel, off_fidx, off_fvalid;
+  size_t off_attcnt, off_selws, off_attpart, off_gmax, off_sel;
   size_t zero_bytes, selws_bytes, bytes;
 };
 
@@ -28,8 +28,6 @@ static StepLayout step_layout(int B, int Hq, int Hkv, int T, int k, int sink, in
   L.off_attpart = off; off += ap.partial_bytes;
   L.off_gmax = off;    off += round_up(sizeof(float) * (size_t)L.R * (size_t)T, 256);
   L.off_sel = off;     off += round_up(sizeof(int32_t) * (size_t)L.R * (size_t)(L.kk > 0 ? L.kk : 1), 256);
-  L.off_fidx = off;    off += round_up(sizeof(int32_t) * (size_t)L.R * (size_t)(L.S > 0 ? L.S : 1), 256);
-  L.off_fvalid = off;  off += round_up((size_t)L.R * (size_t)(L.S > 0 ? L.S : 1), 256);
   L.bytes = off;
   return L;
 }
@@ -64,8 +62,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   float* attpart = reinterpret_cast<float*>(ws + L.off_attpart);
   float* gmax = reinterpret_cast<float*>(ws + L.off_gmax);
   int32_t* sel = p->sel_idx_out ? p->sel_idx_out : reinterpret_cast<int32_t*>(ws + L.off_sel);
-  int32_t* fidx = reinterpret_cast<int32_t*>(ws + L.off_fidx);
-  uint8_t* fvalid = ws + L.off_fvalid;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
 
@@ -82,19 +78,24 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   rc = select_run(gmax, T, nullptr, L.R, T, p->top_k, 0, /*order=*/1, sel, nullptr, nullptr, nullptr,
                   /*hist_in_workspace=*/true, /*zeroed=*/true, selws, L.selws_bytes, device, st);
   if (rc != KVB_OK) return rc;
-  rc = kvb_build_final_indices(sel, nullptr, L.R, L.kk, T, T + 1, p->protect_sink, p->protect_recent, p->keep_self,
-                               p->append_protected, fidx, fvalid, device, stream);
-  if (rc != KVB_OK) return rc;
+  // The attention kernel reads the list  selected || sink || recent || self  implicitly (no list is
+  // materialised) and its chunk-0 warps append the decoded token's K row to the int4 cache.
+  const FinalLayout f = final_layout(L.kk, T, p->protect_sink, p->protect_recent, p->keep_self);
+  AttendList list{};
+  list.implicit = 1;
+  list.selected = sel; list.kk = L.kk;
+  list.sink_end = f.sink_end; list.n_recent = f.n_recent; list.recent_from = f.recent_from;
+  list.recent_start = f.recent_start; list.recent_on = f.recent_on; list.history = T;
+  list.append_protected = p->append_protected;
+  AttendAppend ap{};
+  ap.enabled = p->append_self ? 1 : 0;
+  ap.channel_idx = p->channel_idx; ap.C = p->C;
+  ap.packed = p->packed; ap.packed_sb = p->packed_sb; ap.packed_sh = p->packed_sh;
+  ap.scale = p->scale; ap.scale_sb = p->scale_sb; ap.scale_sh = p->scale_sh;
+  ap.t_src = T; ap.t_dst = T;
   rc = attend_run(p->query, p->q_sb, p->q_sh, p->key, p->k_sb, p->k_sh, p->k_st, p->value, p->v_sb, p->v_sh, p->v_st,
-                  fidx, 0, fvalid, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D, L.S, p->scaling,
+                  list, &ap, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D, L.S, p->scaling,
                   p->out, nullptr, attcnt, attpart, /*counters_zeroed=*/true, device, st);
   if (rc != KVB_OK) return rc;
-  if (p->append_self) {
-    // Row T of key (the token being decoded) joins the int4 cache for the following steps.
-    const __nv_bfloat16* self_row = reinterpret_cast<const __nv_bfloat16*>(p->key) + (int64_t)T * p->k_st;
-    rc = kvb_quantize_append(self_row, p->k_sb, p->k_sh, p->channel_idx, p->packed, p->packed_sb, p->packed_sh,
-                             p->scale, p->scale_sb, p->scale_sh, p->B, p->Hkv, p->D, p->C, T, device, stream);
-    if (rc != KVB_OK) return rc;
-  }
   return KVB_OK;
 }

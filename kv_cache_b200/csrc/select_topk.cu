@@ -23,6 +23,8 @@ constexpr int SEL_HIST_BINS = 1 << SEL_HIST_BITS;
 constexpr int SEL_SCAN_THREADS = 256;
 constexpr int SEL_FINAL_THREADS = 1024;
 constexpr int SEL_MAX_K = 16384;
+constexpr int SEL_COUNT_STRIDE = 32;        // words between per-row candidate counters: one 128-byte line each,
+                                            // so the atomics of different rows do not queue on one L2 line
 
 struct SelectParams {
   const float* scores;
@@ -35,7 +37,7 @@ struct SelectParams {
   float* out_scores;
   const uint32_t* hist;       // [R, 4096]
   uint64_t* cand;             // [R, cap]
-  uint32_t* cand_count;       // [R]
+  uint32_t* cand_count;       // [R * SEL_COUNT_STRIDE]
   int cap;
   int tokens_per_cta;         // scan kernels: tokens per CTA along a row
   uint4* thresholds;          // [R] (bin, above, in-bin, unused)
@@ -162,26 +164,28 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS) select_threshold_kernel(Sele
 
 // Appends every element whose top-12-bit bin is >= the threshold bin to the row's candidate list
 // (skipped for rows whose candidate set would not fit; the final kernel handles those).
-// Each thread holds SEL_TOK_PER_THREAD elements in registers; the CTA reserves its output range
-// with ONE atomic and writes its candidates in token order.
+// Warps work alone: a warp holds 512 elements in registers (16 per lane, loads issued before the
+// threshold is read), ranks its candidates with a shuffle scan and reserves its output range with
+// ONE atomic; there is no block barrier.
 constexpr int SEL_TOK_PER_THREAD = 16;
+constexpr int SEL_TOK_PER_WARP = SEL_TOK_PER_THREAD * 32;                 // 512
 constexpr int SEL_TOK_PER_CTA = SEL_TOK_PER_THREAD * SEL_SCAN_THREADS;   // 4096
 
 template <bool VEC>
-__global__ void __launch_bounds__(SEL_SCAN_THREADS, 8) select_collect_kernel(SelectParams p) {
-  __shared__ uint32_t s_warp[SEL_SCAN_THREADS / 32 + 2];
-  __shared__ uint32_t s_base;
+__global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(SelectParams p) {
   const int row = blockIdx.y;
   const float* src = p.scores + (int64_t)row * p.row_stride;
-  const int64_t t0 = (int64_t)blockIdx.x * SEL_TOK_PER_CTA;
-  const int tid = threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int64_t t0 = (int64_t)blockIdx.x * SEL_TOK_PER_CTA + (threadIdx.x >> 5) * SEL_TOK_PER_WARP;
+  if (t0 >= p.T) return;
 
   float v[SEL_TOK_PER_THREAD];
   if (VEC) {
 #pragma unroll
     for (int j = 0; j < SEL_TOK_PER_THREAD / 4; ++j) {
-      const int64_t t = t0 + j * (SEL_SCAN_THREADS * 4) + tid * 4;
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int64_t t = t0 + j * 128 + lane * 4;
+      const float qnan = __int_as_float(0x7fc00000);       // padding compares false against anything
+      float4 x = make_float4(qnan, qnan, qnan, qnan);
       if (t + 3 < p.T) {
         x = __ldcg(reinterpret_cast<const float4*>(src + t));
       } else {
@@ -196,31 +200,40 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS, 8) select_collect_kernel(Sel
     for (int j = 0; j < SEL_TOK_PER_THREAD / 4; ++j)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int64_t t = t0 + j * (SEL_SCAN_THREADS * 4) + tid * 4 + i;
-        v[4 * j + i] = t < p.T ? src[t] : 0.0f;
+        const int64_t t = t0 + j * 128 + lane * 4 + i;
+        v[4 * j + i] = t < p.T ? src[t] : __int_as_float(0x7fc00000);
       }
   }
   // the row's threshold is read after the element loads were issued, so both latencies overlap
   const uint4 thr = __ldcg(p.thresholds + row);
   if (thr.y + thr.z > (uint32_t)p.cap) return;
-  const uint32_t bin = thr.x;
+  // key(v) >= bin << 20  <=>  v >= the float whose key is bin << 20 (keys are order preserving;
+  // bins that only NaN patterns can reach are clamped to -inf / "nothing").
+  const uint32_t key_lo = thr.x << (32 - SEL_HIST_BITS);
+  float f_lo = key_to_float(key_lo);
+  if (key_lo <= 0x007FFFFFu) f_lo = -INFINITY;
   uint32_t takemask = 0;
 #pragma unroll
-  for (int e = 0; e < SEL_TOK_PER_THREAD; ++e) {
-    const int64_t t = t0 + (e >> 2) * (SEL_SCAN_THREADS * 4) + tid * 4 + (e & 3);
-    if (t < p.T && (float_to_key(v[e]) >> (32 - SEL_HIST_BITS)) >= bin) takemask |= 1u << e;
+  for (int e = 0; e < SEL_TOK_PER_THREAD; ++e)
+    if (v[e] >= f_lo) takemask |= 1u << e;
+  const uint32_t cnt = (uint32_t)__popc(takemask);
+  uint32_t incl = cnt;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t n = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += n;
   }
-  uint32_t total;
-  const uint32_t off = block_exclusive_scan<SEL_SCAN_THREADS>((uint32_t)__popc(takemask), s_warp, total);
+  const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
   if (total == 0) return;
-  if (tid == 0) s_base = atomicAdd(p.cand_count + row, total);
-  __syncthreads();
+  uint32_t base = 0;
+  if (lane == 0) base = atomicAdd(p.cand_count + (int64_t)row * SEL_COUNT_STRIDE, total);
+  base = __shfl_sync(0xffffffffu, base, 0);
   uint64_t* cand = p.cand + (int64_t)row * p.cap;
-  uint32_t pos = s_base + off;
+  uint32_t pos = base + incl - cnt;
 #pragma unroll
   for (int e = 0; e < SEL_TOK_PER_THREAD; ++e) {
     if (takemask & (1u << e)) {
-      const int64_t t = t0 + (e >> 2) * (SEL_SCAN_THREADS * 4) + tid * 4 + (e & 3);
+      const int64_t t = t0 + (e >> 2) * 128 + lane * 4 + (e & 3);
       if (pos < (uint32_t)p.cap) cand[pos] = make_composite(v[e], element_index(p, row, t));
       ++pos;
     }
@@ -265,7 +278,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   int n;                                                // candidates in s_cand: all with composite >= prefix
   if (thr.y + thr.z <= (uint32_t)p.cap) {
     n = (int)(thr.y + thr.z);
-    const uint32_t have = p.cand_count[row];
+    const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
     if ((uint32_t)n > have) n = (int)have;              // cannot happen; keeps reads in bounds
     const uint64_t* cand = p.cand + (int64_t)row * p.cap;
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
@@ -418,7 +431,7 @@ static SelectWorkspace select_carve(void* base, int R, int k) {
   uint8_t* ptr = reinterpret_cast<uint8_t*>(base);
   size_t off = 0;
   w.count = reinterpret_cast<uint32_t*>(ptr + off);
-  off += round_up(sizeof(uint32_t) * (size_t)R, 256);
+  off += round_up(sizeof(uint32_t) * (size_t)R * SEL_COUNT_STRIDE, 256);
   w.hist = reinterpret_cast<uint32_t*>(ptr + off);
   off += round_up(sizeof(uint32_t) * (size_t)R * SEL_HIST_BINS, 256);
   w.zero_bytes = off;
@@ -464,10 +477,10 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
 
   if (hist_in_workspace) {
     p.hist = w.hist;
-    if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(w.count, 0, sizeof(uint32_t) * (size_t)R, st));
+    if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(w.count, 0, sizeof(uint32_t) * (size_t)R * SEL_COUNT_STRIDE, st));
   } else if (hist_in) {
     p.hist = hist_in;
-    if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(w.count, 0, sizeof(uint32_t) * (size_t)R, st));
+    if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(w.count, 0, sizeof(uint32_t) * (size_t)R * SEL_COUNT_STRIDE, st));
   } else {
     if (!zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(workspace, 0, w.zero_bytes, st));
     p.hist = w.hist;

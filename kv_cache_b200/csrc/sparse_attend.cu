@@ -1,34 +1,56 @@
 // Stage 4: exact attention of one decode query per sequence over a list of gathered K/V rows.
 //
-// One CTA handles a chunk of the index list of one (batch, index-head) pair and ALL query heads
-// that share that list (the G heads of a KV head), so each 256-byte K row and V row is fetched
-// once per KV head. Rows are gathered with 16-byte cp.async copies into a 3-stage ring of
-// 32-row tiles (row pitch 272 bytes, bank-conflict free for the fragment loads below). QK^T and
-// PV run on mma.sync m16n8k16 bf16 with fp32 accumulators (heads padded to the 16-row A tile),
-// softmax is online in fp32, and the chunks of a list are combined by the last CTA to finish
-// (log-sum-exp merge), so no second launch and no spinning is needed.
+// Work item = one chunk of the index list of one (batch, index-head) pair, handled by ONE WARP for
+// all query heads that share the list (the G heads of a KV head), so each 256-byte K row and V
+// row is fetched once per KV head. The warp gathers rows with 16-byte cp.async copies into its own
+// 3-stage ring of 16-row tiles (row pitch 272 bytes: conflict-free fragment loads), computes
+// Q K^T and P V with mma.sync m16n8k16 bf16 / fp32 accumulate (heads padded to the 16-row A tile;
+// the score fragment is re-used in registers as the P fragment), keeps an online softmax in fp32,
+// and never waits for another warp. The chunks of a list are combined by a small second launch
+// (log-sum-exp merge, one CTA per (list, head)): folding it into the last warp to finish put a
+// long chain of dependent L2 round trips on the tail of the kernel.
 #include "common.cuh"
 
 namespace kvb {
 
-constexpr int AT_THREADS = 128;
-constexpr int AT_TILE = 32;                 // rows per tile
+constexpr int AT_WARPS = 4;
+constexpr int AT_THREADS = AT_WARPS * 32;
+constexpr int AT_TILE = 16;                 // rows per tile
 constexpr int AT_D = 128;
 constexpr int AT_PITCH = 272;               // bytes per staged row (256 + 16)
 constexpr int AT_STAGES = 3;
-constexpr int AT_TILE_BYTES = AT_TILE * AT_PITCH;        // 8704
+constexpr int AT_TILE_BYTES = AT_TILE * AT_PITCH;        // 4352
 constexpr int AT_STAGE_BYTES = 2 * AT_TILE_BYTES;        // K then V
-constexpr int AT_MAX_TILES_PER_CTA = 32;
-constexpr int AT_MAX_ROWS_PER_CTA = AT_MAX_TILES_PER_CTA * AT_TILE;
-constexpr int AT_S_PITCH = 40;              // floats per score row
-constexpr int AT_TARGET_CTAS = 444;         // one wave: 148 SMs x 3 resident CTAs (shared memory bound)
+constexpr int AT_WARP_SMEM = AT_STAGES * (AT_STAGE_BYTES + AT_TILE * 8);   // stages + per-row (token, mask)
+constexpr int AT_TARGET_WARPS = 1184;       // one wave: 148 SMs x 2 CTAs x 4 warps
+
+// How the logical list of S entries is produced.
+//   explicit: indices[row, s] (+ valid[row, s])
+//   implicit: selected[row, 0..kk) || [0, sink_end) || [recent_from, recent_from + n_recent) || self
+//             with the protected ranges removed from the selected part (the rule of
+//             _qabs_final_indices_from_selected, or of ..._append_protected when append_protected)
+struct AttendList {
+  const void* indices; int idx_is_i64; const uint8_t* valid;      // explicit
+  int implicit;
+  const int32_t* selected; int kk;
+  int sink_end, n_recent, recent_from, recent_start, recent_on, history, append_protected;
+};
+
+// Optional extra duty of the warp that owns chunk 0 of a list: quantize the newest K row into the
+// int4 side cache (the append of the fused decode step).
+struct AttendAppend {
+  int enabled;
+  const int32_t* channel_idx; int C;
+  uint8_t* packed; int64_t packed_sb, packed_sh;
+  float* scale; int64_t scale_sb, scale_sh;
+  int64_t t_src, t_dst;
+};
 
 struct AttendParams {
   const __nv_bfloat16* query; int64_t q_sb, q_sh;
   const __nv_bfloat16* key;   int64_t k_sb, k_sh, k_st;
   const __nv_bfloat16* value; int64_t v_sb, v_sh, v_st;
-  const void* indices; int idx_is_i64;
-  const uint8_t* valid;
+  AttendList list;
   const float* mask; int64_t mask_sb;
   int B, Hq, Hkv, Hi, Tk, S;
   int G;                      // Hq / Hkv
@@ -37,7 +59,8 @@ struct AttendParams {
   float* out_partial;
   float* ws_partial;          // [B*Hi, nsplit, GG, D+2]
   uint32_t* ws_counter;       // [B*Hi]
-  int nsplit, tiles_per_cta;
+  int nsplit, tiles_per_split;
+  AttendAppend append;
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -56,66 +79,121 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
                : "memory");
 }
 
-// GG = query heads that share one index list (1, 2, 4 or 8).
-template <int GG>
-__global__ void __launch_bounds__(AT_THREADS) sparse_attend_kernel(AttendParams p) {
-  extern __shared__ __align__(128) uint8_t at_smem[];
-  uint8_t* s_stage = at_smem;                                                  // [stages][K|V][32][272]
-  float* s_S = reinterpret_cast<float*>(s_stage + AT_STAGES * AT_STAGE_BYTES);  // [8][40]
-  int* s_idx = reinterpret_cast<int*>(s_S + 8 * AT_S_PITCH);                    // [rows of this CTA]
-  float* s_maskv = reinterpret_cast<float*>(s_idx + AT_MAX_ROWS_PER_CTA);       // [rows of this CTA]
-  __shared__ int s_is_last;
+// Entry s of the logical list of `row`: token id, or -1 when it contributes nothing.
+__device__ __forceinline__ int attend_fetch(const AttendParams& p, int row, int s) {
+  const AttendList& L = p.list;
+  int64_t raw;
+  bool ok = true;
+  if (!L.implicit) {
+    const int64_t o = (int64_t)row * p.S + s;
+    raw = L.idx_is_i64 ? reinterpret_cast<const int64_t*>(L.indices)[o]
+                       : (int64_t) reinterpret_cast<const int32_t*>(L.indices)[o];
+    ok = (L.valid == nullptr) || (L.valid[o] != 0);
+  } else if (s < L.kk) {
+    raw = L.selected[(int64_t)row * L.kk + s];
+    if (!L.append_protected) {
+      if (L.recent_on && raw >= L.recent_start && raw < L.history) ok = false;
+      if (L.sink_end > 0 && raw < L.sink_end) ok = false;
+    }
+  } else if (s < L.kk + L.sink_end) {
+    raw = s - L.kk;
+  } else if (s < L.kk + L.sink_end + L.n_recent) {
+    raw = L.recent_from + (s - L.kk - L.sink_end);
+  } else {
+    raw = (int64_t)p.Tk - 1;                                   // the token being decoded
+  }
+  return (ok && raw >= 0 && raw < (int64_t)p.Tk) ? (int)raw : -1;
+}
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, t4 = lane & 3;
-  const int split = blockIdx.x;
-  const int row = blockIdx.y;                         // (b, index head)
-  const int b = row / p.Hi, hi = row - b * p.Hi;
-  const int head0 = hi * GG;                          // first query head served
-  const int kvh = head0 / p.G;
-
-  const int s_begin = split * p.tiles_per_cta * AT_TILE;
-  int s_end = s_begin + p.tiles_per_cta * AT_TILE;
-  if (s_end > p.S) s_end = p.S;
-  const int nrows = s_end - s_begin;                  // >= 1 by construction of nsplit
-  const int ntile = (nrows + AT_TILE - 1) / AT_TILE;
-
-  // Index list of this chunk: -1 marks an entry that contributes nothing.
-  {
-    const int64_t base = (int64_t)row * p.S + s_begin;
-    for (int i = tid; i < ntile * AT_TILE; i += AT_THREADS) {
-      int tok = -1;
-      float mv = 0.0f;
-      if (i < nrows) {
-        const int64_t raw = p.idx_is_i64 ? reinterpret_cast<const int64_t*>(p.indices)[base + i]
-                                         : (int64_t) reinterpret_cast<const int32_t*>(p.indices)[base + i];
-        const bool ok = (p.valid == nullptr || p.valid[base + i] != 0) && raw >= 0 && raw < (int64_t)p.Tk;
-        if (ok) {
-          tok = (int)raw;
-          if (p.mask) mv = p.mask[(int64_t)b * p.mask_sb + raw];
-        }
-      }
-      s_idx[i] = tok;
-      s_maskv[i] = mv;
+// One warp quantizes one bf16 K row to int4 (same arithmetic as quantize_pack_kernel).
+__device__ __forceinline__ void quantize_row_warp(const __nv_bfloat16* krow, const int32_t* ch, int C, uint8_t* dst,
+                                                  float* scale_dst, int lane) {
+  const int nb = C >> 1;                       // <= 64 bytes: at most two per lane
+  float x[4];
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int byte = lane + 32 * j;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      x[2 * j + i] = (byte < nb) ? __bfloat162float(krow[ch[2 * byte + i]]) : 0.0f;
+      amax = fmaxf(amax, fabsf(x[2 * j + i]));
     }
   }
-  __syncthreads();
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const float sc = __fdiv_rn(fmaxf(amax, 5.9604644775390625e-08f /* 2^-24 */), 7.0f);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int byte = lane + 32 * j;
+    if (byte < nb) {
+      float lo = rintf(__fdiv_rn(x[2 * j], sc)), hi = rintf(__fdiv_rn(x[2 * j + 1], sc));
+      lo = fminf(fmaxf(lo, -7.0f), 7.0f);
+      hi = fminf(fmaxf(hi, -7.0f), 7.0f);
+      dst[byte] = (uint8_t)((((int)lo) & 0xF) | ((((int)hi) & 0xF) << 4));
+    }
+  }
+  if (lane == 0) *scale_dst = sc;
+}
+
+// GG = query heads that share one index list (1, 2, 4 or 8).
+template <int GG>
+__global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendParams p) {
+  extern __shared__ __align__(128) uint8_t at_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int task = blockIdx.x * AT_WARPS + warp;
+  if (task >= p.B * p.Hi * p.nsplit) return;             // warps are independent: no block barrier below
+  const int row = task / p.nsplit;                       // (b, index head)
+  const int split = task - row * p.nsplit;
+  const int b = row / p.Hi, hi = row - b * p.Hi;
+  const int head0 = hi * GG;                             // first query head served
+  const int kvh = head0 / p.G;
+
+  uint8_t* my = at_smem + warp * AT_WARP_SMEM;           // [stages][K|V][16][272] | tok[stages][16] | mask[stages][16]
+  int* s_tok = reinterpret_cast<int*>(my + AT_STAGES * AT_STAGE_BYTES);
+  float* s_msk = reinterpret_cast<float*>(s_tok + AT_STAGES * AT_TILE);
+
+  const int s_begin = split * p.tiles_per_split * AT_TILE;
+  int s_end = s_begin + p.tiles_per_split * AT_TILE;
+  if (s_end > p.S) s_end = p.S;
+  const int nrows = s_end - s_begin;                     // >= 1 by construction of nsplit
+  const int ntile = (nrows + AT_TILE - 1) / AT_TILE;
 
   const __nv_bfloat16* kbase = p.key + (int64_t)b * p.k_sb + (int64_t)kvh * p.k_sh;
   const __nv_bfloat16* vbase = p.value + (int64_t)b * p.v_sb + (int64_t)kvh * p.v_sh;
 
-  auto load_tile = [&](int tile) {
-    uint8_t* sk = s_stage + (tile % AT_STAGES) * AT_STAGE_BYTES;
+  if (p.append.enabled && split == 0) {
+    const AttendAppend& A = p.append;
+    quantize_row_warp(kbase + A.t_src * p.k_st, A.channel_idx + (int64_t)kvh * A.C, A.C,
+                      A.packed + (int64_t)b * A.packed_sb + (int64_t)kvh * A.packed_sh + A.t_dst * (A.C >> 1),
+                      A.scale + (int64_t)b * A.scale_sb + (int64_t)kvh * A.scale_sh + A.t_dst, lane);
+  }
+
+  // List entries are fetched one tile AHEAD of the gather that uses them, so the global-memory
+  // latency of the index (and mask) read overlaps the math of the tile in between.
+  auto fetch_tile = [&](int tile, int& tok, float& mv) {
+    const int s = s_begin + tile * AT_TILE + (lane & 15);      // lanes 16..31 mirror lanes 0..15
+    tok = (tile < ntile && s < s_end) ? attend_fetch(p, row, s) : -1;
+    mv = (tok >= 0 && p.mask) ? p.mask[(int64_t)b * p.mask_sb + tok] : 0.0f;
+  };
+  auto load_tile = [&](int tile, int tok, float mv) {
+    const int stage = tile % AT_STAGES;
+    uint8_t* sk = my + stage * AT_STAGE_BYTES;
     uint8_t* sv = sk + AT_TILE_BYTES;
-    const int c16 = tid & 15;
-    const int r0 = tid >> 4;
+    if (lane < AT_TILE) {
+      s_tok[stage * AT_TILE + lane] = tok;
+      s_msk[stage * AT_TILE + lane] = mv;
+    }
+    if (tok < 0) tok = 0;                                 // weight is forced to zero later; any live row will do
+    const int c16 = lane & 15;
+    const int r0 = lane >> 4;
 #pragma unroll
-    for (int j = 0; j < AT_TILE / 8; ++j) {
-      const int r = r0 + 8 * j;
-      int tok = s_idx[tile * AT_TILE + r];
-      if (tok < 0) tok = 0;                            // weight is forced to zero later; any live row will do
-      cp_async_16(sk + r * AT_PITCH + c16 * 16, kbase + (int64_t)tok * p.k_st + c16 * 8);
-      cp_async_16(sv + r * AT_PITCH + c16 * 16, vbase + (int64_t)tok * p.v_st + c16 * 8);
+    for (int j = 0; j < AT_TILE / 2; ++j) {
+      const int r = r0 + 2 * j;
+      const int tr = __shfl_sync(0xffffffffu, tok, r);
+      cp_async_16(sk + r * AT_PITCH + c16 * 16, kbase + (int64_t)tr * p.k_st + c16 * 8);
+      cp_async_16(sv + r * AT_PITCH + c16 * 16, vbase + (int64_t)tr * p.v_st + c16 * 8);
     }
   };
 
@@ -132,62 +210,68 @@ __global__ void __launch_bounds__(AT_THREADS) sparse_attend_kernel(AttendParams 
     }
   }
 
-  float o[4][4];
+  float o[16][4];
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt)
+  for (int nt = 0; nt < 16; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[nt][i] = 0.0f;
   float m_run = -INFINITY, l_run = 0.0f;
 
+  int tok_cur, tok_nxt;
+  float mv_cur, mv_nxt;
+  {
+    int tk[AT_STAGES];
+    float mk[AT_STAGES];
 #pragma unroll
-  for (int s = 0; s < AT_STAGES - 1; ++s) {
-    if (s < ntile) load_tile(s);
-    cp_async_commit();
+    for (int s = 0; s < AT_STAGES; ++s) fetch_tile(s, tk[s], mk[s]);      // all in flight together
+#pragma unroll
+    for (int s = 0; s < AT_STAGES - 1; ++s) {
+      if (s < ntile) load_tile(s, tk[s], mk[s]);
+      cp_async_commit();
+    }
+    tok_cur = tk[AT_STAGES - 1];
+    mv_cur = mk[AT_STAGES - 1];
   }
 
   for (int i = 0; i < ntile; ++i) {
-    if (i + AT_STAGES - 1 < ntile) load_tile(i + AT_STAGES - 1);
+    fetch_tile(i + AT_STAGES, tok_nxt, mv_nxt);           // used by the NEXT iteration's gather
+    if (i + AT_STAGES - 1 < ntile) load_tile(i + AT_STAGES - 1, tok_cur, mv_cur);
     cp_async_commit();
+    tok_cur = tok_nxt;
+    mv_cur = mv_nxt;
     cp_async_wait<AT_STAGES - 1>();
-    __syncthreads();
+    __syncwarp();
 
-    const uint8_t* sk = s_stage + (i % AT_STAGES) * AT_STAGE_BYTES;
+    const int stage = i % AT_STAGES;
+    const uint8_t* sk = my + stage * AT_STAGE_BYTES;
     const uint8_t* sv = sk + AT_TILE_BYTES;
 
-    // ---- S = Q K^T for this warp's 8 rows of the tile ----
-    {
-      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      const uint8_t* krow = sk + (8 * warp + g) * AT_PITCH;
+    // ---- S = Q K^T: two 8-row halves of the tile, independent accumulators ----
+    float c[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
+      const uint8_t* krow = sk + (8 * nt + g) * AT_PITCH;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + (16 * ks + 2 * t4) * 2);
         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + (16 * ks + 2 * t4 + 8) * 2);
-        mma_bf16_16816(c, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+        mma_bf16_16816(c[nt], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
       }
-      const int r = 8 * warp + 2 * t4;                 // tile-local rows of c[0], c[1]
-      const int gi = i * AT_TILE + r;
-      float s0 = c[0] * p.scaling + s_maskv[gi];
-      float s1 = c[1] * p.scaling + s_maskv[gi + 1];
-      if (s_idx[gi] < 0) s0 = -INFINITY;
-      if (s_idx[gi + 1] < 0) s1 = -INFINITY;
-      *reinterpret_cast<float2*>(&s_S[g * AT_S_PITCH + r]) = make_float2(s0, s1);
     }
-    __syncthreads();
-
-    // ---- online softmax (every warp keeps the same running statistics for head g) ----
-    float sc[8];
-    {
-      const float* srow = s_S + g * AT_S_PITCH;
-      const float2 v0 = *reinterpret_cast<const float2*>(srow + 2 * t4);
-      const float2 v1 = *reinterpret_cast<const float2*>(srow + 2 * t4 + 8);
-      const float2 v2 = *reinterpret_cast<const float2*>(srow + 2 * t4 + 16);
-      const float2 v3 = *reinterpret_cast<const float2*>(srow + 2 * t4 + 24);
-      sc[0] = v0.x; sc[1] = v0.y; sc[2] = v1.x; sc[3] = v1.y;
-      sc[4] = v2.x; sc[5] = v2.y; sc[6] = v3.x; sc[7] = v3.y;
-    }
-    float mx = sc[0];
+    // c[nt][0], c[nt][1]: head g, tile rows 8*nt + 2*t4, + 1
+    float sc[4];
 #pragma unroll
-    for (int j = 1; j < 8; ++j) mx = fmaxf(mx, sc[j]);
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int r = 8 * nt + 2 * t4 + e;
+        const float v = c[nt][e] * p.scaling + s_msk[stage * AT_TILE + r];
+        sc[2 * nt + e] = (s_tok[stage * AT_TILE + r] < 0) ? -INFINITY : v;
+      }
+
+    // ---- online softmax for head g (the four lanes of a quad hold the 16 rows) ----
+    float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m_run, mx);
@@ -195,7 +279,7 @@ __global__ void __launch_bounds__(AT_THREADS) sparse_attend_kernel(AttendParams 
     const float alpha = __expf(m_run - m_use);          // 0 when m_run == -inf
     float psum = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 4; ++j) {
       sc[j] = __expf(sc[j] - m_use);                    // 0 for -inf
       psum += sc[j];
     }
@@ -204,28 +288,25 @@ __global__ void __launch_bounds__(AT_THREADS) sparse_attend_kernel(AttendParams 
     l_run = l_run * alpha + psum;
     m_run = m_new;
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < 16; ++nt) {
       o[nt][0] *= alpha;
       o[nt][1] *= alpha;
     }
-    // P fragments (A operand): k-step 0 = rows 0..15 of the tile, k-step 1 = rows 16..31
-    const uint32_t pa[2][2] = {{pack_bf16x2(sc[0], sc[1]), pack_bf16x2(sc[2], sc[3])},
-                               {pack_bf16x2(sc[4], sc[5]), pack_bf16x2(sc[6], sc[7])}};
+    // The score fragment is already laid out as the A fragment of P V: rows 2*t4, 2*t4+1 and +8.
+    const uint32_t pa0 = pack_bf16x2(sc[0], sc[1]);
+    const uint32_t pa2 = pack_bf16x2(sc[2], sc[3]);
 
-    // ---- O += P V for this warp's 32 output dims ----
+    // ---- O += P V over all 128 output dims ----
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
-#pragma unroll
-      for (int jp = 0; jp < 2; ++jp) {
-        const int vrow = 16 * ks + ((lane >> 3) & 1) * 8 + (lane & 7);
-        const int vdim = 32 * warp + 16 * jp + (lane >> 4) * 8;
-        uint32_t r0, r1, r2, r3;
-        ldmatrix_x4_trans(r0, r1, r2, r3, smem_u32(sv + vrow * AT_PITCH + vdim * 2));
-        mma_bf16_16816(o[2 * jp], pa[ks][0], 0u, pa[ks][1], 0u, r0, r1);
-        mma_bf16_16816(o[2 * jp + 1], pa[ks][0], 0u, pa[ks][1], 0u, r2, r3);
-      }
+    for (int jp = 0; jp < 8; ++jp) {
+      const int vrow = ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int vdim = 16 * jp + (lane >> 4) * 8;
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4_trans(r0, r1, r2, r3, smem_u32(sv + vrow * AT_PITCH + vdim * 2));
+      mma_bf16_16816(o[2 * jp], pa0, 0u, pa2, 0u, r0, r1);
+      mma_bf16_16816(o[2 * jp + 1], pa0, 0u, pa2, 0u, r2, r3);
     }
-    __syncthreads();   // s_S and this stage are rewritten by the next iterations
+    __syncwarp();   // the stage is refilled by the load issued at the top of the next iteration
   }
   cp_async_wait<0>();
 
@@ -234,48 +315,78 @@ __global__ void __launch_bounds__(AT_THREADS) sparse_attend_kernel(AttendParams 
   float* part = p.ws_partial + ((int64_t)row * p.nsplit + split) * GG * PW;
   if (g < GG) {
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-      const int d = 32 * warp + 8 * nt + 2 * t4;
+    for (int nt = 0; nt < 16; ++nt) {
+      const int d = 8 * nt + 2 * t4;
       *reinterpret_cast<float2*>(&part[g * PW + d]) = make_float2(o[nt][0], o[nt][1]);
     }
-    if (warp == 0 && t4 == 0) {
+    if (t4 == 0) {
       part[g * PW + AT_D] = m_run;
       part[g * PW + AT_D + 1] = l_run;
     }
   }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const uint32_t prev = atomicAdd(&p.ws_counter[row], 1u);
-    s_is_last = (prev == (uint32_t)(p.nsplit - 1));
-    if (s_is_last) p.ws_counter[row] = 0;              // leave the counter ready for the next call
+}
+
+// Log-sum-exp merge of the nsplit chunk partials of every (list, head): one CTA per (row, head),
+// thread d owns output dim d. Chunk maxima / sums are staged in shared memory (one round trip),
+// then every thread streams its column with independent loads.
+template <int GG>
+__global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
+  constexpr int PW = AT_D + 2;
+  __shared__ float s_w[64];
+  __shared__ float s_ml[2];
+  const int row = blockIdx.x / GG, hd = blockIdx.x - row * GG;
+  const int b = row / p.Hi, hi = row - b * p.Hi;
+  const int head = hi * GG + hd;
+  const int d = threadIdx.x;
+  const float* parts = p.ws_partial + (int64_t)row * p.nsplit * GG * PW;
+  if (d < 32) {
+    float m_a = -INFINITY, l_a = 0.0f, m_b = -INFINITY, l_b = 0.0f;
+    if (d < p.nsplit) {
+      m_a = __ldcg(&parts[(d * GG + hd) * PW + AT_D]);
+      l_a = __ldcg(&parts[(d * GG + hd) * PW + AT_D + 1]);
+    }
+    if (d + 32 < p.nsplit) {
+      m_b = __ldcg(&parts[((d + 32) * GG + hd) * PW + AT_D]);
+      l_b = __ldcg(&parts[((d + 32) * GG + hd) * PW + AT_D + 1]);
+    }
+    float M = fmaxf(m_a, m_b);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float Mu = (M == -INFINITY) ? 0.0f : M;
+    const float w_a = __expf(m_a - Mu), w_b = __expf(m_b - Mu);    // 0 for absent chunks (m = -inf)
+    float L = l_a * w_a + l_b * w_b;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+    s_w[d] = w_a;
+    s_w[d + 32] = w_b;
+    if (d == 0) { s_ml[0] = M; s_ml[1] = L; }
   }
   __syncthreads();
-  if (!s_is_last) return;
-  __threadfence();
-
-  // ---- log-sum-exp merge of the chunks by the last CTA: thread d handles output dim d ----
-  const float* parts = p.ws_partial + (int64_t)row * p.nsplit * GG * PW;
-  for (int hd = 0; hd < GG; ++hd) {
-    float M = -INFINITY;
-    for (int sp = 0; sp < p.nsplit; ++sp) M = fmaxf(M, __ldcg(&parts[(sp * GG + hd) * PW + AT_D]));
-    const float Mu = (M == -INFINITY) ? 0.0f : M;
-    float L = 0.0f, O = 0.0f;
-    for (int sp = 0; sp < p.nsplit; ++sp) {
-      const float* ps = parts + (sp * GG + hd) * PW;
-      const float w = __expf(__ldcg(&ps[AT_D]) - Mu);
-      L += __ldcg(&ps[AT_D + 1]) * w;
-      O += __ldcg(&ps[tid]) * w;
-    }
-    const int head = head0 + hd;
-    if (p.out) p.out[((int64_t)b * p.Hq + head) * AT_D + tid] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
-    if (p.out_partial) {
-      float* op = p.out_partial + ((int64_t)b * p.Hq + head) * PW;
-      op[tid] = O;
-      if (tid == 0) {
-        op[AT_D] = M;
-        op[AT_D + 1] = L;
-      }
+  float O = 0.0f;
+  const float* col = parts + hd * PW + d;
+  int sp = 0;
+  for (; sp + 8 <= p.nsplit; sp += 8) {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) x[u] = __ldcg(col + (int64_t)(sp + u) * GG * PW);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) O += x[u] * s_w[sp + u];
+  }
+  {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) x[u] = (sp + u < p.nsplit) ? __ldcg(col + (int64_t)(sp + u) * GG * PW) : 0.0f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) O += (sp + u < p.nsplit) ? x[u] * s_w[sp + u] : 0.0f;
+  }
+  const float M = s_ml[0], L = s_ml[1];
+  if (p.out) p.out[((int64_t)b * p.Hq + head) * AT_D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+  if (p.out_partial) {
+    float* op = p.out_partial + ((int64_t)b * p.Hq + head) * PW;
+    op[d] = O;
+    if (d == 0) {
+      op[AT_D] = M;
+      op[AT_D + 1] = L;
     }
   }
 }
@@ -355,7 +466,7 @@ static FinalLayout final_layout(int kk, int history, int sink, int recent, int k
 }
 
 struct AttendPlan {
-  int tiles_per_cta, nsplit;
+  int tiles_per_split, nsplit;
   size_t counter_bytes, partial_bytes, bytes;
 };
 
@@ -364,15 +475,15 @@ static AttendPlan attend_plan(int B, int Hq, int Hi, int S) {
   const int R = B * Hi;
   const int GG = Hq / Hi;
   const int ntiles = ceil_div(S, AT_TILE);
-  // As many chunks per list as fit in ONE wave of resident CTAs: long chunks keep the 3-stage
+  // As many chunks per list as fit in ONE wave of resident warps: long chunks keep the 3-stage
   // gather pipeline full and make the final merge short.
-  int want_splits = AT_TARGET_CTAS / R;
+  int want_splits = AT_TARGET_WARPS / R;
   if (want_splits < 1) want_splits = 1;
-  int tpc = ceil_div(ntiles, want_splits);
-  if (tpc < 1) tpc = 1;
-  if (tpc > AT_MAX_TILES_PER_CTA) tpc = AT_MAX_TILES_PER_CTA;
-  a.tiles_per_cta = tpc;
-  a.nsplit = ceil_div(ntiles, tpc);
+  if (want_splits > 64) want_splits = 64;
+  int tps = ceil_div(ntiles, want_splits);
+  if (tps < 1) tps = 1;
+  a.tiles_per_split = tps;
+  a.nsplit = ceil_div(ntiles, tps);
   a.counter_bytes = round_up(sizeof(uint32_t) * (size_t)R, 256);
   a.partial_bytes = round_up(sizeof(float) * (size_t)R * a.nsplit * GG * (AT_D + 2), 256);
   a.bytes = a.counter_bytes + a.partial_bytes;
@@ -381,15 +492,17 @@ static AttendPlan attend_plan(int B, int Hq, int Hi, int S) {
 
 template <int GG>
 static int attend_launch(const AttendParams& p, int device, cudaStream_t st) {
-  const size_t smem = (size_t)AT_STAGES * AT_STAGE_BYTES + sizeof(float) * 8 * AT_S_PITCH +
-                      (sizeof(int) + sizeof(float)) * AT_MAX_ROWS_PER_CTA;
+  const size_t smem = (size_t)AT_WARPS * AT_WARP_SMEM;
   auto kern = sparse_attend_kernel<GG>;
   static bool attr_done[64] = {false};
   if (device < 64 && !attr_done[device]) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_done[device] = true;
   }
-  kern<<<dim3(p.nsplit, p.B * p.Hi), AT_THREADS, smem, st>>>(p);
+  const int tasks = p.B * p.Hi * p.nsplit;
+  kern<<<ceil_div(tasks, AT_WARPS), AT_THREADS, smem, st>>>(p);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  attend_merge_kernel<GG><<<p.B * p.Hi * GG, AT_D, 0, st>>>(p);
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
 }
@@ -407,11 +520,12 @@ namespace kvb {
 // cleared ws_counter on this stream.
 static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh,
                       int64_t k_st, const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st,
-                      const void* indices, int idx_is_i64, const uint8_t* valid, const float* mask, int64_t mask_sb,
+                      const AttendList& list, const AttendAppend* append, const float* mask, int64_t mask_sb,
                       int B, int Hq, int Hkv, int Hi, int Tk, int D, int S, float scaling, void* out,
                       float* out_partial, uint32_t* ws_counter, float* ws_partial, bool counters_zeroed, int device,
                       cudaStream_t st) {
-  if (!query || !key || !value || !indices || !ws_counter || !ws_partial) return KVB_BAD_ARG;
+  if (!query || !key || !value || !ws_counter || !ws_partial) return KVB_BAD_ARG;
+  if (list.implicit ? (!list.selected && list.kk > 0) : !list.indices) return KVB_BAD_ARG;
   if (!out && !out_partial) return KVB_BAD_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hi <= 0 || Tk <= 0 || S <= 0) return KVB_BAD_SHAPE;
   if (D != AT_D || (Hq % Hkv) || (Hi != Hkv && Hi != Hq)) return KVB_BAD_SHAPE;
@@ -421,8 +535,10 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
   if (!aligned_to(query, 16) || !aligned_to(key, 16) || !aligned_to(value, 16)) return KVB_BAD_ALIGN;
   if ((q_sb % 8) || (q_sh % 8) || (k_sb % 8) || (k_sh % 8) || (k_st % 8) || (v_sb % 8) || (v_sh % 8) || (v_st % 8))
     return KVB_BAD_ALIGN;
-  if (!aligned_to(indices, idx_is_i64 ? 8 : 4) || !aligned_to(ws_partial, 16)) return KVB_BAD_ALIGN;
-  if (out && !aligned_to(out, 2)) return KVB_BAD_ALIGN;
+  if (!list.implicit && !aligned_to(list.indices, list.idx_is_i64 ? 8 : 4)) return KVB_BAD_ALIGN;
+  if (!aligned_to(ws_partial, 16)) return KVB_BAD_ALIGN;
+  if (append && append->enabled && (append->C > 128 || (append->C & 1))) return KVB_BAD_SHAPE;
+  if (out && !aligned_to(out, 8)) return KVB_BAD_ALIGN;
   const AttendPlan plan = attend_plan(B, Hq, Hi, S);
   DeviceGuard guard(device);
   if (!guard.ok) return KVB_BAD_DEVICE;
@@ -431,17 +547,18 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
   p.query = reinterpret_cast<const __nv_bfloat16*>(query); p.q_sb = q_sb; p.q_sh = q_sh;
   p.key = reinterpret_cast<const __nv_bfloat16*>(key); p.k_sb = k_sb; p.k_sh = k_sh; p.k_st = k_st;
   p.value = reinterpret_cast<const __nv_bfloat16*>(value); p.v_sb = v_sb; p.v_sh = v_sh; p.v_st = v_st;
-  p.indices = indices; p.idx_is_i64 = idx_is_i64; p.valid = valid;
+  p.list = list;
   p.mask = mask; p.mask_sb = mask_sb;
+  if (append) p.append = *append; else p.append.enabled = 0;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Hi = Hi; p.Tk = Tk; p.S = S; p.G = Hq / Hkv;
   p.scaling = scaling;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.out_partial = out_partial;
   p.ws_counter = ws_counter;
   p.ws_partial = ws_partial;
-  p.nsplit = plan.nsplit; p.tiles_per_cta = plan.tiles_per_cta;
+  p.nsplit = plan.nsplit; p.tiles_per_split = plan.tiles_per_split;
 
-  if (!counters_zeroed) KVB_CHECK_CUDA(cudaMemsetAsync(p.ws_counter, 0, sizeof(uint32_t) * (size_t)B * Hi, st));
+  (void)counters_zeroed;   // the chunk merge is its own launch: no arrival counters to clear
   switch (GG) {
     case 1: return attend_launch<1>(p, device, st);
     case 2: return attend_launch<2>(p, device, st);
@@ -463,7 +580,9 @@ extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(
   if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
   const AttendPlan plan = attend_plan(B, Hq, Hi, S);
   if (workspace_bytes < plan.bytes) return KVB_WORKSPACE_TOO_SMALL;
-  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, indices, idx_is_i64, valid,
+  AttendList list{};
+  list.indices = indices; list.idx_is_i64 = idx_is_i64; list.valid = valid; list.implicit = 0;
+  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, list, nullptr,
                     mask, mask_sb, B, Hq, Hkv, Hi, Tk, D, S, scaling, out, out_partial,
                     reinterpret_cast<uint32_t*>(workspace),
                     reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes),
