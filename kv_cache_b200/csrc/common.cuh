@@ -139,6 +139,10 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   return p;
 }
 
+__device__ __forceinline__ void st_global_hint_f32(float* p, float v, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(policy) : "memory");
+}
+
 // ---- cp.async (LDGSTS) 16-byte copies ---------------------------------------------------
 
 __device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src_gmem) {

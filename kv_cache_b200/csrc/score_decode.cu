@@ -171,6 +171,9 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
   __syncthreads();
 
   const uint64_t policy = l2_policy_evict_first();
+  // The group-max row is re-read by the selector right away and overwritten by the next step:
+  // ask L2 to keep it so that it need not travel to HBM and back.
+  const uint64_t keep = l2_policy_evict_last();
   const int64_t u_begin = (int64_t)blockIdx.x * p.total_units / gridDim.x;
   const int64_t u_end = (int64_t)(blockIdx.x + 1) * p.total_units / gridDim.x;
 
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
               // the lane alone holds both heads of its two tokens
               if (m0 == 0.0f) m0 = 0.0f;
               if (m1 == 0.0f) m1 = 0.0f;
-              if (gmax_row) { gmax_row[t0 + tl[0]] = m0; gmax_row[t0 + tl[2]] = m1; }
+              if (gmax_row) { st_global_hint_f32(gmax_row + t0 + tl[0], m0, keep); st_global_hint_f32(gmax_row + t0 + tl[2], m1, keep); }
               if (HIST) {
                 atomicAdd(&s_hist[float_to_key(m0) >> (32 - SC_HIST_BITS)], 1u);
                 atomicAdd(&s_hist[float_to_key(m1) >> (32 - SC_HIST_BITS)], 1u);
@@ -335,7 +338,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
               const bool writer = (G == 4) ? true : (t4 < 2);
               if (m == 0.0f) m = 0.0f;
               if (writer) {
-                if (gmax_row) gmax_row[t0 + tok] = m;
+                if (gmax_row) st_global_hint_f32(gmax_row + t0 + tok, m, keep);
                 if (HIST) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
               }
             }
@@ -345,7 +348,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
             for (int v = 0; v < 4; ++v) {
               float m = d[v];
               if (m == 0.0f) m = 0.0f;
-              if (gmax_row) gmax_row[t0 + tl[v]] = m;
+              if (gmax_row) st_global_hint_f32(gmax_row + t0 + tl[v], m, keep);
               if (HIST) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
             }
           }

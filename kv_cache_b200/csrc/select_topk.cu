@@ -171,42 +171,38 @@ constexpr int SEL_TOK_PER_THREAD = 16;
 constexpr int SEL_TOK_PER_WARP = SEL_TOK_PER_THREAD * 32;                 // 512
 constexpr int SEL_TOK_PER_CTA = SEL_TOK_PER_THREAD * SEL_SCAN_THREADS;   // 4096
 
+// One 512-element chunk per warp, 16 elements per lane held in registers (loads issued before the
+// threshold is read). Winners are first queued in shared memory (a few predicated stores per
+// element), then the lanes copy the queue out together: the 64-bit composites are built and
+// stored once per winner, coalesced, instead of once per element slot.
 template <bool VEC>
 __global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(SelectParams p) {
+  __shared__ uint2 s_queue[SEL_SCAN_THREADS / 32][SEL_TOK_PER_WARP];
   const int row = blockIdx.y;
   const float* src = p.scores + (int64_t)row * p.row_stride;
-  const int lane = threadIdx.x & 31;
-  const int64_t t0 = (int64_t)blockIdx.x * SEL_TOK_PER_CTA + (threadIdx.x >> 5) * SEL_TOK_PER_WARP;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t0 = blockIdx.x * SEL_TOK_PER_CTA + warp * SEL_TOK_PER_WARP;     // T < 2^31
   if (t0 >= p.T) return;
 
   float v[SEL_TOK_PER_THREAD];
-  if (VEC) {
+  const float qnan = __int_as_float(0x7fc00000);           // padding compares false against anything
 #pragma unroll
-    for (int j = 0; j < SEL_TOK_PER_THREAD / 4; ++j) {
-      const int64_t t = t0 + j * 128 + lane * 4;
-      const float qnan = __int_as_float(0x7fc00000);       // padding compares false against anything
-      float4 x = make_float4(qnan, qnan, qnan, qnan);
-      if (t + 3 < p.T) {
-        x = __ldcg(reinterpret_cast<const float4*>(src + t));
-      } else {
-        if (t < p.T) x.x = src[t];
-        if (t + 1 < p.T) x.y = src[t + 1];
-        if (t + 2 < p.T) x.z = src[t + 2];
-      }
-      v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+  for (int j = 0; j < SEL_TOK_PER_THREAD / 4; ++j) {
+    const int t = t0 + j * 128 + lane * 4;
+    float4 x = make_float4(qnan, qnan, qnan, qnan);
+    if (VEC && t + 3 < p.T) {
+      x = __ldcg(reinterpret_cast<const float4*>(src + t));
+    } else {
+      if (t < p.T) x.x = __ldcg(src + t);
+      if (t + 1 < p.T) x.y = __ldcg(src + t + 1);
+      if (t + 2 < p.T) x.z = __ldcg(src + t + 2);
+      if (t + 3 < p.T) x.w = __ldcg(src + t + 3);
     }
-  } else {
-#pragma unroll
-    for (int j = 0; j < SEL_TOK_PER_THREAD / 4; ++j)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int64_t t = t0 + j * 128 + lane * 4 + i;
-        v[4 * j + i] = t < p.T ? src[t] : __int_as_float(0x7fc00000);
-      }
+    v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
   }
   // the row's threshold is read after the element loads were issued, so both latencies overlap
   const uint4 thr = __ldcg(p.thresholds + row);
-  if (thr.y + thr.z > (uint32_t)p.cap) return;
+  if (thr.y + thr.z > (uint32_t)p.cap) return;             // this row is refined by the final kernel instead
   // key(v) >= bin << 20  <=>  v >= the float whose key is bin << 20 (keys are order preserving;
   // bins that only NaN patterns can reach are clamped to -inf / "nothing").
   const uint32_t key_lo = thr.x << (32 - SEL_HIST_BITS);
@@ -227,16 +223,22 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(Sel
   if (total == 0) return;
   uint32_t base = 0;
   if (lane == 0) base = atomicAdd(p.cand_count + (int64_t)row * SEL_COUNT_STRIDE, total);
-  base = __shfl_sync(0xffffffffu, base, 0);
-  uint64_t* cand = p.cand + (int64_t)row * p.cap;
-  uint32_t pos = base + incl - cnt;
+  uint2* q = s_queue[warp];
+  uint32_t qpos = incl - cnt;
 #pragma unroll
   for (int e = 0; e < SEL_TOK_PER_THREAD; ++e) {
     if (takemask & (1u << e)) {
-      const int64_t t = t0 + (e >> 2) * 128 + lane * 4 + (e & 3);
-      if (pos < (uint32_t)p.cap) cand[pos] = make_composite(v[e], element_index(p, row, t));
-      ++pos;
+      q[qpos] = make_uint2(__float_as_uint(v[e]), (uint32_t)((e >> 2) * 128 + lane * 4 + (e & 3)));
+      ++qpos;
     }
+  }
+  base = __shfl_sync(0xffffffffu, base, 0);
+  __syncwarp();                                            // queue writes visible to the whole warp
+  uint64_t* cand = p.cand + (int64_t)row * p.cap;
+  for (uint32_t i = lane; i < total; i += 32) {
+    const uint2 e = q[i];
+    const int t = t0 + (int)e.y;
+    if (base + i < (uint32_t)p.cap) cand[base + i] = make_composite(__uint_as_float(e.x), element_index(p, row, t));
   }
 }
 
