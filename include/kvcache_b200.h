@@ -196,6 +196,29 @@ int kvb_sparse_attend(const void* query, int64_t q_sb, int64_t q_sh,
                       void* workspace, size_t workspace_bytes,
                       int device, void* stream);
 
+/* Attention over the IMPLICIT list  selected || sink || recent || self  (nothing materialised):
+ * the composition of kvb_build_final_indices and kvb_sparse_attend, i.e. the tail of
+ * _qabs_candidate_attention_forward (EVAL:4460-4501), with one list per KV head.
+ *
+ *   selected   int32 [B*Hkv, kk] token ids; an id contributes iff 0 <= id - id_base < history_count
+ *              (and it is not in a protected range unless append_protected). With id_base != 0
+ *              the ids are global and this rank owns [id_base, id_base + history_count): what a
+ *              sequence shard needs after the global top-k merge.
+ *   key/value  views whose rows 0 .. history_count-1 are the history and, when keep_self != 0,
+ *              row history_count is the token being decoded (Tk >= history_count + keep_self).
+ *   out / out_partial / mask / workspace as in kvb_sparse_attend; workspace size from
+ *   kvb_sparse_attend_workspace_bytes(B, Hq, Hkv, kvb_final_index_count(kk, history_count, ...)). */
+int kvb_attend_selected(const void* query, int64_t q_sb, int64_t q_sh,
+                        const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+                        const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st,
+                        const int32_t* selected, int kk, int64_t id_base, int history_count,
+                        int protect_sink, int protect_recent, int keep_self, int append_protected,
+                        const float* mask, int64_t mask_sb,
+                        int B, int Hq, int Hkv, int Tk, int D, float scaling,
+                        void* out, float* out_partial,
+                        void* workspace, size_t workspace_bytes,
+                        int device, void* stream);
+
 /* Combine N shard partials [N,B,Hq,D+2] (layout of out_partial above) into bf16 [B,1,Hq,D]:
  * o = sum_r e^{m_r-m} o_r / sum_r e^{m_r-m} l_r, shards with l == 0 ignored. No reference
  * counterpart (the reference has no sequence sharding). */

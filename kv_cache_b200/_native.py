@@ -67,6 +67,9 @@ SIGNATURES = {
     "kvb_sparse_attend": (_i, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64,
                                _p, _i, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f,
                                _p, _p, _p, _sz, _i, _p]),
+    "kvb_attend_selected": (_i, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64,
+                                 _p, _i, _i64, _i, _i, _i, _i, _i, _p, _i64,
+                                 _i, _i, _i, _i, _i, _f, _p, _p, _p, _sz, _i, _p]),
     "kvb_lse_merge": (_i, [_p, _i, _i, _i, _i, _p, _i, _p]),
     "kvb_decode_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i, _i]),
     "kvb_decode_step": (_i, [C.POINTER(DecodeStepParams), _i, _p]),

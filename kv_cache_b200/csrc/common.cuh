@@ -75,7 +75,7 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
   return __uint_as_float(u);
 }
 
-// ---- mbarrier + bulk async copy (TMA engine, 1-D, no tensor map, no multicast) ----------
+// ---- mbarrier + bulk async copy (TMA engine, 1-D, no tensor map, one destination CTA) ----------
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

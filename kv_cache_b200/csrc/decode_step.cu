@@ -84,6 +84,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   AttendList list{};
   list.implicit = 1;
   list.selected = sel; list.kk = L.kk;
+  list.sel_base = 0; list.sel_limit = T;
   list.sink_end = f.sink_end; list.n_recent = f.n_recent; list.recent_from = f.recent_from;
   list.recent_start = f.recent_start; list.recent_on = f.recent_on; list.history = T;
   list.append_protected = p->append_protected;

@@ -33,6 +33,7 @@ struct AttendList {
   const void* indices; int idx_is_i64; const uint8_t* valid;      // explicit
   int implicit;
   const int32_t* selected; int kk;
+  int64_t sel_base; int sel_limit;       // selected ids are global: local row = id - sel_base, kept iff in [0, sel_limit)
   int sink_end, n_recent, recent_from, recent_start, recent_on, history, append_protected;
 };
 
@@ -90,7 +91,8 @@ __device__ __forceinline__ int attend_fetch(const AttendParams& p, int row, int 
                        : (int64_t) reinterpret_cast<const int32_t*>(L.indices)[o];
     ok = (L.valid == nullptr) || (L.valid[o] != 0);
   } else if (s < L.kk) {
-    raw = L.selected[(int64_t)row * L.kk + s];
+    raw = (int64_t)L.selected[(int64_t)row * L.kk + s] - L.sel_base;
+    if (raw >= L.sel_limit) ok = false;
     if (!L.append_protected) {
       if (L.recent_on && raw >= L.recent_start && raw < L.history) ok = false;
       if (L.sink_end > 0 && raw < L.sink_end) ok = false;
@@ -584,6 +586,36 @@ extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(
   list.indices = indices; list.idx_is_i64 = idx_is_i64; list.valid = valid; list.implicit = 0;
   return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, list, nullptr,
                     mask, mask_sb, B, Hq, Hkv, Hi, Tk, D, S, scaling, out, out_partial,
+                    reinterpret_cast<uint32_t*>(workspace),
+                    reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes),
+                    /*counters_zeroed=*/false, device, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_attend_selected(
+    const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+    const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st, const int32_t* selected, int kk, int64_t id_base,
+    int history_count, int protect_sink, int protect_recent, int keep_self, int append_protected, const float* mask,
+    int64_t mask_sb, int B, int Hq, int Hkv, int Tk, int D, float scaling, void* out, float* out_partial,
+    void* workspace, size_t workspace_bytes, int device, void* stream) {
+  using namespace kvb;
+  if (!workspace || (!selected && kk > 0)) return KVB_BAD_ARG;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || kk < 0 || history_count < 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
+  if (Tk < history_count + (keep_self ? 1 : 0)) return KVB_BAD_SHAPE;
+  if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
+  const FinalLayout f = final_layout(kk, history_count, protect_sink, protect_recent, keep_self);
+  if (f.S <= 0) return KVB_BAD_SHAPE;
+  const AttendPlan plan = attend_plan(B, Hq, Hkv, f.S);
+  if (workspace_bytes < plan.bytes) return KVB_WORKSPACE_TOO_SMALL;
+  AttendList list{};
+  list.implicit = 1;
+  list.selected = selected; list.kk = kk;
+  list.sel_base = id_base; list.sel_limit = history_count;
+  list.sink_end = f.sink_end; list.n_recent = f.n_recent; list.recent_from = f.recent_from;
+  list.recent_start = f.recent_start; list.recent_on = f.recent_on; list.history = history_count;
+  list.append_protected = append_protected;
+  // the "self" entry of the implicit list is row Tk - 1, so the view must end at the decoded token
+  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, list, nullptr, mask, mask_sb,
+                    B, Hq, Hkv, Hkv, keep_self ? history_count + 1 : history_count, D, f.S, scaling, out, out_partial,
                     reinterpret_cast<uint32_t*>(workspace),
                     reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes),
                     /*counters_zeroed=*/false, device, reinterpret_cast<cudaStream_t>(stream));

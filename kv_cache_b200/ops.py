@@ -329,6 +329,43 @@ def sparse_attend(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, i
     return part if return_partial else out
 
 
+def attend_selected(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, selected: torch.Tensor,
+                    history_count: int, *, id_base: int = 0, protect_sink: int = 0, protect_recent: int = 0,
+                    keep_self: bool = True, append_protected: bool = False, scaling: Optional[float] = None,
+                    attention_mask: Optional[torch.Tensor] = None, return_partial: bool = False):
+    """Attention over the implicit list ``selected ‖ sink ‖ recent ‖ self`` (one list per KV head,
+    int32 ``[B,Hkv,kk]``). Ids outside ``[id_base, id_base + history_count)`` contribute nothing,
+    which is how a sequence shard attends to the part of a global selection that it owns."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    Hkv, Tk = key.shape[1], key.shape[2]
+    key = _rows_contiguous(key)
+    value = _rows_contiguous(value)
+    if selected.dtype != torch.int32 or selected.dim() != 3 or selected.shape[1] != Hkv:
+        raise RuntimeError("selected must be int32 [B,Hkv,kk]")
+    selected = selected.contiguous()
+    kk = selected.shape[2]
+    if scaling is None:
+        scaling = float(D) ** -0.5
+    dev = query.device
+    mask = _mask_rows(attention_mask, B, Tk)
+    lib = _native.lib()
+    S = lib.kvb_final_index_count(kk, history_count, protect_sink, protect_recent, int(keep_self))
+    ws_bytes = lib.kvb_sparse_attend_workspace_bytes(B, Hq, Hkv, S)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    out = None if return_partial else torch.empty((B, 1, Hq, D), dtype=torch.bfloat16, device=dev)
+    part = torch.empty((B, Hq, D + 2), dtype=torch.float32, device=dev) if return_partial else None
+    check(lib.kvb_attend_selected(
+        query.data_ptr(), query.stride(0), query.stride(1),
+        key.data_ptr(), key.stride(0), key.stride(1), key.stride(2),
+        value.data_ptr(), value.stride(0), value.stride(1), value.stride(2),
+        selected.data_ptr(), kk, int(id_base), int(history_count), int(protect_sink), int(protect_recent),
+        int(keep_self), int(append_protected), _ptr(mask), 0 if mask is None else mask.stride(0),
+        B, Hq, Hkv, Tk, D, float(scaling), _ptr(out), _ptr(part), ws.data_ptr(), ws.numel(),
+        _dev(query), _stream(dev)), "kvb_attend_selected")
+    return part if return_partial else out
+
+
 def lse_merge(partials: torch.Tensor) -> torch.Tensor:
     """Combines shard partials fp32 ``[N,B,Hq,D+2]`` into bf16 ``[B,1,Hq,D]``."""
     N, B, Hq, PW = partials.shape

@@ -1,0 +1,57 @@
+"""The CUDA backend of the sharded step on one GPU: a world of one, and the per-shard stages run
+for every shard of a two-way split inside one process (what each rank would compute), merged
+exactly as the ranks would."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from kv_cache_b200 import ops
+from kv_cache_b200.sharded import CudaBackend, ShardedSparseDecode, shard_bounds
+from oracle import oracle
+from tests.gpu_util import cpu, make_case
+
+pytestmark = pytest.mark.gpu
+
+
+def test_two_shards_emulated_in_one_process(cuda_device):
+    T, k, N = 3000, 256, 2
+    w, q, key, value = make_case(cuda_device, batch=2, q_heads=8, kv_heads=2, context=T, channels=64)
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    be = CudaBackend()
+    scs, ids, shards = [], [], []
+    for r in range(N):
+        t0, t1 = shard_bounds(T, N, r)
+        tl = t1 - t0
+        k_loc = torch.cat((key[:, :, t0:t1], key[:, :, T:]), dim=2).contiguous()
+        v_loc = torch.cat((value[:, :, t0:t1], value[:, :, T:]), dim=2).contiguous()
+        packed, scale = ops.quantize(k_loc[:, :, :tl], ch)
+        sc, idx = be.local_candidates(q, packed, scale, ch, tl, k, t0)
+        scs.append(sc), ids.append(idx), shards.append((k_loc, v_loc, tl, t0))
+    sel = be.merge(torch.stack(scs), torch.stack(ids), k).view(2, 2, -1)
+    parts = [be.attend_partial(q, kl, vl, sel, tl, t0, r == N - 1, None) for r, (kl, vl, tl, t0) in enumerate(shards)]
+    out = be.combine(torch.stack(parts))
+    want = oracle.decode_step(*cpu(q, key, value, ch), k)
+    assert torch.equal(sel.cpu().long(), torch.sort(want["selected"], dim=-1).values)
+    torch.testing.assert_close(out.float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
+
+
+def test_world_of_one(cuda_device):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        T, k = 2000, 128
+        w, q, key, value = make_case(cuda_device, batch=1, q_heads=4, kv_heads=2, context=T, channels=32)
+        ch = ops.choose_channels(key[:, :, :T], 32)
+        packed, scale = ops.quantize(key[:, :, :T], ch)
+        out, sel = ShardedSparseDecode(k).step(q, key, value, packed, scale, ch, T, 0)
+        want = oracle.decode_step(*cpu(q, key, value, ch), k)
+        assert torch.equal(sel.cpu().long(), torch.sort(want["selected"], dim=-1).values)
+        torch.testing.assert_close(out.float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
+    finally:
+        dist.destroy_process_group()
