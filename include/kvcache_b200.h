@@ -35,7 +35,8 @@ typedef enum kvb_status {
   KVB_WORKSPACE_TOO_SMALL = 4,
   KVB_TIMEOUT = 5,            /* a bounded device-side wait gave up (see kvb_device_status)*/
   KVB_CUDA_ERROR = 6,         /* a CUDA runtime call or a launch returned an error        */
-  KVB_BAD_ARG = 7             /* null pointer where one is required, bad flag, ...        */
+  KVB_BAD_ARG = 7,            /* null pointer where one is required, bad flag, ...        */
+  KVB_SCRATCH_LIMIT = 8       /* the problem needs more than the library's built-in scratch */
 } kvb_status;
 
 /* Library version (major*10000 + minor*100 + patch) and a static string for a status. */
@@ -138,6 +139,29 @@ int kvb_select_topk(const float* scores, int64_t row_stride, const int32_t* payl
                     const uint32_t* hist_in,
                     void* workspace, size_t workspace_bytes,
                     int device, void* stream);
+
+/* Top-k select for callers that cannot allocate device memory. It has no counterpart in the
+ * reference. Some hosts of this library own no allocator they may call at this point: code that
+ * runs inside a stream-ordered region where cudaMalloc would synchronise the device, a plugin
+ * whose embedding runtime forbids it from allocating, a tight memory budget already handed out in
+ * full. kvb_select_topk needs a workspace from its caller; this variant keeps the same workspace
+ * in a fixed array inside the library image instead (kvb_select_topk_static_limit_bytes() bytes,
+ * 4 MiB; every GPU that loads the library carries it until the process ends). Inputs and outputs
+ * are still the caller's. Same semantics and arguments as kvb_select_topk without payload,
+ * hist_in and workspace.
+ *   - Problems whose workspace (kvb_select_topk_workspace_bytes(R, T, k)) exceeds the limit are
+ *     refused with KVB_SCRATCH_LIMIT before anything is launched (about 50 rows at k <= 4096).
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call outside any stream capture.
+ *   - Nothing is allocated or freed; counters and histogram are cleared by the call itself.
+ *   - All calls share the one array: two calls that may overlap on the GPU (different streams)
+ *     race with each other. Serialise them on one stream or with events. */
+size_t kvb_select_topk_static_limit_bytes(void);
+
+int kvb_select_topk_static(const float* scores, int64_t row_stride, int R, int T, int k,
+                           int64_t idx_offset, int order,
+                           int32_t* out_idx32, int64_t* out_idx64, float* out_scores,
+                           int device, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Final index list — selected || sink || recent || self with protected ranges invalidated.

@@ -20,6 +20,7 @@ STATUS_NAMES = {
     5: "KVB_TIMEOUT",
     6: "KVB_CUDA_ERROR",
     7: "KVB_BAD_ARG",
+    8: "KVB_SCRATCH_LIMIT",
 }
 
 _i, _i64, _p, _sz, _f = C.c_int, C.c_int64, C.c_void_p, C.c_size_t, C.c_float
@@ -61,6 +62,8 @@ SIGNATURES = {
                               _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _p]),
     "kvb_select_topk_workspace_bytes": (_sz, [_i, _i, _i]),
     "kvb_select_topk": (_i, [_p, _i64, _p, _i, _i, _i, _i64, _i, _p, _p, _p, _p, _p, _sz, _i, _p]),
+    "kvb_select_topk_static_limit_bytes": (_sz, []),
+    "kvb_select_topk_static": (_i, [_p, _i64, _i, _i, _i, _i64, _i, _p, _p, _p, _i, _p]),
     "kvb_final_index_count": (_i, [_i, _i, _i, _i, _i]),
     "kvb_build_final_indices": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p]),
     "kvb_sparse_attend_workspace_bytes": (_sz, [_i, _i, _i, _i]),

@@ -20,6 +20,7 @@ extern "C" __attribute__((visibility("default"))) const char* kvb_status_string(
     case KVB_TIMEOUT: return "device-side wait timed out";
     case KVB_CUDA_ERROR: return "CUDA error";
     case KVB_BAD_ARG: return "bad argument";
+    case KVB_SCRATCH_LIMIT: return "problem exceeds the built-in scratch";
     default: return "unknown status";
   }
 }

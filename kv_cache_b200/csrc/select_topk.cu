@@ -516,7 +516,53 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   return KVB_OK;
 }
 
+// ---- built-in scratch for callers that cannot allocate ------------------------------------
+// A fixed device array that lives in the library image: every GPU that loads the library holds
+// these bytes until the process exits. Host code must not pass the array's name to a kernel (on
+// the host it is only a stand-in symbol); the device address is looked up once per device.
+constexpr size_t SEL_STATIC_SCRATCH_BYTES = 4u << 20;    // 4 MiB
+static __device__ __align__(256) unsigned char g_select_static_scratch[SEL_STATIC_SCRATCH_BYTES];
+
+// Device address of the built-in scratch on `device` (which must be current); looked up on the
+// first call per device and remembered.
+static int select_static_scratch(int device, void** out) {
+  static void* cached[64] = {nullptr};
+  if (device < 0 || device >= 64) return KVB_BAD_DEVICE;
+  if (!cached[device]) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_select_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return KVB_CUDA_ERROR;
+    cached[device] = ptr;
+  }
+  *out = cached[device];
+  return KVB_OK;
+}
+
 }  // namespace kvb
+
+extern "C" __attribute__((visibility("default"))) size_t kvb_select_topk_static_limit_bytes(void) {
+  return kvb::SEL_STATIC_SCRATCH_BYTES;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_select_topk_static(
+    const float* scores, int64_t row_stride, int R, int T, int k, int64_t idx_offset, int order, int32_t* out_idx32,
+    int64_t* out_idx64, float* out_scores, int device, void* stream) {
+  using namespace kvb;
+  if (R <= 0 || T <= 0 || k <= 0) return KVB_BAD_SHAPE;
+  const int kk = k < T ? k : T;
+  if (kk > SEL_MAX_K) return KVB_BAD_SHAPE;
+  if (select_carve(nullptr, R, kk).bytes > SEL_STATIC_SCRATCH_BYTES) return KVB_SCRATCH_LIMIT;
+  DeviceGuard guard(device);
+  if (!guard.ok) return KVB_BAD_DEVICE;
+  void* scratch = nullptr;
+  const int rc = select_static_scratch(device, &scratch);
+  if (rc != KVB_OK) return rc;
+  // select_run clears the counters and the histogram itself (memset nodes, no allocation); the
+  // candidate area needs no clearing because only the counted prefix is ever read.
+  return select_run(scores, row_stride, nullptr, R, T, k, idx_offset, order, out_idx32, out_idx64, out_scores,
+                    nullptr, /*hist_in_workspace=*/false, /*zeroed=*/false, scratch, SEL_STATIC_SCRATCH_BYTES, device,
+                    reinterpret_cast<cudaStream_t>(stream));
+}
 
 extern "C" __attribute__((visibility("default"))) size_t kvb_select_topk_workspace_bytes(int R, int T, int k) {
   (void)T;
