@@ -250,6 +250,40 @@ int kvb_lse_merge(const float* partials, int N, int B, int Hq, int D, void* out,
                   int device, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Chunked-prefill block scoring (Tq query tokens at once) and block-level selection.
+ *
+ * No counterpart in the reference: every QABS path there refuses query_count != 1
+ * (EVAL:4006-4007, 4413-4414). The nearest analogs are the decode-only block maximum
+ * (EVAL:5036-5046: pad, view(B,H,nblk,blk).amax(-1), topk over blocks) and the block-mean scoring
+ * for q_len > 1 in ymluo/projects/qwen3_kcache_avg_topk/src/qwen3_kcache_avg_topk.py:82-103.
+ *
+ * kvb_quantize_query_tokens: per (b, head, token) int8 codes of the query over the channels of
+ *   its KV head: qscale = max(absmax, 2^-24) / 127, code = clamp(rint(q / qscale), -127, 127).
+ *   query bf16 [B,Hq,Tq,D] with element strides q_sb/q_sh/q_st; qcode int8 [B,Hq,Tq,C] dense,
+ *   qscale fp32 [B,Hq,Tq] dense.
+ * kvb_score_prefill_blocks: block_scores[b,g,i,j] = max over the G heads of KV head g and the
+ *   tokens t of block j (block_size = 64; the last block may be short) of
+ *   (float(sum_c qcode*code) * kscale[b,g,t]) * qscale[b,h,i]; all Tk keys are visible to every
+ *   query of the chunk. C in {32,64,128}, G in {1,2,4,8}; packed/scale aligned as for the
+ *   streaming decode scorer. block_scores fp32 [B,Hkv,Tq,ceil(Tk/64)] dense; -0 stored as +0.
+ * kvb_block_topk: per row of block scores ([R,nblk], nblk <= 4096) the min(k,nblk) best blocks
+ *   ordered by (score desc, block asc); out_idx int32 [R,kk], out_scores fp32 [R,kk] or NULL.
+ * ------------------------------------------------------------------------------------- */
+int kvb_quantize_query_tokens(const void* query, int64_t q_sb, int64_t q_sh, int64_t q_st,
+                              const int32_t* channel_idx, int8_t* qcode, float* qscale,
+                              int B, int Hq, int Hkv, int Tq, int D, int C,
+                              int device, void* stream);
+
+int kvb_score_prefill_blocks(const int8_t* qcode, const float* qscale,
+                             const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                             const float* scale, int64_t scale_sb, int64_t scale_sh,
+                             int B, int Hq, int Hkv, int Tq, int Tk, int C, int block_size,
+                             float* block_scores, int device, void* stream);
+
+int kvb_block_topk(const float* block_scores, int64_t row_stride, int64_t R, int nblk, int k,
+                   int32_t* out_idx, float* out_scores, int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Fused decode step for one layer: quantize-append of the new K row, score, select,
  * final index list, attend — all enqueued on `stream`, nothing else touched.
  * Equivalent to the sequence _qabs_candidate_attention_forward runs (EVAL:4400-4502) with the

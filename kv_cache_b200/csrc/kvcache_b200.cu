@@ -7,6 +7,7 @@
 #include "select_topk.cu"
 #include "sparse_attend.cu"
 #include "decode_step.cu"
+#include "score_prefill.cu"
 
 extern "C" __attribute__((visibility("default"))) int kvb_version(void) { return 100; /* 0.1.0 */ }
 

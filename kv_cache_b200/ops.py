@@ -377,6 +377,78 @@ def lse_merge(partials: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------------------
+# chunked prefill: block scoring and block selection
+# ------------------------------------------------------------------------------------------
+
+PREFILL_BLOCK = 64
+
+
+def quantize_query_tokens(query: torch.Tensor, channel_idx: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-token int8 codes of a query chunk bf16 ``[B,Hq,Tq,D]`` over the channels of each head's KV
+    head: returns ``(qcode int8 [B,Hq,Tq,C], qscale fp32 [B,Hq,Tq])``."""
+    if query.dtype != torch.bfloat16 or query.dim() != 4:
+        raise RuntimeError("query must be bf16 [B,Hq,Tq,D]")
+    if query.stride(-1) != 1:
+        query = query.contiguous()
+    B, Hq, Tq, D = query.shape
+    Hkv, C_ = channel_idx.shape
+    dev = query.device
+    channel_idx = channel_idx.to(device=dev, dtype=torch.int32).contiguous()
+    qcode = torch.empty((B, Hq, Tq, C_), dtype=torch.int8, device=dev)
+    qscale = torch.empty((B, Hq, Tq), dtype=torch.float32, device=dev)
+    check(_native.lib().kvb_quantize_query_tokens(
+        query.data_ptr(), query.stride(0), query.stride(1), query.stride(2), channel_idx.data_ptr(),
+        qcode.data_ptr(), qscale.data_ptr(), B, Hq, Hkv, Tq, D, C_, _dev(query), _stream(dev)),
+        "kvb_quantize_query_tokens")
+    return qcode, qscale
+
+
+def score_prefill_blocks(qcode: torch.Tensor, qscale: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
+                         key_count: Optional[int] = None) -> torch.Tensor:
+    """Block scores fp32 ``[B,Hkv,Tq,ceil(Tk/64)]``: max over the GQA group and the 64 tokens of each
+    key block of the dequantised int8 x int4 partial score; every query sees all ``key_count`` keys."""
+    B, Hq, Tq, C_ = qcode.shape
+    Hkv = packed.shape[1]
+    _check_side_cache(packed, scale, C_)
+    Tk = packed.shape[2] if key_count is None else int(key_count)
+    dev = qcode.device
+    nblk = (Tk + PREFILL_BLOCK - 1) // PREFILL_BLOCK
+    out = torch.empty((B, Hkv, Tq, nblk), dtype=torch.float32, device=dev)
+    check(_native.lib().kvb_score_prefill_blocks(
+        qcode.contiguous().data_ptr(), qscale.contiguous().data_ptr(),
+        packed.data_ptr(), packed.stride(0), packed.stride(1),
+        scale.data_ptr(), scale.stride(0), scale.stride(1),
+        B, Hq, Hkv, Tq, Tk, C_, PREFILL_BLOCK, out.data_ptr(), _dev(qcode), _stream(dev)),
+        "kvb_score_prefill_blocks")
+    return out
+
+
+def block_topk(block_scores: torch.Tensor, k: int, return_scores: bool = False):
+    """The ``min(k, nblk)`` best blocks of every row ``[..., nblk]`` ordered by (score desc, block asc),
+    int32 ``[..., kk]``."""
+    lead, nblk = block_scores.shape[:-1], block_scores.shape[-1]
+    s2 = block_scores.reshape(-1, nblk)
+    if s2.stride(-1) != 1:
+        s2 = s2.contiguous()
+    R, kk = s2.shape[0], min(int(k), nblk)
+    dev = block_scores.device
+    idx = torch.empty((R, kk), dtype=torch.int32, device=dev)
+    val = torch.empty((R, kk), dtype=torch.float32, device=dev) if return_scores else None
+    check(_native.lib().kvb_block_topk(s2.data_ptr(), s2.stride(0), R, nblk, int(k), idx.data_ptr(), _ptr(val),
+                                       _dev(block_scores), _stream(dev)), "kvb_block_topk")
+    idx = idx.reshape(*lead, kk)
+    return (idx, val.reshape(*lead, kk)) if return_scores else idx
+
+
+def prefill_select_blocks(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
+                          key_count: int, top_blocks: int = 32):
+    """Query chunk ``[B,Hq,Tq,D]`` -> ``(block_idx int32 [B,Hkv,Tq,top_blocks], block_scores)``."""
+    qcode, qscale = quantize_query_tokens(query, channel_idx)
+    bs = score_prefill_blocks(qcode, qscale, packed, scale, key_count)
+    return block_topk(bs, top_blocks), bs
+
+
+# ------------------------------------------------------------------------------------------
 # fused decode step
 # ------------------------------------------------------------------------------------------
 

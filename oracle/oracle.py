@@ -172,6 +172,38 @@ def decode_step(query, key, value, channel_idx, top_k, *, protect_sink=0, protec
                 selected=sel, selected_scores=sel_scores, final_indices=fidx, final_valid=fvalid, out=out, m=m, l=l)
 
 
+def quantize_query_tokens(query: torch.Tensor, channel_idx: torch.Tensor):
+    """query bf16 [B,Hq,Tq,D] -> per-token qcode int8 [B,Hq,Tq,C], qscale fp32 [B,Hq,Tq]."""
+    B, Hq, Tq, D = query.shape
+    qc, qs = quantize_query(query.permute(0, 2, 1, 3).reshape(B * Tq, Hq, D), channel_idx)
+    C = qc.shape[-1]
+    return qc.view(B, Tq, Hq, C).permute(0, 2, 1, 3).contiguous(), qs.view(B, Tq, Hq).permute(0, 2, 1).contiguous()
+
+
+def prefill_block_scores(qcode: torch.Tensor, qscale: torch.Tensor, codes: torch.Tensor, kscale: torch.Tensor,
+                         block: int = 64):
+    """blk[b,g,i,j] = max over the G heads of g and the tokens of block j of
+    (float(acc) * kscale[b,g,t]) * qscale[b,h,i]; the last block may be short; -0 -> +0.
+    Every query sees every key (no causal term inside the chunk)."""
+    B, Hq, Tq, C = qcode.shape
+    Hkv, Tk = codes.shape[1], codes.shape[2]
+    G = Hq // Hkv
+    nblk = (Tk + block - 1) // block
+    out = torch.empty((B, Hkv, Tq, nblk), dtype=torch.float32)
+    cf = codes.to(torch.float64)
+    for b in range(B):
+        for g in range(Hkv):
+            qf = qcode[b, g * G:(g + 1) * G].to(torch.float64)                       # [G,Tq,C]
+            acc = torch.einsum("hic,tc->hit", qf, cf[b, g]).round().to(torch.float32)  # exact small integers
+            deq = (acc * kscale[b, g][None, None, :]) * qscale[b, g * G:(g + 1) * G][:, :, None]
+            gm = deq.amax(0)                                                          # [Tq,Tk]
+            pad = nblk * block - Tk
+            if pad:
+                gm = torch.cat((gm, torch.full((Tq, pad), float("-inf"))), dim=1)
+            out[b, g] = gm.view(Tq, nblk, block).amax(-1) + 0.0
+    return out
+
+
 def merge_shards(cand_scores: torch.Tensor, cand_idx: torch.Tensor, k: int):
     """Global top-k from per-shard candidate lists [N,R,kk] (scores, global ids): concatenated
     along the shard axis and selected with the same (score desc, id asc) rule."""

@@ -1,0 +1,53 @@
+"""Chunked-prefill block scoring: per-token query codes, block scores and selected block ids
+bit-exact against the oracle (parity unpinned by the reference, which has no prefill scorer)."""
+import pytest
+import torch
+
+from kv_cache_b200 import inputs, ops
+from oracle import oracle
+from tests.gpu_util import cpu
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(dev, B, Hq, Hkv, Tq, Tk, C, seed=3):
+    w = inputs.small_workload(batch=B, q_heads=Hq, kv_heads=Hkv, context=Tk, channels=C, seed=seed)
+    key, _ = inputs.make_kv(w, dev, 0, Tk)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q = inputs.rope(torch.randn(B, Hq, Tq, 128, generator=g, device=dev), torch.arange(Tk, Tk + Tq, device=dev))
+    return key, q.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Tq,Tk,C", [
+    (1, 8, 2, 128, 4096, 64),       # the full small case of the specification
+    (2, 4, 2, 150, 1000, 64),       # ragged query tile and a short last key block
+    (1, 2, 2, 16, 64, 32),          # G = 1, one block
+    (1, 16, 2, 40, 700, 32),        # G = 8
+    (1, 4, 2, 33, 2048 + 70, 128),  # C = 128, G = 2
+])
+def test_block_scores_and_topk_bit_exact(cuda_device, B, Hq, Hkv, Tq, Tk, C):
+    key, q = _case(cuda_device, B, Hq, Hkv, Tq, Tk, C)
+    ch = ops.choose_channels(key, C)
+    packed, scale = ops.quantize(key, ch)
+    qcode, qscale = ops.quantize_query_tokens(q, ch)
+    qcode_o, qscale_o = oracle.quantize_query_tokens(q.cpu(), ch.cpu())
+    assert torch.equal(qcode.cpu(), qcode_o) and torch.equal(qscale.cpu(), qscale_o)
+    bs = ops.score_prefill_blocks(qcode, qscale, packed, scale, Tk)
+    codes_o, _, kscale_o = oracle.quantize_pack(key.cpu(), ch.cpu())
+    want = oracle.prefill_block_scores(qcode_o, qscale_o, codes_o, kscale_o)
+    assert torch.equal(bs.cpu().view(torch.int32), want.view(torch.int32))
+    idx, val = ops.block_topk(bs, 32, return_scores=True)
+    want_i, want_v = oracle.select(want, 32)
+    assert torch.equal(idx.cpu().long(), want_i) and torch.equal(val.cpu(), want_v)
+    idx2, _ = ops.prefill_select_blocks(q, packed, scale, ch, Tk, 32)
+    assert torch.equal(idx2, idx)
+
+
+def test_block_topk_ties_and_short_rows(cuda_device):
+    s = torch.tensor([[1.0, 5.0, 5.0, -0.0, 0.0, 5.0]], device=cuda_device)
+    assert ops.block_topk(s, 4).tolist() == [[1, 2, 5, 0]]
+    assert ops.block_topk(s, 100).tolist() == [[1, 2, 5, 0, 3, 4]]
+    g = torch.Generator(device=cuda_device).manual_seed(1)
+    big = torch.randint(-3, 4, (70, 2048), generator=g, device=cuda_device).float()
+    want, _ = oracle.select(big.cpu(), 32)
+    assert torch.equal(ops.block_topk(big, 32).cpu().long(), want)
