@@ -75,6 +75,11 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
   return __uint_as_float(u);
 }
 
+// Unique 64-bit sort key of (score, index): larger composite <=> better score, then LOWER index.
+__device__ __forceinline__ uint64_t make_composite(float score, uint32_t idx) {
+  return ((uint64_t)float_to_key(score) << 32) | (uint64_t)(0xFFFFFFFFu - idx);
+}
+
 // ---- mbarrier + bulk async copy (TMA engine, 1-D, no tensor map, one destination CTA) ----------
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

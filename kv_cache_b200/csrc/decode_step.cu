@@ -5,12 +5,196 @@
 
 namespace kvb {
 
+// ---- fast path of the fused step ---------------------------------------------------------
+// The scorer can hand the selector its candidates directly (no group-max row in memory, no
+// histogram, no collect pass) if it knows, per row, a threshold tau with
+//     k  <=  #{t : gmax[t] >= tau}  <=  candidate capacity.
+// tau comes from a SAMPLE of the row: 32 evenly spaced runs of tokens (1/32 of the row, at most
+// 4096 tokens) are scored first and tau is set to the sample value whose rank predicts about
+// 1.75 k tokens above it in the whole row (rank ~ 112: the prediction is good to about +-10 %, so
+// both bounds hold by many standard deviations). The bounds are CHECKED, not assumed: a row whose
+// count misses them (heavy ties, adversarial layouts) is re-scored into the group-max workspace by
+// a rescue kernel and selected by the exact refinement path, so the result is always the exact
+// top-k.
+constexpr int FS_THREADS = 512;
+constexpr int FS_RUNS = 32;                    // evenly spaced runs of sampled tokens per row
+constexpr int FS_MAX_SAMPLE = 4096;            // sampled tokens per row (8 per thread, loaded four at a time)
+constexpr int FS_PER_THREAD = FS_MAX_SAMPLE / FS_THREADS;
+
+struct SampleParams {
+  ScoreParams sp;             // query / packed / scale / channels / shapes (outputs unused)
+  float* tau;                 // [R]
+  int kk;                     // min(k, T)
+  int cap;                    // candidate capacity per row
+  int run_len;                // tokens per run (multiple of FS_PER_THREAD), 0 => take every token (tau = -inf)
+  int rank;                   // rank (1-based, from the top) of the sample value that becomes tau
+};
+
+template <int C, int G>
+__global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q) {
+  __shared__ float s_qv[G * C];
+  __shared__ float s_qscale[SC_MAX_G];
+  __shared__ int8_t s_qcode[G * C];
+  __shared__ uint32_t s_hist[SEL_HIST_BINS];
+  __shared__ uint32_t s_tmp[80];
+  const ScoreParams& p = q.sp;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  if (q.run_len == 0) {                         // short rows: every token is a candidate
+    if (tid == 0) q.tau[row] = -INFINITY;
+    return;
+  }
+  const int b = row / p.Hkv, g = row - b * p.Hkv;
+  for (int i = tid; i < SEL_HIST_BINS; i += FS_THREADS) s_hist[i] = 0;
+  quantize_query_group<FS_THREADS>(p, b, g, G, s_qv, s_qcode, s_qscale);
+  // query words in shared memory (every thread reads the same word: a broadcast): word w of a token
+  // holds channels 8w + {0,2,4,6} in its low nibbles and 8w + {1,3,5,7} in its high nibbles
+  constexpr int W = C / 8;
+  __shared__ int s_qlo[G][W], s_qhi[G][W];
+  for (int i = tid; i < G * W; i += FS_THREADS) {
+    const int hd = i / W, w = i - hd * W;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= (uint32_t)(uint8_t)s_qcode[hd * C + 8 * w + 2 * j] << (8 * j);
+      hi |= (uint32_t)(uint8_t)s_qcode[hd * C + 8 * w + 2 * j + 1] << (8 * j);
+    }
+    s_qlo[hd][w] = (int)lo;
+    s_qhi[hd][w] = (int)hi;
+  }
+  __syncthreads();
+  // thread -> run (tid / threads_per_run), FS_PER_THREAD consecutive tokens inside the run
+  const int threads_per_run = q.run_len / FS_PER_THREAD;
+  const int run = tid / threads_per_run;
+  const int64_t t0 = (int64_t)run * (p.T / FS_RUNS) + (int64_t)(tid - run * threads_per_run) * FS_PER_THREAD;
+  const bool live = run < FS_RUNS;
+  const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)g * p.packed_sh;
+  const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)g * p.scale_sh;
+  float v[FS_PER_THREAD];
+#pragma unroll
+  for (int e0 = 0; e0 < FS_PER_THREAD; e0 += 4) {
+    // four tokens at a time: all their loads are issued before the first use
+    uint32_t wv[4][W];
+    float ks[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool ok = live && t0 + e0 + e < p.T;
+      const uint4* src = reinterpret_cast<const uint4*>(packed_row + (t0 + e0 + e) * (C / 2));
+#pragma unroll
+      for (int x = 0; x < C / 32; ++x) {
+        const uint4 u = ok ? __ldg(src + x) : make_uint4(0, 0, 0, 0);
+        wv[e][4 * x] = u.x; wv[e][4 * x + 1] = u.y; wv[e][4 * x + 2] = u.z; wv[e][4 * x + 3] = u.w;
+      }
+      ks[e] = ok ? scale_row[t0 + e0 + e] : 0.0f;
+    }
+    int acc[4][G];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+#pragma unroll
+      for (int hd = 0; hd < G; ++hd) acc[e][hd] = 0;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+#pragma unroll
+      for (int hd = 0; hd < G; ++hd) {
+        const int ql = s_qlo[hd][w], qh = s_qhi[hd][w];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[e][hd] = __dp4a((int)((wv[e][w] << 4) & 0xF0F0F0F0u), ql, acc[e][hd]);
+          acc[e][hd] = __dp4a((int)(wv[e][w] & 0xF0F0F0F0u), qh, acc[e][hd]);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int hd = 0; hd < G; ++hd) {
+        const float f = __int_as_float(acc[e][hd] + 0x4B400000) - 12582912.0f;     // 16 * dot, exact
+        m = fmaxf(m, __fmul_rn(__fmul_rn(f, ks[e]), s_qscale[hd] * 0.0625f));
+      }
+      if (m == 0.0f) m = 0.0f;
+      const bool ok = live && t0 + e0 + e < p.T;
+      v[e0 + e] = ok ? m : __int_as_float(0x7fc00000);
+      if (ok) atomicAdd(&s_hist[float_to_key(m) >> (32 - SEL_HIST_BITS)], 1u);
+    }
+  }
+  __syncthreads();
+  uint32_t bin, above, inb;
+  find_threshold<FS_THREADS>(s_hist, SEL_HIST_BINS, (uint32_t)q.rank, s_tmp, bin, above, inb);
+  // second level: 11 more key bits inside the bin
+  for (int i = tid; i < 2048; i += FS_THREADS) s_hist[i] = 0;
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < FS_PER_THREAD; ++e) {
+    if (v[e] == v[e]) {
+      const uint32_t key = float_to_key(v[e]);
+      if ((key >> (32 - SEL_HIST_BITS)) == bin) atomicAdd(&s_hist[(key >> 9) & 2047u], 1u);
+    }
+  }
+  __syncthreads();
+  uint32_t d, ab2, in2;
+  find_threshold<FS_THREADS>(s_hist, 2048, (uint32_t)q.rank - above, s_tmp, d, ab2, in2);
+  if (tid == 0) {
+    const uint32_t key_lo = (bin << (32 - SEL_HIST_BITS)) | (d << 9);
+    float t = key_to_float(key_lo);
+    if (key_lo <= 0x007FFFFFu || t != t) t = -INFINITY;       // NaN patterns: take everything
+    q.tau[row] = t;
+  }
+}
+
+template <int C>
+static void sample_launch_g(const SampleParams& q, int R, cudaStream_t st) {
+  switch (q.sp.G) {
+    case 1: score_sample_kernel<C, 1><<<R, FS_THREADS, 0, st>>>(q); break;
+    case 2: score_sample_kernel<C, 2><<<R, FS_THREADS, 0, st>>>(q); break;
+    case 4: score_sample_kernel<C, 4><<<R, FS_THREADS, 0, st>>>(q); break;
+    default: score_sample_kernel<C, 8><<<R, FS_THREADS, 0, st>>>(q); break;
+  }
+}
+
+// Rows whose candidate count missed [kk, cap] are scored again, whole, into the group-max
+// workspace and flagged; every other CTA leaves at once.
+struct RescueParams {
+  ScoreParams sp;             // gmax_out = workspace rows
+  const uint32_t* cand_count;
+  uint32_t* row_failed;
+  int kk, cap;
+};
+
+constexpr int RS_THREADS = 256;
+
+__global__ void __launch_bounds__(RS_THREADS) score_rescue_kernel(RescueParams q) {
+  __shared__ float s_qv[SC_MAX_G * SC_MAX_C];
+  __shared__ float s_qscale[SC_MAX_G];
+  __shared__ int8_t s_qcode[SC_MAX_G * SC_MAX_C];
+  const ScoreParams& p = q.sp;
+  const int row = blockIdx.x;
+  const uint32_t n = q.cand_count[(int64_t)row * SC_COUNT_STRIDE];
+  if (n >= (uint32_t)q.kk && n <= (uint32_t)q.cap) return;
+  const int b = row / p.Hkv, g = row - b * p.Hkv;
+  quantize_query_group<RS_THREADS>(p, b, g, p.G, s_qv, s_qcode, s_qscale);
+  ScoreParams pp = p;
+  pp.acc_out = nullptr; pp.deq_out = nullptr;
+  for (int64_t t = threadIdx.x; t < p.T; t += RS_THREADS)
+    p.gmax_out[(int64_t)row * p.T + t] = score_token_plain<SC_MAX_G>(pp, p.G, b, g, t, s_qcode, s_qscale);
+  if (threadIdx.x == 0) q.row_failed[row] = 1u;
+}
+
+// Candidate capacity of the fast path: room for ~1.75 k expected candidates plus a wide margin.
+static int fast_cap(int kk) {
+  int c = 8192;
+  while (c < 3 * kk && c < SEL_MAX_K) c <<= 1;
+  return c;
+}
+
 // Workspace of the fused step. The regions that must start at zero (attention split counters,
 // select candidate counters, histogram) are adjacent so ONE memset per step clears them.
 struct StepLayout {
   int R, kk, S;
   size_t off_attcnt, off_selws, off_attpart, off_gmax, off_sel;
   size_t zero_bytes, selws_bytes, bytes;
+  // fast path (scorer emits candidates): counters + failed flags are zeroed per step
+  size_t off_fcount, off_ffailed, off_ftau, off_fcand, fzero_bytes;
+  int fcap;
 };
 
 static StepLayout step_layout(int B, int Hq, int Hkv, int T, int k, int sink, int recent, int keep_self) {
@@ -28,6 +212,12 @@ static StepLayout step_layout(int B, int Hq, int Hkv, int T, int k, int sink, in
   L.off_attpart = off; off += ap.partial_bytes;
   L.off_gmax = off;    off += round_up(sizeof(float) * (size_t)L.R * (size_t)T, 256);
   L.off_sel = off;     off += round_up(sizeof(int32_t) * (size_t)L.R * (size_t)(L.kk > 0 ? L.kk : 1), 256);
+  L.fcap = fast_cap(L.kk > 0 ? L.kk : 1);
+  L.off_fcount = off;  off += round_up(sizeof(uint32_t) * (size_t)L.R * SC_COUNT_STRIDE, 256);
+  L.off_ffailed = off; off += round_up(sizeof(uint32_t) * (size_t)L.R, 256);
+  L.fzero_bytes = off - L.off_fcount;
+  L.off_ftau = off;    off += round_up(sizeof(float) * (size_t)L.R, 256);
+  L.off_fcand = off;   off += round_up(sizeof(uint64_t) * (size_t)L.R * L.fcap, 256);
   L.bytes = off;
   return L;
 }
@@ -65,19 +255,101 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
 
-  {
-    DeviceGuard guard(device);
-    if (!guard.ok) return KVB_BAD_DEVICE;
-    KVB_CHECK_CUDA(cudaMemsetAsync(ws + L.off_attcnt, 0, L.zero_bytes, st));
+  // Fast path: sample -> tau, scorer emits candidates, rescue check, exact finish. Needs the
+  // streaming scorer, a row longer than the candidate capacity but short enough for the 4096-token
+  // sample to be a 1/32 fraction, and k small enough for the capacity.
+  const int G = p->Hq / p->Hkv;
+  const int fcap = L.fcap;
+  const bool stream_ok = score_stream_supported(p->C, G, p->packed, p->packed_sb, p->packed_sh, p->scale,
+                                                p->scale_sb, p->scale_sh);
+  // sample geometry: 32 runs of run_len tokens, 4096 tokens in all when the row is long enough
+  int run_len = (T / FS_RUNS) / FS_PER_THREAD * FS_PER_THREAD;
+  if (run_len > FS_MAX_SAMPLE / FS_RUNS) run_len = FS_MAX_SAMPLE / FS_RUNS;
+  const double frac = run_len > 0 ? (double)(run_len * FS_RUNS) / (double)T : 0.0;
+  double expect = 1.75 * L.kk;                              // candidates aimed at
+  if (frac > 0.0 && expect * frac < 96.0) expect = 96.0 / frac;   // keep the rank statistically stable
+  const bool all_candidates = T <= fcap;                    // short rows: tau = -inf, every token is a candidate
+  const bool fast = stream_ok && 3 * L.kk <= fcap &&
+                    (all_candidates || (run_len >= FS_PER_THREAD && 1.7 * expect <= (double)fcap));
+  if (fast) {
+    {
+      DeviceGuard guard(device);
+      if (!guard.ok) return KVB_BAD_DEVICE;
+      KVB_CHECK_CUDA(cudaMemsetAsync(ws + L.off_fcount, 0, L.fzero_bytes, st));
+      uint32_t* fcount = reinterpret_cast<uint32_t*>(ws + L.off_fcount);
+      uint32_t* ffailed = reinterpret_cast<uint32_t*>(ws + L.off_ffailed);
+      float* ftau = reinterpret_cast<float*>(ws + L.off_ftau);
+      uint64_t* fcand = reinterpret_cast<uint64_t*>(ws + L.off_fcand);
+
+      SampleParams sq;
+      sq.sp.query = reinterpret_cast<const __nv_bfloat16*>(p->query); sq.sp.q_sb = p->q_sb; sq.sp.q_sh = p->q_sh;
+      sq.sp.packed = p->packed; sq.sp.packed_sb = p->packed_sb; sq.sp.packed_sh = p->packed_sh;
+      sq.sp.scale = p->scale; sq.sp.scale_sb = p->scale_sb; sq.sp.scale_sh = p->scale_sh;
+      sq.sp.channel_idx = p->channel_idx;
+      sq.sp.B = p->B; sq.sp.Hq = p->Hq; sq.sp.Hkv = p->Hkv; sq.sp.T = T; sq.sp.D = p->D; sq.sp.C = p->C; sq.sp.G = G;
+      sq.sp.gmax_out = nullptr; sq.sp.acc_out = nullptr; sq.sp.deq_out = nullptr; sq.sp.hist_out = nullptr;
+      sq.sp.tau = nullptr; sq.sp.cand = nullptr; sq.sp.cand_count = nullptr; sq.sp.cand_cap = 0;
+      sq.sp.units_per_row = 0; sq.sp.full_tiles = 0; sq.sp.total_units = 0;
+      sq.tau = ftau; sq.kk = L.kk; sq.cap = fcap;
+      sq.run_len = all_candidates ? 0 : run_len;
+      int rank = (int)(expect * frac + 0.999);
+      if (rank < 1) rank = 1;
+      if (rank > run_len * FS_RUNS) rank = run_len * FS_RUNS;
+      sq.rank = rank;
+      if (p->C == 32) sample_launch_g<32>(sq, L.R, st);
+      else if (p->C == 64) sample_launch_g<64>(sq, L.R, st);
+      else sample_launch_g<128>(sq, L.R, st);
+      KVB_CHECK_CUDA(cudaGetLastError());
+
+      ScoreEmit emit{ftau, fcand, fcount, fcap};
+      rc = score_run(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
+                     p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, nullptr, nullptr, nullptr,
+                     nullptr, &emit, device, st);
+      if (rc != KVB_OK) return rc;
+
+      RescueParams rq;
+      rq.sp = sq.sp;
+      rq.sp.gmax_out = gmax;
+      rq.cand_count = fcount; rq.row_failed = ffailed; rq.kk = L.kk; rq.cap = fcap;
+      score_rescue_kernel<<<L.R, RS_THREADS, 0, st>>>(rq);
+      KVB_CHECK_CUDA(cudaGetLastError());
+
+      SelectParams sp;
+      sp.scores = gmax; sp.row_stride = T; sp.payload = nullptr;
+      sp.R = L.R; sp.T = T; sp.k = p->top_k; sp.kk = L.kk; sp.idx_offset = 0;
+      sp.out_idx32 = sel; sp.out_idx64 = nullptr; sp.out_scores = nullptr;
+      sp.hist = nullptr; sp.cand = fcand; sp.cand_count = fcount; sp.cap = fcap;
+      sp.tokens_per_cta = 0; sp.thresholds = nullptr;
+      sp.order_by_index = 1;
+      sp.from_candidates = 1; sp.row_failed = ffailed;
+      const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
+      size_t smem = (size_t)fcap * 8 + SEL_FINAL_FIXED_SMEM;
+      sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
+      if (sp.use_bitmap) smem += bitmap_bytes;
+      static bool attr_done[64] = {false};
+      if (device < 64 && !attr_done[device]) {
+        KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)SEL_SMEM_LIMIT));
+        attr_done[device] = true;
+      }
+      select_final_kernel<<<L.R, SEL_FINAL_THREADS, smem, st>>>(sp);
+      KVB_CHECK_CUDA(cudaGetLastError());
+    }
+  } else {
+    {
+      DeviceGuard guard(device);
+      if (!guard.ok) return KVB_BAD_DEVICE;
+      KVB_CHECK_CUDA(cudaMemsetAsync(ws + L.off_attcnt, 0, L.zero_bytes, st));
+    }
+    rc = kvb_score_decode(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
+                          p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, gmax, nullptr, nullptr,
+                          sw.hist, device, stream);
+    if (rc != KVB_OK) return rc;
+    // ascending-index order: the set is what matters to the attention, and it is the cheapest to emit
+    rc = select_run(gmax, T, nullptr, L.R, T, p->top_k, 0, /*order=*/1, sel, nullptr, nullptr, nullptr,
+                    /*hist_in_workspace=*/true, /*zeroed=*/true, selws, L.selws_bytes, device, st);
+    if (rc != KVB_OK) return rc;
   }
-  rc = kvb_score_decode(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
-                        p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, gmax, nullptr, nullptr,
-                        sw.hist, device, stream);
-  if (rc != KVB_OK) return rc;
-  // ascending-index order: the set is what matters to the attention, and it is the cheapest to emit
-  rc = select_run(gmax, T, nullptr, L.R, T, p->top_k, 0, /*order=*/1, sel, nullptr, nullptr, nullptr,
-                  /*hist_in_workspace=*/true, /*zeroed=*/true, selws, L.selws_bytes, device, st);
-  if (rc != KVB_OK) return rc;
   // The attention kernel reads the list  selected || sink || recent || self  implicitly (no list is
   // materialised) and its chunk-0 warps append the decoded token's K row to the int4 cache.
   const FinalLayout f = final_layout(L.kk, T, p->protect_sink, p->protect_recent, p->keep_self);

@@ -17,6 +17,10 @@ constexpr int SC_HIST_BITS = 12;
 constexpr int SC_HIST_BINS = 1 << SC_HIST_BITS;
 constexpr int SC_MAX_C = 128;
 constexpr int SC_MAX_G = 16;
+constexpr int SC_COUNT_STRIDE = 32;              // words between per-row counters (one 128-byte line each)
+constexpr int SC_EMIT_WARP_BUF = 512;            // composites a warp buffers per row segment before one global reservation
+constexpr int SC_EMIT_BUF = 8 * SC_EMIT_WARP_BUF; // per CTA (8 warps)
+enum { SC_MODE_PLAIN = 0, SC_MODE_HIST = 1, SC_MODE_EMIT = 2 };
 
 struct ScoreParams {
   const __nv_bfloat16* query;
@@ -31,6 +35,12 @@ struct ScoreParams {
   int32_t* acc_out;
   float* deq_out;
   uint32_t* hist_out;
+  // candidate emission (fused decode step): tokens whose group max reaches tau[row] are appended
+  // to cand[row] as composites; cand_count[row * SC_COUNT_STRIDE] counts them (may exceed cand_cap)
+  const float* tau;
+  uint64_t* cand;
+  uint32_t* cand_count;
+  int cand_cap;
   int units_per_row;     // full tiles per row + 1 if the row has a ragged tail
   int full_tiles;        // T / tile tokens
   int64_t total_units;   // rows * units_per_row
@@ -68,10 +78,10 @@ __device__ __forceinline__ void quantize_query_group(const ScoreParams& p, int b
 }
 
 // One token scored the plain way (byte loads): the ragged tail of a row and the generic kernel.
+// Returns the group maximum (with -0 folded into +0); writes acc/deq when asked.
 template <int GMAX>
-__device__ __forceinline__ void score_token_plain(const ScoreParams& p, int G, int row, int b, int g, int64_t t,
-                                                  const int8_t* s_qcode, const float* s_qscale,
-                                                  uint32_t* s_hist /* or nullptr */) {
+__device__ __forceinline__ float score_token_plain(const ScoreParams& p, int G, int b, int g, int64_t t,
+                                                   const int8_t* s_qcode, const float* s_qscale) {
   const int C = p.C;
   const uint8_t* src = p.packed + (int64_t)b * p.packed_sb + (int64_t)g * p.packed_sh + t * (C >> 1);
   int acc[GMAX];
@@ -99,8 +109,7 @@ __device__ __forceinline__ void score_token_plain(const ScoreParams& p, int G, i
     }
   }
   if (best == 0.0f) best = 0.0f;   // -0 -> +0
-  if (p.gmax_out) p.gmax_out[(int64_t)row * p.T + t] = best;
-  if (s_hist) atomicAdd(&s_hist[float_to_key(best) >> (32 - SC_HIST_BITS)], 1u);
+  return best;
 }
 
 // int8 tensor-core tile: D[16x8] (int32) += A[16x32] (int8, row) * B[32x8] (int8, col).
@@ -138,8 +147,10 @@ struct ScoreCfg {
   static constexpr int STAGE_BYTES = PACKED_BYTES + TW * 4;
 };
 
-template <int C, int G, int NS, bool HIST>
+template <int C, int G, int NS, int MODE>
 __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_stream_kernel(ScoreParams p) {
+  constexpr bool HIST = MODE == SC_MODE_HIST;
+  constexpr bool EMIT = MODE == SC_MODE_EMIT;
   using Cfg = ScoreCfg<C, G>;
   constexpr int KS = Cfg::KS, TPA = Cfg::TPA, TW = Cfg::TW, IT = Cfg::IT;
   constexpr int WARPS = Cfg::WARPS, THREADS = Cfg::THREADS;
@@ -152,7 +163,8 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
   float* s_qv = reinterpret_cast<float*>(s_bar + WARPS * NS);
   float* s_qscale = s_qv + G * C;
   int8_t* s_qcode = reinterpret_cast<int8_t*>(s_qscale + SC_MAX_G);
-  uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_qcode + G * C);   // G*C is a multiple of 32
+  uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_qcode + G * C);   // G*C is a multiple of 32 (HIST)
+  uint64_t* s_cbuf = reinterpret_cast<uint64_t*>(s_qcode + G * C);   // same place, EMIT: [warps][SC_EMIT_WARP_BUF]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -227,6 +239,37 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
     const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)kvh * p.packed_sh;
     const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)kvh * p.scale_sh;
     float* gmax_row = p.gmax_out ? p.gmax_out + (int64_t)row * p.T : nullptr;
+    const float tau = EMIT ? p.tau[row] : 0.0f;
+    uint64_t* cand_row = EMIT ? p.cand + (int64_t)row * p.cand_cap : nullptr;
+    uint32_t* count_row = EMIT ? p.cand_count + (int64_t)row * SC_COUNT_STRIDE : nullptr;
+
+    // What happens to a finished token: group max m (already +0-normalised) of token t of this row.
+    // Called by ALL lanes of the warp together; `active` says whether this lane really has a token.
+    // Candidate emission keeps a warp-private buffer whose fill count lives in a register (the
+    // ballot gives every taker its slot), so the hot loop has no atomics at all.
+    uint64_t* wbuf = s_cbuf + warp * SC_EMIT_WARP_BUF;
+    uint32_t wcount = 0;
+    auto finish = [&](float m, int64_t t, bool active) {
+      if (gmax_row && active) st_global_hint_f32(gmax_row + t, m, keep);
+      if (HIST && active) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
+      if (EMIT) {
+        const bool take = active && (m >= tau);
+        const uint32_t mask = __ballot_sync(0xffffffffu, take);
+        if (mask) {
+          if (take) {
+            const uint64_t c = make_composite(m, (uint32_t)t);
+            const uint32_t pos = wcount + (uint32_t)__popc(mask & ((1u << lane) - 1u));
+            if (pos < (uint32_t)SC_EMIT_WARP_BUF) {
+              wbuf[pos] = c;
+            } else {                                           // buffer full: straight to the row's list
+              const uint32_t gp = atomicAdd(count_row, 1u);
+              if (gp < (uint32_t)p.cand_cap) cand_row[gp] = c;
+            }
+          }
+          wcount += (uint32_t)__popc(mask);
+        }
+      }
+    };
 
     // Full tiles of this segment: [ta, tb); warp w takes ta + w, ta + w + WARPS, ...
     const int ta = ua;
@@ -324,11 +367,8 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
               // the lane alone holds both heads of its two tokens
               if (m0 == 0.0f) m0 = 0.0f;
               if (m1 == 0.0f) m1 = 0.0f;
-              if (gmax_row) { st_global_hint_f32(gmax_row + t0 + tl[0], m0, keep); st_global_hint_f32(gmax_row + t0 + tl[2], m1, keep); }
-              if (HIST) {
-                atomicAdd(&s_hist[float_to_key(m0) >> (32 - SC_HIST_BITS)], 1u);
-                atomicAdd(&s_hist[float_to_key(m1) >> (32 - SC_HIST_BITS)], 1u);
-              }
+              finish(m0, t0 + tl[0], true);
+              finish(m1, t0 + tl[2], true);
             } else {
               // G == 4: lanes (t4, t4^1) share two tokens -> even lane finishes row g, odd lane row g+8.
               // G == 8: the quad shares two tokens -> lane t4 == 0 finishes row g, t4 == 1 row g+8.
@@ -337,10 +377,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
               const int tok = second ? tl[2] : tl[0];
               const bool writer = (G == 4) ? true : (t4 < 2);
               if (m == 0.0f) m = 0.0f;
-              if (writer) {
-                if (gmax_row) st_global_hint_f32(gmax_row + t0 + tok, m, keep);
-                if (HIST) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
-              }
+              finish(m, t0 + tok, writer);
             }
           } else {
             // G == 1: four tokens per lane, no reduction
@@ -348,8 +385,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
             for (int v = 0; v < 4; ++v) {
               float m = d[v];
               if (m == 0.0f) m = 0.0f;
-              if (gmax_row) st_global_hint_f32(gmax_row + t0 + tl[v], m, keep);
-              if (HIST) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
+              finish(m, t0 + tl[v], true);
             }
           }
         }
@@ -366,10 +402,24 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
     // Ragged tail of the row (fewer than TW tokens), owned by the segment that holds the tail unit.
     if (ub > p.full_tiles) {
       const int64_t tail0 = (int64_t)p.full_tiles * TW;
-      for (int64_t t = tail0 + tid; t < p.T; t += THREADS)
-        score_token_plain<G>(p, G, row, b, kvh, t, s_qcode, s_qscale, HIST ? s_hist : nullptr);
+      for (int64_t tb = tail0 + warp * 32; tb < p.T; tb += THREADS) {      // warp-uniform trips (ballot in finish)
+        const int64_t t = tb + lane;
+        const bool live = t < p.T;
+        const float m = live ? score_token_plain<G>(p, G, b, kvh, t, s_qcode, s_qscale) : 0.0f;
+        finish(m, t, live);
+      }
     }
-
+    if (EMIT) {
+      // hand the warp's buffered candidates of this row over with ONE reservation
+      __syncwarp();
+      const uint32_t n = wcount < (uint32_t)SC_EMIT_WARP_BUF ? wcount : (uint32_t)SC_EMIT_WARP_BUF;
+      uint32_t base = 0;
+      if (lane == 0 && n) base = atomicAdd(count_row, n);
+      base = __shfl_sync(0xffffffffu, base, 0);
+      for (uint32_t i = lane; i < n; i += 32)
+        if (base + i < (uint32_t)p.cand_cap) cand_row[base + i] = wbuf[i];
+      __syncwarp();
+    }
     if (HIST) {
       __syncthreads();
       uint32_t* gh = p.hist_out + (int64_t)row * SC_HIST_BINS;
@@ -398,8 +448,11 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_generic_kernel(ScoreP
     for (int i = threadIdx.x; i < SC_HIST_BINS; i += SC_THREADS) s_hist[i] = 0;
   }
   quantize_query_group<SC_THREADS>(p, b, g, p.G, s_qv, s_qcode, s_qscale);
-  for (int64_t t = (int64_t)blockIdx.x * SC_THREADS + threadIdx.x; t < p.T; t += (int64_t)gridDim.x * SC_THREADS)
-    score_token_plain<SC_MAX_G>(p, p.G, row, b, g, t, s_qcode, s_qscale, hist ? s_hist : nullptr);
+  for (int64_t t = (int64_t)blockIdx.x * SC_THREADS + threadIdx.x; t < p.T; t += (int64_t)gridDim.x * SC_THREADS) {
+    const float m = score_token_plain<SC_MAX_G>(p, p.G, b, g, t, s_qcode, s_qscale);
+    if (p.gmax_out) p.gmax_out[(int64_t)row * p.T + t] = m;
+    if (hist) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
+  }
   if (hist) {
     __syncthreads();
     uint32_t* gh = p.hist_out + (int64_t)row * SC_HIST_BINS;
@@ -410,24 +463,25 @@ __global__ void __launch_bounds__(SC_THREADS) score_decode_generic_kernel(ScoreP
   }
 }
 
-template <int C, int G, int NS, bool HIST>
+template <int C, int G, int NS, int MODE>
 static size_t score_stream_smem_bytes() {
   using Cfg = ScoreCfg<C, G>;
   size_t s = (size_t)Cfg::WARPS * NS * Cfg::STAGE_BYTES + sizeof(uint64_t) * Cfg::WARPS * NS +
              sizeof(float) * G * C + sizeof(float) * SC_MAX_G + (size_t)G * C;
-  if (HIST) s += sizeof(uint32_t) * SC_HIST_BINS;
+  if (MODE == SC_MODE_HIST) s += sizeof(uint32_t) * SC_HIST_BINS;
+  if (MODE == SC_MODE_EMIT) s += sizeof(uint64_t) * SC_EMIT_BUF;
   return s;
 }
 
-template <int C, int G, int NS, bool HIST>
+template <int C, int G, int NS, int MODE>
 static int score_stream_launch(const ScoreParams& p0, int device, cudaStream_t st) {
   using Cfg = ScoreCfg<C, G>;
   ScoreParams p = p0;
   p.full_tiles = p.T / Cfg::TW;
   p.units_per_row = p.full_tiles + ((p.T % Cfg::TW) ? 1 : 0);
   p.total_units = (int64_t)p.B * p.Hkv * p.units_per_row;
-  const size_t smem = score_stream_smem_bytes<C, G, NS, HIST>();
-  auto kern = score_decode_stream_kernel<C, G, NS, HIST>;
+  const size_t smem = score_stream_smem_bytes<C, G, NS, MODE>();
+  auto kern = score_decode_stream_kernel<C, G, NS, MODE>;
   static bool attr_done[64] = {false};
   if (device < 64 && !attr_done[device]) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -453,28 +507,43 @@ constexpr int score_stages() {
   return budget / per_stage >= 4 ? 4 : (budget / per_stage >= 2 ? budget / per_stage : 2);
 }
 
-template <int C, bool HIST>
+template <int C, int MODE>
 static int score_stream_dispatch_g(const ScoreParams& p, int device, cudaStream_t st) {
   switch (p.G) {
-    case 1: return score_stream_launch<C, 1, score_stages<C, 1>(), HIST>(p, device, st);
-    case 2: return score_stream_launch<C, 2, score_stages<C, 2>(), HIST>(p, device, st);
-    case 4: return score_stream_launch<C, 4, score_stages<C, 4>(), HIST>(p, device, st);
-    case 8: return score_stream_launch<C, 8, score_stages<C, 8>(), HIST>(p, device, st);
+    case 1: return score_stream_launch<C, 1, score_stages<C, 1>(), MODE>(p, device, st);
+    case 2: return score_stream_launch<C, 2, score_stages<C, 2>(), MODE>(p, device, st);
+    case 4: return score_stream_launch<C, 4, score_stages<C, 4>(), MODE>(p, device, st);
+    case 8: return score_stream_launch<C, 8, score_stages<C, 8>(), MODE>(p, device, st);
     default: return -1;
   }
 }
 
-}  // namespace kvb
+struct ScoreEmit {
+  const float* tau;        // [B*Hkv] emission thresholds
+  uint64_t* cand;          // [B*Hkv, cand_cap]
+  uint32_t* cand_count;    // [B*Hkv * SC_COUNT_STRIDE], zeroed by the caller
+  int cand_cap;
+};
 
-extern "C" __attribute__((visibility("default"))) int kvb_score_decode(const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed,
-                                int64_t packed_sb, int64_t packed_sh, const float* scale, int64_t scale_sb,
-                                int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T, int D,
-                                int C, float* gmax_out, int32_t* acc_out, float* deq_out, uint32_t* hist_out,
-                                int device, void* stream) {
-  using namespace kvb;
+// The streaming kernel's preconditions (everything else takes the generic kernel).
+static bool score_stream_supported(int C, int G, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                                   const float* scale, int64_t scale_sb, int64_t scale_sh) {
+  return (C == 32 || C == 64 || C == 128) && (G == 1 || G == 2 || G == 4 || G == 8) && aligned_to(packed, 16) &&
+         (packed_sb % 16) == 0 && (packed_sh % 16) == 0 && aligned_to(scale, 16) && (scale_sb % 4) == 0 &&
+         (scale_sh % 4) == 0;
+}
+
+// Shared by kvb_score_decode and the fused step. With `emit` the kernel appends candidates instead
+// of (or besides) writing gmax; that mode exists only in the streaming kernel.
+static int score_run(const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb,
+                     int64_t packed_sh, const float* scale, int64_t scale_sb, int64_t scale_sh,
+                     const int32_t* channel_idx, int B, int Hq, int Hkv, int T, int D, int C, float* gmax_out,
+                     int32_t* acc_out, float* deq_out, uint32_t* hist_out, const ScoreEmit* emit, int device,
+                     cudaStream_t st) {
   if (!query || !packed || !scale || !channel_idx) return KVB_BAD_ARG;
-  if (!gmax_out && !acc_out && !deq_out) return KVB_BAD_ARG;
+  if (!gmax_out && !acc_out && !deq_out && !emit) return KVB_BAD_ARG;
   if (hist_out && !gmax_out) return KVB_BAD_ARG;
+  if (emit && hist_out) return KVB_BAD_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || T < 0 || D <= 0) return KVB_BAD_SHAPE;
   if (Hq % Hkv) return KVB_BAD_SHAPE;
   const int G = Hq / Hkv;
@@ -484,7 +553,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_score_decode(const voi
   if (T == 0) return KVB_OK;
   DeviceGuard guard(device);
   if (!guard.ok) return KVB_BAD_DEVICE;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
   ScoreParams p;
   p.query = reinterpret_cast<const __nv_bfloat16*>(query);
@@ -494,24 +562,30 @@ extern "C" __attribute__((visibility("default"))) int kvb_score_decode(const voi
   p.channel_idx = channel_idx;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.T = T; p.D = D; p.C = C; p.G = G;
   p.gmax_out = gmax_out; p.acc_out = acc_out; p.deq_out = deq_out; p.hist_out = hist_out;
+  p.tau = emit ? emit->tau : nullptr;
+  p.cand = emit ? emit->cand : nullptr;
+  p.cand_count = emit ? emit->cand_count : nullptr;
+  p.cand_cap = emit ? emit->cand_cap : 0;
   p.units_per_row = 0; p.full_tiles = 0; p.total_units = 0;
 
-  const bool stream_ok = (C == 32 || C == 64 || C == 128) && (G == 1 || G == 2 || G == 4 || G == 8) &&
-                         aligned_to(packed, 16) && (packed_sb % 16) == 0 && (packed_sh % 16) == 0 &&
-                         aligned_to(scale, 16) && (scale_sb % 4) == 0 && (scale_sh % 4) == 0;
-  if (stream_ok) {
+  if (score_stream_supported(C, G, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh)) {
     int rc = -1;
-    if (hist_out) {
-      if (C == 32) rc = score_stream_dispatch_g<32, true>(p, device, st);
-      else if (C == 64) rc = score_stream_dispatch_g<64, true>(p, device, st);
-      else rc = score_stream_dispatch_g<128, true>(p, device, st);
+    if (emit) {
+      if (C == 32) rc = score_stream_dispatch_g<32, SC_MODE_EMIT>(p, device, st);
+      else if (C == 64) rc = score_stream_dispatch_g<64, SC_MODE_EMIT>(p, device, st);
+      else rc = score_stream_dispatch_g<128, SC_MODE_EMIT>(p, device, st);
+    } else if (hist_out) {
+      if (C == 32) rc = score_stream_dispatch_g<32, SC_MODE_HIST>(p, device, st);
+      else if (C == 64) rc = score_stream_dispatch_g<64, SC_MODE_HIST>(p, device, st);
+      else rc = score_stream_dispatch_g<128, SC_MODE_HIST>(p, device, st);
     } else {
-      if (C == 32) rc = score_stream_dispatch_g<32, false>(p, device, st);
-      else if (C == 64) rc = score_stream_dispatch_g<64, false>(p, device, st);
-      else rc = score_stream_dispatch_g<128, false>(p, device, st);
+      if (C == 32) rc = score_stream_dispatch_g<32, SC_MODE_PLAIN>(p, device, st);
+      else if (C == 64) rc = score_stream_dispatch_g<64, SC_MODE_PLAIN>(p, device, st);
+      else rc = score_stream_dispatch_g<128, SC_MODE_PLAIN>(p, device, st);
     }
     if (rc >= 0) return rc;
   }
+  if (emit) return KVB_BAD_SHAPE;     // callers check score_stream_supported() first
   int gx = ceil_div(T, SC_THREADS);
   const int cap = ceil_div(sm_count(device) * 16, B * Hkv);
   if (gx > cap) gx = cap < 1 ? 1 : cap;
@@ -519,4 +593,15 @@ extern "C" __attribute__((visibility("default"))) int kvb_score_decode(const voi
   score_decode_generic_kernel<<<grid, SC_THREADS, 0, st>>>(p);
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
+}
+
+}  // namespace kvb
+
+extern "C" __attribute__((visibility("default"))) int kvb_score_decode(
+    const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
+    int D, int C, float* gmax_out, int32_t* acc_out, float* deq_out, uint32_t* hist_out, int device, void* stream) {
+  return kvb::score_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq,
+                        Hkv, T, D, C, gmax_out, acc_out, deq_out, hist_out, nullptr, device,
+                        reinterpret_cast<cudaStream_t>(stream));
 }

@@ -43,11 +43,9 @@ struct SelectParams {
   uint4* thresholds;          // [R] (bin, above, in-bin, unused)
   int order_by_index;         // 0: (score desc, index asc); 1: ascending index
   int use_bitmap;             // order_by_index served by the shared-memory bitmap
+  int from_candidates;        // the candidate lists were filled by the scorer: no histogram / thresholds
+  const uint32_t* row_failed; // [R] with from_candidates: rows whose list is unusable; `scores` holds their full row
 };
-
-__device__ __forceinline__ uint64_t make_composite(float score, uint32_t idx) {
-  return ((uint64_t)float_to_key(score) << 32) | (uint64_t)(0xFFFFFFFFu - idx);
-}
 
 __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row, int64_t t) {
   return p.payload ? (uint32_t)p.payload[(int64_t)row * p.row_stride + t] : (uint32_t)(t + p.idx_offset);
@@ -178,11 +176,11 @@ constexpr int SEL_TOK_PER_CTA = SEL_TOK_PER_THREAD * SEL_SCAN_THREADS;   // 4096
 template <bool VEC>
 __global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(SelectParams p) {
   __shared__ uint2 s_queue[SEL_SCAN_THREADS / 32][SEL_TOK_PER_WARP];
+  __shared__ uint32_t s_wtotal[SEL_SCAN_THREADS / 32 + 1];
   const int row = blockIdx.y;
   const float* src = p.scores + (int64_t)row * p.row_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t0 = blockIdx.x * SEL_TOK_PER_CTA + warp * SEL_TOK_PER_WARP;     // T < 2^31
-  if (t0 >= p.T) return;
+  const int t0 = blockIdx.x * SEL_TOK_PER_CTA + warp * SEL_TOK_PER_WARP;     // T < 2^31; may lie past the row end
 
   float v[SEL_TOK_PER_THREAD];
   const float qnan = __int_as_float(0x7fc00000);           // padding compares false against anything
@@ -202,7 +200,7 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(Sel
   }
   // the row's threshold is read after the element loads were issued, so both latencies overlap
   const uint4 thr = __ldcg(p.thresholds + row);
-  if (thr.y + thr.z > (uint32_t)p.cap) return;             // this row is refined by the final kernel instead
+  if (thr.y + thr.z > (uint32_t)p.cap) return;             // (CTA-uniform) this row is refined by the final kernel instead
   // key(v) >= bin << 20  <=>  v >= the float whose key is bin << 20 (keys are order preserving;
   // bins that only NaN patterns can reach are clamped to -inf / "nothing").
   const uint32_t key_lo = thr.x << (32 - SEL_HIST_BITS);
@@ -220,9 +218,9 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(Sel
     if (lane >= off) incl += n;
   }
   const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-  if (total == 0) return;
-  uint32_t base = 0;
-  if (lane == 0) base = atomicAdd(p.cand_count + (int64_t)row * SEL_COUNT_STRIDE, total);
+  // One global atomic per CTA (same-address atomics of a row queue up in L2): warp totals meet in
+  // shared memory, thread 0 reserves the CTA's range, every warp takes its slice.
+  if (lane == 0) s_wtotal[warp] = total;
   uint2* q = s_queue[warp];
   uint32_t qpos = incl - cnt;
 #pragma unroll
@@ -232,8 +230,20 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(Sel
       ++qpos;
     }
   }
-  base = __shfl_sync(0xffffffffu, base, 0);
-  __syncwarp();                                            // queue writes visible to the whole warp
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t sum = 0;
+#pragma unroll
+    for (int w = 0; w < SEL_SCAN_THREADS / 32; ++w) {
+      const uint32_t c = s_wtotal[w];
+      s_wtotal[w] = sum;
+      sum += c;
+    }
+    s_wtotal[SEL_SCAN_THREADS / 32] = sum ? atomicAdd(p.cand_count + (int64_t)row * SEL_COUNT_STRIDE, sum) : 0u;
+  }
+  __syncthreads();
+  if (total == 0) return;
+  const uint32_t base = s_wtotal[SEL_SCAN_THREADS / 32] + s_wtotal[warp];
   uint64_t* cand = p.cand + (int64_t)row * p.cap;
   for (uint32_t i = lane; i < total; i += 32) {
     const uint2 e = q[i];
@@ -272,21 +282,39 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   const int tid = threadIdx.x;
   const float* src = p.scores + (int64_t)row * p.row_stride;
 
-  const uint4 thr = p.thresholds[row];
-  uint64_t prefix = thr.x;                              // top `fixed` bits of the k-th composite so far
-  int fixed = SEL_HIST_BITS;
-  uint32_t need = (uint32_t)p.kk - thr.y;               // still to take from inside the prefix
-  uint32_t in_prefix = thr.z;
-  int n;                                                // candidates in s_cand: all with composite >= prefix
-  if (thr.y + thr.z <= (uint32_t)p.cap) {
-    n = (int)(thr.y + thr.z);
-    const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
-    if ((uint32_t)n > have) n = (int)have;              // cannot happen; keeps reads in bounds
+  uint64_t prefix;                                      // top `fixed` bits of the k-th composite so far
+  int fixed;
+  uint32_t need;                                        // still to take from inside the prefix
+  uint32_t in_prefix;
+  int n = 0;                                            // candidates in s_cand: all with composite >= prefix
+  bool have_candidates;
+  if (p.from_candidates) {
+    prefix = 0; fixed = 0; need = (uint32_t)p.kk;
+    const bool failed = p.row_failed != nullptr && p.row_failed[row] != 0;
+    have_candidates = !failed;
+    if (failed) {
+      in_prefix = (uint32_t)p.T;
+    } else {
+      const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
+      n = (int)(have < (uint32_t)p.cap ? have : (uint32_t)p.cap);
+      in_prefix = (uint32_t)n;
+    }
+  } else {
+    const uint4 thr = p.thresholds[row];
+    prefix = thr.x; fixed = SEL_HIST_BITS; need = (uint32_t)p.kk - thr.y; in_prefix = thr.z;
+    have_candidates = thr.y + thr.z <= (uint32_t)p.cap;
+    if (have_candidates) {
+      n = (int)(thr.y + thr.z);
+      const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
+      if ((uint32_t)n > have) n = (int)have;            // cannot happen; keeps reads in bounds
+    }
+  }
+  if (have_candidates) {
     const uint64_t* cand = p.cand + (int64_t)row * p.cap;
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
     __syncthreads();
   } else {
-    // Too many candidates share the threshold bin: refine over the row itself until they fit.
+    // Too many candidates share the prefix (or none were prepared): refine over the row itself.
     while ((uint32_t)p.kk - need + in_prefix > (uint32_t)p.cap && fixed < 64) {
       const int width = (64 - fixed) >= 11 ? 11 : (64 - fixed);
       const int shift = 64 - fixed - width;
@@ -295,7 +323,8 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
       __syncthreads();
       for (int64_t t = tid; t < p.T; t += SEL_FINAL_THREADS) {
         const uint64_t c = make_composite(src[t], element_index(p, row, t));
-        if ((c >> (64 - fixed)) == prefix) atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
+        if (fixed == 0 || (c >> (64 - fixed)) == prefix)
+          atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
       }
       __syncthreads();
       uint32_t d, ab, in;
@@ -310,7 +339,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     const int sh = 64 - fixed;
     for (int64_t t = tid; t < p.T; t += SEL_FINAL_THREADS) {
       const uint64_t c = make_composite(src[t], element_index(p, row, t));
-      const bool take = (sh == 0) ? (c >= prefix) : ((c >> sh) >= prefix);
+      const bool take = (sh == 0) ? (c >= prefix) : (sh >= 64 ? true : ((c >> sh) >= prefix));
       if (take) {
         const uint32_t pos = atomicAdd(s_count, 1u);
         if (pos < (uint32_t)p.cap) s_cand[pos] = c;
@@ -330,7 +359,8 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     __syncthreads();
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
       const uint64_t c = s_cand[i];
-      if ((c >> (64 - fixed)) == prefix) atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
+      if (fixed == 0 || (c >> (64 - fixed)) == prefix)
+        atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
     }
     __syncthreads();
     uint32_t d, ab, in;
@@ -340,7 +370,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     prefix = (prefix << width) | d;
     fixed += width;
   }
-  const uint64_t kth = fixed >= 64 ? prefix : (prefix << (64 - fixed));   // the winners: composite >= kth
+  const uint64_t kth = fixed >= 64 ? prefix : (fixed == 0 ? 0ull : (prefix << (64 - fixed)));   // winners: composite >= kth
 
   if (p.use_bitmap) {
     // Ascending-index output: one bit per token of the row, read out in order.
@@ -472,6 +502,8 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   p.cand = w.cand; p.cand_count = w.count; p.cap = select_cap(kk);
   p.thresholds = w.thresholds;
   p.order_by_index = order;
+  p.from_candidates = 0;
+  p.row_failed = nullptr;
   const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
   size_t smem = (size_t)p.cap * 8 + SEL_FINAL_FIXED_SMEM;
   p.use_bitmap = (order == 1 && !payload && smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;

@@ -17,6 +17,10 @@ RTOL, ATOL = 2e-2, 1e-2
     (2, 8, 2, 1000, 64, 64, 10, 10),
     (2, 4, 4, 300, 32, 512, 3, 2),          # k > T
     (1, 8, 1, 70, 128, 16, 0, 0),
+    (2, 8, 2, 20000, 64, 512, 0, 0),        # longer than the candidate capacity: sampled threshold path
+    (1, 4, 2, 40000, 32, 2048, 5, 5),
+    (2, 16, 2, 9000, 64, 100, 0, 0),        # small k: the rank floor of the sample decides tau
+    (1, 2, 2, 33000, 128, 3000, 0, 0),      # G = 1, C = 128, k above 8192 / 3
 ])
 def test_step_matches_oracle(cuda_device, B, Hq, Hkv, T, C, k, sink, recent):
     w, q, key, value = make_case(cuda_device, batch=B, q_heads=Hq, kv_heads=Hkv, context=T, channels=C, seed=B + T)
@@ -59,3 +63,32 @@ def test_device_status_is_clean(cuda_device):
     st = ctypes.c_int(-1)
     assert _native.lib().kvb_device_status(0, ctypes.byref(st)) == 0
     assert st.value == 0
+
+
+@pytest.mark.parametrize("T,k", [(30000, 512), (12000, 4000)])
+def test_heavy_ties_take_the_rescue_path(cuda_device, T, k):
+    """Keys quantised from a handful of distinct rows: scores tie massively, the sampled threshold
+    admits far more candidates than fit, and the exact refinement over the re-scored row must take over."""
+    w, q, key, value = make_case(cuda_device, batch=2, q_heads=8, kv_heads=2, context=T, channels=64, seed=5)
+    key = key.clone()
+    key[:, :, :T] = key[:, :, :3].repeat(1, 1, (T + 2) // 3, 1)[:, :, :T]
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    packed, scale = ops.alloc_side_cache(2, 2, T + 1, 64, cuda_device)
+    ops.quantize(key[:, :, :T], ch, out=(packed, scale))
+    sel = torch.empty((2, 2, k), dtype=torch.int32, device=cuda_device)
+    out = ops.DecodeStep(k)(q, key, value, packed, scale, ch, selected_out=sel)
+    r = oracle.decode_step(*cpu(q, key, value, ch), k)
+    assert torch.equal(sel.cpu().long(), torch.sort(r["selected"], dim=-1).values)
+    torch.testing.assert_close(out.float().cpu(), r["out"], rtol=RTOL, atol=ATOL)
+
+
+def test_all_zero_keys(cuda_device):
+    T, k = 10000, 256
+    w, q, key, value = make_case(cuda_device, batch=1, q_heads=4, kv_heads=2, context=T, channels=32)
+    key = torch.zeros_like(key)
+    ch = torch.arange(32, dtype=torch.int32, device=cuda_device).repeat(2, 1)
+    packed, scale = ops.alloc_side_cache(1, 2, T + 1, 32, cuda_device)
+    ops.quantize(key[:, :, :T], ch, out=(packed, scale))
+    sel = torch.empty((1, 2, k), dtype=torch.int32, device=cuda_device)
+    ops.DecodeStep(k)(q, key, value, packed, scale, ch, selected_out=sel)
+    assert torch.equal(sel.cpu(), torch.arange(k, dtype=torch.int32).expand(1, 2, k))     # all tie: lowest indices win
