@@ -174,30 +174,21 @@ def run_single_gpu(args, w) -> None:
         ms_scorer = event_time_ms(run_scorer, max(args.steps, 10), stream)
         clocks = sampler.stop()
 
-        # end to end through the Python operator with host buffers
-        h_q = torch.empty_like(query, device="cpu").pin_memory()
-        h_k = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory()
-        h_v = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory()
-        h_q.copy_(query)
-        h_k.copy_(key[:, :, T:T + 1])
-        h_v.copy_(value[:, :, T:T + 1])
-        h_out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16).pin_memory()
-        d_q = torch.empty_like(query)
-
-        def e2e_step():
-            d_q.copy_(h_q, non_blocking=True)
-            key[:, :, T:T + 1].copy_(h_k, non_blocking=True)
-            value[:, :, T:T + 1].copy_(h_v, non_blocking=True)
-            step(d_q, key, value, packed, scale, ch, out=out)
-            h_out.copy_(out, non_blocking=True)
-            stream.synchronize()
-
+        # end to end through the public graph API with host buffers: every step copies the query and
+        # the new K/V row from pinned host memory, scatters the row into the cache at the device-side
+        # position, runs the fused step and copies the output back; the host waits for it.
+        # (advance=False keeps the history at T so that every timed step is the same workload.)
+        gd = ops.GraphedDecode(step, key, value, packed, scale, ch, history=T, q_heads=Hq, advance=False)
+        gd.h_query.copy_(query)
+        gd.h_key_row.copy_(key[:, :, T:T + 1])
+        gd.h_value_row.copy_(value[:, :, T:T + 1])
         for _ in range(3):
-            e2e_step()
+            gd()
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            e2e_step()
+            h_out = gd()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        h_q, h_k, h_v = gd.h_query, gd.h_key_row, gd.h_value_row
 
     tokens = B * T
     peak, peak_kind = hbm_peak()
@@ -221,8 +212,8 @@ def run_single_gpu(args, w) -> None:
         "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e3, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2,
                 "d2h_bytes_per_step": h_out.numel() * 2,
-                "api": "kv_cache_b200.ops.DecodeStep.__call__ -> kvb_decode_step"},
-        "gpu_launches": 6 * args.steps,
+                "api": "kv_cache_b200.ops.GraphedDecode.__call__ (H2D + kvb_decode_step + D2H in one CUDA graph, device-side history length)"},
+        "gpu_launches": 7 * args.steps,
         "roofline": {"bound": "hbm", "kernel": "score_decode_stream_kernel", "achieved": scorer_gbs, "peak": peak,
                      "unit": "GB/s", "frac": scorer_gbs / peak, "peak_source": peak_kind, "traffic": None,
                      "algorithmic_bytes": alg["scan"], "kernel_ms": ms_scorer,

@@ -301,7 +301,7 @@ typedef struct kvb_decode_step_params {
   const int32_t* channel_idx;                             /* int32 [Hkv,C]            */
   const float* mask;  int64_t mask_sb;                    /* fp32 [B,key_count] or NULL */
   int B, Hq, Hkv, D, C;
-  int history_count;                                      /* T; key_count = T + 1     */
+  int history_count;                                      /* T; key_count = T + 1 (the upper bound of T when history_count_dev is set) */
   int top_k;
   int protect_sink, protect_recent, keep_self, append_protected;
   int append_self;
@@ -309,6 +309,13 @@ typedef struct kvb_decode_step_params {
   void* out;                                              /* bf16 [B,1,Hq,D]          */
   int32_t* sel_idx_out;                                   /* int32 [B,Hkv,kk] or NULL */
   void* workspace; size_t workspace_bytes;
+  /* Optional device-side history length, for CUDA-graph replays over a growing cache: when not
+   * NULL the kernels read T from *history_count_dev (int32, 1 <= T <= history_count; sizes and the
+   * workspace are derived from history_count) and, with advance_history != 0, add one to it at the
+   * end of the step. Only the streaming configurations support it (C in {32,64,128}, G in
+   * {1,2,4,8}, aligned side cache, top_k <= history_count <= 131072); others return KVB_BAD_SHAPE. */
+  const int32_t* history_count_dev;
+  int advance_history;
 } kvb_decode_step_params;
 
 size_t kvb_decode_step_workspace_bytes(int B, int Hq, int Hkv, int history_count, int top_k,

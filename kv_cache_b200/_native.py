@@ -46,6 +46,7 @@ class DecodeStepParams(C.Structure):
         ("out", _p),
         ("sel_idx_out", _p),
         ("workspace", _p), ("workspace_bytes", _sz),
+        ("history_count_dev", _p), ("advance_history", _i),
     ]
 
 

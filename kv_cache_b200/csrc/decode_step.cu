@@ -24,10 +24,8 @@ constexpr int FS_PER_THREAD = FS_MAX_SAMPLE / FS_THREADS;
 struct SampleParams {
   ScoreParams sp;             // query / packed / scale / channels / shapes (outputs unused)
   float* tau;                 // [R]
-  int kk;                     // min(k, T)
+  int top_k;
   int cap;                    // candidate capacity per row
-  int run_len;                // tokens per run (multiple of FS_PER_THREAD), 0 => take every token (tau = -inf)
-  int rank;                   // rank (1-based, from the top) of the sample value that becomes tau
 };
 
 template <int C, int G>
@@ -39,10 +37,22 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   __shared__ uint32_t s_tmp[80];
   const ScoreParams& p = q.sp;
   const int row = blockIdx.x, tid = threadIdx.x;
-  if (q.run_len == 0) {                         // short rows: every token is a candidate
+  const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
+  if (T <= q.cap) {                             // short rows: every token is a candidate
     if (tid == 0) q.tau[row] = -INFINITY;
     return;
   }
+  // sample geometry: FS_RUNS runs of run_len tokens; rank = the sample rank that predicts about
+  // 1.75 k (at least 96 / fraction) tokens above tau in the whole row
+  int run_len = (T / FS_RUNS) / FS_PER_THREAD * FS_PER_THREAD;
+  if (run_len > FS_MAX_SAMPLE / FS_RUNS) run_len = FS_MAX_SAMPLE / FS_RUNS;
+  const float frac = (float)(run_len * FS_RUNS) / (float)T;
+  const int kk = q.top_k < T ? q.top_k : T;
+  float expect = 1.75f * (float)kk;
+  if (expect * frac < 96.0f) expect = 96.0f / frac;
+  int rank = (int)(expect * frac + 0.999f);
+  if (rank < 1) rank = 1;
+  if (rank > run_len * FS_RUNS) rank = run_len * FS_RUNS;
   const int b = row / p.Hkv, g = row - b * p.Hkv;
   for (int i = tid; i < SEL_HIST_BINS; i += FS_THREADS) s_hist[i] = 0;
   quantize_query_group<FS_THREADS>(p, b, g, G, s_qv, s_qcode, s_qscale);
@@ -63,9 +73,9 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   }
   __syncthreads();
   // thread -> run (tid / threads_per_run), FS_PER_THREAD consecutive tokens inside the run
-  const int threads_per_run = q.run_len / FS_PER_THREAD;
+  const int threads_per_run = run_len / FS_PER_THREAD;
   const int run = tid / threads_per_run;
-  const int64_t t0 = (int64_t)run * (p.T / FS_RUNS) + (int64_t)(tid - run * threads_per_run) * FS_PER_THREAD;
+  const int64_t t0 = (int64_t)run * (T / FS_RUNS) + (int64_t)(tid - run * threads_per_run) * FS_PER_THREAD;
   const bool live = run < FS_RUNS;
   const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)g * p.packed_sh;
   const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)g * p.scale_sh;
@@ -77,7 +87,7 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
     float ks[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const bool ok = live && t0 + e0 + e < p.T;
+      const bool ok = live && t0 + e0 + e < T;
       const uint4* src = reinterpret_cast<const uint4*>(packed_row + (t0 + e0 + e) * (C / 2));
 #pragma unroll
       for (int x = 0; x < C / 32; ++x) {
@@ -112,14 +122,14 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
         m = fmaxf(m, __fmul_rn(__fmul_rn(f, ks[e]), s_qscale[hd] * 0.0625f));
       }
       if (m == 0.0f) m = 0.0f;
-      const bool ok = live && t0 + e0 + e < p.T;
+      const bool ok = live && t0 + e0 + e < T;
       v[e0 + e] = ok ? m : __int_as_float(0x7fc00000);
       if (ok) atomicAdd(&s_hist[float_to_key(m) >> (32 - SEL_HIST_BITS)], 1u);
     }
   }
   __syncthreads();
   uint32_t bin, above, inb;
-  find_threshold<FS_THREADS>(s_hist, SEL_HIST_BINS, (uint32_t)q.rank, s_tmp, bin, above, inb);
+  find_threshold<FS_THREADS>(s_hist, SEL_HIST_BINS, (uint32_t)rank, s_tmp, bin, above, inb);
   // second level: 11 more key bits inside the bin
   for (int i = tid; i < 2048; i += FS_THREADS) s_hist[i] = 0;
   __syncthreads();
@@ -132,7 +142,7 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   }
   __syncthreads();
   uint32_t d, ab2, in2;
-  find_threshold<FS_THREADS>(s_hist, 2048, (uint32_t)q.rank - above, s_tmp, d, ab2, in2);
+  find_threshold<FS_THREADS>(s_hist, 2048, (uint32_t)rank - above, s_tmp, d, ab2, in2);
   if (tid == 0) {
     const uint32_t key_lo = (bin << (32 - SEL_HIST_BITS)) | (d << 9);
     float t = key_to_float(key_lo);
@@ -157,7 +167,7 @@ struct RescueParams {
   ScoreParams sp;             // gmax_out = workspace rows
   const uint32_t* cand_count;
   uint32_t* row_failed;
-  int kk, cap;
+  int top_k, cap;
 };
 
 constexpr int RS_THREADS = 256;
@@ -168,13 +178,15 @@ __global__ void __launch_bounds__(RS_THREADS) score_rescue_kernel(RescueParams q
   __shared__ int8_t s_qcode[SC_MAX_G * SC_MAX_C];
   const ScoreParams& p = q.sp;
   const int row = blockIdx.x;
+  const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
+  const int kk = q.top_k < T ? q.top_k : T;
   const uint32_t n = q.cand_count[(int64_t)row * SC_COUNT_STRIDE];
-  if (n >= (uint32_t)q.kk && n <= (uint32_t)q.cap) return;
+  if (n >= (uint32_t)kk && n <= (uint32_t)q.cap) return;
   const int b = row / p.Hkv, g = row - b * p.Hkv;
   quantize_query_group<RS_THREADS>(p, b, g, p.G, s_qv, s_qcode, s_qscale);
   ScoreParams pp = p;
   pp.acc_out = nullptr; pp.deq_out = nullptr;
-  for (int64_t t = threadIdx.x; t < p.T; t += RS_THREADS)
+  for (int64_t t = threadIdx.x; t < T; t += RS_THREADS)
     p.gmax_out[(int64_t)row * p.T + t] = score_token_plain<SC_MAX_G>(pp, p.G, b, g, t, s_qcode, s_qscale);
   if (threadIdx.x == 0) q.row_failed[row] = 1u;
 }
@@ -262,15 +274,18 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   const int fcap = L.fcap;
   const bool stream_ok = score_stream_supported(p->C, G, p->packed, p->packed_sb, p->packed_sh, p->scale,
                                                 p->scale_sb, p->scale_sh);
-  // sample geometry: 32 runs of run_len tokens, 4096 tokens in all when the row is long enough
+  // the sample kernel aims at max(1.75 k, 96 / sampled fraction) candidates: that, with margin, must
+  // fit the capacity at the (largest) history length this call can see
   int run_len = (T / FS_RUNS) / FS_PER_THREAD * FS_PER_THREAD;
   if (run_len > FS_MAX_SAMPLE / FS_RUNS) run_len = FS_MAX_SAMPLE / FS_RUNS;
   const double frac = run_len > 0 ? (double)(run_len * FS_RUNS) / (double)T : 0.0;
-  double expect = 1.75 * L.kk;                              // candidates aimed at
-  if (frac > 0.0 && expect * frac < 96.0) expect = 96.0 / frac;   // keep the rank statistically stable
+  double expect = 1.75 * L.kk;
+  if (frac > 0.0 && expect * frac < 96.0) expect = 96.0 / frac;
   const bool all_candidates = T <= fcap;                    // short rows: tau = -inf, every token is a candidate
   const bool fast = stream_ok && 3 * L.kk <= fcap &&
                     (all_candidates || (run_len >= FS_PER_THREAD && 1.7 * expect <= (double)fcap));
+  const int32_t* T_dev = p->history_count_dev;
+  if (T_dev && !fast) return KVB_BAD_SHAPE;
   if (fast) {
     {
       DeviceGuard guard(device);
@@ -287,15 +302,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       sq.sp.scale = p->scale; sq.sp.scale_sb = p->scale_sb; sq.sp.scale_sh = p->scale_sh;
       sq.sp.channel_idx = p->channel_idx;
       sq.sp.B = p->B; sq.sp.Hq = p->Hq; sq.sp.Hkv = p->Hkv; sq.sp.T = T; sq.sp.D = p->D; sq.sp.C = p->C; sq.sp.G = G;
+      sq.sp.T_dev = T_dev;
       sq.sp.gmax_out = nullptr; sq.sp.acc_out = nullptr; sq.sp.deq_out = nullptr; sq.sp.hist_out = nullptr;
       sq.sp.tau = nullptr; sq.sp.cand = nullptr; sq.sp.cand_count = nullptr; sq.sp.cand_cap = 0;
       sq.sp.units_per_row = 0; sq.sp.full_tiles = 0; sq.sp.total_units = 0;
-      sq.tau = ftau; sq.kk = L.kk; sq.cap = fcap;
-      sq.run_len = all_candidates ? 0 : run_len;
-      int rank = (int)(expect * frac + 0.999);
-      if (rank < 1) rank = 1;
-      if (rank > run_len * FS_RUNS) rank = run_len * FS_RUNS;
-      sq.rank = rank;
+      sq.tau = ftau; sq.top_k = p->top_k; sq.cap = fcap;
       if (p->C == 32) sample_launch_g<32>(sq, L.R, st);
       else if (p->C == 64) sample_launch_g<64>(sq, L.R, st);
       else sample_launch_g<128>(sq, L.R, st);
@@ -304,13 +315,13 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       ScoreEmit emit{ftau, fcand, fcount, fcap};
       rc = score_run(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
                      p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, nullptr, nullptr, nullptr,
-                     nullptr, &emit, device, st);
+                     nullptr, &emit, T_dev, device, st);
       if (rc != KVB_OK) return rc;
 
       RescueParams rq;
       rq.sp = sq.sp;
       rq.sp.gmax_out = gmax;
-      rq.cand_count = fcount; rq.row_failed = ffailed; rq.kk = L.kk; rq.cap = fcap;
+      rq.cand_count = fcount; rq.row_failed = ffailed; rq.top_k = p->top_k; rq.cap = fcap;
       score_rescue_kernel<<<L.R, RS_THREADS, 0, st>>>(rq);
       KVB_CHECK_CUDA(cudaGetLastError());
 
@@ -321,7 +332,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       sp.hist = nullptr; sp.cand = fcand; sp.cand_count = fcount; sp.cap = fcap;
       sp.tokens_per_cta = 0; sp.thresholds = nullptr;
       sp.order_by_index = 1;
-      sp.from_candidates = 1; sp.row_failed = ffailed;
+      sp.from_candidates = 1; sp.row_failed = ffailed; sp.T_dev = T_dev;
       const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
       size_t smem = (size_t)fcap * 8 + SEL_FINAL_FIXED_SMEM;
       sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
@@ -355,7 +366,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   const FinalLayout f = final_layout(L.kk, T, p->protect_sink, p->protect_recent, p->keep_self);
   AttendList list{};
   list.implicit = 1;
-  list.selected = sel; list.kk = L.kk;
+  list.selected = sel; list.kk = L.kk; list.sel_pitch = L.kk;
   list.sel_base = 0; list.sel_limit = T;
   list.sink_end = f.sink_end; list.n_recent = f.n_recent; list.recent_from = f.recent_from;
   list.recent_start = f.recent_start; list.recent_on = f.recent_on; list.history = T;
@@ -366,8 +377,9 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   ap.packed = p->packed; ap.packed_sb = p->packed_sb; ap.packed_sh = p->packed_sh;
   ap.scale = p->scale; ap.scale_sb = p->scale_sb; ap.scale_sh = p->scale_sh;
   ap.t_src = T; ap.t_dst = T;
+  AttendDeviceLength adl{T_dev, p->top_k, p->protect_sink, p->protect_recent, p->keep_self, p->advance_history};
   rc = attend_run(p->query, p->q_sb, p->q_sh, p->key, p->k_sb, p->k_sh, p->k_st, p->value, p->v_sb, p->v_sh, p->v_st,
-                  list, &ap, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D, L.S, p->scaling,
+                  list, &ap, T_dev ? &adl : nullptr, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D, L.S, p->scaling,
                   p->out, nullptr, attcnt, attpart, /*counters_zeroed=*/true, device, st);
   if (rc != KVB_OK) return rc;
   return KVB_OK;

@@ -30,7 +30,8 @@ struct ScoreParams {
   const float* scale;
   int64_t scale_sb, scale_sh;
   const int32_t* channel_idx;
-  int B, Hq, Hkv, T, D, C, G;
+  int B, Hq, Hkv, T, D, C, G;      // T: history length, or its upper bound (= row pitch of gmax) when T_dev is set
+  const int32_t* T_dev;            // optional: the history length lives on the device (graph replays with a growing cache)
   float* gmax_out;
   int32_t* acc_out;
   float* deq_out;
@@ -186,8 +187,13 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
   // The group-max row is re-read by the selector right away and overwritten by the next step:
   // ask L2 to keep it so that it need not travel to HBM and back.
   const uint64_t keep = l2_policy_evict_last();
-  const int64_t u_begin = (int64_t)blockIdx.x * p.total_units / gridDim.x;
-  const int64_t u_end = (int64_t)(blockIdx.x + 1) * p.total_units / gridDim.x;
+  // work geometry from the history length (read from the device when it lives there)
+  const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
+  const int full_tiles = T / TW;
+  const int units_per_row = full_tiles + ((T % TW) ? 1 : 0);
+  const int64_t total_units = (int64_t)p.B * p.Hkv * units_per_row;
+  const int64_t u_begin = (int64_t)blockIdx.x * total_units / gridDim.x;
+  const int64_t u_end = (int64_t)(blockIdx.x + 1) * total_units / gridDim.x;
 
   uint32_t ring = 0;        // tiles this warp has consumed so far (stage = ring % NS, parity = ring / NS & 1)
   bool dead = false;        // a bounded wait gave up: skip all further streaming work
@@ -201,10 +207,10 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
 
   int64_t u = u_begin;
   while (u < u_end) {
-    const int row = (int)(u / p.units_per_row);
-    const int ua = (int)(u - (int64_t)row * p.units_per_row);
-    int64_t row_end_u = (int64_t)(row + 1) * p.units_per_row;
-    const int ub = (int)((row_end_u < u_end ? row_end_u : u_end) - (int64_t)row * p.units_per_row);
+    const int row = (int)(u / units_per_row);
+    const int ua = (int)(u - (int64_t)row * units_per_row);
+    int64_t row_end_u = (int64_t)(row + 1) * units_per_row;
+    const int ub = (int)((row_end_u < u_end ? row_end_u : u_end) - (int64_t)row * units_per_row);
     u += (ub - ua);
     const int b = row / p.Hkv, kvh = row - b * p.Hkv;
 
@@ -273,7 +279,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
 
     // Full tiles of this segment: [ta, tb); warp w takes ta + w, ta + w + WARPS, ...
     const int ta = ua;
-    const int tb = ub < p.full_tiles ? ub : p.full_tiles;
+    const int tb = ub < full_tiles ? ub : full_tiles;
     const int nmy = (tb - ta - warp + WARPS - 1) / WARPS;   // <= 0 when none
 
     auto issue = [&](int j, uint32_t slot) {
@@ -400,11 +406,11 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
     }
 
     // Ragged tail of the row (fewer than TW tokens), owned by the segment that holds the tail unit.
-    if (ub > p.full_tiles) {
-      const int64_t tail0 = (int64_t)p.full_tiles * TW;
-      for (int64_t tb = tail0 + warp * 32; tb < p.T; tb += THREADS) {      // warp-uniform trips (ballot in finish)
+    if (ub > full_tiles) {
+      const int64_t tail0 = (int64_t)full_tiles * TW;
+      for (int64_t tb = tail0 + warp * 32; tb < T; tb += THREADS) {        // warp-uniform trips (ballot in finish)
         const int64_t t = tb + lane;
-        const bool live = t < p.T;
+        const bool live = t < T;
         const float m = live ? score_token_plain<G>(p, G, b, kvh, t, s_qcode, s_qscale) : 0.0f;
         finish(m, t, live);
       }
@@ -538,8 +544,8 @@ static bool score_stream_supported(int C, int G, const uint8_t* packed, int64_t 
 static int score_run(const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb,
                      int64_t packed_sh, const float* scale, int64_t scale_sb, int64_t scale_sh,
                      const int32_t* channel_idx, int B, int Hq, int Hkv, int T, int D, int C, float* gmax_out,
-                     int32_t* acc_out, float* deq_out, uint32_t* hist_out, const ScoreEmit* emit, int device,
-                     cudaStream_t st) {
+                     int32_t* acc_out, float* deq_out, uint32_t* hist_out, const ScoreEmit* emit,
+                     const int32_t* T_dev, int device, cudaStream_t st) {
   if (!query || !packed || !scale || !channel_idx) return KVB_BAD_ARG;
   if (!gmax_out && !acc_out && !deq_out && !emit) return KVB_BAD_ARG;
   if (hist_out && !gmax_out) return KVB_BAD_ARG;
@@ -562,6 +568,7 @@ static int score_run(const void* query, int64_t q_sb, int64_t q_sh, const uint8_
   p.channel_idx = channel_idx;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.T = T; p.D = D; p.C = C; p.G = G;
   p.gmax_out = gmax_out; p.acc_out = acc_out; p.deq_out = deq_out; p.hist_out = hist_out;
+  p.T_dev = T_dev;
   p.tau = emit ? emit->tau : nullptr;
   p.cand = emit ? emit->cand : nullptr;
   p.cand_count = emit ? emit->cand_count : nullptr;
@@ -585,7 +592,7 @@ static int score_run(const void* query, int64_t q_sb, int64_t q_sh, const uint8_
     }
     if (rc >= 0) return rc;
   }
-  if (emit) return KVB_BAD_SHAPE;     // callers check score_stream_supported() first
+  if (emit || T_dev) return KVB_BAD_SHAPE;     // callers check score_stream_supported() first
   int gx = ceil_div(T, SC_THREADS);
   const int cap = ceil_div(sm_count(device) * 16, B * Hkv);
   if (gx > cap) gx = cap < 1 ? 1 : cap;
@@ -602,6 +609,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_score_decode(
     const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
     int D, int C, float* gmax_out, int32_t* acc_out, float* deq_out, uint32_t* hist_out, int device, void* stream) {
   return kvb::score_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq,
-                        Hkv, T, D, C, gmax_out, acc_out, deq_out, hist_out, nullptr, device,
+                        Hkv, T, D, C, gmax_out, acc_out, deq_out, hist_out, nullptr, nullptr, device,
                         reinterpret_cast<cudaStream_t>(stream));
 }

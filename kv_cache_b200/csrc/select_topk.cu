@@ -45,6 +45,7 @@ struct SelectParams {
   int use_bitmap;             // order_by_index served by the shared-memory bitmap
   int from_candidates;        // the candidate lists were filled by the scorer: no histogram / thresholds
   const uint32_t* row_failed; // [R] with from_candidates: rows whose list is unusable; `scores` holds their full row
+  const int32_t* T_dev;       // optional (fused step): the row length lives on the device; T is then its upper bound
 };
 
 __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row, int64_t t) {
@@ -270,7 +271,15 @@ __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
 }
 
 // One CTA per row: candidates -> exact k-th composite -> the k winners in the requested order.
-__global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectParams p) {
+__global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectParams pin) {
+  // the row length (and with it the count to select) may live on the device
+  SelectParams p = pin;
+  const int out_pitch = pin.kk;                         // rows of the outputs stay kk_max apart
+  if (p.T_dev) {
+    const int t = *p.T_dev;
+    p.T = t < pin.T ? t : pin.T;
+    p.kk = p.k < p.T ? p.k : p.T;
+  }
   extern __shared__ __align__(16) uint8_t sel_smem[];
   uint64_t* s_cand = reinterpret_cast<uint64_t*>(sel_smem);                     // [cap]
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(sel_smem + (size_t)p.cap * 8);  // [2048]
@@ -400,7 +409,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
         bits &= bits - 1;
         const uint32_t local = (uint32_t)(w0 + j) * 32u + (uint32_t)bit;
         if (pos < (uint32_t)p.kk) {
-          const int64_t o = (int64_t)row * p.kk + pos;
+          const int64_t o = (int64_t)row * out_pitch + pos;
           const uint32_t idx = local + (uint32_t)p.idx_offset;
           if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
           if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
@@ -432,7 +441,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     uint64_t c = s_cand[i];
     if (p.order_by_index) c = ((c & 0xFFFFFFFFull) << 32) | (c >> 32);
     const uint32_t idx = 0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull);
-    const int64_t o = (int64_t)row * p.kk + i;
+    const int64_t o = (int64_t)row * out_pitch + i;
     if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
     if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
     if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(c >> 32));
@@ -504,6 +513,7 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   p.order_by_index = order;
   p.from_candidates = 0;
   p.row_failed = nullptr;
+  p.T_dev = nullptr;
   const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
   size_t smem = (size_t)p.cap * 8 + SEL_FINAL_FIXED_SMEM;
   p.use_bitmap = (order == 1 && !payload && smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;

@@ -24,6 +24,28 @@ constexpr int AT_STAGE_BYTES = 2 * AT_TILE_BYTES;        // K then V
 constexpr int AT_WARP_SMEM = AT_STAGES * (AT_STAGE_BYTES + AT_TILE * 8);   // stages + per-row (token, mask)
 constexpr int AT_TARGET_WARPS = 1184;       // one wave: 148 SMs x 2 CTAs x 4 warps
 
+struct FinalLayout {
+  int sink_end, recent_on, recent_start, recent_from, n_recent, S;
+};
+
+__host__ __device__ inline FinalLayout final_layout(int kk, int history, int sink, int recent, int keep_self) {
+  FinalLayout f;
+  f.sink_end = sink > 0 ? (sink < history ? sink : history) : 0;
+  f.recent_on = recent > 0 ? 1 : 0;
+  f.recent_start = history;
+  f.recent_from = history;
+  f.n_recent = 0;
+  if (recent > 0) {
+    f.recent_start = history - recent > 0 ? history - recent : 0;
+    if (f.recent_start < history) {
+      f.recent_from = f.recent_start > f.sink_end ? f.recent_start : f.sink_end;
+      if (f.recent_from < history) f.n_recent = history - f.recent_from;
+    }
+  }
+  f.S = kk + f.sink_end + f.n_recent + (keep_self ? 1 : 0);
+  return f;
+}
+
 // How the logical list of S entries is produced.
 //   explicit: indices[row, s] (+ valid[row, s])
 //   implicit: selected[row, 0..kk) || [0, sink_end) || [recent_from, recent_from + n_recent) || self
@@ -32,7 +54,7 @@ constexpr int AT_TARGET_WARPS = 1184;       // one wave: 148 SMs x 2 CTAs x 4 wa
 struct AttendList {
   const void* indices; int idx_is_i64; const uint8_t* valid;      // explicit
   int implicit;
-  const int32_t* selected; int kk;
+  const int32_t* selected; int kk; int sel_pitch;   // kk entries used of rows sel_pitch apart
   int64_t sel_base; int sel_limit;       // selected ids are global: local row = id - sel_base, kept iff in [0, sel_limit)
   int sink_end, n_recent, recent_from, recent_start, recent_on, history, append_protected;
 };
@@ -62,6 +84,11 @@ struct AttendParams {
   uint32_t* ws_counter;       // [B*Hi]
   int nsplit, tiles_per_split;
   AttendAppend append;
+  // optional (fused step): the history length lives on the device; the list layout is then derived
+  // in the kernel from the raw policy below, and the host-side figures are upper bounds
+  const int32_t* T_dev;
+  int top_k, protect_sink, protect_recent, keep_self;
+  int advance_history;        // the merge kernel adds one to *T_dev when everything else is done
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -91,7 +118,7 @@ __device__ __forceinline__ int attend_fetch(const AttendParams& p, int row, int 
                        : (int64_t) reinterpret_cast<const int32_t*>(L.indices)[o];
     ok = (L.valid == nullptr) || (L.valid[o] != 0);
   } else if (s < L.kk) {
-    raw = (int64_t)L.selected[(int64_t)row * L.kk + s] - L.sel_base;
+    raw = (int64_t)L.selected[(int64_t)row * L.sel_pitch + s] - L.sel_base;
     if (raw >= L.sel_limit) ok = false;
     if (!L.append_protected) {
       if (L.recent_on && raw >= L.recent_start && raw < L.history) ok = false;
@@ -140,12 +167,26 @@ __device__ __forceinline__ void quantize_row_warp(const __nv_bfloat16* krow, con
 
 // GG = query heads that share one index list (1, 2, 4 or 8).
 template <int GG>
-__global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendParams p) {
+__global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendParams pin) {
   extern __shared__ __align__(128) uint8_t at_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int task = blockIdx.x * AT_WARPS + warp;
-  if (task >= p.B * p.Hi * p.nsplit) return;             // warps are independent: no block barrier below
+  if (task >= pin.B * pin.Hi * pin.nsplit) return;       // warps are independent: no block barrier below
+  AttendParams p = pin;
+  if (p.T_dev) {
+    // history length from the device: rebuild the implicit list's layout for it
+    int T = *p.T_dev;
+    if (T > pin.list.history) T = pin.list.history;      // never beyond what the host sized for
+    const int kk = p.top_k < T ? p.top_k : T;
+    const FinalLayout f = final_layout(kk, T, p.protect_sink, p.protect_recent, p.keep_self);
+    p.list.kk = kk; p.list.sel_limit = T; p.list.history = T;
+    p.list.sink_end = f.sink_end; p.list.n_recent = f.n_recent; p.list.recent_from = f.recent_from;
+    p.list.recent_start = f.recent_start; p.list.recent_on = f.recent_on;
+    p.S = f.S;
+    p.Tk = T + (p.keep_self ? 1 : 0);
+    p.append.t_src = T; p.append.t_dst = T;
+  }
   const int row = task / p.nsplit;                       // (b, index head)
   const int split = task - row * p.nsplit;
   const int b = row / p.Hi, hi = row - b * p.Hi;
@@ -159,8 +200,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendPara
   const int s_begin = split * p.tiles_per_split * AT_TILE;
   int s_end = s_begin + p.tiles_per_split * AT_TILE;
   if (s_end > p.S) s_end = p.S;
-  const int nrows = s_end - s_begin;                     // >= 1 by construction of nsplit
-  const int ntile = (nrows + AT_TILE - 1) / AT_TILE;
+  const int nrows = s_end - s_begin;                     // >= 1 by construction of nsplit unless the device-side length shrank the list
+  const int ntile = nrows > 0 ? (nrows + AT_TILE - 1) / AT_TILE : 0;
 
   const __nv_bfloat16* kbase = p.key + (int64_t)b * p.k_sb + (int64_t)kvh * p.k_sh;
   const __nv_bfloat16* vbase = p.value + (int64_t)b * p.v_sb + (int64_t)kvh * p.v_sh;
@@ -383,6 +424,7 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
   }
   const float M = s_ml[0], L = s_ml[1];
   if (p.out) p.out[((int64_t)b * p.Hq + head) * AT_D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+  if (p.advance_history && p.T_dev && blockIdx.x == 0 && d == 0) *const_cast<int32_t*>(p.T_dev) += 1;
   if (p.out_partial) {
     float* op = p.out_partial + ((int64_t)b * p.Hq + head) * PW;
     op[d] = O;
@@ -445,28 +487,6 @@ __global__ void build_final_indices_kernel(const int32_t* sel_idx, const uint8_t
   out_valid[i] = ok ? 1 : 0;
 }
 
-struct FinalLayout {
-  int sink_end, recent_on, recent_start, recent_from, n_recent, S;
-};
-
-static FinalLayout final_layout(int kk, int history, int sink, int recent, int keep_self) {
-  FinalLayout f;
-  f.sink_end = sink > 0 ? (sink < history ? sink : history) : 0;
-  f.recent_on = recent > 0 ? 1 : 0;
-  f.recent_start = history;
-  f.recent_from = history;
-  f.n_recent = 0;
-  if (recent > 0) {
-    f.recent_start = history - recent > 0 ? history - recent : 0;
-    if (f.recent_start < history) {
-      f.recent_from = f.recent_start > f.sink_end ? f.recent_start : f.sink_end;
-      if (f.recent_from < history) f.n_recent = history - f.recent_from;
-    }
-  }
-  f.S = kk + f.sink_end + f.n_recent + (keep_self ? 1 : 0);
-  return f;
-}
-
 struct AttendPlan {
   int tiles_per_split, nsplit;
   size_t counter_bytes, partial_bytes, bytes;
@@ -520,9 +540,16 @@ namespace kvb {
 
 // Shared by kvb_sparse_attend and the fused step. `counters_zeroed` tells that the caller already
 // cleared ws_counter on this stream.
+// Device-side history length of the fused step (see AttendParams).
+struct AttendDeviceLength {
+  const int32_t* T_dev;
+  int top_k, protect_sink, protect_recent, keep_self, advance_history;
+};
+
 static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh,
                       int64_t k_st, const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st,
-                      const AttendList& list, const AttendAppend* append, const float* mask, int64_t mask_sb,
+                      const AttendList& list, const AttendAppend* append, const AttendDeviceLength* dev,
+                      const float* mask, int64_t mask_sb,
                       int B, int Hq, int Hkv, int Hi, int Tk, int D, int S, float scaling, void* out,
                       float* out_partial, uint32_t* ws_counter, float* ws_partial, bool counters_zeroed, int device,
                       cudaStream_t st) {
@@ -552,6 +579,10 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
   p.list = list;
   p.mask = mask; p.mask_sb = mask_sb;
   if (append) p.append = *append; else p.append.enabled = 0;
+  p.T_dev = dev ? dev->T_dev : nullptr;
+  p.top_k = dev ? dev->top_k : 0; p.protect_sink = dev ? dev->protect_sink : 0;
+  p.protect_recent = dev ? dev->protect_recent : 0; p.keep_self = dev ? dev->keep_self : 0;
+  p.advance_history = dev ? dev->advance_history : 0;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Hi = Hi; p.Tk = Tk; p.S = S; p.G = Hq / Hkv;
   p.scaling = scaling;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
@@ -584,7 +615,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(
   if (workspace_bytes < plan.bytes) return KVB_WORKSPACE_TOO_SMALL;
   AttendList list{};
   list.indices = indices; list.idx_is_i64 = idx_is_i64; list.valid = valid; list.implicit = 0;
-  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, list, nullptr,
+  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, list, nullptr, nullptr,
                     mask, mask_sb, B, Hq, Hkv, Hi, Tk, D, S, scaling, out, out_partial,
                     reinterpret_cast<uint32_t*>(workspace),
                     reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes),
@@ -608,13 +639,13 @@ extern "C" __attribute__((visibility("default"))) int kvb_attend_selected(
   if (workspace_bytes < plan.bytes) return KVB_WORKSPACE_TOO_SMALL;
   AttendList list{};
   list.implicit = 1;
-  list.selected = selected; list.kk = kk;
+  list.selected = selected; list.kk = kk; list.sel_pitch = kk;
   list.sel_base = id_base; list.sel_limit = history_count;
   list.sink_end = f.sink_end; list.n_recent = f.n_recent; list.recent_from = f.recent_from;
   list.recent_start = f.recent_start; list.recent_on = f.recent_on; list.history = history_count;
   list.append_protected = append_protected;
   // the "self" entry of the implicit list is row Tk - 1, so the view must end at the decoded token
-  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, list, nullptr, mask, mask_sb,
+  return attend_run(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, list, nullptr, nullptr, mask, mask_sb,
                     B, Hq, Hkv, Hkv, keep_self ? history_count + 1 : history_count, D, f.S, scaling, out, out_partial,
                     reinterpret_cast<uint32_t*>(workspace),
                     reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes),

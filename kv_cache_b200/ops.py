@@ -477,9 +477,15 @@ class DecodeStep:
     def __call__(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, packed: torch.Tensor,
                  scale: torch.Tensor, channel_idx: torch.Tensor, scaling: Optional[float] = None,
                  attention_mask: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 selected_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 selected_out: Optional[torch.Tensor] = None, history_dev: Optional[torch.Tensor] = None,
+                 advance_history: bool = False) -> torch.Tensor:
         """``key``/``value`` hold history+1 rows (the last is the token being decoded); the side
-        cache holds the history rows. Returns bf16 ``[B,1,Hq,D]``."""
+        cache holds the history rows. Returns bf16 ``[B,1,Hq,D]``.
+
+        With ``history_dev`` (int32 device tensor of one element) the history length is read on
+        the device and ``key``/``value`` are the whole cache (capacity rows): the same launch
+        sequence then serves every step of a CUDA-graph replayed decode loop; ``advance_history``
+        makes the step add one to it when it is done."""
         query = _query3(query)
         B, Hq, D = query.shape
         Hkv, key_count = key.shape[1], key.shape[2]
@@ -515,5 +521,68 @@ class DecodeStep:
         p.out = out.data_ptr()
         p.sel_idx_out = _ptr(selected_out)
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        p.history_count_dev = _ptr(history_dev)
+        p.advance_history = int(advance_history)
         check(_native.lib().kvb_decode_step(C.byref(p), _dev(query), _stream(dev)), "kvb_decode_step")
         return out
+
+
+class GraphedDecode:
+    """A decode loop step as ONE CUDA graph: copies of the step's inputs (query, new K row, new V
+    row) from pinned host buffers, their scatter into the cache at the device-side position, the
+    fused step, and the copy of the output back to a pinned host buffer. The history length lives
+    on the device (``self.history``), so the same graph serves every step until the cache is full.
+
+        g = GraphedDecode(DecodeStep(k), key_cache, value_cache, packed, scale, channel_idx, history=T)
+        g.h_query.copy_(q); g.h_key_row.copy_(k_new); g.h_value_row.copy_(v_new)
+        out = g()            # pinned host tensor [B,1,Hq,D]; history has advanced by one
+    """
+
+    def __init__(self, step: DecodeStep, key: torch.Tensor, value: torch.Tensor, packed: torch.Tensor,
+                 scale: torch.Tensor, channel_idx: torch.Tensor, history: int, q_heads: int,
+                 advance: bool = True, scaling: Optional[float] = None):
+        dev = key.device
+        B, Hkv, rows, D = key.shape
+        if history + 1 > rows:
+            raise RuntimeError("the cache has no room for the decoded token")
+        self.step, self.advance = step, advance
+        self.history = torch.tensor([history], dtype=torch.int32, device=dev)
+        self.h_query = torch.empty((B, q_heads, D), dtype=torch.bfloat16).pin_memory()
+        self.h_key_row = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory()
+        self.h_value_row = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory()
+        self.h_out = torch.empty((B, 1, q_heads, D), dtype=torch.bfloat16).pin_memory()
+        self._q = torch.empty((B, q_heads, D), dtype=torch.bfloat16, device=dev)
+        self._k = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16, device=dev)
+        self._v = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16, device=dev)
+        self._out = torch.empty((B, 1, q_heads, D), dtype=torch.bfloat16, device=dev)
+        self.stream = torch.cuda.Stream(dev)
+        self.h_query.zero_(); self.h_key_row.zero_(); self.h_value_row.zero_()
+
+        def body():
+            self._q.copy_(self.h_query, non_blocking=True)
+            self._k.copy_(self.h_key_row, non_blocking=True)
+            self._v.copy_(self.h_value_row, non_blocking=True)
+            pos = self.history.to(torch.int64)
+            key.index_copy_(2, pos, self._k)
+            value.index_copy_(2, pos, self._v)
+            step(self._q, key, value, packed, scale, channel_idx, scaling=scaling, out=self._out,
+                 history_dev=self.history, advance_history=advance)
+            self.h_out.copy_(self._out, non_blocking=True)
+
+        with torch.cuda.stream(self.stream):
+            saved = self.history.clone()
+            for _ in range(2):                       # warm-up outside capture (first-call set-up, workspace)
+                body()
+                self.history.copy_(saved)
+            self.stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                body()
+            self.history.copy_(saved)                # capture does not run the work; start from `history`
+            self.stream.synchronize()
+
+    def __call__(self) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            self.graph.replay()
+        self.stream.synchronize()
+        return self.h_out

@@ -92,3 +92,31 @@ def test_all_zero_keys(cuda_device):
     sel = torch.empty((1, 2, k), dtype=torch.int32, device=cuda_device)
     ops.DecodeStep(k)(q, key, value, packed, scale, ch, selected_out=sel)
     assert torch.equal(sel.cpu(), torch.arange(k, dtype=torch.int32).expand(1, 2, k))     # all tie: lowest indices win
+
+
+def test_graphed_decode_loop_with_device_side_history(cuda_device):
+    """One captured graph replayed for consecutive tokens: the history length lives on the device and
+    advances by one per replay; every replay must equal the oracle step at that length."""
+    T0, k, steps = 12000, 256, 3
+    w, q, key, value = make_case(cuda_device, batch=2, q_heads=8, kv_heads=2, context=T0 + steps, channels=64, seed=9)
+    ch = ops.choose_channels(key[:, :, :T0], 64)
+    cache_k = torch.zeros((2, 2, T0 + steps + 4, 128), dtype=torch.bfloat16, device=cuda_device)
+    cache_v = torch.zeros_like(cache_k)
+    cache_k[:, :, :T0], cache_v[:, :, :T0] = key[:, :, :T0], value[:, :, :T0]
+    packed, scale = ops.alloc_side_cache(2, 2, T0 + steps + 4, 64, cuda_device)
+    ops.quantize(key[:, :, :T0], ch, out=(packed, scale))
+    g = ops.GraphedDecode(ops.DecodeStep(k), cache_k, cache_v, packed, scale, ch, history=T0, q_heads=8)
+    for i in range(steps):
+        T = T0 + i
+        g.h_query.copy_(q)
+        g.h_key_row.copy_(key[:, :, T:T + 1])
+        g.h_value_row.copy_(value[:, :, T:T + 1])
+        out = g().clone()
+        assert int(g.history.item()) == T + 1
+        want = oracle.decode_step(*cpu(q, key[:, :, :T + 1], value[:, :, :T + 1], ch), k)
+        torch.testing.assert_close(out.float(), want["out"], rtol=RTOL, atol=ATOL)
+    # the cache and the int4 side cache were extended by the three decoded tokens
+    assert torch.equal(cache_k[:, :, :T0 + steps], key[:, :, :T0 + steps])
+    _, packed_o, scale_o = oracle.quantize_pack(key[:, :, :T0 + steps].cpu(), ch.cpu())
+    assert torch.equal(packed[:, :, :T0 + steps].cpu(), packed_o)
+    assert torch.equal(scale[:, :, :T0 + steps].cpu(), scale_o)
