@@ -111,6 +111,37 @@ int kvb_score_decode(const void* query, int64_t q_sb, int64_t q_sh,
                      uint32_t* hist_out,
                      int device, void* stream);
 
+/* Stage 2, candidate form (what the fused step uses): instead of writing a score per token, the
+ * scorer appends every token whose group maximum reaches a per-row threshold to that row's
+ * candidate list, so no score row ever goes to memory. No counterpart in the reference.
+ *
+ * kvb_candidate_capacity(top_k): entries per row the lists must hold (0 if top_k is too large).
+ * kvb_sample_thresholds: tau[b*Hkv+g] from a 1/32 sample of the row (32 evenly spaced runs, at most
+ *   4096 tokens): the sample value whose rank predicts max(1.75 top_k, 96 / sampled fraction)
+ *   tokens above it; -inf when T <= capacity. The prediction is statistical: callers must check
+ *   top_k <= count <= capacity afterwards (kvb_decode_step does, and re-scores the rare failing
+ *   row exactly).
+ * kvb_score_candidates: cand[row, i] = (order-preserving key of gmax) << 32 | (0xFFFFFFFF - token),
+ *   cand_count[row * 32] = number appended (it keeps counting past cand_cap; entries beyond the
+ *   capacity are dropped). cand_count must be zeroed by the caller. Streaming configurations only
+ *   (C in {32,64,128}, G in {1,2,4,8}, aligned side cache), else KVB_BAD_SHAPE. */
+int kvb_candidate_capacity(int top_k);
+
+int kvb_sample_thresholds(const void* query, int64_t q_sb, int64_t q_sh,
+                          const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                          const float* scale, int64_t scale_sb, int64_t scale_sh,
+                          const int32_t* channel_idx,
+                          int B, int Hq, int Hkv, int T, int D, int C, int top_k,
+                          float* tau, int device, void* stream);
+
+int kvb_score_candidates(const void* query, int64_t q_sb, int64_t q_sh,
+                         const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                         const float* scale, int64_t scale_sb, int64_t scale_sh,
+                         const int32_t* channel_idx,
+                         int B, int Hq, int Hkv, int T, int D, int C,
+                         const float* tau, uint64_t* cand, uint32_t* cand_count, int cand_cap,
+                         int device, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Stage 3 — exact top-k select per row; among equal scores the lower index wins.
  *

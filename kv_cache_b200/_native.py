@@ -61,6 +61,11 @@ SIGNATURES = {
                                  _i, _i, _i, _i, _i64, _i, _p]),
     "kvb_score_decode": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
                               _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _p]),
+    "kvb_candidate_capacity": (_i, [_i]),
+    "kvb_sample_thresholds": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
+                                   _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),
+    "kvb_score_candidates": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
+                                  _i, _i, _i, _i, _i, _i, _p, _p, _p, _i, _i, _p]),
     "kvb_select_topk_workspace_bytes": (_sz, [_i, _i, _i]),
     "kvb_select_topk": (_i, [_p, _i64, _p, _i, _i, _i, _i64, _i, _p, _p, _p, _p, _p, _sz, _i, _p]),
     "kvb_select_topk_static_limit_bytes": (_sz, []),

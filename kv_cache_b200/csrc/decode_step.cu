@@ -198,6 +198,32 @@ static int fast_cap(int kk) {
   return c;
 }
 
+static void fill_score_params(ScoreParams& sp, const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed,
+                              int64_t packed_sb, int64_t packed_sh, const float* scale, int64_t scale_sb,
+                              int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T, int D, int C,
+                              const int32_t* T_dev) {
+  sp.query = reinterpret_cast<const __nv_bfloat16*>(query); sp.q_sb = q_sb; sp.q_sh = q_sh;
+  sp.packed = packed; sp.packed_sb = packed_sb; sp.packed_sh = packed_sh;
+  sp.scale = scale; sp.scale_sb = scale_sb; sp.scale_sh = scale_sh;
+  sp.channel_idx = channel_idx;
+  sp.B = B; sp.Hq = Hq; sp.Hkv = Hkv; sp.T = T; sp.D = D; sp.C = C; sp.G = Hq / Hkv;
+  sp.T_dev = T_dev;
+  sp.gmax_out = nullptr; sp.acc_out = nullptr; sp.deq_out = nullptr; sp.hist_out = nullptr;
+  sp.tau = nullptr; sp.cand = nullptr; sp.cand_count = nullptr; sp.cand_cap = 0;
+  sp.units_per_row = 0; sp.full_tiles = 0; sp.total_units = 0;
+}
+
+static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cudaStream_t st) {
+  SampleParams sq;
+  sq.sp = sp; sq.tau = tau; sq.top_k = top_k; sq.cap = cap;
+  const int R = sp.B * sp.Hkv;
+  if (sp.C == 32) sample_launch_g<32>(sq, R, st);
+  else if (sp.C == 64) sample_launch_g<64>(sq, R, st);
+  else sample_launch_g<128>(sq, R, st);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  return KVB_OK;
+}
+
 // Workspace of the fused step. The regions that must start at zero (attention split counters,
 // select candidate counters, histogram) are adjacent so ONE memset per step clears them.
 struct StepLayout {
@@ -296,21 +322,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       float* ftau = reinterpret_cast<float*>(ws + L.off_ftau);
       uint64_t* fcand = reinterpret_cast<uint64_t*>(ws + L.off_fcand);
 
-      SampleParams sq;
-      sq.sp.query = reinterpret_cast<const __nv_bfloat16*>(p->query); sq.sp.q_sb = p->q_sb; sq.sp.q_sh = p->q_sh;
-      sq.sp.packed = p->packed; sq.sp.packed_sb = p->packed_sb; sq.sp.packed_sh = p->packed_sh;
-      sq.sp.scale = p->scale; sq.sp.scale_sb = p->scale_sb; sq.sp.scale_sh = p->scale_sh;
-      sq.sp.channel_idx = p->channel_idx;
-      sq.sp.B = p->B; sq.sp.Hq = p->Hq; sq.sp.Hkv = p->Hkv; sq.sp.T = T; sq.sp.D = p->D; sq.sp.C = p->C; sq.sp.G = G;
-      sq.sp.T_dev = T_dev;
-      sq.sp.gmax_out = nullptr; sq.sp.acc_out = nullptr; sq.sp.deq_out = nullptr; sq.sp.hist_out = nullptr;
-      sq.sp.tau = nullptr; sq.sp.cand = nullptr; sq.sp.cand_count = nullptr; sq.sp.cand_cap = 0;
-      sq.sp.units_per_row = 0; sq.sp.full_tiles = 0; sq.sp.total_units = 0;
-      sq.tau = ftau; sq.top_k = p->top_k; sq.cap = fcap;
-      if (p->C == 32) sample_launch_g<32>(sq, L.R, st);
-      else if (p->C == 64) sample_launch_g<64>(sq, L.R, st);
-      else sample_launch_g<128>(sq, L.R, st);
-      KVB_CHECK_CUDA(cudaGetLastError());
+      ScoreParams base;
+      fill_score_params(base, p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
+                        p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, T_dev);
+      rc = sample_run(base, ftau, p->top_k, fcap, st);
+      if (rc != KVB_OK) return rc;
 
       ScoreEmit emit{ftau, fcand, fcount, fcap};
       rc = score_run(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
@@ -319,7 +335,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       if (rc != KVB_OK) return rc;
 
       RescueParams rq;
-      rq.sp = sq.sp;
+      rq.sp = base;
       rq.sp.gmax_out = gmax;
       rq.cand_count = fcount; rq.row_failed = ffailed; rq.top_k = p->top_k; rq.cap = fcap;
       score_rescue_kernel<<<L.R, RS_THREADS, 0, st>>>(rq);
@@ -383,4 +399,41 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                   p->out, nullptr, attcnt, attpart, /*counters_zeroed=*/true, device, st);
   if (rc != KVB_OK) return rc;
   return KVB_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_candidate_capacity(int top_k) {
+  if (top_k <= 0 || 3 * top_k > kvb::SEL_MAX_K) return 0;
+  return kvb::fast_cap(top_k);
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_sample_thresholds(
+    const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
+    int D, int C, int top_k, float* tau, int device, void* stream) {
+  using namespace kvb;
+  if (!query || !packed || !scale || !channel_idx || !tau) return KVB_BAD_ARG;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || (Hq % Hkv) || top_k <= 0) return KVB_BAD_SHAPE;
+  if (!score_stream_supported(C, Hq / Hkv, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh)) return KVB_BAD_SHAPE;
+  const int cap = kvb_candidate_capacity(top_k < T ? top_k : T);
+  if (cap == 0) return KVB_BAD_SHAPE;
+  DeviceGuard guard(device);
+  if (!guard.ok) return KVB_BAD_DEVICE;
+  ScoreParams sp;
+  fill_score_params(sp, query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq,
+                    Hkv, T, D, C, nullptr);
+  return sample_run(sp, tau, top_k, cap, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_score_candidates(
+    const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
+    int D, int C, const float* tau, uint64_t* cand, uint32_t* cand_count, int cand_cap, int device, void* stream) {
+  using namespace kvb;
+  if (!tau || !cand || !cand_count || cand_cap <= 0) return KVB_BAD_ARG;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
+  if (!score_stream_supported(C, Hq / Hkv, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh)) return KVB_BAD_SHAPE;
+  ScoreEmit emit{tau, cand, cand_count, cand_cap};
+  return score_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq, Hkv,
+                   T, D, C, nullptr, nullptr, nullptr, nullptr, &emit, nullptr, device,
+                   reinterpret_cast<cudaStream_t>(stream));
 }

@@ -188,6 +188,36 @@ def score(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channe
     return ScoreResult(acc, deq, gmax, hist)
 
 
+def score_candidates(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
+                     history_count: int, top_k: int, tau: Optional[torch.Tensor] = None):
+    """Candidate form of the scorer: per KV head the tokens whose group maximum reaches a sampled
+    threshold, as 64-bit composites ``key << 32 | ~token``. Returns ``(cand uint64-as-int64 [B*Hkv,cap],
+    count int32 [B*Hkv], tau fp32 [B*Hkv])``; ``count`` may exceed ``cap`` (entries beyond it are lost)."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    Hkv = packed.shape[1]
+    C_ = int(channel_idx.shape[-1])
+    _check_side_cache(packed, scale, C_)
+    T = int(history_count)
+    dev = query.device
+    lib = _native.lib()
+    cap = lib.kvb_candidate_capacity(min(int(top_k), T))
+    if cap == 0:
+        raise RuntimeError("top_k too large for the candidate form")
+    channel_idx = channel_idx.to(device=dev, dtype=torch.int32).contiguous()
+    common = (query.data_ptr(), query.stride(0), query.stride(1), packed.data_ptr(), packed.stride(0), packed.stride(1),
+              scale.data_ptr(), scale.stride(0), scale.stride(1), channel_idx.data_ptr(), B, Hq, Hkv, T, D, C_)
+    if tau is None:
+        tau = torch.empty((B * Hkv,), dtype=torch.float32, device=dev)
+        check(lib.kvb_sample_thresholds(*common, int(top_k), tau.data_ptr(), _dev(query), _stream(dev)),
+              "kvb_sample_thresholds")
+    cand = torch.empty((B * Hkv, cap), dtype=torch.int64, device=dev)
+    count = torch.zeros((B * Hkv, 32), dtype=torch.int32, device=dev)
+    check(lib.kvb_score_candidates(*common, tau.data_ptr(), cand.data_ptr(), count.data_ptr(), cap, _dev(query),
+                                   _stream(dev)), "kvb_score_candidates")
+    return cand, count[:, 0], tau
+
+
 # ------------------------------------------------------------------------------------------
 # stage 3: select
 # ------------------------------------------------------------------------------------------

@@ -70,3 +70,30 @@ def test_gmax_only_and_strided_side_cache(cuda_device):
     assert r.acc is None and r.deq is None
     assert torch.equal(r.gmax, full.gmax)
     assert torch.equal(full.gmax, full.deq.view(2, 2, 4, -1).amax(2) + 0.0)
+
+
+@pytest.mark.parametrize("T,k,C,G", [(40000, 1024, 64, 4), (20000, 256, 32, 2), (5000, 300, 64, 4)])
+def test_candidate_form_contains_the_exact_top_k(cuda_device, T, k, C, G):
+    """The scorer's candidate lists: every entry is (key of the exact group max, token), the count is
+    within [k, capacity] on this data, and the exact top-k is a subset."""
+    w, q, key, _ = make_case(cuda_device, batch=2, q_heads=2 * G, kv_heads=2, context=T, channels=C)
+    ch = ops.choose_channels(key[:, :, :T], C)
+    packed, scale = ops.quantize(key[:, :, :T], ch)
+    cand, count, tau = ops.score_candidates(q, packed, scale, ch, T, k)
+    full = ops.score(q, packed, scale, ch, T, want_acc=False, want_deq=False).gmax.view(-1, T)
+    want, _ = oracle.select(full.cpu(), k)
+    cap = cand.shape[1]
+    for r in range(full.shape[0]):
+        n = int(count[r])
+        assert k <= n <= cap
+        c = cand[r, :n].cpu()
+        tok = 0xFFFFFFFF - (c & 0xFFFFFFFF)
+        keybits = (c >> 32) & 0xFFFFFFFF
+        g = full[r].cpu()[tok]
+        gk = g.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        gk = torch.where(gk >= 2**31, (~gk) & 0xFFFFFFFF, gk | 2**31)
+        assert torch.equal(keybits, gk)                                   # composites carry the exact score keys
+        assert len(set(tok.tolist())) == n                                # no token twice
+        assert (g >= tau[r].cpu()).all()
+        assert int((full[r] >= tau[r]).sum()) == n                        # and none missed
+        assert set(want[r].tolist()) <= set(tok.tolist())
