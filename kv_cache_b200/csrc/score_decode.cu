@@ -255,13 +255,15 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
     // ballot gives every taker its slot), so the hot loop has no atomics at all.
     uint64_t* wbuf = s_cbuf + warp * SC_EMIT_WARP_BUF;
     uint32_t wcount = 0;
+    bool wdead = false;          // the row's list is already over capacity: it will be re-scored, stop feeding it
     auto finish = [&](float m, int64_t t, bool active) {
       if (gmax_row && active) st_global_hint_f32(gmax_row + t, m, keep);
       if (HIST && active) atomicAdd(&s_hist[float_to_key(m) >> (32 - SC_HIST_BITS)], 1u);
       if (EMIT) {
-        const bool take = active && (m >= tau);
+        const bool take = active && !wdead && (m >= tau);
         const uint32_t mask = __ballot_sync(0xffffffffu, take);
         if (mask) {
+          bool over = false;
           if (take) {
             const uint64_t c = make_composite(m, (uint32_t)t);
             const uint32_t pos = wcount + (uint32_t)__popc(mask & ((1u << lane) - 1u));
@@ -270,9 +272,11 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
             } else {                                           // buffer full: straight to the row's list
               const uint32_t gp = atomicAdd(count_row, 1u);
               if (gp < (uint32_t)p.cand_cap) cand_row[gp] = c;
+              else over = true;                                // count > capacity already marks the row as failed
             }
           }
           wcount += (uint32_t)__popc(mask);
+          if (__any_sync(0xffffffffu, over)) wdead = true;
         }
       }
     };

@@ -586,7 +586,10 @@ class GraphedDecode:
         self._v = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16, device=dev)
         self._out = torch.empty((B, 1, q_heads, D), dtype=torch.bfloat16, device=dev)
         self.stream = torch.cuda.Stream(dev)
-        self.h_query.zero_(); self.h_key_row.zero_(); self.h_value_row.zero_()
+        # warm-up contents: a well-spread query (an all-zero one would tie every score and send every row
+        # through the slow exact-refinement path), zero K/V rows
+        self.h_query.copy_(torch.randn((B, q_heads, D), generator=torch.Generator().manual_seed(0)).to(torch.bfloat16))
+        self.h_key_row.zero_(); self.h_value_row.zero_()
 
         def body():
             self._q.copy_(self.h_query, non_blocking=True)
