@@ -274,6 +274,33 @@ int kvb_attend_selected(const void* query, int64_t q_sb, int64_t q_sh,
                         void* workspace, size_t workspace_bytes,
                         int device, void* stream);
 
+/* Sequence-shard front end and merge (no counterpart in the reference, which has no sharding).
+ *
+ * kvb_shard_candidates: the exact local top-k of a shard in one call (sampled threshold, candidate
+ *   scorer, bounds check with exact rescue, exact finish): out_comp uint64 [B*Hkv, kk],
+ *   kk = min(top_k, T), each entry (order-preserving key of the group max) << 32 |
+ *   (0xFFFFFFFF - (token + id_offset)), in no particular order. Needs the streaming configuration
+ *   and top_k small enough for the candidate capacity (else KVB_BAD_SHAPE: use kvb_score_decode +
+ *   kvb_select_topk). workspace >= kvb_shard_candidates_workspace_bytes(B, Hkv, T, top_k).
+ * kvb_merge_candidates: the global top-k of N such lists after an all-gather: gathered uint64
+ *   [N, R, kk] -> out_idx int32 [R, min(top_k, N*kk)] global token ids, ascending when
+ *   id_range (the total token count) is small enough for the on-chip bitmap (about 1.2 M),
+ *   otherwise in arbitrary order. With N > 1 every list must hold top_k entries (kk == top_k).
+ *   The composites are unique, so every rank that runs this on the same gathered data gets the
+ *   same set. */
+size_t kvb_shard_candidates_workspace_bytes(int B, int Hkv, int T, int top_k);
+
+int kvb_shard_candidates(const void* query, int64_t q_sb, int64_t q_sh,
+                         const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                         const float* scale, int64_t scale_sb, int64_t scale_sh,
+                         const int32_t* channel_idx,
+                         int B, int Hq, int Hkv, int T, int D, int C, int top_k, int64_t id_offset,
+                         uint64_t* out_comp, void* workspace, size_t workspace_bytes,
+                         int device, void* stream);
+
+int kvb_merge_candidates(const uint64_t* gathered, int N, int R, int kk, int top_k, int64_t id_range,
+                         int32_t* out_idx, int device, void* stream);
+
 /* Combine N shard partials [N,B,Hq,D+2] (layout of out_partial above) into bf16 [B,1,Hq,D]:
  * o = sum_r e^{m_r-m} o_r / sum_r e^{m_r-m} l_r, shards with l == 0 ignored. No reference
  * counterpart (the reference has no sequence sharding). */

@@ -349,6 +349,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       sp.tokens_per_cta = 0; sp.thresholds = nullptr;
       sp.order_by_index = 1;
       sp.from_candidates = 1; sp.row_failed = ffailed; sp.T_dev = T_dev;
+      sp.out_comp = nullptr; sp.gather = nullptr; sp.gather_n = 0; sp.gather_len = 0; sp.gather_stride = 0;
       const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
       size_t smem = (size_t)fcap * 8 + SEL_FINAL_FIXED_SMEM;
       sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
@@ -398,6 +399,154 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                   list, &ap, T_dev ? &adl : nullptr, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D, L.S, p->scaling,
                   p->out, nullptr, attcnt, attpart, /*counters_zeroed=*/true, device, st);
   if (rc != KVB_OK) return rc;
+  return KVB_OK;
+}
+
+namespace kvb {
+
+// Workspace of kvb_shard_candidates: [counters | failed flags] (zeroed per call) | tau | candidates | gmax rows (rescue only)
+struct ShardLayout {
+  int R, kk, cap;
+  size_t off_count, off_failed, zero_bytes, off_tau, off_cand, off_gmax, bytes;
+};
+
+static ShardLayout shard_layout(int B, int Hkv, int T, int top_k) {
+  ShardLayout L;
+  L.R = B * Hkv;
+  L.kk = top_k < T ? top_k : T;
+  L.cap = fast_cap(L.kk > 0 ? L.kk : 1);
+  size_t off = 0;
+  L.off_count = off;  off += round_up(sizeof(uint32_t) * (size_t)L.R * SC_COUNT_STRIDE, 256);
+  L.off_failed = off; off += round_up(sizeof(uint32_t) * (size_t)L.R, 256);
+  L.zero_bytes = off;
+  L.off_tau = off;    off += round_up(sizeof(float) * (size_t)L.R, 256);
+  L.off_cand = off;   off += round_up(sizeof(uint64_t) * (size_t)L.R * L.cap, 256);
+  L.off_gmax = off;   off += round_up(sizeof(float) * (size_t)L.R * (size_t)T, 256);
+  L.bytes = off;
+  return L;
+}
+
+// The conditions under which the sampled-threshold front end applies to rows of length T.
+static bool fast_front_ok(int C, int G, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                          const float* scale, int64_t scale_sb, int64_t scale_sh, int T, int kk, int cap) {
+  if (!score_stream_supported(C, G, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh)) return false;
+  if (3 * kk > cap) return false;
+  if (T <= cap) return true;
+  int run_len = (T / FS_RUNS) / FS_PER_THREAD * FS_PER_THREAD;
+  if (run_len > FS_MAX_SAMPLE / FS_RUNS) run_len = FS_MAX_SAMPLE / FS_RUNS;
+  if (run_len < FS_PER_THREAD) return false;
+  const double frac = (double)(run_len * FS_RUNS) / (double)T;
+  double expect = 1.75 * kk;
+  if (expect * frac < 96.0) expect = 96.0 / frac;
+  return 1.7 * expect <= (double)cap;
+}
+
+}  // namespace kvb
+
+extern "C" __attribute__((visibility("default"))) size_t kvb_shard_candidates_workspace_bytes(int B, int Hkv, int T,
+                                                                                              int top_k) {
+  if (B <= 0 || Hkv <= 0 || T <= 0 || top_k <= 0) return 0;
+  return kvb::shard_layout(B, Hkv, T, top_k).bytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
+    const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
+    int D, int C, int top_k, int64_t id_offset, uint64_t* out_comp, void* workspace, size_t workspace_bytes,
+    int device, void* stream) {
+  using namespace kvb;
+  if (!query || !packed || !scale || !channel_idx || !out_comp || !workspace) return KVB_BAD_ARG;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || top_k <= 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
+  if (id_offset < 0 || id_offset + T > 0x7fffffffLL) return KVB_BAD_SHAPE;
+  if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
+  const ShardLayout L = shard_layout(B, Hkv, T, top_k);
+  if (workspace_bytes < L.bytes) return KVB_WORKSPACE_TOO_SMALL;
+  if (!fast_front_ok(C, Hq / Hkv, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, T, L.kk, L.cap))
+    return KVB_BAD_SHAPE;
+  DeviceGuard guard(device);
+  if (!guard.ok) return KVB_BAD_DEVICE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  uint32_t* count = reinterpret_cast<uint32_t*>(ws + L.off_count);
+  uint32_t* failed = reinterpret_cast<uint32_t*>(ws + L.off_failed);
+  float* tau = reinterpret_cast<float*>(ws + L.off_tau);
+  uint64_t* cand = reinterpret_cast<uint64_t*>(ws + L.off_cand);
+  float* gmax = reinterpret_cast<float*>(ws + L.off_gmax);
+  KVB_CHECK_CUDA(cudaMemsetAsync(ws, 0, L.zero_bytes, st));
+
+  ScoreParams base;
+  fill_score_params(base, query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B,
+                    Hq, Hkv, T, D, C, nullptr);
+  int rc = sample_run(base, tau, top_k, L.cap, st);
+  if (rc != KVB_OK) return rc;
+  ScoreEmit emit{tau, cand, count, L.cap};
+  rc = score_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq, Hkv, T,
+                 D, C, nullptr, nullptr, nullptr, nullptr, &emit, nullptr, device, st);
+  if (rc != KVB_OK) return rc;
+  RescueParams rq;
+  rq.sp = base;
+  rq.sp.gmax_out = gmax;
+  rq.cand_count = count; rq.row_failed = failed; rq.top_k = top_k; rq.cap = L.cap;
+  score_rescue_kernel<<<L.R, RS_THREADS, 0, st>>>(rq);
+  KVB_CHECK_CUDA(cudaGetLastError());
+
+  SelectParams sp;
+  sp.scores = gmax; sp.row_stride = T; sp.payload = nullptr;
+  sp.R = L.R; sp.T = T; sp.k = top_k; sp.kk = L.kk; sp.idx_offset = id_offset;
+  sp.out_idx32 = nullptr; sp.out_idx64 = nullptr; sp.out_scores = nullptr; sp.out_comp = out_comp;
+  sp.hist = nullptr; sp.cand = cand; sp.cand_count = count; sp.cap = L.cap;
+  sp.tokens_per_cta = 0; sp.thresholds = nullptr;
+  sp.order_by_index = 2; sp.use_bitmap = 0;
+  sp.from_candidates = 1; sp.row_failed = failed; sp.T_dev = nullptr;
+  sp.gather = nullptr; sp.gather_n = 0; sp.gather_len = 0; sp.gather_stride = 0;
+  const size_t smem = (size_t)L.cap * 8 + SEL_FINAL_FIXED_SMEM;
+  static bool attr_done[64] = {false};
+  if (device < 64 && !attr_done[device]) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)SEL_SMEM_LIMIT));
+    attr_done[device] = true;
+  }
+  select_final_kernel<<<L.R, SEL_FINAL_THREADS, smem, st>>>(sp);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  return KVB_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(const uint64_t* gathered, int N, int R,
+                                                                            int kk, int top_k, int64_t id_range,
+                                                                            int32_t* out_idx, int device,
+                                                                            void* stream) {
+  using namespace kvb;
+  if (!gathered || !out_idx) return KVB_BAD_ARG;
+  if (N <= 0 || R <= 0 || kk <= 0 || top_k <= 0 || id_range <= 0 || id_range > 0x7fffffffLL) return KVB_BAD_SHAPE;
+  if (kk < top_k && N > 1) return KVB_BAD_SHAPE;            // every shard must bring top_k entries (see header)
+  const int64_t total = (int64_t)N * kk;
+  const int kout = (int)(top_k < total ? top_k : total);
+  if (kout > SEL_MAX_K) return KVB_BAD_SHAPE;
+  DeviceGuard guard(device);
+  if (!guard.ok) return KVB_BAD_DEVICE;
+  SelectParams sp;
+  sp.scores = nullptr; sp.row_stride = 0; sp.payload = nullptr;
+  sp.R = R; sp.T = (int)id_range; sp.k = top_k; sp.kk = kout; sp.idx_offset = 0;
+  sp.out_idx32 = out_idx; sp.out_idx64 = nullptr; sp.out_scores = nullptr; sp.out_comp = nullptr;
+  sp.hist = nullptr; sp.cand = nullptr; sp.cand_count = nullptr; sp.cap = select_cap(kout);
+  sp.tokens_per_cta = 0; sp.thresholds = nullptr;
+  sp.from_candidates = 0; sp.row_failed = nullptr; sp.T_dev = nullptr;
+  sp.gather = gathered; sp.gather_n = N; sp.gather_len = kk; sp.gather_stride = (int64_t)R * kk;
+  const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((id_range + 31) / 32);
+  size_t smem = (size_t)sp.cap * 8 + SEL_FINAL_FIXED_SMEM;
+  if (smem + bitmap_bytes <= SEL_SMEM_LIMIT) {
+    sp.order_by_index = 1; sp.use_bitmap = 1; smem += bitmap_bytes;      // ascending global ids
+  } else {
+    sp.order_by_index = 2; sp.use_bitmap = 0;                              // exact set, arbitrary order
+  }
+  static bool attr_done[64] = {false};
+  if (device < 64 && !attr_done[device]) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)SEL_SMEM_LIMIT));
+    attr_done[device] = true;
+  }
+  select_final_kernel<<<R, SEL_FINAL_THREADS, smem, reinterpret_cast<cudaStream_t>(stream)>>>(sp);
+  KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
 }
 

@@ -46,6 +46,13 @@ struct SelectParams {
   int from_candidates;        // the candidate lists were filled by the scorer: no histogram / thresholds
   const uint32_t* row_failed; // [R] with from_candidates: rows whose list is unusable; `scores` holds their full row
   const int32_t* T_dev;       // optional (fused step): the row length lives on the device; T is then its upper bound
+  uint64_t* out_comp;         // optional output: the winners' composites, re-based to the returned (global) index
+  // gathered source (merge of sequence shards): the row's elements are gather_n segments of gather_len
+  // ready-made composites (global ids), segment s of row r at gather + s*gather_stride + r*gather_len;
+  // T is then the global id range (for the bitmap), and every segment must hold at least k real entries
+  const uint64_t* gather;
+  int gather_n, gather_len;
+  int64_t gather_stride;
 };
 
 __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row, int64_t t) {
@@ -289,7 +296,17 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
-  const float* src = p.scores + (int64_t)row * p.row_stride;
+  const float* src = p.scores ? p.scores + (int64_t)row * p.row_stride : nullptr;
+  const bool gathered = p.gather_n > 0;
+  const int64_t n_src = gathered ? (int64_t)p.gather_n * p.gather_len : (int64_t)p.T;     // elements of the row
+  // composite of element t of this row, whatever the source
+  auto load_comp = [&](int64_t t) -> uint64_t {
+    if (gathered) {
+      const int64_t seg = t / p.gather_len;
+      return __ldcg(p.gather + seg * p.gather_stride + (int64_t)row * p.gather_len + (t - seg * p.gather_len));
+    }
+    return make_composite(src[t], element_index(p, row, t));
+  };
 
   uint64_t prefix;                                      // top `fixed` bits of the k-th composite so far
   int fixed;
@@ -297,7 +314,47 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   uint32_t in_prefix;
   int n = 0;                                            // candidates in s_cand: all with composite >= prefix
   bool have_candidates;
-  if (p.from_candidates) {
+  const uint64_t* cand = p.cand ? p.cand + (int64_t)row * p.cap : nullptr;
+  if (gathered) {
+    // Every segment holds >= kk real entries, so the k-th best overall is at least as good as the
+    // WORST entry of any one segment: everything below  tau = max over segments of (segment minimum)
+    // can be dropped at once. Usually that leaves little more than kk elements.
+    prefix = 0; fixed = 0; need = (uint32_t)p.kk; in_prefix = (uint32_t)n_src;
+    uint64_t tau = 0;
+    for (int sgm = 0; sgm < p.gather_n; ++sgm) {
+      uint64_t mn = ~0ull;
+      for (int j = tid; j < p.gather_len; j += SEL_FINAL_THREADS) {
+        const uint64_t c = load_comp((int64_t)sgm * p.gather_len + j);
+        mn = c < mn ? c : mn;
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) {
+        const uint64_t o = __shfl_xor_sync(0xffffffffu, mn, off);
+        mn = o < mn ? o : mn;
+      }
+      uint64_t* s_red = reinterpret_cast<uint64_t*>(s_hist);
+      if ((tid & 31) == 0) s_red[tid >> 5] = mn;
+      __syncthreads();
+      uint64_t m2 = s_red[0];
+      for (int w = 1; w < SEL_FINAL_THREADS / 32; ++w) m2 = s_red[w] < m2 ? s_red[w] : m2;
+      tau = m2 > tau ? m2 : tau;
+      __syncthreads();
+    }
+    if (tid == 0) *s_count = 0;
+    __syncthreads();
+    for (int64_t t = tid; t < n_src; t += SEL_FINAL_THREADS) {
+      const uint64_t c = load_comp(t);
+      if (c >= tau) {
+        const uint32_t pos = atomicAdd(s_count, 1u);
+        if (pos < (uint32_t)p.cap) s_cand[pos] = c;
+      }
+    }
+    __syncthreads();
+    const uint32_t kept = *s_count;
+    __syncthreads();
+    have_candidates = kept <= (uint32_t)p.cap;
+    if (have_candidates) { n = (int)kept; in_prefix = kept; }
+  } else if (p.from_candidates) {
     prefix = 0; fixed = 0; need = (uint32_t)p.kk;
     const bool failed = p.row_failed != nullptr && p.row_failed[row] != 0;
     have_candidates = !failed;
@@ -307,6 +364,8 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
       const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
       n = (int)(have < (uint32_t)p.cap ? have : (uint32_t)p.cap);
       in_prefix = (uint32_t)n;
+      for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
+      __syncthreads();
     }
   } else {
     const uint4 thr = p.thresholds[row];
@@ -316,13 +375,11 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
       n = (int)(thr.y + thr.z);
       const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
       if ((uint32_t)n > have) n = (int)have;            // cannot happen; keeps reads in bounds
+      for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
+      __syncthreads();
     }
   }
-  if (have_candidates) {
-    const uint64_t* cand = p.cand + (int64_t)row * p.cap;
-    for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
-    __syncthreads();
-  } else {
+  if (!have_candidates) {
     // Too many candidates share the prefix (or none were prepared): refine over the row itself.
     while ((uint32_t)p.kk - need + in_prefix > (uint32_t)p.cap && fixed < 64) {
       const int width = (64 - fixed) >= 11 ? 11 : (64 - fixed);
@@ -330,8 +387,8 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
       const int nb = 1 << width;
       for (int i = tid; i < nb; i += SEL_FINAL_THREADS) s_hist[i] = 0;
       __syncthreads();
-      for (int64_t t = tid; t < p.T; t += SEL_FINAL_THREADS) {
-        const uint64_t c = make_composite(src[t], element_index(p, row, t));
+      for (int64_t t = tid; t < n_src; t += SEL_FINAL_THREADS) {
+        const uint64_t c = load_comp(t);
         if (fixed == 0 || (c >> (64 - fixed)) == prefix)
           atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
       }
@@ -346,8 +403,8 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     if (tid == 0) *s_count = 0;
     __syncthreads();
     const int sh = 64 - fixed;
-    for (int64_t t = tid; t < p.T; t += SEL_FINAL_THREADS) {
-      const uint64_t c = make_composite(src[t], element_index(p, row, t));
+    for (int64_t t = tid; t < n_src; t += SEL_FINAL_THREADS) {
+      const uint64_t c = load_comp(t);
       const bool take = (sh == 0) ? (c >= prefix) : (sh >= 64 ? true : ((c >> sh) >= prefix));
       if (take) {
         const uint32_t pos = atomicAdd(s_count, 1u);
@@ -381,6 +438,30 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   }
   const uint64_t kth = fixed >= 64 ? prefix : (fixed == 0 ? 0ull : (prefix << (64 - fixed)));   // winners: composite >= kth
 
+  // Composites built from scores carry index + idx_offset; scorer-made lists carry row-local ids and
+  // gathered ones global ids: id_sub maps a composite's id to the bitmap position, id_add to the output.
+  const uint32_t id_sub = (p.from_candidates || gathered) ? 0u : (uint32_t)p.idx_offset;
+  const uint32_t id_add = gathered ? 0u : (uint32_t)p.idx_offset;
+  if (p.order_by_index == 2) {
+    // Unordered output: the winners in whatever order the threads meet them (the SET is exact).
+    if (tid == 0) *s_count = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
+      const uint64_t c = s_cand[i];
+      if (c >= kth) {
+        const uint32_t pos = atomicAdd(s_count, 1u);
+        if (pos < (uint32_t)p.kk) {
+          const int64_t o = (int64_t)row * out_pitch + pos;
+          const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
+          if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
+          if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
+          if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(c >> 32));
+          if (p.out_comp) p.out_comp[o] = (c & 0xFFFFFFFF00000000ull) | (uint64_t)(0xFFFFFFFFu - idx);
+        }
+      }
+    }
+    return;
+  }
   if (p.use_bitmap) {
     // Ascending-index output: one bit per token of the row, read out in order.
     const int words = (p.T + 31) >> 5;
@@ -389,7 +470,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
       const uint64_t c = s_cand[i];
       if (c >= kth) {
-        const uint32_t local = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - (uint32_t)p.idx_offset;
+        const uint32_t local = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub;
         atomicOr(&s_bitmap[local >> 5], 1u << (local & 31));
       }
     }
@@ -410,10 +491,10 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
         const uint32_t local = (uint32_t)(w0 + j) * 32u + (uint32_t)bit;
         if (pos < (uint32_t)p.kk) {
           const int64_t o = (int64_t)row * out_pitch + pos;
-          const uint32_t idx = local + (uint32_t)p.idx_offset;
+          const uint32_t idx = local + id_add;
           if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
           if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
-          if (p.out_scores) {
+          if (p.out_scores && src) {
             float sv = src[local];
             if (sv == 0.0f) sv = 0.0f;
             p.out_scores[o] = sv;
@@ -440,7 +521,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   for (int i = tid; i < p.kk; i += SEL_FINAL_THREADS) {
     uint64_t c = s_cand[i];
     if (p.order_by_index) c = ((c & 0xFFFFFFFFull) << 32) | (c >> 32);
-    const uint32_t idx = 0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull);
+    const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
     const int64_t o = (int64_t)row * out_pitch + i;
     if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
     if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
@@ -493,7 +574,7 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   if (!scores || !workspace) return KVB_BAD_ARG;
   if (!out_idx32 && !out_idx64 && !out_scores) return KVB_BAD_ARG;
   if (R <= 0 || T <= 0 || k <= 0 || R > 65535) return KVB_BAD_SHAPE;
-  if (order != 0 && order != 1) return KVB_BAD_ARG;
+  if (order != 0 && order != 1 && order != 2) return KVB_BAD_ARG;
   const int kk = k < T ? k : T;
   if (kk > SEL_MAX_K) return KVB_BAD_SHAPE;
   if (row_stride < T) return KVB_BAD_SHAPE;
@@ -514,6 +595,8 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   p.from_candidates = 0;
   p.row_failed = nullptr;
   p.T_dev = nullptr;
+  p.out_comp = nullptr;
+  p.gather = nullptr; p.gather_n = 0; p.gather_len = 0; p.gather_stride = 0;
   const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
   size_t smem = (size_t)p.cap * 8 + SEL_FINAL_FIXED_SMEM;
   p.use_bitmap = (order == 1 && !payload && smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;

@@ -396,6 +396,44 @@ def attend_selected(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
     return part if return_partial else out
 
 
+def shard_candidates(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
+                     history_count: int, top_k: int, id_offset: int = 0,
+                     workspace: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """Exact local top-``k`` of a sequence shard as 64-bit composites with GLOBAL token ids, int64
+    ``[B*Hkv, min(k,T)]``, unordered. Returns ``None`` when the configuration has no candidate front
+    end (the caller then uses ``score`` + ``select``)."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    Hkv = packed.shape[1]
+    C_ = int(channel_idx.shape[-1])
+    _check_side_cache(packed, scale, C_)
+    T = int(history_count)
+    dev = query.device
+    lib = _native.lib()
+    need = lib.kvb_shard_candidates_workspace_bytes(B, Hkv, T, int(top_k))
+    ws = workspace if workspace is not None and workspace.numel() >= need else torch.empty(need, dtype=torch.uint8, device=dev)
+    out = torch.empty((B * Hkv, min(int(top_k), T)), dtype=torch.int64, device=dev)
+    rc = lib.kvb_shard_candidates(
+        query.data_ptr(), query.stride(0), query.stride(1), packed.data_ptr(), packed.stride(0), packed.stride(1),
+        scale.data_ptr(), scale.stride(0), scale.stride(1), channel_idx.data_ptr(), B, Hq, Hkv, T, D, C_, int(top_k),
+        int(id_offset), out.data_ptr(), ws.data_ptr(), ws.numel(), _dev(query), _stream(dev))
+    if rc == 1:          # KVB_BAD_SHAPE: not a streaming configuration / k too large for the candidate capacity
+        return None
+    check(rc, "kvb_shard_candidates")
+    return out
+
+
+def merge_candidates(gathered: torch.Tensor, top_k: int, id_range: int) -> torch.Tensor:
+    """Global top-``k`` token ids (int32 ``[R, k']``) from all-gathered composite lists int64 ``[N,R,kk]``."""
+    N, R, kk = gathered.shape
+    gathered = gathered.contiguous()
+    kout = min(int(top_k), N * kk)
+    out = torch.empty((R, kout), dtype=torch.int32, device=gathered.device)
+    check(_native.lib().kvb_merge_candidates(gathered.data_ptr(), N, R, kk, int(top_k), int(id_range), out.data_ptr(),
+                                             _dev(gathered), _stream(gathered.device)), "kvb_merge_candidates")
+    return out
+
+
 def lse_merge(partials: torch.Tensor) -> torch.Tensor:
     """Combines shard partials fp32 ``[N,B,Hq,D+2]`` into bf16 ``[B,1,Hq,D]``."""
     N, B, Hq, PW = partials.shape

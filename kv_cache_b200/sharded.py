@@ -77,12 +77,47 @@ class CudaBackend:
 class ShardedSparseDecode:
     """One layer's sharded decode step. All ranks of ``group`` call ``step`` collectively."""
 
-    def __init__(self, top_k: int, group: Optional[dist.ProcessGroup] = None, backend=None):
+    def __init__(self, top_k: int, group: Optional[dist.ProcessGroup] = None, backend=None,
+                 total_tokens: Optional[int] = None):
         self.top_k = int(top_k)
         self.group = group
         self.backend = backend if backend is not None else CudaBackend()
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self.total_tokens = total_tokens      # global history length: enables the one-kernel merge (ascending ids)
+        self._fast: Optional[bool] = None     # agreed by all ranks on the first step
+        self._ws: Optional[torch.Tensor] = None
+
+    def _fast_step(self, query, key_local, value_local, packed, scale, channel_idx, t_local, id_offset, scaling):
+        """Front end and merge as single C calls: sampled-threshold candidate scorer -> exact local
+        top-k as composites -> ONE all-gather -> one-kernel global merge. Returns None when this
+        configuration has no candidate front end."""
+        N = self.world
+        B, Hkv = key_local.shape[0], key_local.shape[1]
+        comp = ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset, self._ws)
+        if comp is None:
+            return None
+        gathered = _all_gather(comp, N, self.group) if N > 1 else comp[None]
+        sel = ops.merge_candidates(gathered, self.top_k, self.total_tokens).view(B, Hkv, -1)
+        part = self.backend.attend_partial(query, key_local, value_local, sel, t_local, id_offset,
+                                           self.rank == N - 1, scaling)
+        parts = _all_gather(part, N, self.group) if N > 1 else part[None]
+        return self.backend.combine(parts), sel
+
+    def capture(self, *args, **kwargs):
+        """Captures one step (collectives included) into a CUDA graph after two eager warm-up steps;
+        returns ``(graph, outputs)``: replaying the graph refreshes ``outputs`` in place. All ranks
+        must capture and replay together."""
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                self.step(*args, **kwargs)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                outputs = self.step(*args, **kwargs)
+        stream.synchronize()
+        return graph, outputs
 
     def step(self, query: torch.Tensor, key_local: torch.Tensor, value_local: torch.Tensor, packed: torch.Tensor,
              scale: torch.Tensor, channel_idx: torch.Tensor, t_local: int, id_offset: int,
@@ -93,6 +128,19 @@ class ShardedSparseDecode:
         every rank."""
         be, N = self.backend, self.world
         B, Hkv = key_local.shape[0], key_local.shape[1]
+        if self._fast is None:
+            # every rank must take the same path (the paths issue different collectives): agree once
+            ok = (isinstance(be, CudaBackend) and self.total_tokens is not None and self.top_k <= t_local
+                  and ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset) is not None)
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=query.device)
+            if N > 1:
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            self._fast = bool(flag.item())
+            if self._fast:
+                need = ops._native.lib().kvb_shard_candidates_workspace_bytes(B, Hkv, t_local + 1, self.top_k)
+                self._ws = torch.empty(need, dtype=torch.uint8, device=query.device)
+        if self._fast:
+            return self._fast_step(query, key_local, value_local, packed, scale, channel_idx, t_local, id_offset, scaling)
         sc, idx = be.local_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset)
         R, kk = sc.shape
         # pack (score bits, id) into one buffer so that a single all-gather carries both
@@ -163,7 +211,7 @@ def bench_main(args, w) -> None:
     ops.quantize(key[:, :, :t_local], ch, out=(packed, scale))
     torch.cuda.synchronize()
 
-    eng = ShardedSparseDecode(k)
+    eng = ShardedSparseDecode(k, total_tokens=T)
     stream = torch.cuda.Stream(dev)
 
     def run():
@@ -171,9 +219,17 @@ def bench_main(args, w) -> None:
 
     from .benchutil import METRIC, UNIT, ClockSampler, hbm_peak
 
+    launch = "eager Python step"
+    try:
+        graph, (out, sel) = eng.capture(query, key, value, packed, scale, ch, t_local, t0)
+        run = graph.replay
+        launch = "CUDA graph replay (kernels and both NCCL all-gathers captured)"
+    except Exception as exc:                                   # keep the eager step if capture is not possible
+        launch = f"eager Python step (graph capture failed: {type(exc).__name__})"
+
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
-            out, sel = run()
+            run()
         stream.synchronize()
         sampler = ClockSampler(local_rank)
         if rank == 0:
@@ -181,13 +237,14 @@ def bench_main(args, w) -> None:
         dist.barrier()
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        nrep = max(1, int(1000.0 / max(0.3 * args.steps, 1e-3)))     # about a second of timed work
         start.record(stream)
-        for _ in range(args.steps):
-            out, sel = run()
+        for _ in range(args.steps * nrep):
+            run()
         end.record(stream)
         dist.barrier()
         torch.cuda.synchronize()
-        ms = torch.tensor([start.elapsed_time(end) / args.steps], dtype=torch.float64, device=dev)
+        ms = torch.tensor([start.elapsed_time(end) / (args.steps * nrep)], dtype=torch.float64, device=dev)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         clocks = sampler.stop() if rank == 0 else None
 
@@ -229,7 +286,7 @@ def bench_main(args, w) -> None:
             "dtype": "int4xint8->int32 scores, bf16 attention (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": w.name, "batch": B, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "context": T,
                        "partial_channels": C, "top_k": k, "sharding": f"sequence/{world}",
-                       "collectives": "2 NCCL all-gathers per step (candidates, LSE partials)",
+                       "collectives": "2 NCCL all-gathers per step (candidates, LSE partials)", "launch": launch,
                        "l2": "inputs larger than L2 (scan stream %d MiB per rank)" % ((alg["scan"] // world) >> 20)},
             "clocks": clocks,
             "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e3, "unit": UNIT, "ms_per_step": e2e_ms,

@@ -55,3 +55,31 @@ def test_world_of_one(cuda_device):
         torch.testing.assert_close(out.float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("N,T,k", [(2, 24000, 512), (4, 40000, 1024), (8, 80000, 256)])
+def test_candidate_front_end_and_one_kernel_merge(cuda_device, N, T, k):
+    """kvb_shard_candidates on every shard, concatenated as the all-gather would, then
+    kvb_merge_candidates: the global selection must equal the un-sharded oracle top-k."""
+    w, q, key, value = make_case(cuda_device, batch=2, q_heads=8, kv_heads=2, context=T, channels=64, seed=N)
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    lists = []
+    for r in range(N):
+        t0, t1 = shard_bounds(T, N, r)
+        packed, scale = ops.quantize(key[:, :, t0:t1].contiguous(), ch)
+        comp = ops.shard_candidates(q, packed, scale, ch, t1 - t0, k, id_offset=t0)
+        assert comp is not None and comp.shape == (4, k)
+        lists.append(comp)
+    sel = ops.merge_candidates(torch.stack(lists), k, id_range=T)
+    want = oracle.decode_step(*cpu(q, key, value, ch), k)["selected"].reshape(4, k)
+    assert torch.equal(sel.cpu().long(), torch.sort(want, dim=-1).values)
+
+
+def test_merge_candidates_heavy_ties(cuda_device):
+    """All scores equal: the segment-minimum filter keeps everything, the refinement path decides by id."""
+    N, R, kk = 4, 3, 2048
+    ids = torch.arange(N * kk, device=cuda_device).view(N, 1, kk).expand(N, R, kk)
+    key_bits = 0xC0000000                                   # any fixed score key
+    comp = (torch.full_like(ids, key_bits) << 32) | (0xFFFFFFFF - ids)
+    sel = ops.merge_candidates(comp.contiguous(), kk, id_range=N * kk)
+    assert torch.equal(sel.cpu(), torch.arange(kk, dtype=torch.int32).expand(R, kk))
