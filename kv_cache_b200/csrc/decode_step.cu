@@ -18,8 +18,10 @@ namespace kvb {
 // top-k.
 constexpr int FS_THREADS = 512;
 constexpr int FS_RUNS = 32;                    // evenly spaced runs of sampled tokens per row
-constexpr int FS_MAX_SAMPLE = 4096;            // sampled tokens per row (8 per thread, loaded four at a time)
-constexpr int FS_PER_THREAD = FS_MAX_SAMPLE / FS_THREADS;
+constexpr int FS_PER_THREAD = 8;                // sampled tokens per thread for rows up to FS_LONG_ROW (4096 per row) ...
+constexpr int FS_PER_THREAD_LONG = 16;          // ... and beyond it (8192 per row), loaded four at a time
+constexpr int FS_LONG_ROW = 262144;
+__host__ __device__ inline int fs_per_thread(int T) { return T > FS_LONG_ROW ? FS_PER_THREAD_LONG : FS_PER_THREAD; }
 
 struct SampleParams {
   ScoreParams sp;             // query / packed / scale / channels / shapes (outputs unused)
@@ -44,8 +46,9 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   }
   // sample geometry: FS_RUNS runs of run_len tokens; rank = the sample rank that predicts about
   // 1.75 k (at least 96 / fraction) tokens above tau in the whole row
-  int run_len = (T / FS_RUNS) / FS_PER_THREAD * FS_PER_THREAD;
-  if (run_len > FS_MAX_SAMPLE / FS_RUNS) run_len = FS_MAX_SAMPLE / FS_RUNS;
+  const int per_thread = fs_per_thread(T);
+  int run_len = (T / FS_RUNS) / per_thread * per_thread;
+  if (run_len > per_thread * FS_THREADS / FS_RUNS) run_len = per_thread * FS_THREADS / FS_RUNS;
   const float frac = (float)(run_len * FS_RUNS) / (float)T;
   const int kk = q.top_k < T ? q.top_k : T;
   float expect = 1.75f * (float)kk;
@@ -73,15 +76,15 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   }
   __syncthreads();
   // thread -> run (tid / threads_per_run), FS_PER_THREAD consecutive tokens inside the run
-  const int threads_per_run = run_len / FS_PER_THREAD;
+  const int threads_per_run = run_len / per_thread;
   const int run = tid / threads_per_run;
-  const int64_t t0 = (int64_t)run * (T / FS_RUNS) + (int64_t)(tid - run * threads_per_run) * FS_PER_THREAD;
+  const int64_t t0 = (int64_t)run * (T / FS_RUNS) + (int64_t)(tid - run * threads_per_run) * per_thread;
   const bool live = run < FS_RUNS;
   const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)g * p.packed_sh;
   const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)g * p.scale_sh;
-  float v[FS_PER_THREAD];
-#pragma unroll
-  for (int e0 = 0; e0 < FS_PER_THREAD; e0 += 4) {
+  float v[FS_PER_THREAD_LONG];
+#pragma unroll 1
+  for (int e0 = 0; e0 < per_thread; e0 += 4) {
     // four tokens at a time: all their loads are issued before the first use
     uint32_t wv[4][W];
     float ks[4];
@@ -133,8 +136,7 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   // second level: 11 more key bits inside the bin
   for (int i = tid; i < 2048; i += FS_THREADS) s_hist[i] = 0;
   __syncthreads();
-#pragma unroll
-  for (int e = 0; e < FS_PER_THREAD; ++e) {
+  for (int e = 0; e < per_thread; ++e) {
     if (v[e] == v[e]) {
       const uint32_t key = float_to_key(v[e]);
       if ((key >> (32 - SEL_HIST_BITS)) == bin) atomicAdd(&s_hist[(key >> 9) & 2047u], 1u);
@@ -302,14 +304,15 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                                                 p->scale_sb, p->scale_sh);
   // the sample kernel aims at max(1.75 k, 96 / sampled fraction) candidates: that, with margin, must
   // fit the capacity at the (largest) history length this call can see
-  int run_len = (T / FS_RUNS) / FS_PER_THREAD * FS_PER_THREAD;
-  if (run_len > FS_MAX_SAMPLE / FS_RUNS) run_len = FS_MAX_SAMPLE / FS_RUNS;
+  const int per_thread = fs_per_thread(T);
+  int run_len = (T / FS_RUNS) / per_thread * per_thread;
+  if (run_len > per_thread * FS_THREADS / FS_RUNS) run_len = per_thread * FS_THREADS / FS_RUNS;
   const double frac = run_len > 0 ? (double)(run_len * FS_RUNS) / (double)T : 0.0;
   double expect = 1.75 * L.kk;
   if (frac > 0.0 && expect * frac < 96.0) expect = 96.0 / frac;
   const bool all_candidates = T <= fcap;                    // short rows: tau = -inf, every token is a candidate
   const bool fast = stream_ok && 3 * L.kk <= fcap &&
-                    (all_candidates || (run_len >= FS_PER_THREAD && 1.7 * expect <= (double)fcap));
+                    (all_candidates || (run_len >= per_thread && 1.7 * expect <= (double)fcap));
   const int32_t* T_dev = p->history_count_dev;
   if (T_dev && !fast) return KVB_BAD_SHAPE;
   if (fast) {
@@ -432,9 +435,10 @@ static bool fast_front_ok(int C, int G, const uint8_t* packed, int64_t packed_sb
   if (!score_stream_supported(C, G, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh)) return false;
   if (3 * kk > cap) return false;
   if (T <= cap) return true;
-  int run_len = (T / FS_RUNS) / FS_PER_THREAD * FS_PER_THREAD;
-  if (run_len > FS_MAX_SAMPLE / FS_RUNS) run_len = FS_MAX_SAMPLE / FS_RUNS;
-  if (run_len < FS_PER_THREAD) return false;
+  const int per_thread = fs_per_thread(T);
+  int run_len = (T / FS_RUNS) / per_thread * per_thread;
+  if (run_len > per_thread * FS_THREADS / FS_RUNS) run_len = per_thread * FS_THREADS / FS_RUNS;
+  if (run_len < per_thread) return false;
   const double frac = (double)(run_len * FS_RUNS) / (double)T;
   double expect = 1.75 * kk;
   if (expect * frac < 96.0) expect = 96.0 / frac;

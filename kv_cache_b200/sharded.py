@@ -56,7 +56,7 @@ class CudaBackend:
         r = ops.score(query, packed, scale, channel_idx, t_local, want_acc=False, want_deq=False, want_hist=True)
         B, Hkv, _ = r.gmax.shape
         idx, sc = ops.select(r.gmax.view(B * Hkv, t_local), k, idx_offset=id_offset, hist=r.hist,
-                             return_scores=True, index_dtype=torch.int32, order="score")
+                             return_scores=True, index_dtype=torch.int32, order="index")
         return sc, idx
 
     def merge(self, scores, ids, k: int):
@@ -219,13 +219,15 @@ def bench_main(args, w) -> None:
 
     from .benchutil import METRIC, UNIT, ClockSampler, hbm_peak
 
-    launch = "eager Python step"
-    try:
+    # The step is captured into a CUDA graph (kernels and both NCCL all-gathers). A capture failure is
+    # fatal on purpose: falling back on one rank only would leave the ranks issuing different collectives.
+    graph = None
+    if os.environ.get("KVB_SHARDED_EAGER") == "1":
+        launch = "eager Python step"
+    else:
         graph, (out, sel) = eng.capture(query, key, value, packed, scale, ch, t_local, t0)
         run = graph.replay
         launch = "CUDA graph replay (kernels and both NCCL all-gathers captured)"
-    except Exception as exc:                                   # keep the eager step if capture is not possible
-        launch = f"eager Python step (graph capture failed: {type(exc).__name__})"
 
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
@@ -300,5 +302,14 @@ def bench_main(args, w) -> None:
             "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
+    # Teardown: drop the captured graph (it references the communicator) before anything else, and leave
+    # without tearing the process group down: destroying a communicator that a captured graph used
+    # has been seen to block forever, and the process is about to exit anyway.
+    graph = None
+    run = None
+    torch.cuda.synchronize()
     dist.barrier()
-    dist.destroy_process_group()
+    import sys
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
