@@ -94,15 +94,32 @@ class ShardedSparseDecode:
         configuration has no candidate front end."""
         N = self.world
         B, Hkv = key_local.shape[0], key_local.shape[1]
+        mark = self._mark
+        mark("start")
         comp = ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset, self._ws)
         if comp is None:
             return None
+        mark("local top-k")
         gathered = _all_gather(comp, N, self.group) if N > 1 else comp[None]
+        mark("all-gather candidates")
         sel = ops.merge_candidates(gathered, self.top_k, self.total_tokens).view(B, Hkv, -1)
+        mark("global merge")
         part = self.backend.attend_partial(query, key_local, value_local, sel, t_local, id_offset,
                                            self.rank == N - 1, scaling)
+        mark("attend owned rows")
         parts = _all_gather(part, N, self.group) if N > 1 else part[None]
-        return self.backend.combine(parts), sel
+        mark("all-gather partials")
+        out = self.backend.combine(parts)
+        mark("LSE combine")
+        return out, sel
+
+    def _mark(self, name: str) -> None:
+        """Stage timing hook: records a CUDA event when ``self.stage_events`` is a list (eager runs only)."""
+        ev = getattr(self, "stage_events", None)
+        if ev is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            ev.append((name, e))
 
     def capture(self, *args, **kwargs):
         """Captures one step (collectives included) into a CUDA graph after two eager warm-up steps;
@@ -228,6 +245,22 @@ def bench_main(args, w) -> None:
         graph, (out, sel) = eng.capture(query, key, value, packed, scale, ch, t_local, t0)
         run = graph.replay
         launch = "CUDA graph replay (kernels and both NCCL all-gathers captured)"
+
+    if os.environ.get("KVB_SHARDED_STAGES") == "1":
+        # per-stage device times of eager steps (host launch gaps included), printed by rank 0 to stderr
+        import sys
+        acc: dict = {}
+        for it in range(25):
+            eng.stage_events = []
+            eng.step(query, key, value, packed, scale, ch, t_local, t0)
+            torch.cuda.synchronize()
+            ev = eng.stage_events
+            if it >= 5:
+                for (n0, e0), (n1, e1) in zip(ev, ev[1:]):
+                    acc.setdefault(n1, []).append(e0.elapsed_time(e1) * 1e3)
+        eng.stage_events = None
+        if rank == 0:
+            print("stage medians (us): " + ", ".join(f"{n}={statistics.median(v):.1f}" for n, v in acc.items()), file=sys.stderr)
 
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
