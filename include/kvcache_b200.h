@@ -284,8 +284,8 @@ int kvb_attend_selected(const void* query, int64_t q_sb, int64_t q_sh,
  *   kvb_select_topk). workspace >= kvb_shard_candidates_workspace_bytes(B, Hkv, T, top_k).
  * kvb_merge_candidates: the global top-k of N such lists after an all-gather: gathered uint64
  *   [N, R, kk] -> out_idx int32 [R, min(top_k, N*kk)] global token ids, ascending when
- *   id_range (the total token count) is small enough for the on-chip bitmap (about 1.2 M),
- *   otherwise in arbitrary order. With N > 1 every list must hold top_k entries (kk == top_k).
+ *   id_range (the total token count) is at most 262144 (a cheap on-chip bitmap), otherwise in
+ *   arbitrary order (the set is exact either way). With N > 1 every list must hold top_k entries (kk == top_k).
  *   The composites are unique, so every rank that runs this on the same gathered data gets the
  *   same set. */
 size_t kvb_shard_candidates_workspace_bytes(int B, int Hkv, int T, int top_k);

@@ -2,6 +2,7 @@
 // attend — six stream-ordered launches sharing one caller-provided workspace. Intermediate
 // tensors (group-max scores, histogram, selected ids, final list) never leave the workspace.
 #include "common.cuh"
+#include "score_common.cuh"
 
 namespace kvb {
 
@@ -58,10 +59,33 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   if (rank > run_len * FS_RUNS) rank = run_len * FS_RUNS;
   const int b = row / p.Hkv, g = row - b * p.Hkv;
   for (int i = tid; i < SEL_HIST_BINS; i += FS_THREADS) s_hist[i] = 0;
+  // thread -> run (tid / threads_per_run), per_thread consecutive tokens inside the run
+  constexpr int W = C / 8;
+  const int threads_per_run = run_len / per_thread;
+  const int run = tid / threads_per_run;
+  const int64_t t0 = (int64_t)run * (T / FS_RUNS) + (int64_t)(tid - run * threads_per_run) * per_thread;
+  const bool live = run < FS_RUNS;
+  const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)g * p.packed_sh;
+  const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)g * p.scale_sh;
+  // four tokens at a time: all their loads are issued before the first use
+  auto load_batch = [&](int e0, uint32_t (&wv)[4][W], float (&ks)[4]) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool ok = live && t0 + e0 + e < T;
+      const uint4* src = reinterpret_cast<const uint4*>(packed_row + (t0 + e0 + e) * (C / 2));
+#pragma unroll
+      for (int x = 0; x < C / 32; ++x) {
+        const uint4 u = ok ? __ldg(src + x) : make_uint4(0, 0, 0, 0);
+        wv[e][4 * x] = u.x; wv[e][4 * x + 1] = u.y; wv[e][4 * x + 2] = u.z; wv[e][4 * x + 3] = u.w;
+      }
+      ks[e] = ok ? scale_row[t0 + e0 + e] : 0.0f;
+    }
+  };
+  uint32_t wv[4][W];
+  float ks[4];
   quantize_query_group<FS_THREADS>(p, b, g, G, s_qv, s_qcode, s_qscale);
   // query words in shared memory (every thread reads the same word: a broadcast): word w of a token
   // holds channels 8w + {0,2,4,6} in its low nibbles and 8w + {1,3,5,7} in its high nibbles
-  constexpr int W = C / 8;
   __shared__ int s_qlo[G][W], s_qhi[G][W];
   for (int i = tid; i < G * W; i += FS_THREADS) {
     const int hd = i / W, w = i - hd * W;
@@ -75,30 +99,10 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
     s_qhi[hd][w] = (int)hi;
   }
   __syncthreads();
-  // thread -> run (tid / threads_per_run), FS_PER_THREAD consecutive tokens inside the run
-  const int threads_per_run = run_len / per_thread;
-  const int run = tid / threads_per_run;
-  const int64_t t0 = (int64_t)run * (T / FS_RUNS) + (int64_t)(tid - run * threads_per_run) * per_thread;
-  const bool live = run < FS_RUNS;
-  const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)g * p.packed_sh;
-  const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)g * p.scale_sh;
   float v[FS_PER_THREAD_LONG];
 #pragma unroll 1
   for (int e0 = 0; e0 < per_thread; e0 += 4) {
-    // four tokens at a time: all their loads are issued before the first use
-    uint32_t wv[4][W];
-    float ks[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const bool ok = live && t0 + e0 + e < T;
-      const uint4* src = reinterpret_cast<const uint4*>(packed_row + (t0 + e0 + e) * (C / 2));
-#pragma unroll
-      for (int x = 0; x < C / 32; ++x) {
-        const uint4 u = ok ? __ldg(src + x) : make_uint4(0, 0, 0, 0);
-        wv[e][4 * x] = u.x; wv[e][4 * x + 1] = u.y; wv[e][4 * x + 2] = u.z; wv[e][4 * x + 3] = u.w;
-      }
-      ks[e] = ok ? scale_row[t0 + e0 + e] : 0.0f;
-    }
+    load_batch(e0, wv, ks);
     int acc[4][G];
 #pragma unroll
     for (int e = 0; e < 4; ++e)
@@ -161,36 +165,6 @@ static void sample_launch_g(const SampleParams& q, int R, cudaStream_t st) {
     case 4: score_sample_kernel<C, 4><<<R, FS_THREADS, 0, st>>>(q); break;
     default: score_sample_kernel<C, 8><<<R, FS_THREADS, 0, st>>>(q); break;
   }
-}
-
-// Rows whose candidate count missed [kk, cap] are scored again, whole, into the group-max
-// workspace and flagged; every other CTA leaves at once.
-struct RescueParams {
-  ScoreParams sp;             // gmax_out = workspace rows
-  const uint32_t* cand_count;
-  uint32_t* row_failed;
-  int top_k, cap;
-};
-
-constexpr int RS_THREADS = 256;
-
-__global__ void __launch_bounds__(RS_THREADS) score_rescue_kernel(RescueParams q) {
-  __shared__ float s_qv[SC_MAX_G * SC_MAX_C];
-  __shared__ float s_qscale[SC_MAX_G];
-  __shared__ int8_t s_qcode[SC_MAX_G * SC_MAX_C];
-  const ScoreParams& p = q.sp;
-  const int row = blockIdx.x;
-  const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
-  const int kk = q.top_k < T ? q.top_k : T;
-  const uint32_t n = q.cand_count[(int64_t)row * SC_COUNT_STRIDE];
-  if (n >= (uint32_t)kk && n <= (uint32_t)q.cap) return;
-  const int b = row / p.Hkv, g = row - b * p.Hkv;
-  quantize_query_group<RS_THREADS>(p, b, g, p.G, s_qv, s_qcode, s_qscale);
-  ScoreParams pp = p;
-  pp.acc_out = nullptr; pp.deq_out = nullptr;
-  for (int64_t t = threadIdx.x; t < T; t += RS_THREADS)
-    p.gmax_out[(int64_t)row * p.T + t] = score_token_plain<SC_MAX_G>(pp, p.G, b, g, t, s_qcode, s_qscale);
-  if (threadIdx.x == 0) q.row_failed[row] = 1u;
 }
 
 // Candidate capacity of the fast path: room for ~1.75 k expected candidates plus a wide margin.
@@ -321,7 +295,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       if (!guard.ok) return KVB_BAD_DEVICE;
       KVB_CHECK_CUDA(cudaMemsetAsync(ws + L.off_fcount, 0, L.fzero_bytes, st));
       uint32_t* fcount = reinterpret_cast<uint32_t*>(ws + L.off_fcount);
-      uint32_t* ffailed = reinterpret_cast<uint32_t*>(ws + L.off_ffailed);
       float* ftau = reinterpret_cast<float*>(ws + L.off_ftau);
       uint64_t* fcand = reinterpret_cast<uint64_t*>(ws + L.off_fcand);
 
@@ -337,13 +310,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                      nullptr, &emit, T_dev, device, st);
       if (rc != KVB_OK) return rc;
 
-      RescueParams rq;
-      rq.sp = base;
-      rq.sp.gmax_out = gmax;
-      rq.cand_count = fcount; rq.row_failed = ffailed; rq.top_k = p->top_k; rq.cap = fcap;
-      score_rescue_kernel<<<L.R, RS_THREADS, 0, st>>>(rq);
-      KVB_CHECK_CUDA(cudaGetLastError());
-
       SelectParams sp;
       sp.scores = gmax; sp.row_stride = T; sp.payload = nullptr;
       sp.R = L.R; sp.T = T; sp.k = p->top_k; sp.kk = L.kk; sp.idx_offset = 0;
@@ -351,8 +317,9 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       sp.hist = nullptr; sp.cand = fcand; sp.cand_count = fcount; sp.cap = fcap;
       sp.tokens_per_cta = 0; sp.thresholds = nullptr;
       sp.order_by_index = 1;
-      sp.from_candidates = 1; sp.row_failed = ffailed; sp.T_dev = T_dev;
+      sp.from_candidates = 1; sp.row_failed = nullptr; sp.T_dev = T_dev;
       sp.out_comp = nullptr; sp.gather = nullptr; sp.gather_n = 0; sp.gather_len = 0; sp.gather_stride = 0;
+      sp.rescue = 1; sp.rescue_sp = base;          // rows that miss [kk, cap] are re-scored inside the kernel
       const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
       size_t smem = (size_t)fcap * 8 + SEL_FINAL_FIXED_SMEM;
       sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
@@ -472,7 +439,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   uint32_t* count = reinterpret_cast<uint32_t*>(ws + L.off_count);
-  uint32_t* failed = reinterpret_cast<uint32_t*>(ws + L.off_failed);
   float* tau = reinterpret_cast<float*>(ws + L.off_tau);
   uint64_t* cand = reinterpret_cast<uint64_t*>(ws + L.off_cand);
   float* gmax = reinterpret_cast<float*>(ws + L.off_gmax);
@@ -487,13 +453,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   rc = score_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq, Hkv, T,
                  D, C, nullptr, nullptr, nullptr, nullptr, &emit, nullptr, device, st);
   if (rc != KVB_OK) return rc;
-  RescueParams rq;
-  rq.sp = base;
-  rq.sp.gmax_out = gmax;
-  rq.cand_count = count; rq.row_failed = failed; rq.top_k = top_k; rq.cap = L.cap;
-  score_rescue_kernel<<<L.R, RS_THREADS, 0, st>>>(rq);
-  KVB_CHECK_CUDA(cudaGetLastError());
-
   SelectParams sp;
   sp.scores = gmax; sp.row_stride = T; sp.payload = nullptr;
   sp.R = L.R; sp.T = T; sp.k = top_k; sp.kk = L.kk; sp.idx_offset = id_offset;
@@ -501,8 +460,9 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   sp.hist = nullptr; sp.cand = cand; sp.cand_count = count; sp.cap = L.cap;
   sp.tokens_per_cta = 0; sp.thresholds = nullptr;
   sp.order_by_index = 2; sp.use_bitmap = 0;
-  sp.from_candidates = 1; sp.row_failed = failed; sp.T_dev = nullptr;
+  sp.from_candidates = 1; sp.row_failed = nullptr; sp.T_dev = nullptr;
   sp.gather = nullptr; sp.gather_n = 0; sp.gather_len = 0; sp.gather_stride = 0;
+  sp.rescue = 1; sp.rescue_sp = base;
   const size_t smem = (size_t)L.cap * 8 + SEL_FINAL_FIXED_SMEM;
   static bool attr_done[64] = {false};
   if (device < 64 && !attr_done[device]) {
@@ -536,10 +496,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(const
   sp.tokens_per_cta = 0; sp.thresholds = nullptr;
   sp.from_candidates = 0; sp.row_failed = nullptr; sp.T_dev = nullptr;
   sp.gather = gathered; sp.gather_n = N; sp.gather_len = kk; sp.gather_stride = (int64_t)R * kk;
+  sp.rescue = 0;
   const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((id_range + 31) / 32);
   size_t smem = (size_t)sp.cap * 8 + SEL_FINAL_FIXED_SMEM;
-  if (smem + bitmap_bytes <= SEL_SMEM_LIMIT) {
-    sp.order_by_index = 1; sp.use_bitmap = 1; smem += bitmap_bytes;      // ascending global ids
+  if (id_range <= 262144 && smem + bitmap_bytes <= SEL_SMEM_LIMIT) {
+    sp.order_by_index = 1; sp.use_bitmap = 1; smem += bitmap_bytes;      // ascending global ids (cheap bitmap only)
   } else {
     sp.order_by_index = 2; sp.use_bitmap = 0;                              // exact set, arbitrary order
   }

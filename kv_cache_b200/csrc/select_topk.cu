@@ -15,6 +15,7 @@
 // last kernel first refines the prefix with 11-bit passes over the row itself until the
 // candidate set fits; that path is slower but exact for any input.
 #include "common.cuh"
+#include "score_common.cuh"
 
 namespace kvb {
 
@@ -53,6 +54,10 @@ struct SelectParams {
   const uint64_t* gather;
   int gather_n, gather_len;
   int64_t gather_stride;
+  // with from_candidates: a row whose candidate count misses [kk, cap] is re-scored, whole, by this
+  // kernel into `scores` (the group-max workspace) and then selected by the refinement path
+  int rescue;
+  ScoreParams rescue_sp;
 };
 
 __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row, int64_t t) {
@@ -316,47 +321,33 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   bool have_candidates;
   const uint64_t* cand = p.cand ? p.cand + (int64_t)row * p.cap : nullptr;
   if (gathered) {
-    // Every segment holds >= kk real entries, so the k-th best overall is at least as good as the
-    // WORST entry of any one segment: everything below  tau = max over segments of (segment minimum)
-    // can be dropped at once. Usually that leaves little more than kk elements.
+    // All-gathered shard lists: up to gather_n * gather_len composites, far more than fit on chip. The
+    // refinement below narrows them with 11-bit histogram passes over global memory (two passes bring
+    // i.i.d. shard lists under the capacity) and then collects the survivors.
+    // (Dropping everything below "max over segments of the segment minimum" is exact but useless here:
+    // each shard's worst entry lies far below the global k-th one.)
     prefix = 0; fixed = 0; need = (uint32_t)p.kk; in_prefix = (uint32_t)n_src;
-    uint64_t tau = 0;
-    for (int sgm = 0; sgm < p.gather_n; ++sgm) {
-      uint64_t mn = ~0ull;
-      for (int j = tid; j < p.gather_len; j += SEL_FINAL_THREADS) {
-        const uint64_t c = load_comp((int64_t)sgm * p.gather_len + j);
-        mn = c < mn ? c : mn;
-      }
-#pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) {
-        const uint64_t o = __shfl_xor_sync(0xffffffffu, mn, off);
-        mn = o < mn ? o : mn;
-      }
-      uint64_t* s_red = reinterpret_cast<uint64_t*>(s_hist);
-      if ((tid & 31) == 0) s_red[tid >> 5] = mn;
-      __syncthreads();
-      uint64_t m2 = s_red[0];
-      for (int w = 1; w < SEL_FINAL_THREADS / 32; ++w) m2 = s_red[w] < m2 ? s_red[w] : m2;
-      tau = m2 > tau ? m2 : tau;
-      __syncthreads();
-    }
-    if (tid == 0) *s_count = 0;
-    __syncthreads();
-    for (int64_t t = tid; t < n_src; t += SEL_FINAL_THREADS) {
-      const uint64_t c = load_comp(t);
-      if (c >= tau) {
-        const uint32_t pos = atomicAdd(s_count, 1u);
-        if (pos < (uint32_t)p.cap) s_cand[pos] = c;
-      }
-    }
-    __syncthreads();
-    const uint32_t kept = *s_count;
-    __syncthreads();
-    have_candidates = kept <= (uint32_t)p.cap;
-    if (have_candidates) { n = (int)kept; in_prefix = kept; }
+    have_candidates = false;
   } else if (p.from_candidates) {
     prefix = 0; fixed = 0; need = (uint32_t)p.kk;
-    const bool failed = p.row_failed != nullptr && p.row_failed[row] != 0;
+    bool failed = p.row_failed != nullptr && p.row_failed[row] != 0;
+    if (p.rescue && !failed) {
+      const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
+      if (have < (uint32_t)p.kk || have > (uint32_t)p.cap) {
+        // the sampled threshold missed its bounds for this row: score the whole row again, exactly
+        const ScoreParams& sp = p.rescue_sp;
+        float* r_qv = reinterpret_cast<float*>(s_cand);                    // scratch inside the (still unused) candidate area
+        float* r_qscale = r_qv + SC_MAX_G * SC_MAX_C;
+        int8_t* r_qcode = reinterpret_cast<int8_t*>(r_qscale + SC_MAX_G);
+        const int rb = row / sp.Hkv, rg = row - rb * sp.Hkv;
+        quantize_query_group<SEL_FINAL_THREADS>(sp, rb, rg, sp.G, r_qv, r_qcode, r_qscale);
+        float* dst = const_cast<float*>(src);
+        for (int64_t t = tid; t < p.T; t += SEL_FINAL_THREADS)
+          dst[t] = score_token_plain<SC_MAX_G>(sp, sp.G, rb, rg, t, r_qcode, r_qscale);
+        __syncthreads();
+        failed = true;
+      }
+    }
     have_candidates = !failed;
     if (failed) {
       in_prefix = (uint32_t)p.T;
@@ -597,6 +588,7 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   p.T_dev = nullptr;
   p.out_comp = nullptr;
   p.gather = nullptr; p.gather_n = 0; p.gather_len = 0; p.gather_stride = 0;
+  p.rescue = 0;
   const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
   size_t smem = (size_t)p.cap * 8 + SEL_FINAL_FIXED_SMEM;
   p.use_bitmap = (order == 1 && !payload && smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;

@@ -72,7 +72,7 @@ def test_candidate_front_end_and_one_kernel_merge(cuda_device, N, T, k):
         lists.append(comp)
     sel = ops.merge_candidates(torch.stack(lists), k, id_range=T)
     want = oracle.decode_step(*cpu(q, key, value, ch), k)["selected"].reshape(4, k)
-    assert torch.equal(sel.cpu().long(), torch.sort(want, dim=-1).values)
+    assert torch.equal(torch.sort(sel.cpu().long(), dim=-1).values, torch.sort(want, dim=-1).values)
 
 
 def test_merge_candidates_heavy_ties(cuda_device):
