@@ -342,6 +342,34 @@ int kvb_block_topk(const float* block_scores, int64_t row_stride, int64_t R, int
                    int32_t* out_idx, float* out_scores, int device, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The reference's fp32 front-end operators on un-quantised bf16 K, kept for call sites that use them.
+ *
+ * kvb_qabs_partial_scores replaces partial_scores (QCK:654-656, kernel QCK:98-158) when dim_indices
+ *   is NULL — per (batch, head) the dim_count channels with the largest |q| are chosen greedily,
+ *   ties to the lower channel (QCK:123-145) — and partial_scores_dim_major (QCK:659-665, kernel
+ *   QCK:63-96) when dim_indices int64 [B,H,S] is given. out[b,h,t] = sum_s q[idx_s] * K[t, idx_s]
+ *   in fp32 (torch form: EVAL:4443-4446). key is a [B,Hk,T,D] VIEW with element strides
+ *   k_sb/k_sh/k_st/k_sd (token-major: k_sd = 1; dim-major storage: k_st = 1); Hk may be the number
+ *   of KV heads (head h reads KV head h / (H/Hk)) or H (keys repeated, as the reference passes them).
+ *   query bf16 [B,H,D] dense, out fp32 [B,H,T] dense.
+ * kvb_qabs_candidate_full_scores replaces candidate_full_scores (QCK:668-691, kernel QCK:160-216):
+ *   out[b,h,t] = scaling * q.k over all D channels where current | previous_candidate |
+ *   previous_final (uint8 [B,H,T]; the previous_* may be NULL) or t < protect_sink or
+ *   t >= T - protect_recent; -inf elsewhere. key token-major with D contiguous.
+ * ------------------------------------------------------------------------------------- */
+int kvb_qabs_partial_scores(const void* query, const void* key,
+                            int64_t k_sb, int64_t k_sh, int64_t k_st, int64_t k_sd,
+                            const int64_t* dim_indices, int dim_count, float* out,
+                            int B, int H, int Hk, int T, int D, int device, void* stream);
+
+int kvb_qabs_candidate_full_scores(const void* query, const void* key,
+                                   int64_t k_sb, int64_t k_sh, int64_t k_st,
+                                   const uint8_t* current, const uint8_t* previous_candidate,
+                                   const uint8_t* previous_final, int protect_sink, int protect_recent,
+                                   float scaling, float* out,
+                                   int B, int H, int Hk, int T, int D, int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Fused decode step for one layer: quantize-append of the new K row, score, select,
  * final index list, attend — all enqueued on `stream`, nothing else touched.
  * Equivalent to the sequence _qabs_candidate_attention_forward runs (EVAL:4400-4502) with the

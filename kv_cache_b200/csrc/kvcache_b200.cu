@@ -8,6 +8,7 @@
 #include "sparse_attend.cu"
 #include "decode_step.cu"
 #include "score_prefill.cu"
+#include "qabs_fp32.cu"
 
 extern "C" __attribute__((visibility("default"))) int kvb_version(void) { return 100; /* 0.1.0 */ }
 

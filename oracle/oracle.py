@@ -335,3 +335,22 @@ def qabs_candidate_attention(query_states, key_states, value_states, attention_m
     fidx, fvalid = final_indices_from_selected(cand, torch.ones_like(cand, dtype=torch.bool), history, key_count,
                                                always_keep_self, protect_sink, protect_recent)
     return attention_from_final_indices(query_states, key_states, value_states, attention_mask, fidx, fvalid, scaling)
+
+
+def qabs_candidate_full_scores(query, key_history, current, previous_candidate, previous_final, protect_sink,
+                               protect_recent, scaling):
+    """QCK:160-216 (qabs_candidate_full_scores_kernel) restated: fp32 q.k over all channels times scaling
+    on current | previous_candidate | previous_final | [0, sink) | [T - recent, T); -inf elsewhere.
+    query [B,H,D], key_history [B,H,T,D], masks bool [B,H,T]."""
+    T = key_history.shape[2]
+    sel = current.clone()
+    if previous_candidate is not None:
+        sel |= previous_candidate
+    if previous_final is not None:
+        sel |= previous_final
+    if protect_sink > 0:
+        sel[..., :protect_sink] = True
+    if protect_recent > 0:
+        sel[..., max(0, T - protect_recent):] = True
+    scores = torch.einsum("bhd,bhtd->bht", query.float(), key_history.float()) * scaling
+    return torch.where(sel, scores, torch.full_like(scores, float("-inf")))
