@@ -324,6 +324,11 @@ int kvb_lse_merge(const float* partials, int N, int B, int Hq, int D, void* out,
  *   (float(sum_c qcode*code) * kscale[b,g,t]) * qscale[b,h,i]; all Tk keys are visible to every
  *   query of the chunk. C in {32,64,128}, G in {1,2,4,8}; packed/scale aligned as for the
  *   streaming decode scorer. block_scores fp32 [B,Hkv,Tq,ceil(Tk/64)] dense; -0 stored as +0.
+ *   kvb_score_prefill_blocks_engine is the same with the implementation chosen by the caller
+ *   (all give identical bits): 0 = automatic (tensor-memory path; the environment variable
+ *   KVB_PREFILL_ENGINE = mma | i8 | f16 overrides it), 1 = warp-level int8 MMA, 2 = tcgen05
+ *   kind::i8 with int32 accumulators in tensor memory, 3 = tcgen05 kind::f16 with the integer
+ *   codes carried exactly as fp16 values and fp32 accumulators.
  * kvb_block_topk: per row of block scores ([R,nblk], nblk <= 4096) the min(k,nblk) best blocks
  *   ordered by (score desc, block asc); out_idx int32 [R,kk], out_scores fp32 [R,kk] or NULL.
  * ------------------------------------------------------------------------------------- */
@@ -337,6 +342,12 @@ int kvb_score_prefill_blocks(const int8_t* qcode, const float* qscale,
                              const float* scale, int64_t scale_sb, int64_t scale_sh,
                              int B, int Hq, int Hkv, int Tq, int Tk, int C, int block_size,
                              float* block_scores, int device, void* stream);
+
+int kvb_score_prefill_blocks_engine(const int8_t* qcode, const float* qscale,
+                                    const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                                    const float* scale, int64_t scale_sb, int64_t scale_sh,
+                                    int B, int Hq, int Hkv, int Tq, int Tk, int C, int block_size,
+                                    float* block_scores, int engine, int device, void* stream);
 
 int kvb_block_topk(const float* block_scores, int64_t row_stride, int64_t R, int nblk, int k,
                    int32_t* out_idx, float* out_scores, int device, void* stream);

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <stdlib.h>
 
 #include "../../include/kvcache_b200.h"
 
@@ -166,6 +167,44 @@ __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Inside a chain of kernels on one stream the next kernel may be made resident while the current
+// one still runs: its blocks start, do whatever does not depend on the predecessor and then block
+// in pdl_wait() until the predecessor has completed and its writes are visible. Both instructions
+// are no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Whether launches made by this host thread ask for the early start (set only while a fused chain
+// whose kernels all begin with pdl_wait() is being enqueued).
+static thread_local bool t_chain_launch = false;
+struct ChainLaunchScope {
+  bool prev;
+  ChainLaunchScope() : prev(t_chain_launch) {}
+  void on() {
+    static const bool disabled = [] { const char* e = getenv("KVB_NO_CHAIN_LAUNCH"); return e && e[0] == '1'; }();
+    t_chain_launch = !disabled;
+  }
+  ~ChainLaunchScope() { t_chain_launch = prev; }
+};
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                        Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = t_chain_launch ? attr : nullptr;
+  cfg.numAttrs = t_chain_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
 }  // namespace kvb

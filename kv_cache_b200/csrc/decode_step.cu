@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   __shared__ uint32_t s_tmp[80];
   const ScoreParams& p = q.sp;
   const int row = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();                      // the scorer may become resident and prepare its query codes
+  pdl_wait();
   const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
   if (T <= q.cap) {                             // short rows: every token is a candidate
     if (tid == 0) q.tau[row] = -INFINITY;
@@ -158,13 +160,14 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
 }
 
 template <int C>
-static void sample_launch_g(const SampleParams& q, int R, cudaStream_t st) {
+static int sample_launch_g(const SampleParams& q, int R, cudaStream_t st) {
   switch (q.sp.G) {
-    case 1: score_sample_kernel<C, 1><<<R, FS_THREADS, 0, st>>>(q); break;
-    case 2: score_sample_kernel<C, 2><<<R, FS_THREADS, 0, st>>>(q); break;
-    case 4: score_sample_kernel<C, 4><<<R, FS_THREADS, 0, st>>>(q); break;
-    default: score_sample_kernel<C, 8><<<R, FS_THREADS, 0, st>>>(q); break;
+    case 1: KVB_CHECK_CUDA(launch_kernel(score_sample_kernel<C, 1>, dim3(R), dim3(FS_THREADS), 0, st, q)); break;
+    case 2: KVB_CHECK_CUDA(launch_kernel(score_sample_kernel<C, 2>, dim3(R), dim3(FS_THREADS), 0, st, q)); break;
+    case 4: KVB_CHECK_CUDA(launch_kernel(score_sample_kernel<C, 4>, dim3(R), dim3(FS_THREADS), 0, st, q)); break;
+    default: KVB_CHECK_CUDA(launch_kernel(score_sample_kernel<C, 8>, dim3(R), dim3(FS_THREADS), 0, st, q)); break;
   }
+  return KVB_OK;
 }
 
 // Candidate capacity of the fast path: room for ~1.75 k expected candidates plus a wide margin.
@@ -193,11 +196,9 @@ static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cud
   SampleParams sq;
   sq.sp = sp; sq.tau = tau; sq.top_k = top_k; sq.cap = cap;
   const int R = sp.B * sp.Hkv;
-  if (sp.C == 32) sample_launch_g<32>(sq, R, st);
-  else if (sp.C == 64) sample_launch_g<64>(sq, R, st);
-  else sample_launch_g<128>(sq, R, st);
-  KVB_CHECK_CUDA(cudaGetLastError());
-  return KVB_OK;
+  if (sp.C == 32) return sample_launch_g<32>(sq, R, st);
+  if (sp.C == 64) return sample_launch_g<64>(sq, R, st);
+  return sample_launch_g<128>(sq, R, st);
 }
 
 // Workspace of the fused step. The regions that must start at zero (attention split counters,
@@ -268,6 +269,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   int32_t* sel = p->sel_idx_out ? p->sel_idx_out : reinterpret_cast<int32_t*>(ws + L.off_sel);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
+  ChainLaunchScope chain;
 
   // Fast path: sample -> tau, scorer emits candidates, rescue check, exact finish. Needs the
   // streaming scorer, a row longer than the candidate capacity but short enough for the 4096-token
@@ -303,6 +305,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                         p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, T_dev);
       rc = sample_run(base, ftau, p->top_k, fcap, st);
       if (rc != KVB_OK) return rc;
+      chain.on();                             // every later kernel of the step starts early and waits inside
 
       ScoreEmit emit{ftau, fcand, fcount, fcap};
       rc = score_run(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
@@ -330,8 +333,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                                             (int)SEL_SMEM_LIMIT));
         attr_done[device] = true;
       }
-      select_final_kernel<<<L.R, SEL_FINAL_THREADS, smem, st>>>(sp);
-      KVB_CHECK_CUDA(cudaGetLastError());
+      KVB_CHECK_CUDA(launch_kernel(select_final_kernel, dim3(L.R), dim3(SEL_FINAL_THREADS), smem, st, sp));
     }
   } else {
     {

@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
+  pdl_launch_dependents();
   uint8_t* my_stage = s_stage + warp * NS * STAGE_BYTES;
   uint64_t* my_bar = s_bar + warp * NS;
 
@@ -145,6 +146,9 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
     const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)kvh * p.packed_sh;
     const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)kvh * p.scale_sh;
     float* gmax_row = p.gmax_out ? p.gmax_out + (int64_t)row * p.T : nullptr;
+    // Everything above reads only the caller's inputs; the thresholds (and the zeroed counters) come
+    // from the kernels before this one.
+    pdl_wait();
     const float tau = EMIT ? p.tau[row] : 0.0f;
     uint64_t* cand_row = EMIT ? p.cand + (int64_t)row * p.cand_cap : nullptr;
     uint32_t* count_row = EMIT ? p.cand_count + (int64_t)row * SC_COUNT_STRIDE : nullptr;
@@ -406,7 +410,7 @@ static int score_stream_launch(const ScoreParams& p0, int device, cudaStream_t s
   const int64_t max_ctas = (p.total_units + 1) / 2;        // at least two units per CTA
   if (grid > max_ctas) grid = max_ctas;
   if (grid < 1) grid = 1;
-  kern<<<(unsigned)grid, Cfg::THREADS, smem, st>>>(p);
+  KVB_CHECK_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(Cfg::THREADS), smem, st, p));
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
 }

@@ -14,6 +14,8 @@
 // block maximum instead of once per element without changing a single bit.
 #include "common.cuh"
 
+#include <string.h>
+
 namespace kvb {
 
 constexpr int PF_WARPS = 8;
@@ -325,33 +327,78 @@ extern "C" __attribute__((visibility("default"))) int kvb_quantize_query_tokens(
   return KVB_OK;
 }
 
-extern "C" __attribute__((visibility("default"))) int kvb_score_prefill_blocks(
-    const int8_t* qcode, const float* qscale, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
-    const float* scale, int64_t scale_sb, int64_t scale_sh, int B, int Hq, int Hkv, int Tq, int Tk, int C,
-    int block_size, float* block_scores, int device, void* stream) {
-  using namespace kvb;
+namespace kvb {
+
+// engine: 0 = automatic, 1 = mma.sync int8 (score_prefill_kernel), 2 = tcgen05 kind::i8, 3 = tcgen05 kind::f16.
+static int prefill_engine_default() {
+  static const int e = [] {
+    const char* v = getenv("KVB_PREFILL_ENGINE");
+    if (!v) return 0;
+    if (!strcmp(v, "mma")) return 1;
+    if (!strcmp(v, "i8")) return 2;
+    if (!strcmp(v, "f16")) return 3;
+    return 0;
+  }();
+  return e;
+}
+
+static int prefill_blocks_run(const int8_t* qcode, const float* qscale, const uint8_t* packed, int64_t packed_sb,
+                              int64_t packed_sh, const float* scale, int64_t scale_sb, int64_t scale_sh, int B, int Hq,
+                              int Hkv, int Tq, int Tk, int C, int block_size, float* block_scores, int engine,
+                              int device, void* stream) {
   if (!qcode || !qscale || !packed || !scale || !block_scores) return KVB_BAD_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Tq <= 0 || Tk <= 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
   if (block_size != PF_BLOCK) return KVB_BAD_SHAPE;
   if (C != 32 && C != 64 && C != 128) return KVB_BAD_SHAPE;
+  if (engine < 0 || engine > 3) return KVB_BAD_ARG;
   if ((int64_t)B * Hkv > 65535) return KVB_BAD_SHAPE;
   if (!aligned_to(qcode, 8) || !aligned_to(packed, 16) || (packed_sb % 16) || (packed_sh % 16) ||
       !aligned_to(scale, 16) || (scale_sb % 4) || (scale_sh % 4))
     return KVB_BAD_ALIGN;
   DeviceGuard guard(device);
   if (!guard.ok) return KVB_BAD_DEVICE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int G = Hq / Hkv;
+  if (engine == 0) engine = prefill_engine_default();
+  if (engine == 0) engine = 3;                      // tensor-memory path, fp16 encoding of the integer codes
+  if (engine >= 2) {
+    PrefillTcParams t;
+    t.qcode = qcode; t.qscale = qscale;
+    t.packed = packed; t.packed_sb = packed_sb; t.packed_sh = packed_sh;
+    t.scale = scale; t.scale_sb = scale_sb; t.scale_sh = scale_sh;
+    t.out = block_scores;
+    t.B = B; t.Hq = Hq; t.Hkv = Hkv; t.Tq = Tq; t.Tk = Tk; t.nblk = ceil_div(Tk, PF_BLOCK);
+    return prefill_tc_run(t, C, G, engine == 2 ? 0 : 1, device, st);
+  }
   PrefillParams p;
   p.qcode = qcode; p.qscale = qscale;
   p.packed = packed; p.packed_sb = packed_sb; p.packed_sh = packed_sh;
   p.scale = scale; p.scale_sb = scale_sb; p.scale_sh = scale_sh;
   p.out = block_scores;
-  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Tq = Tq; p.Tk = Tk; p.C = C; p.G = Hq / Hkv;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Tq = Tq; p.Tk = Tk; p.C = C; p.G = G;
   p.nblk = ceil_div(Tk, PF_BLOCK);
   p.blocks_per_cta = p.nblk;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (C == 32) return prefill_dispatch_g<32>(p, device, st);
   if (C == 64) return prefill_dispatch_g<64>(p, device, st);
   return prefill_dispatch_g<128>(p, device, st);
+}
+
+}  // namespace kvb
+
+extern "C" __attribute__((visibility("default"))) int kvb_score_prefill_blocks(
+    const int8_t* qcode, const float* qscale, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, int B, int Hq, int Hkv, int Tq, int Tk, int C,
+    int block_size, float* block_scores, int device, void* stream) {
+  return kvb::prefill_blocks_run(qcode, qscale, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, B, Hq, Hkv, Tq,
+                                 Tk, C, block_size, block_scores, 0, device, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_score_prefill_blocks_engine(
+    const int8_t* qcode, const float* qscale, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, int B, int Hq, int Hkv, int Tq, int Tk, int C,
+    int block_size, float* block_scores, int engine, int device, void* stream) {
+  return kvb::prefill_blocks_run(qcode, qscale, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, B, Hq, Hkv, Tq,
+                                 Tk, C, block_size, block_scores, engine, device, stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int kvb_block_topk(const float* block_scores, int64_t row_stride,

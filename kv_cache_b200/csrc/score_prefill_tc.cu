@@ -1,0 +1,567 @@
+// Chunked-prefill block scoring on the 5th-generation tensor cores (tcgen05 + tensor memory).
+//
+// Same result, bit for bit, as score_prefill_kernel (score_prefill.cu):
+//   blk[b,g,i,j] = max over the G heads of KV head g and the 64 tokens of key block j of
+//                  fl(fl(float(acc) * kscale[t]) * qscale[h,i]),  acc = sum_c qcode * kcode  (exact)
+//
+// One CTA owns QT tiles of 128 accumulator rows (a tile = 128/G queries x the G heads of one KV head)
+// and walks the whole key range in tiles of 128 tokens (two blocks):
+//   * 4 producer warps read the packed int4 codes, widen them and store them as the K-major,
+//     un-swizzled core-matrix layout the tensor core reads from shared memory (4-stage ring);
+//   * 1 thread issues tcgen05.mma (M=128, N=128) into a double-buffered accumulator in tensor memory
+//     and signals completion with tcgen05.commit -> mbarrier;
+//   * 16 epilogue warps (four per TMEM lane quadrant, one 64-token block of one accumulator tile each)
+//     pull the accumulators with tcgen05.ld in 16-column chunks, the next chunk in flight while the
+//     current one is scaled (packed fp32 multiply) and reduced (3-input maximum), combine the heads
+//     through shared memory and write eight block maxima per query at a time.
+// The contraction is only C (32..128) deep, so the kernel is bound by the instructions of the
+// per-element epilogue, not by the MMA; that is why most warps are epilogue warps.
+//
+// Two operand encodings give the same integers:
+//   KIND 0: kind::i8  — int8 codes (K codes as 16*code, the exact 1/16 folded into the key scale),
+//                       int32 accumulators, int -> float in the epilogue (2 extra instructions/element);
+//   KIND 1: kind::f16 — the same integers as fp16 values with fp32 accumulation. |acc| <= 127*7*C
+//                       < 2^17, every partial sum is an integer far below 2^24, so the fp32
+//                       accumulator holds exactly the int32 result and the epilogue needs no conversion.
+// Every wait on an mbarrier is bounded; a wait that gives up records KVB_TIMEOUT, and all roles leave
+// their loops, meet at the final barrier and free the tensor memory.
+#include "common.cuh"
+
+#include <cuda_fp16.h>
+
+namespace kvb {
+
+constexpr int TC_EPI_WARPS = 16;                   // four per TMEM lane quadrant: one (tile, block) unit each
+constexpr int TC_PROD_WARPS = 4;
+constexpr int TC_WARPS = TC_EPI_WARPS + TC_PROD_WARPS + 1;
+constexpr int TC_THREADS = TC_WARPS * 32;
+constexpr int TC_UNITS = TC_EPI_WARPS / 4;         // epilogue warps per quadrant
+constexpr int TC_QT_PER_WARP = 4 / TC_UNITS;       // (tile, block) units per tile are 2 * TC_QT = 4
+constexpr int TC_NTILE = 128;                      // key tokens per MMA tile (two 64-token blocks)
+constexpr int TC_QT = 2;                           // 128-row accumulator tiles per CTA
+constexpr int TC_ASTAGES = 2;                      // accumulator stages in tensor memory
+constexpr int TC_TMEM_COLS = TC_ASTAGES * TC_QT * TC_NTILE;   // 512: all of it
+constexpr int TC_OUT_BLOCKS = 8;                   // block maxima buffered per query before a flush
+constexpr int TC_CHW = 16;                         // accumulator columns per tensor-memory load
+constexpr int TC_KS_SLOTS = 8;                     // tiles of key scales resident in shared memory
+constexpr int TC_LBO = 128;                        // bytes between core matrices along K
+
+struct PrefillTcParams {
+  const int8_t* qcode;      // [B,Hq,Tq,C]
+  const float* qscale;      // [B,Hq,Tq]
+  const uint8_t* packed; int64_t packed_sb, packed_sh;
+  const float* scale; int64_t scale_sb, scale_sh;
+  float* out;               // [B,Hkv,Tq,nblk]
+  int B, Hq, Hkv, Tq, Tk, nblk;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_alloc(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (KIND == 0) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// 32 consecutive accumulator columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+// Waits for every tcgen05.ld of this thread. The registers of the load are passed through the statement
+// so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld32(uint32_t* v) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+        "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]),
+        "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]),
+        "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+      :
+      : "memory");
+}
+// 16-column forms of the two above
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld16(uint32_t* v) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+        "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+      :
+      : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, no swizzle. A core matrix is 8 rows x 16 bytes stored
+// contiguously (128 bytes); `lbo` is the distance between core matrices that follow each other along
+// K, `sbo` between groups of 8 rows. Bits [46,48) carry the descriptor version of this architecture.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
+         (1ull << 46);
+}
+// Instruction descriptor: dense, no negation, both operands K-major, M x N accumulator tile.
+//   KIND 0: int8 x int8 -> int32;  KIND 1: fp16 x fp16 -> fp32.
+template <int KIND>
+__host__ __device__ constexpr uint32_t tc_instr_desc(int M, int N) {
+  const uint32_t cfmt = KIND == 0 ? 2u : 1u;      // S32 : F32
+  const uint32_t abfmt = KIND == 0 ? 1u : 0u;     // signed 8-bit : F16
+  return (cfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <int C, int KIND>
+struct TcCfg {
+  static constexpr int ES = KIND == 0 ? 1 : 2;                 // operand element bytes
+  static constexpr int ROWB = C * ES;                          // bytes of one operand row (all of K)
+  static constexpr int CHUNKS = ROWB / 16;                     // 16-byte K chunks per row
+  static constexpr int SBO = CHUNKS * TC_LBO;                  // bytes between 8-row groups
+  static constexpr int KSTEPS = ROWB / 32;                     // MMAs per tile: 32 bytes of K each
+  static constexpr int A_TILE = 128 * ROWB;
+  static constexpr int B_STAGE = TC_NTILE * ROWB;
+  static constexpr int BSTAGES = ROWB >= 256 ? 3 : 4;
+  // shared memory carve-up
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + TC_QT * A_TILE;
+  static constexpr int OFF_KS = OFF_B + BSTAGES * B_STAGE;                 // [8 tiles][2 halves][64] key scales
+  static constexpr int OFF_X = OFF_KS + TC_KS_SLOTS * 2 * 64 * 4;                    // [2][QT][2][128] per-head block maxima
+  static constexpr int OFF_OUT = OFF_X + 2 * TC_QT * 2 * 128 * 4;          // [2][QT*128][8] buffered outputs (worst case G=1)
+  static constexpr int OFF_BAR = OFF_OUT + 2 * TC_QT * 128 * TC_OUT_BLOCKS * 4;
+  static constexpr int NBAR = 2 * BSTAGES + 2 * TC_ASTAGES + 1;
+  static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;                      // tmem base, dead flag
+  static constexpr int BYTES = OFF_MISC + 16;
+};
+
+template <int C, int G, int KIND>
+__global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(PrefillTcParams p) {
+  using Cfg = TcCfg<C, KIND>;
+  constexpr int QPT = 128 / G;                      // queries per accumulator tile
+  constexpr int QCTA = TC_QT * QPT;                 // queries per CTA
+  constexpr int W = C / 8;                          // packed words per token
+  constexpr int BSTAGES = Cfg::BSTAGES;
+  extern __shared__ __align__(1024) uint8_t tc_smem[];
+  uint8_t* s_a = tc_smem + Cfg::OFF_A;
+  uint8_t* s_b = tc_smem + Cfg::OFF_B;
+  float* s_ks = reinterpret_cast<float*>(tc_smem + Cfg::OFF_KS);
+  float* s_x = reinterpret_cast<float*>(tc_smem + Cfg::OFF_X);
+  float* s_out = reinterpret_cast<float*>(tc_smem + Cfg::OFF_OUT);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tc_smem + Cfg::OFF_BAR);
+  uint64_t* b_full = bars;                          // [BSTAGES] producers -> MMA (128 arrivals)
+  uint64_t* b_empty = bars + BSTAGES;               // [BSTAGES] MMA -> producers (commit)
+  uint64_t* acc_full = bars + 2 * BSTAGES;          // [ASTAGES] MMA -> epilogue (commit)
+  uint64_t* acc_empty = acc_full + TC_ASTAGES;      // [ASTAGES] epilogue -> MMA (256 arrivals)
+  uint64_t* all_done = acc_empty + TC_ASTAGES;      // every MMA of the CTA has completed
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tc_smem + Cfg::OFF_MISC);
+  volatile uint32_t* s_dead = s_tmem + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.Hkv, kvh = bh - b * p.Hkv;
+  const int q0 = blockIdx.x * QCTA;
+  const int ntiles = (p.Tk + TC_NTILE - 1) / TC_NTILE;
+
+  if (tid == 0) {
+    for (int s = 0; s < BSTAGES; ++s) { mbar_init(&b_full[s], TC_PROD_WARPS * 32); mbar_init(&b_empty[s], 1); }
+    for (int a = 0; a < TC_ASTAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TC_EPI_WARPS * 32); }
+    mbar_init(all_done, 1);
+    *s_dead = 0;
+    fence_mbar_init();
+  }
+  if (warp == TC_WARPS - 1) {                       // the MMA warp owns the tensor-memory allocation
+    tc_alloc(s_tmem, TC_TMEM_COLS);
+    tc_relinquish();
+  }
+
+  // ---- A tiles: row r of tile qt = head r / QPT, query q0 + qt*QPT + r % QPT; K order inside each group of
+  // 8 channels is (even channels, odd channels), the order in which the widened key words deliver them.
+  for (int item = tid; item < TC_QT * 128 * W; item += TC_THREADS) {
+    const int w = item % W;
+    const int r = (item / W) % 128;
+    const int qt = item / (W * 128);
+    const int hd = r / QPT, qi = r - hd * QPT;
+    const int q = q0 + qt * QPT + qi;
+    uint32_t ev = 0, od = 0;
+    if (q < p.Tq) {
+      const int64_t rowoff = ((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q;
+      const uint2 x = *reinterpret_cast<const uint2*>(p.qcode + rowoff * C + 8 * w);
+      ev = __byte_perm(x.x, x.y, 0x6420);          // channels 8w + 0,2,4,6
+      od = __byte_perm(x.x, x.y, 0x7531);          // channels 8w + 1,3,5,7
+    }
+    uint8_t* tile = s_a + qt * Cfg::A_TILE + (r >> 3) * Cfg::SBO + (r & 7) * 16;
+    if constexpr (KIND == 0) {
+      *reinterpret_cast<uint2*>(tile + (w >> 1) * TC_LBO + (w & 1) * 8) = make_uint2(ev, od);
+    } else {
+      uint32_t h[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t src = i == 0 ? ev : od;
+        const __half2 lo = __floats2half2_rn((float)(int8_t)(src & 0xFF), (float)(int8_t)((src >> 8) & 0xFF));
+        const __half2 hi = __floats2half2_rn((float)(int8_t)((src >> 16) & 0xFF), (float)(int8_t)(src >> 24));
+        h[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
+        h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+      *reinterpret_cast<uint4*>(tile + w * TC_LBO) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+  }
+  fence_proxy_async_smem();                         // the tensor core reads shared memory through the async proxy
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)kvh * p.packed_sh;
+  const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)kvh * p.scale_sh;
+
+  if (warp < TC_EPI_WARPS) {
+    // =============================== epilogue ===============================
+    // warp -> TMEM lane quadrant (warp % 4, fixed by the hardware) and unit (warp / 4): a unit is one
+    // 64-token block (`half`) of TC_QT_PER_WARP accumulator tiles.
+    const int quad = warp & 3, unit = warp >> 2;
+    const int half = unit & 1;
+    const int qt0 = (unit >> 1) * TC_QT_PER_WARP;
+    constexpr int GROUP = TC_EPI_WARPS / 2 * 32;    // threads that work on the same block of a tile
+    const int row = quad * 32 + lane;               // accumulator row = TMEM lane
+    const int hd = row / QPT, qi = row - hd * QPT;
+    const bool ks_loader = qt0 == 0 && row < 64;    // one thread per token of the block
+    float qs[TC_QT_PER_WARP];
+#pragma unroll
+    for (int j = 0; j < TC_QT_PER_WARP; ++j) {
+      const int q = q0 + (qt0 + j) * QPT + qi;
+      qs[j] = q < p.Tq ? p.qscale[((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q] : 0.0f;
+    }
+    // Key scales of this half's block live in a ring of TC_KS_SLOTS tiles; 64 threads per half refill four
+    // slots every four tiles from registers that were loaded four tiles earlier, so that the memory latency
+    // is never waited for.
+    auto load_ks = [&](int tile) -> float {
+      const int64_t t = (int64_t)tile * TC_NTILE + half * 64 + row;
+      float v = __int_as_float(0x7fc00000);         // dead token: NaN never wins a max
+      if (ks_loader && tile < ntiles && t < p.Tk) v = KIND == 0 ? scale_row[t] * 0.0625f : scale_row[t];
+      return v;
+    };
+    float kr[4];
+    if (ks_loader) {
+#pragma unroll
+      for (int j = 0; j < TC_KS_SLOTS; ++j) s_ks[(j * 2 + half) * 64 + row] = load_ks(j);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) kr[j] = load_ks(TC_KS_SLOTS + j);
+    named_bar_sync(1 + half, GROUP);
+    // Block maximum of 16 accumulator columns against their key scales: two columns per packed fp32
+    // multiply (each half rounded to nearest, as a scalar multiply) and per 3-input maximum.
+    auto chunk_max = [&](const uint32_t* v, const float* ks, float m) -> float {
+      float ma = m, mb = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < TC_CHW; c += 4) {
+        const ulonglong2 kk = *reinterpret_cast<const ulonglong2*>(ks + c);      // scales of columns c..c+3
+        uint64_t x01, x23, p01, p23;
+        float a0, a1, a2, a3;
+        if constexpr (KIND == 0) {
+          // exact int -> float (|acc| < 2^22): bits of 1.5 * 2^23 + acc, minus 1.5 * 2^23
+          const uint32_t i0 = v[c] + 0x4B400000u, i1 = v[c + 1] + 0x4B400000u;
+          const uint32_t i2 = v[c + 2] + 0x4B400000u, i3 = v[c + 3] + 0x4B400000u;
+          uint64_t y01, y23;
+          const uint64_t bias = 0xCB400000CB400000ull;                           // (-12582912.0f, -12582912.0f)
+          asm("mov.b64 %0, {%1, %2};" : "=l"(y01) : "r"(i0), "r"(i1));
+          asm("mov.b64 %0, {%1, %2};" : "=l"(y23) : "r"(i2), "r"(i3));
+          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(x01) : "l"(y01), "l"(bias));
+          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(x23) : "l"(y23), "l"(bias));
+        } else {
+          asm("mov.b64 %0, {%1, %2};" : "=l"(x01) : "r"(v[c]), "r"(v[c + 1]));
+          asm("mov.b64 %0, {%1, %2};" : "=l"(x23) : "r"(v[c + 2]), "r"(v[c + 3]));
+        }
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p01) : "l"(x01), "l"(kk.x));
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p23) : "l"(x23), "l"(kk.y));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(p01));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(a2), "=f"(a3) : "l"(p23));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(ma) : "f"(a0), "f"(a1));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mb) : "f"(a2), "f"(a3));
+      }
+      return fmaxf(ma, mb);
+    };
+    // The accumulator columns of this warp form one stream of 16-column chunks across tiles; the load of
+    // the next chunk (of the next tile, once its accumulator is complete) is in flight while the current
+    // one is reduced.
+    constexpr int CPB = 64 / TC_CHW;                // chunks per 64-token block
+    constexpr int NCH = CPB * TC_QT_PER_WARP;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(qt0 * TC_NTILE + half * 64);
+    auto chunk_addr = [&](int tile, int ch) -> uint32_t {
+      return lane_base + (uint32_t)((tile & 1) * TC_QT * TC_NTILE + (ch / CPB) * TC_NTILE + (ch % CPB) * TC_CHW);
+    };
+    uint32_t va[TC_CHW], vb[TC_CHW];
+    bool dead = false;
+    auto wait_tile = [&](int tile) {                // accumulator of `tile` complete (bounded)
+      if (dead) return;
+      if (!mbar_wait_bounded(&acc_full[tile & 1], (uint32_t)(tile >> 1) & 1u)) { *s_dead = 1; dead = true; }
+      tc_fence_after();
+    };
+    wait_tile(0);
+    if (!dead) tc_ld16(chunk_addr(0, 0), va);
+    for (int i = 0; i < ntiles; ++i) {
+      const int a = i & 1, par = i & 1;
+      if (*s_dead) dead = true;
+      float mq[TC_QT_PER_WARP];
+#pragma unroll
+      for (int j = 0; j < TC_QT_PER_WARP; ++j) mq[j] = 0.0f;
+      if (!dead) {
+        const float* ksb = s_ks + ((i & (TC_KS_SLOTS - 1)) * 2 + half) * 64;
+        float m = -INFINITY;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          uint32_t* cur = (ch & 1) ? vb : va;
+          uint32_t* nxt = (ch & 1) ? va : vb;
+          tc_wait_ld16(cur);
+          bool late = false;
+          if (ch + 1 < NCH) {
+            tc_ld16(chunk_addr(i, ch + 1), nxt);
+          } else {                                  // everything of this stage is in registers: it may be refilled
+            tc_fence_before();
+            mbar_arrive(&acc_empty[a]);
+            if (i + 1 < ntiles) {
+              if (mbar_try_wait(&acc_full[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u)) {
+                tc_fence_after();
+                tc_ld16(chunk_addr(i + 1, 0), nxt);
+              } else {
+                late = true;                        // not there yet: reduce first, then wait
+              }
+            }
+          }
+          m = chunk_max(cur, ksb + (ch % CPB) * TC_CHW, m);
+          if (ch % CPB == CPB - 1) {
+            mq[ch / CPB] = __fmul_rn(m, qs[ch / CPB]);   // x -> fl(x * qscale) is monotone: scale the maximum only
+            m = -INFINITY;
+          }
+          if (late) {
+            wait_tile(i + 1);
+            if (!dead) tc_ld16(chunk_addr(i + 1, 0), nxt);
+          }
+        }
+      }
+      // heads meet in shared memory; refills of the key-scale ring ride on the same barrier
+#pragma unroll
+      for (int j = 0; j < TC_QT_PER_WARP; ++j) s_x[((par * TC_QT + qt0 + j) * 2 + half) * 128 + row] = mq[j];
+      if ((i & 3) == 0 && i >= 4) {
+        if (ks_loader) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) s_ks[(((i + 4 + j) & (TC_KS_SLOTS - 1)) * 2 + half) * 64 + row] = kr[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kr[j] = load_ks(i + 8 + j);
+      }
+      named_bar_sync(1 + half, GROUP);
+      const int blk = 2 * i + half;
+      const int oslot = (i >> 2) & 1;               // output buffer parity: 4 tiles = 8 blocks per flush
+      if (row < QPT) {
+#pragma unroll
+        for (int j = 0; j < TC_QT_PER_WARP; ++j) {
+          const int qt = qt0 + j;
+          float best = -INFINITY;
+#pragma unroll
+          for (int h2 = 0; h2 < G; ++h2) best = fmaxf(best, s_x[((par * TC_QT + qt) * 2 + half) * 128 + h2 * QPT + row]);
+          if (best == 0.0f) best = 0.0f;            // -0 -> +0
+          s_out[(oslot * QCTA + qt * QPT + row) * TC_OUT_BLOCKS + (blk & (TC_OUT_BLOCKS - 1))] = best;
+        }
+      }
+      if ((i & 3) == 3 || i + 1 == ntiles) {
+        named_bar_sync(3, TC_EPI_WARPS * 32);       // every unit has put its blocks into s_out[oslot]
+        const int jb = (i >> 2) * TC_OUT_BLOCKS;    // first block of the batch
+        for (int e = tid; e < QCTA * TC_OUT_BLOCKS; e += TC_EPI_WARPS * 32) {
+          const int r = e / TC_OUT_BLOCKS, c = e - r * TC_OUT_BLOCKS;
+          const int q = q0 + r;
+          if (q < p.Tq && jb + c < p.nblk && !dead)
+            p.out[(((int64_t)b * p.Hkv + kvh) * p.Tq + q) * p.nblk + jb + c] = s_out[(oslot * QCTA + r) * TC_OUT_BLOCKS + c];
+        }
+      }
+    }
+  } else if (warp < TC_EPI_WARPS + TC_PROD_WARPS) {
+    // =============================== producers ===============================
+    const int pt = tid - TC_EPI_WARPS * 32;         // 0..127: token of the tile
+    uint32_t bufA[W], bufB[W], bufC[W], bufD[W];
+    auto load_tile = [&](int tile, uint32_t (&buf)[W]) {
+      const int64_t t = (int64_t)tile * TC_NTILE + pt;
+      if (tile < ntiles && t < p.Tk) {
+        const uint4* src = reinterpret_cast<const uint4*>(packed_row + t * (C / 2));
+#pragma unroll
+        for (int x = 0; x < W / 4; ++x) {
+          const uint4 u = __ldg(src + x);
+          buf[4 * x] = u.x; buf[4 * x + 1] = u.y; buf[4 * x + 2] = u.z; buf[4 * x + 3] = u.w;
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < W; ++x) buf[x] = 0;
+      }
+    };
+    bool dead = false;
+    auto store_tile = [&](int i, const uint32_t (&buf)[W]) {
+      const int s = i % BSTAGES;
+      if (!dead) {
+        const bool ok = mbar_wait_bounded(&b_empty[s], ((uint32_t)(i / BSTAGES) & 1u) ^ 1u);
+        if (!ok) { *s_dead = 1; dead = true; }
+      }
+      if (*s_dead) dead = true;
+      if (dead) return;
+      uint8_t* dst = s_b + s * Cfg::B_STAGE + (pt >> 3) * Cfg::SBO + (pt & 7) * 16;
+      if constexpr (KIND == 0) {
+#pragma unroll
+        for (int c = 0; c < W / 2; ++c) {           // 16-byte chunk c = words 2c, 2c+1 -> (even, odd, even, odd)
+          const uint32_t w0 = buf[2 * c], w1 = buf[2 * c + 1];
+          *reinterpret_cast<uint4*>(dst + c * TC_LBO) =
+              make_uint4((w0 << 4) & 0xF0F0F0F0u, w0 & 0xF0F0F0F0u, (w1 << 4) & 0xF0F0F0F0u, w1 & 0xF0F0F0F0u);
+        }
+      } else {
+        const __half2 bias = __floats2half2_rn(1032.0f, 1032.0f);
+#pragma unroll
+        for (int c = 0; c < W; ++c) {               // chunk c = word c -> 8 halves (4 even channels, 4 odd)
+          const uint32_t x = buf[c] ^ 0x88888888u;  // two's complement nibble -> code + 8
+          const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
+          uint32_t h[4];
+          h[0] = __byte_perm(lo, 0x64u, 0x4140);    // halves 1024 + (code + 8) of bytes 0, 1
+          h[1] = __byte_perm(lo, 0x64u, 0x4342);
+          h[2] = __byte_perm(hi, 0x64u, 0x4140);
+          h[3] = __byte_perm(hi, 0x64u, 0x4342);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h[j]), bias);
+            h[j] = *reinterpret_cast<const uint32_t*>(&r);
+          }
+          *reinterpret_cast<uint4*>(dst + c * TC_LBO) = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&b_full[s]);
+    };
+    // four tiles of packed codes are in flight in registers
+    load_tile(0, bufA);
+    load_tile(1, bufB);
+    load_tile(2, bufC);
+    load_tile(3, bufD);
+    for (int i = 0; i < ntiles; i += 4) {
+      store_tile(i, bufA);
+      load_tile(i + 4, bufA);
+      if (i + 1 < ntiles) { store_tile(i + 1, bufB); load_tile(i + 5, bufB); }
+      if (i + 2 < ntiles) { store_tile(i + 2, bufC); load_tile(i + 6, bufC); }
+      if (i + 3 < ntiles) { store_tile(i + 3, bufD); load_tile(i + 7, bufD); }
+    }
+  } else if (lane == 0) {
+    // =============================== MMA issuer ===============================
+    const uint32_t idesc = tc_instr_desc<KIND>(128, TC_NTILE);
+    const uint32_t a_addr = smem_u32(s_a), b_addr = smem_u32(s_b);
+    bool dead = false;
+    for (int i = 0; i < ntiles && !dead; ++i) {
+      const int s = i % BSTAGES, a = i & 1;
+      bool ok = mbar_wait_bounded(&b_full[s], (uint32_t)(i / BSTAGES) & 1u);
+      ok = ok && mbar_wait_bounded(&acc_empty[a], ((uint32_t)(i >> 1) & 1u) ^ 1u);
+      if (!ok || *s_dead) { *s_dead = 1; dead = true; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int qt = 0; qt < TC_QT; ++qt) {
+        const uint32_t d = tmem_base + (uint32_t)(a * TC_QT * TC_NTILE + qt * TC_NTILE);
+#pragma unroll
+        for (int k = 0; k < Cfg::KSTEPS; ++k) {
+          const uint64_t ad = tc_smem_desc(a_addr + qt * Cfg::A_TILE + k * 2 * TC_LBO, TC_LBO, Cfg::SBO);
+          const uint64_t bd = tc_smem_desc(b_addr + s * Cfg::B_STAGE + k * 2 * TC_LBO, TC_LBO, Cfg::SBO);
+          tc_mma<KIND>(d, ad, bd, idesc, k > 0 ? 1u : 0u);
+        }
+      }
+      tc_commit(&b_empty[s]);                       // the stage may be overwritten once these MMAs have read it
+      tc_commit(&acc_full[a]);
+    }
+    tc_commit(all_done);
+    mbar_wait_bounded(all_done, 0);                 // nothing of this CTA is still in flight in the tensor core
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == TC_WARPS - 1) {
+    tc_fence_after();
+    tc_dealloc(tmem_base, TC_TMEM_COLS);
+  }
+}
+
+template <int C, int G, int KIND>
+static int prefill_tc_launch(const PrefillTcParams& p, int device, cudaStream_t st) {
+  using Cfg = TcCfg<C, KIND>;
+  static_assert(Cfg::BYTES <= 227 * 1024, "shared memory budget");
+  auto kern = score_prefill_tc_kernel<C, G, KIND>;
+  static bool attr_done[64] = {false};
+  if (device < 64 && !attr_done[device]) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::BYTES));
+    attr_done[device] = true;
+  }
+  constexpr int QCTA = TC_QT * (128 / G);
+  dim3 grid(ceil_div(p.Tq, QCTA), p.B * p.Hkv);
+  kern<<<grid, TC_THREADS, Cfg::BYTES, st>>>(p);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  return KVB_OK;
+}
+
+template <int C, int KIND>
+static int prefill_tc_dispatch_g(const PrefillTcParams& p, int G, int device, cudaStream_t st) {
+  switch (G) {
+    case 1: return prefill_tc_launch<C, 1, KIND>(p, device, st);
+    case 2: return prefill_tc_launch<C, 2, KIND>(p, device, st);
+    case 4: return prefill_tc_launch<C, 4, KIND>(p, device, st);
+    case 8: return prefill_tc_launch<C, 8, KIND>(p, device, st);
+    default: return KVB_BAD_SHAPE;
+  }
+}
+
+// kind: 0 = int8 operands / int32 accumulators, 1 = fp16 operands / fp32 accumulators
+static int prefill_tc_run(const PrefillTcParams& p, int C, int G, int kind, int device, cudaStream_t st) {
+  if (kind == 0) {
+    if (C == 32) return prefill_tc_dispatch_g<32, 0>(p, G, device, st);
+    if (C == 64) return prefill_tc_dispatch_g<64, 0>(p, G, device, st);
+    if (C == 128) return prefill_tc_dispatch_g<128, 0>(p, G, device, st);
+  } else {
+    if (C == 32) return prefill_tc_dispatch_g<32, 1>(p, G, device, st);
+    if (C == 64) return prefill_tc_dispatch_g<64, 1>(p, G, device, st);
+    if (C == 128) return prefill_tc_dispatch_g<128, 1>(p, G, device, st);
+  }
+  return KVB_BAD_SHAPE;
+}
+
+}  // namespace kvb
+

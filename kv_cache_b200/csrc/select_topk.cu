@@ -287,6 +287,8 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   // the row length (and with it the count to select) may live on the device
   SelectParams p = pin;
   const int out_pitch = pin.kk;                         // rows of the outputs stay kk_max apart
+  pdl_launch_dependents();
+  pdl_wait();
   if (p.T_dev) {
     const int t = *p.T_dev;
     p.T = t < pin.T ? t : pin.T;

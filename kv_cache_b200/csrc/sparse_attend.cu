@@ -172,6 +172,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendPara
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int task = blockIdx.x * AT_WARPS + warp;
+  pdl_launch_dependents();
+  pdl_wait();
   if (task >= pin.B * pin.Hi * pin.nsplit) return;       // warps are independent: no block barrier below
   AttendParams p = pin;
   if (p.T_dev) {
@@ -381,6 +383,7 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
   const int b = row / p.Hi, hi = row - b * p.Hi;
   const int head = hi * GG + hd;
   const int d = threadIdx.x;
+  pdl_wait();
   const float* parts = p.ws_partial + (int64_t)row * p.nsplit * GG * PW;
   if (d < 32) {
     float m_a = -INFINITY, l_a = 0.0f, m_b = -INFINITY, l_b = 0.0f;
@@ -522,9 +525,9 @@ static int attend_launch(const AttendParams& p, int device, cudaStream_t st) {
     attr_done[device] = true;
   }
   const int tasks = p.B * p.Hi * p.nsplit;
-  kern<<<ceil_div(tasks, AT_WARPS), AT_THREADS, smem, st>>>(p);
+  KVB_CHECK_CUDA(launch_kernel(kern, dim3(ceil_div(tasks, AT_WARPS)), dim3(AT_THREADS), smem, st, p));
   KVB_CHECK_CUDA(cudaGetLastError());
-  attend_merge_kernel<GG><<<p.B * p.Hi * GG, AT_D, 0, st>>>(p);
+  KVB_CHECK_CUDA(launch_kernel(attend_merge_kernel<GG>, dim3(p.B * p.Hi * GG), dim3(AT_D), 0, st, p));
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
 }

@@ -471,10 +471,16 @@ def quantize_query_tokens(query: torch.Tensor, channel_idx: torch.Tensor) -> tup
     return qcode, qscale
 
 
+PREFILL_ENGINES = {"auto": 0, "mma": 1, "i8": 2, "f16": 3}
+
+
 def score_prefill_blocks(qcode: torch.Tensor, qscale: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                         key_count: Optional[int] = None) -> torch.Tensor:
+                         key_count: Optional[int] = None, engine: str = "auto") -> torch.Tensor:
     """Block scores fp32 ``[B,Hkv,Tq,ceil(Tk/64)]``: max over the GQA group and the 64 tokens of each
-    key block of the dequantised int8 x int4 partial score; every query sees all ``key_count`` keys."""
+    key block of the dequantised int8 x int4 partial score; every query sees all ``key_count`` keys.
+    ``engine``: ``auto`` (tensor-memory path), ``mma`` (warp-level int8 MMA), ``i8`` / ``f16`` (tcgen05 with
+    int8 operands and int32 accumulators / the same integers as fp16 operands with fp32 accumulators);
+    all produce identical bits."""
     B, Hq, Tq, C_ = qcode.shape
     Hkv = packed.shape[1]
     _check_side_cache(packed, scale, C_)
@@ -482,12 +488,12 @@ def score_prefill_blocks(qcode: torch.Tensor, qscale: torch.Tensor, packed: torc
     dev = qcode.device
     nblk = (Tk + PREFILL_BLOCK - 1) // PREFILL_BLOCK
     out = torch.empty((B, Hkv, Tq, nblk), dtype=torch.float32, device=dev)
-    check(_native.lib().kvb_score_prefill_blocks(
+    check(_native.lib().kvb_score_prefill_blocks_engine(
         qcode.contiguous().data_ptr(), qscale.contiguous().data_ptr(),
         packed.data_ptr(), packed.stride(0), packed.stride(1),
         scale.data_ptr(), scale.stride(0), scale.stride(1),
-        B, Hq, Hkv, Tq, Tk, C_, PREFILL_BLOCK, out.data_ptr(), _dev(qcode), _stream(dev)),
-        "kvb_score_prefill_blocks")
+        B, Hq, Hkv, Tq, Tk, C_, PREFILL_BLOCK, out.data_ptr(), PREFILL_ENGINES[engine], _dev(qcode), _stream(dev)),
+        "kvb_score_prefill_blocks_engine")
     return out
 
 

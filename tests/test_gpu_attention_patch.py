@@ -63,3 +63,42 @@ def test_tiny_qwen3_decode_equals_dense_when_everything_is_selected(cuda_device)
         torch.testing.assert_close(sparse.logits.float(), dense.logits.float(), rtol=5e-2, atol=5e-2)
     finally:
         ap.uninstall_qwen3_attention_patch()
+
+
+def test_qwen3_0p6b_shaped_model_decodes_through_all_28_layers(cuda_device):
+    """The layer stack of Qwen3-0.6B (28 layers, 16 query / 8 KV heads of 128, hidden 1024; small vocabulary,
+    random weights): prefill under 'baseline', then decode steps under the sparse mode. With every token
+    selected the logits must match dense attention; at 6.25 % the step must run, stay finite, and extend
+    the int4 side cache of every layer by one row per step."""
+    pytest.importorskip("transformers")
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    import copy
+
+    torch.manual_seed(1)
+    cfg = Qwen3Config(vocab_size=1024, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28,
+                      num_attention_heads=16, num_key_value_heads=8, head_dim=128, max_position_embeddings=40960,
+                      rope_theta=1e6, rms_norm_eps=1e-6, attn_implementation="eager")
+    model = Qwen3ForCausalLM(cfg).to(cuda_device, torch.bfloat16).eval()
+    ap.install_qwen3_attention_patch()
+    try:
+        ids = torch.randint(0, 1024, (2, 1536), device=cuda_device)
+        nxt = torch.randint(0, 1024, (2, 1), device=cuda_device)
+        with torch.inference_mode():
+            with ap.attention_mode("baseline"):
+                pre = model(input_ids=ids, use_cache=True)
+                dense = model(input_ids=nxt, past_key_values=copy.deepcopy(pre.past_key_values), use_cache=True)
+            with ap.attention_mode("qabs32cand100attn", 0.02, 3, True, 0, 0, None) as state:
+                full = model(input_ids=nxt, past_key_values=copy.deepcopy(pre.past_key_values), use_cache=True)
+                assert sorted(state.layers) == list(range(28))
+            torch.testing.assert_close(full.logits.float(), dense.logits.float(), rtol=5e-2, atol=5e-2)
+            with ap.attention_mode("qabs32cand6p25attn", 0.02, 3, True, 4, 16, None) as state:
+                past = pre.past_key_values
+                for step in range(3):
+                    out = model(input_ids=nxt, past_key_values=past, use_cache=True)
+                    past = out.past_key_values
+                    assert torch.isfinite(out.logits.float()).all()
+                    assert all(state.layers[l].count == 1537 + step for l in range(28))
+            # a sparse step stays close to the dense one on this random model (most attention mass is kept)
+            assert (out.logits.float() - dense.logits.float()).abs().mean() < 1.0
+    finally:
+        ap.uninstall_qwen3_attention_patch()
