@@ -259,6 +259,9 @@ int kvb_sparse_attend(const void* query, int64_t q_sb, int64_t q_sh,
  *              (and it is not in a protected range unless append_protected). With id_base != 0
  *              the ids are global and this rank owns [id_base, id_base + history_count): what a
  *              sequence shard needs after the global top-k merge.
+ *   sel_count  optional int32 [B*Hkv]: row r uses only its first sel_count[r] (<= kk) entries of
+ *              `selected`, and the work is divided over that shorter list (the compacted "owned"
+ *              lists of kvb_merge_candidates); NULL = all kk.
  *   key/value  views whose rows 0 .. history_count-1 are the history and, when keep_self != 0,
  *              row history_count is the token being decoded (Tk >= history_count + keep_self).
  *   out / out_partial / mask / workspace as in kvb_sparse_attend; workspace size from
@@ -266,7 +269,8 @@ int kvb_sparse_attend(const void* query, int64_t q_sb, int64_t q_sh,
 int kvb_attend_selected(const void* query, int64_t q_sb, int64_t q_sh,
                         const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
                         const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st,
-                        const int32_t* selected, int kk, int64_t id_base, int history_count,
+                        const int32_t* selected, int kk, const int32_t* sel_count,
+                        int64_t id_base, int history_count,
                         int protect_sink, int protect_recent, int keep_self, int append_protected,
                         const float* mask, int64_t mask_sb,
                         int B, int Hq, int Hkv, int Tk, int D, float scaling,
@@ -279,7 +283,9 @@ int kvb_attend_selected(const void* query, int64_t q_sb, int64_t q_sh,
  * kvb_shard_candidates: the exact local top-k of a shard in one call (sampled threshold, candidate
  *   scorer, bounds check with exact rescue, exact finish): out_comp uint64 [B*Hkv, kk],
  *   kk = min(top_k, T), each entry (order-preserving key of the group max) << 32 |
- *   (0xFFFFFFFF - (token + id_offset)), in no particular order. Needs the streaming configuration
+ *   (0xFFFFFFFF - (token + id_offset)), in no particular order except that, with 0 < split_k < kk,
+ *   the split_k best entries come first (a reader may take that prefix as the local top-split_k).
+ *   Needs the streaming configuration
  *   and top_k small enough for the candidate capacity (else KVB_BAD_SHAPE: use kvb_score_decode +
  *   kvb_select_topk). workspace >= kvb_shard_candidates_workspace_bytes(B, Hkv, T, top_k).
  * kvb_merge_candidates: the global top-k of N such lists after an all-gather: gathered uint64
@@ -287,19 +293,30 @@ int kvb_attend_selected(const void* query, int64_t q_sb, int64_t q_sh,
  *   id_range (the total token count) is at most 262144 (a cheap on-chip bitmap), otherwise in
  *   arbitrary order (the set is exact either way). With N > 1 every list must hold top_k entries (kk == top_k).
  *   The composites are unique, so every rank that runs this on the same gathered data gets the
- *   same set. */
+ *   same set.
+ *   prefix_k > 0 says that every list has its prefix_k best entries first (split_k above). When the
+ *   N prefixes fit on chip (N * prefix_k <= 8192, N <= 64) the kernel selects from them alone and
+ *   accepts the result iff, for every list, the smallest entry of its prefix is itself no larger than
+ *   the k-th winner (nothing behind the prefix can then be a winner); otherwise it repeats the select
+ *   over the whole lists. The result is the same exact set either way.
+ *   out_owned (optional, with out_owned_count int32 [R]): the winners whose id lies in
+ *   [own_base, own_limit), compacted per row (row pitch as out_idx), for kvb_attend_selected's
+ *   sel_count; the output order is then arbitrary. */
 size_t kvb_shard_candidates_workspace_bytes(int B, int Hkv, int T, int top_k);
 
 int kvb_shard_candidates(const void* query, int64_t q_sb, int64_t q_sh,
                          const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
                          const float* scale, int64_t scale_sb, int64_t scale_sh,
                          const int32_t* channel_idx,
-                         int B, int Hq, int Hkv, int T, int D, int C, int top_k, int64_t id_offset,
+                         int B, int Hq, int Hkv, int T, int D, int C, int top_k, int split_k,
+                         int64_t id_offset,
                          uint64_t* out_comp, void* workspace, size_t workspace_bytes,
                          int device, void* stream);
 
 int kvb_merge_candidates(const uint64_t* gathered, int N, int R, int kk, int top_k, int64_t id_range,
-                         int32_t* out_idx, int device, void* stream);
+                         int prefix_k, int32_t* out_idx,
+                         int64_t own_base, int64_t own_limit, int32_t* out_owned, int32_t* out_owned_count,
+                         int device, void* stream);
 
 /* Combine N shard partials [N,B,Hq,D+2] (layout of out_partial above) into bf16 [B,1,Hq,D]:
  * o = sum_r e^{m_r-m} o_r / sum_r e^{m_r-m} l_r, shards with l == 0 ignored. No reference

@@ -77,12 +77,12 @@ SIGNATURES = {
                                _p, _i, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f,
                                _p, _p, _p, _sz, _i, _p]),
     "kvb_attend_selected": (_i, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64,
-                                 _p, _i, _i64, _i, _i, _i, _i, _i, _p, _i64,
+                                 _p, _i, _p, _i64, _i, _i, _i, _i, _i, _p, _i64,
                                  _i, _i, _i, _i, _i, _f, _p, _p, _p, _sz, _i, _p]),
     "kvb_shard_candidates_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "kvb_shard_candidates": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
-                                  _i, _i, _i, _i, _i, _i, _i, _i64, _p, _p, _sz, _i, _p]),
-    "kvb_merge_candidates": (_i, [_p, _i, _i, _i, _i, _i64, _p, _i, _p]),
+                                  _i, _i, _i, _i, _i, _i, _i, _i, _i64, _p, _p, _sz, _i, _p]),
+    "kvb_merge_candidates": (_i, [_p, _i, _i, _i, _i, _i64, _i, _p, _i64, _i64, _p, _p, _i, _p]),
     "kvb_lse_merge": (_i, [_p, _i, _i, _i, _i, _p, _i, _p]),
     "kvb_quantize_query_tokens": (_i, [_p, _i64, _i64, _i64, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     "kvb_score_prefill_blocks": (_i, [_p, _p, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),

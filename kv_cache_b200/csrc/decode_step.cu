@@ -425,11 +425,11 @@ extern "C" __attribute__((visibility("default"))) size_t kvb_shard_candidates_wo
 extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
     const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
     const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
-    int D, int C, int top_k, int64_t id_offset, uint64_t* out_comp, void* workspace, size_t workspace_bytes,
-    int device, void* stream) {
+    int D, int C, int top_k, int split_k, int64_t id_offset, uint64_t* out_comp, void* workspace,
+    size_t workspace_bytes, int device, void* stream) {
   using namespace kvb;
   if (!query || !packed || !scale || !channel_idx || !out_comp || !workspace) return KVB_BAD_ARG;
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || top_k <= 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || top_k <= 0 || split_k < 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
   if (id_offset < 0 || id_offset + T > 0x7fffffffLL) return KVB_BAD_SHAPE;
   if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
   const ShardLayout L = shard_layout(B, Hkv, T, top_k);
@@ -465,6 +465,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   sp.from_candidates = 1; sp.row_failed = nullptr; sp.T_dev = nullptr;
   sp.gather = nullptr; sp.gather_n = 0; sp.gather_len = 0; sp.gather_stride = 0;
   sp.rescue = 1; sp.rescue_sp = base;
+  sp.split_k = split_k;
   const size_t smem = (size_t)L.cap * 8 + SEL_FINAL_FIXED_SMEM;
   static bool attr_done[64] = {false};
   if (device < 64 && !attr_done[device]) {
@@ -477,13 +478,14 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   return KVB_OK;
 }
 
-extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(const uint64_t* gathered, int N, int R,
-                                                                            int kk, int top_k, int64_t id_range,
-                                                                            int32_t* out_idx, int device,
-                                                                            void* stream) {
+extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(
+    const uint64_t* gathered, int N, int R, int kk, int top_k, int64_t id_range, int prefix_k, int32_t* out_idx,
+    int64_t own_base, int64_t own_limit, int32_t* out_owned, int32_t* out_owned_count, int device, void* stream) {
   using namespace kvb;
   if (!gathered || !out_idx) return KVB_BAD_ARG;
-  if (N <= 0 || R <= 0 || kk <= 0 || top_k <= 0 || id_range <= 0 || id_range > 0x7fffffffLL) return KVB_BAD_SHAPE;
+  if (N <= 0 || R <= 0 || kk <= 0 || top_k <= 0 || id_range <= 0 || id_range > 0x7fffffffLL || prefix_k < 0)
+    return KVB_BAD_SHAPE;
+  if (out_owned && (!out_owned_count || own_limit <= own_base)) return KVB_BAD_ARG;
   if (kk < top_k && N > 1) return KVB_BAD_SHAPE;            // every shard must bring top_k entries (see header)
   const int64_t total = (int64_t)N * kk;
   const int kout = (int)(top_k < total ? top_k : total);
@@ -499,9 +501,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(const
   sp.from_candidates = 0; sp.row_failed = nullptr; sp.T_dev = nullptr;
   sp.gather = gathered; sp.gather_n = N; sp.gather_len = kk; sp.gather_stride = (int64_t)R * kk;
   sp.rescue = 0;
+  sp.gather_prefix = prefix_k;
+  sp.out_owned = out_owned; sp.out_owned_count = out_owned_count; sp.own_base = own_base; sp.own_limit = own_limit;
   const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((id_range + 31) / 32);
   size_t smem = (size_t)sp.cap * 8 + SEL_FINAL_FIXED_SMEM;
-  if (id_range <= 262144 && smem + bitmap_bytes <= SEL_SMEM_LIMIT) {
+  if (!out_owned && id_range <= 262144 && smem + bitmap_bytes <= SEL_SMEM_LIMIT) {
     sp.order_by_index = 1; sp.use_bitmap = 1; smem += bitmap_bytes;      // ascending global ids (cheap bitmap only)
   } else {
     sp.order_by_index = 2; sp.use_bitmap = 0;                              // exact set, arbitrary order

@@ -27,6 +27,8 @@ constexpr int SEL_MAX_K = 16384;
 constexpr int SEL_COUNT_STRIDE = 32;        // words between per-row candidate counters: one 128-byte line each,
                                             // so the atomics of different rows do not queue on one L2 line
 
+constexpr int SEL_MAX_SEGMENTS = 64;          // shard lists a prefix merge can take
+
 struct SelectParams {
   const float* scores;
   int64_t row_stride;
@@ -58,6 +60,17 @@ struct SelectParams {
   // kernel into `scores` (the group-max workspace) and then selected by the refinement path
   int rescue;
   ScoreParams rescue_sp;
+  // unordered output only: the split_k best winners are written first (positions [0, split_k)), the
+  // others after them, so that a reader may take a prefix of the list as "the split_k best"
+  int split_k = 0;
+  // gathered source only: every segment has its gather_prefix best entries first (see split_k). The
+  // kernel then selects from the prefixes alone and accepts the result iff no segment can hold a
+  // better entry behind its prefix; otherwise it falls back to the whole segments
+  int gather_prefix = 0;
+  // optional second output: the winners whose id lies in [own_base, own_limit), compacted, and how many
+  int32_t* out_owned = nullptr;
+  int32_t* out_owned_count = nullptr;
+  int64_t own_base = 0, own_limit = 0;
 };
 
 __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row, int64_t t) {
@@ -298,8 +311,9 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   uint64_t* s_cand = reinterpret_cast<uint64_t*>(sel_smem);                     // [cap]
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(sel_smem + (size_t)p.cap * 8);  // [2048]
   uint32_t* s_tmp = s_hist + 2048;                                              // [NT + 40] (80 used)
-  uint32_t* s_count = s_tmp + SEL_FINAL_THREADS + 40;                           // [4]
-  uint32_t* s_bitmap = s_count + 4;                                             // [ceil(T/32)] when use_bitmap
+  uint32_t* s_count = s_tmp + SEL_FINAL_THREADS + 40;                           // [8]
+  unsigned long long* s_segmin = reinterpret_cast<unsigned long long*>(s_count + 8);   // [SEL_MAX_SEGMENTS]
+  uint32_t* s_bitmap = reinterpret_cast<uint32_t*>(s_segmin + SEL_MAX_SEGMENTS); // [ceil(T/32)] when use_bitmap
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -321,8 +335,28 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   uint32_t in_prefix;
   int n = 0;                                            // candidates in s_cand: all with composite >= prefix
   bool have_candidates;
+  uint64_t kth;
   const uint64_t* cand = p.cand ? p.cand + (int64_t)row * p.cap : nullptr;
-  if (gathered) {
+  bool prefix_mode = gathered && p.gather_prefix > 0 && p.gather_prefix < p.gather_len &&
+                     p.gather_n <= SEL_MAX_SEGMENTS && (int64_t)p.gather_n * p.gather_prefix <= (int64_t)p.cap &&
+                     (int64_t)p.gather_n * p.gather_prefix >= (int64_t)p.kk;
+again:
+  if (prefix_mode) {
+    // The best gather_prefix entries of every segment, all on chip; the smallest of each prefix is kept
+    // for the acceptance test after the select.
+    for (int i = tid; i < p.gather_n; i += SEL_FINAL_THREADS) s_segmin[i] = ~0ull;
+    __syncthreads();
+    n = p.gather_n * p.gather_prefix;
+    for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
+      const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
+      const uint64_t c = __ldcg(p.gather + (int64_t)seg * p.gather_stride + (int64_t)row * p.gather_len + j);
+      s_cand[i] = c;
+      atomicMin(&s_segmin[seg], (unsigned long long)c);
+    }
+    __syncthreads();
+    prefix = 0; fixed = 0; need = (uint32_t)p.kk; in_prefix = (uint32_t)n;
+    have_candidates = true;
+  } else if (gathered) {
     // All-gathered shard lists: up to gather_n * gather_len composites, far more than fit on chip. The
     // refinement below narrows them with 11-bit histogram passes over global memory (two passes bring
     // i.i.d. shard lists under the capacity) and then collects the survivors.
@@ -429,29 +463,81 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
     prefix = (prefix << width) | d;
     fixed += width;
   }
-  const uint64_t kth = fixed >= 64 ? prefix : (fixed == 0 ? 0ull : (prefix << (64 - fixed)));   // winners: composite >= kth
+  kth = fixed >= 64 ? prefix : (fixed == 0 ? 0ull : (prefix << (64 - fixed)));   // winners: composite >= kth
+  if (prefix_mode) {
+    // Everything behind a segment's prefix is smaller than the prefix's smallest entry: if that entry is
+    // itself no winner-beating value (<= kth), nothing behind it can be a winner. Otherwise start over
+    // on the whole segments.
+    bool ok = true;
+    for (int sgm = 0; sgm < p.gather_n; ++sgm) ok = ok && (s_segmin[sgm] <= kth);
+    if (!ok) {
+      prefix_mode = false;
+      n = 0;
+      __syncthreads();
+      goto again;
+    }
+  }
 
   // Composites built from scores carry index + idx_offset; scorer-made lists carry row-local ids and
   // gathered ones global ids: id_sub maps a composite's id to the bitmap position, id_add to the output.
   const uint32_t id_sub = (p.from_candidates || gathered) ? 0u : (uint32_t)p.idx_offset;
   const uint32_t id_add = gathered ? 0u : (uint32_t)p.idx_offset;
   if (p.order_by_index == 2) {
-    // Unordered output: the winners in whatever order the threads meet them (the SET is exact).
-    if (tid == 0) *s_count = 0;
+    // Unordered output: the winners in whatever order the threads meet them (the SET is exact); with
+    // split_k the split_k best of them come first.
+    uint64_t kth_split = ~0ull;
+    const bool split = p.split_k > 0 && p.split_k < p.kk;
+    if (split) {
+      // a second radix select over the same on-chip candidates, for rank split_k
+      uint64_t pf = 0;
+      int fx = 0;
+      uint32_t nd = (uint32_t)p.split_k, inp = (uint32_t)n;
+      while (inp > nd && fx < 64) {
+        const int width = (64 - fx) >= 11 ? 11 : (64 - fx);
+        const int shift = 64 - fx - width;
+        const int nb = 1 << width;
+        for (int i = tid; i < nb; i += SEL_FINAL_THREADS) s_hist[i] = 0;
+        __syncthreads();
+        for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
+          const uint64_t c = s_cand[i];
+          if (fx == 0 || (c >> (64 - fx)) == pf) atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
+        }
+        __syncthreads();
+        uint32_t d, ab, in;
+        find_threshold<SEL_FINAL_THREADS>(s_hist, nb, nd, s_tmp, d, ab, in);
+        nd -= ab;
+        inp = in;
+        pf = (pf << width) | d;
+        fx += width;
+      }
+      kth_split = fx >= 64 ? pf : (fx == 0 ? 0ull : (pf << (64 - fx)));
+    }
+    if (tid < 3) s_count[tid] = 0;
     __syncthreads();
+    const bool own = p.out_owned != nullptr;
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
       const uint64_t c = s_cand[i];
       if (c >= kth) {
-        const uint32_t pos = atomicAdd(s_count, 1u);
+        uint32_t pos;
+        if (split && c < kth_split) pos = (uint32_t)p.split_k + atomicAdd(&s_count[1], 1u);
+        else pos = atomicAdd(&s_count[0], 1u);
+        const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
         if (pos < (uint32_t)p.kk) {
           const int64_t o = (int64_t)row * out_pitch + pos;
-          const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
           if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
           if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
           if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(c >> 32));
           if (p.out_comp) p.out_comp[o] = (c & 0xFFFFFFFF00000000ull) | (uint64_t)(0xFFFFFFFFu - idx);
         }
+        if (own && (int64_t)idx >= p.own_base && (int64_t)idx < p.own_limit) {
+          const uint32_t q = atomicAdd(&s_count[2], 1u);
+          if (q < (uint32_t)p.kk) p.out_owned[(int64_t)row * out_pitch + q] = (int32_t)idx;
+        }
       }
+    }
+    if (own && p.out_owned_count) {
+      __syncthreads();
+      if (tid == 0) p.out_owned_count[row] = (int32_t)(s_count[2] < (uint32_t)p.kk ? s_count[2] : (uint32_t)p.kk);
     }
     return;
   }
@@ -529,7 +615,7 @@ static int select_cap(int k) {
   return c;
 }
 
-constexpr size_t SEL_FINAL_FIXED_SMEM = sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 40 + 4);
+constexpr size_t SEL_FINAL_FIXED_SMEM = sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 40 + 8) + 8 * SEL_MAX_SEGMENTS;
 constexpr size_t SEL_SMEM_LIMIT = 227 * 1024;
 
 struct SelectWorkspace {

@@ -56,6 +56,7 @@ struct AttendList {
   int implicit;
   const int32_t* selected; int kk; int sel_pitch;   // kk entries used of rows sel_pitch apart
   int64_t sel_base; int sel_limit;       // selected ids are global: local row = id - sel_base, kept iff in [0, sel_limit)
+  const int32_t* sel_count;              // optional: row r uses only its first sel_count[r] (<= kk) selected entries
   int sink_end, n_recent, recent_from, recent_start, recent_on, history, append_protected;
 };
 
@@ -192,6 +193,18 @@ __global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendPara
   const int row = task / p.nsplit;                       // (b, index head)
   const int split = task - row * p.nsplit;
   const int b = row / p.Hi, hi = row - b * p.Hi;
+  if (p.list.implicit && p.list.sel_count) {
+    // a shorter selected part for this row: the list and the chunking shrink with it
+    int c = p.list.sel_count[row];
+    if (c < 0) c = 0;
+    if (c < p.list.kk) {
+      p.S -= p.list.kk - c;
+      p.list.kk = c;
+      const int tiles = (p.S + AT_TILE - 1) / AT_TILE;
+      p.tiles_per_split = (tiles + p.nsplit - 1) / p.nsplit;
+      if (p.tiles_per_split < 1) p.tiles_per_split = 1;
+    }
+  }
   const int head0 = hi * GG;                             // first query head served
   const int kvh = head0 / p.G;
 
@@ -627,7 +640,8 @@ extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(
 
 extern "C" __attribute__((visibility("default"))) int kvb_attend_selected(
     const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
-    const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st, const int32_t* selected, int kk, int64_t id_base,
+    const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st, const int32_t* selected, int kk,
+    const int32_t* sel_count, int64_t id_base,
     int history_count, int protect_sink, int protect_recent, int keep_self, int append_protected, const float* mask,
     int64_t mask_sb, int B, int Hq, int Hkv, int Tk, int D, float scaling, void* out, float* out_partial,
     void* workspace, size_t workspace_bytes, int device, void* stream) {
@@ -643,6 +657,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_attend_selected(
   AttendList list{};
   list.implicit = 1;
   list.selected = selected; list.kk = kk; list.sel_pitch = kk;
+  list.sel_count = sel_count;
   list.sel_base = id_base; list.sel_limit = history_count;
   list.sink_end = f.sink_end; list.n_recent = f.n_recent; list.recent_from = f.recent_from;
   list.recent_start = f.recent_start; list.recent_on = f.recent_on; list.history = history_count;

@@ -362,10 +362,12 @@ def sparse_attend(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, i
 def attend_selected(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, selected: torch.Tensor,
                     history_count: int, *, id_base: int = 0, protect_sink: int = 0, protect_recent: int = 0,
                     keep_self: bool = True, append_protected: bool = False, scaling: Optional[float] = None,
-                    attention_mask: Optional[torch.Tensor] = None, return_partial: bool = False):
+                    attention_mask: Optional[torch.Tensor] = None, return_partial: bool = False,
+                    selected_count: Optional[torch.Tensor] = None):
     """Attention over the implicit list ``selected ‖ sink ‖ recent ‖ self`` (one list per KV head,
     int32 ``[B,Hkv,kk]``). Ids outside ``[id_base, id_base + history_count)`` contribute nothing,
-    which is how a sequence shard attends to the part of a global selection that it owns."""
+    which is how a sequence shard attends to the part of a global selection that it owns. With
+    ``selected_count`` (int32 ``[B*Hkv]``) only the first ``selected_count[r]`` entries of row ``r`` are used."""
     query = _query3(query)
     B, Hq, D = query.shape
     Hkv, Tk = key.shape[1], key.shape[2]
@@ -389,7 +391,7 @@ def attend_selected(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
         query.data_ptr(), query.stride(0), query.stride(1),
         key.data_ptr(), key.stride(0), key.stride(1), key.stride(2),
         value.data_ptr(), value.stride(0), value.stride(1), value.stride(2),
-        selected.data_ptr(), kk, int(id_base), int(history_count), int(protect_sink), int(protect_recent),
+        selected.data_ptr(), kk, _ptr(selected_count), int(id_base), int(history_count), int(protect_sink), int(protect_recent),
         int(keep_self), int(append_protected), _ptr(mask), 0 if mask is None else mask.stride(0),
         B, Hq, Hkv, Tk, D, float(scaling), _ptr(out), _ptr(part), ws.data_ptr(), ws.numel(),
         _dev(query), _stream(dev)), "kvb_attend_selected")
@@ -398,10 +400,11 @@ def attend_selected(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
 
 def shard_candidates(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
                      history_count: int, top_k: int, id_offset: int = 0,
-                     workspace: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                     workspace: Optional[torch.Tensor] = None, split_k: int = 0) -> Optional[torch.Tensor]:
     """Exact local top-``k`` of a sequence shard as 64-bit composites with GLOBAL token ids, int64
-    ``[B*Hkv, min(k,T)]``, unordered. Returns ``None`` when the configuration has no candidate front
-    end (the caller then uses ``score`` + ``select``)."""
+    ``[B*Hkv, min(k,T)]``, unordered except that the ``split_k`` best come first when ``0 < split_k < k``.
+    Returns ``None`` when the configuration has no candidate front end (the caller then uses
+    ``score`` + ``select``)."""
     query = _query3(query)
     B, Hq, D = query.shape
     Hkv = packed.shape[1]
@@ -416,22 +419,35 @@ def shard_candidates(query: torch.Tensor, packed: torch.Tensor, scale: torch.Ten
     rc = lib.kvb_shard_candidates(
         query.data_ptr(), query.stride(0), query.stride(1), packed.data_ptr(), packed.stride(0), packed.stride(1),
         scale.data_ptr(), scale.stride(0), scale.stride(1), channel_idx.data_ptr(), B, Hq, Hkv, T, D, C_, int(top_k),
-        int(id_offset), out.data_ptr(), ws.data_ptr(), ws.numel(), _dev(query), _stream(dev))
+        int(split_k), int(id_offset), out.data_ptr(), ws.data_ptr(), ws.numel(), _dev(query), _stream(dev))
     if rc == 1:          # KVB_BAD_SHAPE: not a streaming configuration / k too large for the candidate capacity
         return None
     check(rc, "kvb_shard_candidates")
     return out
 
 
-def merge_candidates(gathered: torch.Tensor, top_k: int, id_range: int) -> torch.Tensor:
-    """Global top-``k`` token ids (int32 ``[R, k']``) from all-gathered composite lists int64 ``[N,R,kk]``."""
+def merge_candidates(gathered: torch.Tensor, top_k: int, id_range: int, prefix_k: int = 0,
+                     own: Optional[tuple[int, int]] = None):
+    """Global top-``k`` token ids (int32 ``[R, k']``) from all-gathered composite lists int64 ``[N,R,kk]``.
+    ``prefix_k``: every list has its ``prefix_k`` best entries first (``shard_candidates(split_k=...)``),
+    which lets the kernel work on the prefixes alone when that is provably enough. ``own = (base, limit)``:
+    also return the winners with ``base <= id < limit`` compacted per row and their count:
+    ``(ids, owned int32 [R,k'], owned_count int32 [R])``."""
     N, R, kk = gathered.shape
     gathered = gathered.contiguous()
     kout = min(int(top_k), N * kk)
-    out = torch.empty((R, kout), dtype=torch.int32, device=gathered.device)
-    check(_native.lib().kvb_merge_candidates(gathered.data_ptr(), N, R, kk, int(top_k), int(id_range), out.data_ptr(),
-                                             _dev(gathered), _stream(gathered.device)), "kvb_merge_candidates")
-    return out
+    dev = gathered.device
+    out = torch.empty((R, kout), dtype=torch.int32, device=dev)
+    owned = cnt = None
+    base = limit = 0
+    if own is not None:
+        base, limit = int(own[0]), int(own[1])
+        owned = torch.empty((R, kout), dtype=torch.int32, device=dev)
+        cnt = torch.empty((R,), dtype=torch.int32, device=dev)
+    check(_native.lib().kvb_merge_candidates(gathered.data_ptr(), N, R, kk, int(top_k), int(id_range), int(prefix_k),
+                                             out.data_ptr(), base, limit, _ptr(owned), _ptr(cnt),
+                                             _dev(gathered), _stream(dev)), "kvb_merge_candidates")
+    return out if own is None else (out, owned, cnt)
 
 
 def lse_merge(partials: torch.Tensor) -> torch.Tensor:

@@ -96,16 +96,25 @@ class ShardedSparseDecode:
         B, Hkv = key_local.shape[0], key_local.shape[1]
         mark = self._mark
         mark("start")
-        comp = ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset, self._ws)
+        # Every shard puts its 8192/N best candidates first: the merge then works on those prefixes alone
+        # (all on chip) whenever that is provably the global answer, which it is unless one shard holds far
+        # more than its share of the winners.
+        prefix = min(self.top_k, 8192 // N) if N > 1 else 0
+        comp = ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset, self._ws,
+                                    split_k=prefix)
         if comp is None:
             return None
         mark("local top-k")
         gathered = _all_gather(comp, N, self.group) if N > 1 else comp[None]
         mark("all-gather candidates")
-        sel = ops.merge_candidates(gathered, self.top_k, self.total_tokens).view(B, Hkv, -1)
+        # the merge also hands this rank the winners it owns, compacted: the attention walks only those
+        sel, owned, owned_count = ops.merge_candidates(gathered, self.top_k, self.total_tokens, prefix_k=prefix,
+                                                       own=(id_offset, id_offset + t_local))
+        sel = sel.view(B, Hkv, -1)
         mark("global merge")
-        part = self.backend.attend_partial(query, key_local, value_local, sel, t_local, id_offset,
-                                           self.rank == N - 1, scaling)
+        part = ops.attend_selected(query, key_local, value_local, owned.view(B, Hkv, -1), t_local, id_base=id_offset,
+                                   keep_self=self.rank == N - 1, scaling=scaling, return_partial=True,
+                                   selected_count=owned_count)
         mark("attend owned rows")
         parts = _all_gather(part, N, self.group) if N > 1 else part[None]
         mark("all-gather partials")
