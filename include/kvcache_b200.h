@@ -430,6 +430,11 @@ typedef struct kvb_decode_step_params {
    * {1,2,4,8}, aligned side cache, top_k <= history_count <= 131072); others return KVB_BAD_SHAPE. */
   const int32_t* history_count_dev;
   int advance_history;
+  /* Optional: the decoded token's K and V rows, bf16 [B,Hkv,D] dense. When not NULL the step first
+   * stores them as row T of `key` / `value` (T from history_count_dev when that is set), which spares
+   * a caller inside a graph its own scatter at a device-side position. Both or neither. */
+  const void* new_key_row;
+  const void* new_value_row;
 } kvb_decode_step_params;
 
 size_t kvb_decode_step_workspace_bytes(int B, int Hq, int Hkv, int history_count, int top_k,

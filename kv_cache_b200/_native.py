@@ -47,6 +47,7 @@ class DecodeStepParams(C.Structure):
         ("sel_idx_out", _p),
         ("workspace", _p), ("workspace_bytes", _sz),
         ("history_count_dev", _p), ("advance_history", _i),
+        ("new_key_row", _p), ("new_value_row", _p),
     ]
 
 

@@ -170,6 +170,24 @@ static int sample_launch_g(const SampleParams& q, int R, cudaStream_t st) {
   return KVB_OK;
 }
 
+// Stores the decoded token's K and V rows (bf16 [B*Hkv, 128] dense) as row T of the caches: one warp per
+// (batch, KV head), 16 lanes per row, 16 bytes per lane.
+__global__ void __launch_bounds__(32) store_new_rows_kernel(const uint4* new_k, const uint4* new_v, __nv_bfloat16* key,
+                                                            int64_t k_sb, int64_t k_sh, int64_t k_st,
+                                                            __nv_bfloat16* value, int64_t v_sb, int64_t v_sh,
+                                                            int64_t v_st, int Hkv, int T, const int32_t* T_dev) {
+  const int row = blockIdx.x, lane = threadIdx.x;
+  const int b = row / Hkv, h = row - b * Hkv;
+  const int t = T_dev ? min(*T_dev, T) : T;
+  pdl_launch_dependents();
+  if (lane < 16) {
+    *reinterpret_cast<uint4*>(key + (int64_t)b * k_sb + (int64_t)h * k_sh + (int64_t)t * k_st + lane * 8) = new_k[row * 16 + lane];
+  } else {
+    *reinterpret_cast<uint4*>(value + (int64_t)b * v_sb + (int64_t)h * v_sh + (int64_t)t * v_st + (lane - 16) * 8) =
+        new_v[row * 16 + lane - 16];
+  }
+}
+
 // Candidate capacity of the fast path: room for ~1.75 k expected candidates plus a wide margin.
 static int fast_cap(int kk) {
   int c = 8192;
@@ -291,6 +309,17 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                     (all_candidates || (run_len >= per_thread && 1.7 * expect <= (double)fcap));
   const int32_t* T_dev = p->history_count_dev;
   if (T_dev && !fast) return KVB_BAD_SHAPE;
+  if ((p->new_key_row == nullptr) != (p->new_value_row == nullptr)) return KVB_BAD_ARG;
+  if (p->new_key_row) {
+    if (p->D != 128 || !aligned_to(p->new_key_row, 16) || !aligned_to(p->new_value_row, 16)) return KVB_BAD_ALIGN;
+    DeviceGuard guard(device);
+    if (!guard.ok) return KVB_BAD_DEVICE;
+    store_new_rows_kernel<<<p->B * p->Hkv, 32, 0, st>>>(
+        reinterpret_cast<const uint4*>(p->new_key_row), reinterpret_cast<const uint4*>(p->new_value_row),
+        reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p->key)), p->k_sb, p->k_sh, p->k_st,
+        reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p->value)), p->v_sb, p->v_sh, p->v_st, p->Hkv, T, T_dev);
+    KVB_CHECK_CUDA(cudaGetLastError());
+  }
   if (fast) {
     {
       DeviceGuard guard(device);

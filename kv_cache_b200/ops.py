@@ -568,14 +568,16 @@ class DecodeStep:
                  scale: torch.Tensor, channel_idx: torch.Tensor, scaling: Optional[float] = None,
                  attention_mask: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  selected_out: Optional[torch.Tensor] = None, history_dev: Optional[torch.Tensor] = None,
-                 advance_history: bool = False) -> torch.Tensor:
+                 advance_history: bool = False,
+                 new_rows: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
         """``key``/``value`` hold history+1 rows (the last is the token being decoded); the side
         cache holds the history rows. Returns bf16 ``[B,1,Hq,D]``.
 
         With ``history_dev`` (int32 device tensor of one element) the history length is read on
         the device and ``key``/``value`` are the whole cache (capacity rows): the same launch
         sequence then serves every step of a CUDA-graph replayed decode loop; ``advance_history``
-        makes the step add one to it when it is done."""
+        makes the step add one to it when it is done. ``new_rows = (k_row, v_row)`` (bf16 ``[B,Hkv,D]``
+        dense): the step first stores them as row ``history`` of ``key`` / ``value``."""
         query = _query3(query)
         B, Hq, D = query.shape
         Hkv, key_count = key.shape[1], key.shape[2]
@@ -613,6 +615,12 @@ class DecodeStep:
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
         p.history_count_dev = _ptr(history_dev)
         p.advance_history = int(advance_history)
+        if new_rows is not None:
+            k_row, v_row = new_rows
+            if not (k_row.is_contiguous() and v_row.is_contiguous() and k_row.dtype == v_row.dtype == torch.bfloat16
+                    and k_row.numel() == v_row.numel() == B * Hkv * D):
+                raise RuntimeError("new_rows must be two dense bf16 [B,Hkv,D] tensors")
+            p.new_key_row, p.new_value_row = k_row.data_ptr(), v_row.data_ptr()
         check(_native.lib().kvb_decode_step(C.byref(p), _dev(query), _stream(dev)), "kvb_decode_step")
         return out
 
@@ -637,29 +645,29 @@ class GraphedDecode:
             raise RuntimeError("the cache has no room for the decoded token")
         self.step, self.advance = step, advance
         self.history = torch.tensor([history], dtype=torch.int32, device=dev)
-        self.h_query = torch.empty((B, q_heads, D), dtype=torch.bfloat16).pin_memory()
-        self.h_key_row = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory()
-        self.h_value_row = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory()
+        # one pinned staging buffer and one device buffer: a single host-to-device copy per step
+        nq, nkv = B * q_heads * D, B * Hkv * D
+        self.h_in = torch.empty((nq + 2 * nkv,), dtype=torch.bfloat16).pin_memory()
+        self.h_query = self.h_in[:nq].view(B, q_heads, D)
+        self.h_key_row = self.h_in[nq:nq + nkv].view(B, Hkv, 1, D)
+        self.h_value_row = self.h_in[nq + nkv:].view(B, Hkv, 1, D)
         self.h_out = torch.empty((B, 1, q_heads, D), dtype=torch.bfloat16).pin_memory()
-        self._q = torch.empty((B, q_heads, D), dtype=torch.bfloat16, device=dev)
-        self._k = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16, device=dev)
-        self._v = torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16, device=dev)
+        self._in = torch.empty((nq + 2 * nkv,), dtype=torch.bfloat16, device=dev)
+        self._q = self._in[:nq].view(B, q_heads, D)
+        self._k = self._in[nq:nq + nkv].view(B, Hkv, D)
+        self._v = self._in[nq + nkv:].view(B, Hkv, D)
         self._out = torch.empty((B, 1, q_heads, D), dtype=torch.bfloat16, device=dev)
         self.stream = torch.cuda.Stream(dev)
         # warm-up contents: a well-spread query (an all-zero one would tie every score and send every row
         # through the slow exact-refinement path), zero K/V rows
+        self.h_in.zero_()
         self.h_query.copy_(torch.randn((B, q_heads, D), generator=torch.Generator().manual_seed(0)).to(torch.bfloat16))
-        self.h_key_row.zero_(); self.h_value_row.zero_()
 
         def body():
-            self._q.copy_(self.h_query, non_blocking=True)
-            self._k.copy_(self.h_key_row, non_blocking=True)
-            self._v.copy_(self.h_value_row, non_blocking=True)
-            pos = self.history.to(torch.int64)
-            key.index_copy_(2, pos, self._k)
-            value.index_copy_(2, pos, self._v)
+            self._in.copy_(self.h_in, non_blocking=True)
+            # the step itself stores the new rows at the device-side position
             step(self._q, key, value, packed, scale, channel_idx, scaling=scaling, out=self._out,
-                 history_dev=self.history, advance_history=advance)
+                 history_dev=self.history, advance_history=advance, new_rows=(self._k, self._v))
             self.h_out.copy_(self._out, non_blocking=True)
 
         with torch.cuda.stream(self.stream):
