@@ -10,10 +10,12 @@
 //     un-swizzled core-matrix layout the tensor core reads from shared memory (4-stage ring);
 //   * 1 thread issues tcgen05.mma (M=128, N=128) into a double-buffered accumulator in tensor memory
 //     and signals completion with tcgen05.commit -> mbarrier;
-//   * 16 epilogue warps (four per TMEM lane quadrant, one 64-token block of one accumulator tile each)
-//     pull the accumulators with tcgen05.ld in 16-column chunks, the next chunk in flight while the
-//     current one is scaled (packed fp32 multiply) and reduced (3-input maximum), combine the heads
-//     through shared memory and write eight block maxima per query at a time.
+//   * 16 epilogue warps, four per TMEM lane quadrant: one per (accumulator tile, accumulator stage).
+//     The warps of a stage drain it while the tensor core fills the other one. Each warp pulls its 128
+//     columns with tcgen05.ld in 16-column chunks, the next chunk in flight while the current one is
+//     scaled (packed fp32 multiply) and reduced (3-input maximum); the G heads of a query sit in
+//     neighbouring rows = lanes, so the group maximum is a few shuffles, and the warp writes its two
+//     block maxima per query straight to memory. Epilogue warps never synchronise with each other.
 // The contraction is only C (32..128) deep, so the kernel is bound by the instructions of the
 // per-element epilogue, not by the MMA; that is why most warps are epilogue warps.
 //
@@ -35,15 +37,11 @@ constexpr int TC_EPI_WARPS = 16;                   // four per TMEM lane quadran
 constexpr int TC_PROD_WARPS = 4;
 constexpr int TC_WARPS = TC_EPI_WARPS + TC_PROD_WARPS + 1;
 constexpr int TC_THREADS = TC_WARPS * 32;
-constexpr int TC_UNITS = TC_EPI_WARPS / 4;         // epilogue warps per quadrant
-constexpr int TC_QT_PER_WARP = 4 / TC_UNITS;       // (tile, block) units per tile are 2 * TC_QT = 4
 constexpr int TC_NTILE = 128;                      // key tokens per MMA tile (two 64-token blocks)
 constexpr int TC_QT = 2;                           // 128-row accumulator tiles per CTA
 constexpr int TC_ASTAGES = 2;                      // accumulator stages in tensor memory
 constexpr int TC_TMEM_COLS = TC_ASTAGES * TC_QT * TC_NTILE;   // 512: all of it
-constexpr int TC_OUT_BLOCKS = 8;                   // block maxima buffered per query before a flush
 constexpr int TC_CHW = 16;                         // accumulator columns per tensor-memory load
-constexpr int TC_KS_SLOTS = 8;                     // tiles of key scales resident in shared memory
 constexpr int TC_LBO = 128;                        // bytes between core matrices along K
 
 struct PrefillTcParams {
@@ -167,10 +165,8 @@ struct TcCfg {
   // shared memory carve-up
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + TC_QT * A_TILE;
-  static constexpr int OFF_KS = OFF_B + BSTAGES * B_STAGE;                 // [8 tiles][2 halves][64] key scales
-  static constexpr int OFF_X = OFF_KS + TC_KS_SLOTS * 2 * 64 * 4;                    // [2][QT][2][128] per-head block maxima
-  static constexpr int OFF_OUT = OFF_X + 2 * TC_QT * 2 * 128 * 4;          // [2][QT*128][8] buffered outputs (worst case G=1)
-  static constexpr int OFF_BAR = OFF_OUT + 2 * TC_QT * 128 * TC_OUT_BLOCKS * 4;
+  static constexpr int OFF_KS = OFF_B + BSTAGES * B_STAGE;                 // [epilogue warps][2][128] key scales, warp-private
+  static constexpr int OFF_BAR = OFF_KS + TC_EPI_WARPS * 2 * TC_NTILE * 4;
   static constexpr int NBAR = 2 * BSTAGES + 2 * TC_ASTAGES + 1;
   static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;                      // tmem base, dead flag
   static constexpr int BYTES = OFF_MISC + 16;
@@ -187,13 +183,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
   uint8_t* s_a = tc_smem + Cfg::OFF_A;
   uint8_t* s_b = tc_smem + Cfg::OFF_B;
   float* s_ks = reinterpret_cast<float*>(tc_smem + Cfg::OFF_KS);
-  float* s_x = reinterpret_cast<float*>(tc_smem + Cfg::OFF_X);
-  float* s_out = reinterpret_cast<float*>(tc_smem + Cfg::OFF_OUT);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tc_smem + Cfg::OFF_BAR);
   uint64_t* b_full = bars;                          // [BSTAGES] producers -> MMA (128 arrivals)
   uint64_t* b_empty = bars + BSTAGES;               // [BSTAGES] MMA -> producers (commit)
   uint64_t* acc_full = bars + 2 * BSTAGES;          // [ASTAGES] MMA -> epilogue (commit)
-  uint64_t* acc_empty = acc_full + TC_ASTAGES;      // [ASTAGES] epilogue -> MMA (256 arrivals)
+  uint64_t* acc_empty = acc_full + TC_ASTAGES;      // [ASTAGES] the stage's epilogue warps -> MMA (256 arrivals)
   uint64_t* all_done = acc_empty + TC_ASTAGES;      // every MMA of the CTA has completed
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tc_smem + Cfg::OFF_MISC);
   volatile uint32_t* s_dead = s_tmem + 1;
@@ -206,7 +200,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
 
   if (tid == 0) {
     for (int s = 0; s < BSTAGES; ++s) { mbar_init(&b_full[s], TC_PROD_WARPS * 32); mbar_init(&b_empty[s], 1); }
-    for (int a = 0; a < TC_ASTAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TC_EPI_WARPS * 32); }
+    for (int a = 0; a < TC_ASTAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TC_EPI_WARPS / TC_ASTAGES * 32); }
     mbar_init(all_done, 1);
     *s_dead = 0;
     fence_mbar_init();
@@ -216,13 +210,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
     tc_relinquish();
   }
 
-  // ---- A tiles: row r of tile qt = head r / QPT, query q0 + qt*QPT + r % QPT; K order inside each group of
+  // ---- A tiles: row r of tile qt = query q0 + qt*QPT + r / G, head r % G (the heads of a query are
+  // neighbouring rows, hence neighbouring TMEM lanes of one epilogue warp); K order inside each group of
   // 8 channels is (even channels, odd channels), the order in which the widened key words deliver them.
   for (int item = tid; item < TC_QT * 128 * W; item += TC_THREADS) {
     const int w = item % W;
     const int r = (item / W) % 128;
     const int qt = item / (W * 128);
-    const int hd = r / QPT, qi = r - hd * QPT;
+    const int qi = r / G, hd = r - qi * G;
     const int q = q0 + qt * QPT + qi;
     uint32_t ev = 0, od = 0;
     if (q < p.Tq) {
@@ -258,38 +253,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
 
   if (warp < TC_EPI_WARPS) {
     // =============================== epilogue ===============================
-    // warp -> TMEM lane quadrant (warp % 4, fixed by the hardware) and unit (warp / 4): a unit is one
-    // 64-token block (`half`) of TC_QT_PER_WARP accumulator tiles.
-    const int quad = warp & 3, unit = warp >> 2;
-    const int half = unit & 1;
-    const int qt0 = (unit >> 1) * TC_QT_PER_WARP;
-    constexpr int GROUP = TC_EPI_WARPS / 2 * 32;    // threads that work on the same block of a tile
+    // warp -> TMEM lane quadrant (warp % 4, fixed by the hardware), accumulator tile qt and stage `par`:
+    // the warp handles tiles par, par + 2, ... and reads all 128 columns (two blocks) of its tile qt.
+    const int quad = warp & 3, qt = (warp >> 2) & 1, par = warp >> 3;
     const int row = quad * 32 + lane;               // accumulator row = TMEM lane
-    const int hd = row / QPT, qi = row - hd * QPT;
-    const bool ks_loader = qt0 == 0 && row < 64;    // one thread per token of the block
-    float qs[TC_QT_PER_WARP];
-#pragma unroll
-    for (int j = 0; j < TC_QT_PER_WARP; ++j) {
-      const int q = q0 + (qt0 + j) * QPT + qi;
-      qs[j] = q < p.Tq ? p.qscale[((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q] : 0.0f;
-    }
-    // Key scales of this half's block live in a ring of TC_KS_SLOTS tiles; 64 threads per half refill four
-    // slots every four tiles from registers that were loaded four tiles earlier, so that the memory latency
-    // is never waited for.
-    auto load_ks = [&](int tile) -> float {
-      const int64_t t = (int64_t)tile * TC_NTILE + half * 64 + row;
-      float v = __int_as_float(0x7fc00000);         // dead token: NaN never wins a max
-      if (ks_loader && tile < ntiles && t < p.Tk) v = KIND == 0 ? scale_row[t] * 0.0625f : scale_row[t];
+    const int qi = row / G, hd = row - qi * G;
+    const int q = q0 + qt * QPT + qi;
+    const float qs = q < p.Tq ? p.qscale[((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q] : 0.0f;
+    float* out_row = p.out + (((int64_t)b * p.Hkv + kvh) * p.Tq + (q < p.Tq ? q : 0)) * p.nblk;
+    const bool writer = hd == 0 && q < p.Tq;
+    float* my_ks = s_ks + warp * 2 * TC_NTILE;      // [2][128], private to the warp
+    // Key scales of a tile: lane l fetches tokens 4l .. 4l+3; dead tokens get NaN, which never wins a max.
+    // They are fetched two of this warp's tiles ahead, so the memory latency is never waited for.
+    auto load_ks = [&](int tile) -> float4 {
+      const float nan = __int_as_float(0x7fc00000);
+      float4 v = make_float4(nan, nan, nan, nan);
+      const int64_t t = (int64_t)tile * TC_NTILE + 4 * lane;
+      if (tile < ntiles) {
+        if (t + 3 < p.Tk) {
+          v = *reinterpret_cast<const float4*>(scale_row + t);
+        } else {
+          if (t < p.Tk) v.x = scale_row[t];
+          if (t + 1 < p.Tk) v.y = scale_row[t + 1];
+          if (t + 2 < p.Tk) v.z = scale_row[t + 2];
+        }
+        if constexpr (KIND == 0) { v.x *= 0.0625f; v.y *= 0.0625f; v.z *= 0.0625f; v.w *= 0.0625f; }
+      }
       return v;
     };
-    float kr[4];
-    if (ks_loader) {
-#pragma unroll
-      for (int j = 0; j < TC_KS_SLOTS; ++j) s_ks[(j * 2 + half) * 64 + row] = load_ks(j);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) kr[j] = load_ks(TC_KS_SLOTS + j);
-    named_bar_sync(1 + half, GROUP);
     // Block maximum of 16 accumulator columns against their key scales: two columns per packed fp32
     // multiply (each half rounded to nearest, as a scalar multiply) and per 3-input maximum.
     auto chunk_max = [&](const uint32_t* v, const float* ks, float m) -> float {
@@ -322,97 +313,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
       }
       return fmaxf(ma, mb);
     };
-    // The accumulator columns of this warp form one stream of 16-column chunks across tiles; the load of
-    // the next chunk (of the next tile, once its accumulator is complete) is in flight while the current
-    // one is reduced.
-    constexpr int CPB = 64 / TC_CHW;                // chunks per 64-token block
-    constexpr int NCH = CPB * TC_QT_PER_WARP;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(qt0 * TC_NTILE + half * 64);
-    auto chunk_addr = [&](int tile, int ch) -> uint32_t {
-      return lane_base + (uint32_t)((tile & 1) * TC_QT * TC_NTILE + (ch / CPB) * TC_NTILE + (ch % CPB) * TC_CHW);
-    };
-    uint32_t va[TC_CHW], vb[TC_CHW];
-    bool dead = false;
-    auto wait_tile = [&](int tile) {                // accumulator of `tile` complete (bounded)
-      if (dead) return;
-      if (!mbar_wait_bounded(&acc_full[tile & 1], (uint32_t)(tile >> 1) & 1u)) { *s_dead = 1; dead = true; }
+    constexpr int NCH = TC_NTILE / TC_CHW;          // chunks per tile: 8
+    constexpr int CPB = 64 / TC_CHW;                // chunks per 64-token block: 4
+    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(par * TC_QT * TC_NTILE + qt * TC_NTILE);
+    float4 k_cur = load_ks(par), k_next = load_ks(par + 2);
+    int buf = 0;
+    for (int i = par; i < ntiles; i += TC_ASTAGES, buf ^= 1) {
+      float* ksb = my_ks + buf * TC_NTILE;
+      *reinterpret_cast<float4*>(ksb + 4 * lane) = k_cur;
+      k_cur = k_next;
+      k_next = load_ks(i + 2 * TC_ASTAGES);
+      __syncwarp();
+      if (*s_dead) break;
+      if (!mbar_wait_bounded(&acc_full[par], (uint32_t)(i >> 1) & 1u)) { *s_dead = 1; break; }
       tc_fence_after();
-    };
-    wait_tile(0);
-    if (!dead) tc_ld16(chunk_addr(0, 0), va);
-    for (int i = 0; i < ntiles; ++i) {
-      const int a = i & 1, par = i & 1;
-      if (*s_dead) dead = true;
-      float mq[TC_QT_PER_WARP];
+      uint32_t va[TC_CHW], vb[TC_CHW];
+      tc_ld16(tbase, va);
+      float m = -INFINITY, m0 = 0.0f;
 #pragma unroll
-      for (int j = 0; j < TC_QT_PER_WARP; ++j) mq[j] = 0.0f;
-      if (!dead) {
-        const float* ksb = s_ks + ((i & (TC_KS_SLOTS - 1)) * 2 + half) * 64;
-        float m = -INFINITY;
-#pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) {
-          uint32_t* cur = (ch & 1) ? vb : va;
-          uint32_t* nxt = (ch & 1) ? va : vb;
-          tc_wait_ld16(cur);
-          bool late = false;
-          if (ch + 1 < NCH) {
-            tc_ld16(chunk_addr(i, ch + 1), nxt);
-          } else {                                  // everything of this stage is in registers: it may be refilled
-            tc_fence_before();
-            mbar_arrive(&acc_empty[a]);
-            if (i + 1 < ntiles) {
-              if (mbar_try_wait(&acc_full[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u)) {
-                tc_fence_after();
-                tc_ld16(chunk_addr(i + 1, 0), nxt);
-              } else {
-                late = true;                        // not there yet: reduce first, then wait
-              }
-            }
-          }
-          m = chunk_max(cur, ksb + (ch % CPB) * TC_CHW, m);
-          if (ch % CPB == CPB - 1) {
-            mq[ch / CPB] = __fmul_rn(m, qs[ch / CPB]);   // x -> fl(x * qscale) is monotone: scale the maximum only
-            m = -INFINITY;
-          }
-          if (late) {
-            wait_tile(i + 1);
-            if (!dead) tc_ld16(chunk_addr(i + 1, 0), nxt);
-          }
+      for (int ch = 0; ch < NCH; ++ch) {
+        uint32_t* cur = (ch & 1) ? vb : va;
+        uint32_t* nxt = (ch & 1) ? va : vb;
+        tc_wait_ld16(cur);
+        if (ch + 1 < NCH) {
+          tc_ld16(tbase + (uint32_t)((ch + 1) * TC_CHW), nxt);
+        } else {                                    // the whole tile is in registers: the stage may be refilled
+          tc_fence_before();
+          mbar_arrive(&acc_empty[par]);
         }
+        m = chunk_max(cur, ksb + ch * TC_CHW, m);
+        if (ch == CPB - 1) { m0 = m; m = -INFINITY; }
       }
-      // heads meet in shared memory; refills of the key-scale ring ride on the same barrier
+      // x -> fl(x * qscale) is monotone for qscale > 0: scale the block maxima only; then the group maximum
+      // over the G heads of the query, which are G neighbouring lanes
+      float r0 = __fmul_rn(m0, qs), r1 = __fmul_rn(m, qs);
 #pragma unroll
-      for (int j = 0; j < TC_QT_PER_WARP; ++j) s_x[((par * TC_QT + qt0 + j) * 2 + half) * 128 + row] = mq[j];
-      if ((i & 3) == 0 && i >= 4) {
-        if (ks_loader) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) s_ks[(((i + 4 + j) & (TC_KS_SLOTS - 1)) * 2 + half) * 64 + row] = kr[j];
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) kr[j] = load_ks(i + 8 + j);
+      for (int off = 1; off < G; off <<= 1) {
+        r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, off));
+        r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, off));
       }
-      named_bar_sync(1 + half, GROUP);
-      const int blk = 2 * i + half;
-      const int oslot = (i >> 2) & 1;               // output buffer parity: 4 tiles = 8 blocks per flush
-      if (row < QPT) {
-#pragma unroll
-        for (int j = 0; j < TC_QT_PER_WARP; ++j) {
-          const int qt = qt0 + j;
-          float best = -INFINITY;
-#pragma unroll
-          for (int h2 = 0; h2 < G; ++h2) best = fmaxf(best, s_x[((par * TC_QT + qt) * 2 + half) * 128 + h2 * QPT + row]);
-          if (best == 0.0f) best = 0.0f;            // -0 -> +0
-          s_out[(oslot * QCTA + qt * QPT + row) * TC_OUT_BLOCKS + (blk & (TC_OUT_BLOCKS - 1))] = best;
-        }
-      }
-      if ((i & 3) == 3 || i + 1 == ntiles) {
-        named_bar_sync(3, TC_EPI_WARPS * 32);       // every unit has put its blocks into s_out[oslot]
-        const int jb = (i >> 2) * TC_OUT_BLOCKS;    // first block of the batch
-        for (int e = tid; e < QCTA * TC_OUT_BLOCKS; e += TC_EPI_WARPS * 32) {
-          const int r = e / TC_OUT_BLOCKS, c = e - r * TC_OUT_BLOCKS;
-          const int q = q0 + r;
-          if (q < p.Tq && jb + c < p.nblk && !dead)
-            p.out[(((int64_t)b * p.Hkv + kvh) * p.Tq + q) * p.nblk + jb + c] = s_out[(oslot * QCTA + r) * TC_OUT_BLOCKS + c];
+      if (writer) {
+        if (r0 == 0.0f) r0 = 0.0f;                  // -0 -> +0
+        if (r1 == 0.0f) r1 = 0.0f;
+        const int blk = 2 * i;
+        if (blk + 1 < p.nblk && (p.nblk & 1) == 0) {
+          *reinterpret_cast<float2*>(out_row + blk) = make_float2(r0, r1);
+        } else {
+          out_row[blk] = r0;
+          if (blk + 1 < p.nblk) out_row[blk + 1] = r1;
         }
       }
     }
@@ -487,27 +435,45 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
     }
   } else if (lane == 0) {
     // =============================== MMA issuer ===============================
+    // One thread feeds the tensor core; its instruction stream is the serial part of the whole CTA, so it
+    // is kept short: descriptors differ from a base only in their address field (low word, no carry into
+    // the other fields below 256 KiB), the tile loop is unrolled over the operand ring and the two
+    // accumulator stages so that every index is a constant, and barrier addresses are plain integers.
     const uint32_t idesc = tc_instr_desc<KIND>(128, TC_NTILE);
-    const uint32_t a_addr = smem_u32(s_a), b_addr = smem_u32(s_b);
+    const uint64_t a_desc0 = tc_smem_desc(smem_u32(s_a), TC_LBO, Cfg::SBO);
+    const uint64_t b_desc0 = tc_smem_desc(smem_u32(s_b), TC_LBO, Cfg::SBO);
+    const uint32_t a_lo = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
+    const uint32_t b_lo = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
+    auto desc = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
+    constexpr int U = (BSTAGES % 2 == 0) ? BSTAGES : 2 * BSTAGES;      // tiles per unrolled round
     bool dead = false;
-    for (int i = 0; i < ntiles && !dead; ++i) {
-      const int s = i % BSTAGES, a = i & 1;
-      bool ok = mbar_wait_bounded(&b_full[s], (uint32_t)(i / BSTAGES) & 1u);
-      ok = ok && mbar_wait_bounded(&acc_empty[a], ((uint32_t)(i >> 1) & 1u) ^ 1u);
-      if (!ok || *s_dead) { *s_dead = 1; dead = true; break; }
-      tc_fence_after();
+    uint32_t round = 0;                                               // i0 / U
+    for (int i0 = 0; i0 < ntiles && !dead; i0 += U, ++round) {
 #pragma unroll
-      for (int qt = 0; qt < TC_QT; ++qt) {
-        const uint32_t d = tmem_base + (uint32_t)(a * TC_QT * TC_NTILE + qt * TC_NTILE);
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u;
+        if (i >= ntiles) break;
+        constexpr int dummy = 0; (void)dummy;
+        const int s = u % BSTAGES, a = u & 1;                          // constants after unrolling (U is even and a multiple of BSTAGES)
+        const uint32_t use_b = round * (U / BSTAGES) + (uint32_t)(u / BSTAGES);   // n-th use of operand stage s
+        const uint32_t use_a = round * (U / 2) + (uint32_t)(u / 2);               // n-th use of accumulator stage a
+        bool ok = mbar_wait_bounded(&b_full[s], use_b & 1u);
+        ok = ok && mbar_wait_bounded(&acc_empty[a], (use_a & 1u) ^ 1u);
+        if (!ok) { *s_dead = 1; dead = true; break; }
+        tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < Cfg::KSTEPS; ++k) {
-          const uint64_t ad = tc_smem_desc(a_addr + qt * Cfg::A_TILE + k * 2 * TC_LBO, TC_LBO, Cfg::SBO);
-          const uint64_t bd = tc_smem_desc(b_addr + s * Cfg::B_STAGE + k * 2 * TC_LBO, TC_LBO, Cfg::SBO);
-          tc_mma<KIND>(d, ad, bd, idesc, k > 0 ? 1u : 0u);
+        for (int qt = 0; qt < TC_QT; ++qt) {
+          const uint32_t d = tmem_base + (uint32_t)(a * TC_QT * TC_NTILE + qt * TC_NTILE);
+#pragma unroll
+          for (int k = 0; k < Cfg::KSTEPS; ++k) {
+            const uint64_t ad = desc(a_lo + (uint32_t)((qt * Cfg::A_TILE + k * 2 * TC_LBO) >> 4), a_hi);
+            const uint64_t bd = desc(b_lo + (uint32_t)((s * Cfg::B_STAGE + k * 2 * TC_LBO) >> 4), b_hi);
+            tc_mma<KIND>(d, ad, bd, idesc, k > 0 ? 1u : 0u);
+          }
         }
+        tc_commit(&b_empty[s]);                     // the stage may be overwritten once these MMAs have read it
+        tc_commit(&acc_full[a]);
       }
-      tc_commit(&b_empty[s]);                       // the stage may be overwritten once these MMAs have read it
-      tc_commit(&acc_full[a]);
     }
     tc_commit(all_done);
     mbar_wait_bounded(all_done, 0);                 // nothing of this CTA is still in flight in the tensor core
