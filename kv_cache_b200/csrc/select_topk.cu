@@ -71,6 +71,7 @@ struct SelectParams {
   int32_t* out_owned = nullptr;
   int32_t* out_owned_count = nullptr;
   int64_t own_base = 0, own_limit = 0;
+  int common_start = 1;       // start the on-chip select below the common key prefix of the candidates
 };
 
 __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row, int64_t t) {
@@ -443,6 +444,40 @@ again:
     if (n > p.cap) n = p.cap;
   }
 
+  // When the select starts from scratch on a prepared list, the entries usually share many leading key
+  // bits (all of them passed the same threshold): a digit taken there would send everything to one or two
+  // histogram bins, i.e. thousands of shared-memory atomics on the same word. Start below the common
+  // prefix of the smallest and the largest entry instead.
+  uint64_t common_prefix = 0;
+  int common_bits = 0;
+  if (p.common_start && fixed == 0 && have_candidates && n > 1 && in_prefix > need) {
+    unsigned long long lo = ~0ull, hi = 0ull;
+    for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
+      const unsigned long long c = s_cand[i];
+      lo = c < lo ? c : lo;
+      hi = c > hi ? c : hi;
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const unsigned long long ol = __shfl_xor_sync(0xffffffffu, lo, off), oh = __shfl_xor_sync(0xffffffffu, hi, off);
+      lo = ol < lo ? ol : lo;
+      hi = oh > hi ? oh : hi;
+    }
+    unsigned long long* s_mm = reinterpret_cast<unsigned long long*>(s_tmp);      // [2], 8-byte aligned
+    if (tid == 0) { s_mm[0] = ~0ull; s_mm[1] = 0ull; }
+    __syncthreads();
+    if ((tid & 31) == 0) { atomicMin(&s_mm[0], lo); atomicMax(&s_mm[1], hi); }
+    __syncthreads();
+    lo = s_mm[0]; hi = s_mm[1];
+    __syncthreads();                                  // s_tmp is reused by find_threshold
+    const unsigned long long diff = lo ^ hi;
+    common_bits = diff ? __clzll((long long)diff) : 63;
+    if (common_bits > 0) {
+      common_prefix = hi >> (64 - common_bits);
+      prefix = common_prefix;
+      fixed = common_bits;
+    }
+  }
   // Finish the radix select inside shared memory: stop when exactly `need` elements carry the prefix.
   while (in_prefix > need && fixed < 64) {
     const int width = (64 - fixed) >= 11 ? 11 : (64 - fixed);
@@ -489,8 +524,8 @@ again:
     const bool split = p.split_k > 0 && p.split_k < p.kk;
     if (split) {
       // a second radix select over the same on-chip candidates, for rank split_k
-      uint64_t pf = 0;
-      int fx = 0;
+      uint64_t pf = common_prefix;                    // (0 bits when the first select did not start from scratch)
+      int fx = common_bits;
       uint32_t nd = (uint32_t)p.split_k, inp = (uint32_t)n;
       while (inp > nd && fx < 64) {
         const int width = (64 - fx) >= 11 ? 11 : (64 - fx);
