@@ -54,7 +54,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not is_stale():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB_PATH), str(UNITY)]
+    extra = os.environ.get("KVB_NVCC_EXTRA", "").split()       # e.g. -D switches for experiments
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-o", str(LIB_PATH), str(UNITY)]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd), flush=True)

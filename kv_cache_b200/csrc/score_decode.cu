@@ -22,6 +22,18 @@ __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// First MMA of an accumulation: D = A*B + c with the same register c in all four accumulator slots. With
+// c = 0x4B400000 (the bits of 1.5 * 2^23) the finished accumulator, read as a float, is 1.5 * 2^23 + dot
+// exactly (|dot| < 2^22): the integer add of the int -> float conversion rides on the MMA for free.
+__device__ __forceinline__ void mma_s8_16832_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1, int c) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+constexpr int SC_FLOAT_MAGIC = 0x4B400000;
+
 // Streaming kernel. C in {32,64,128}, G in {1,2,4,8}.
 //
 // A warp owns a ring of NS stages; each stage holds TW tokens (packed bytes + scales) brought in
@@ -217,7 +229,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
 
 #pragma unroll
         for (int it = 0; it < IT; ++it) {
-          int acc[4] = {0, 0, 0, 0};
+          int acc[4];                                       // starts at SC_FLOAT_MAGIC (see mma_s8_16832_first)
 #pragma unroll
           for (int tj = 0; tj < TPA; ++tj) {
             // rows g and g+8 of token tile tj: KS packed words each, from this lane's byte range
@@ -243,7 +255,8 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
               const uint32_t a1 = (w1[s] << 4) & 0xF0F0F0F0u;   // row g+8
               const uint32_t a2 = w0[s] & 0xF0F0F0F0u;          // 16 * high-nibble codes, row g
               const uint32_t a3 = w1[s] & 0xF0F0F0F0u;
-              mma_s8_16832(acc, a0, a1, a2, a3, bq[tj][s][0], bq[tj][s][1]);
+              if (tj == 0 && s == 0) mma_s8_16832_first(acc, a0, a1, a2, a3, bq[tj][s][0], bq[tj][s][1], SC_FLOAT_MAGIC);
+              else mma_s8_16832(acc, a0, a1, a2, a3, bq[tj][s][0], bq[tj][s][1]);
             }
           }
           // acc[0], acc[1]: row g, columns 2*t4, 2*t4+1; acc[2], acc[3]: row g+8, same columns.
@@ -255,7 +268,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
             const int col = v & 1;
             const int tile = G >= 2 ? jt : (2 * t4 + col);
             tl[v] = it * Cfg::ITER_TOKENS + tile * 16 + g + ((v >> 1) ? 8 : 0);
-            const float f = __int_as_float(acc[v] + 0x4B400000) - 12582912.0f;   // exact int -> float, |acc| < 2^22
+            const float f = __int_as_float(acc[v]) - 12582912.0f;   // exact: acc = bits(1.5 * 2^23) + 16 * dot, |16 * dot| < 2^22
             d[v] = __fmul_rn(__fmul_rn(f, ssc[tl[v]]), qs16[G >= 2 ? col : 0]);
           }
           if (p.acc_out || p.deq_out) {
@@ -263,7 +276,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
             for (int v = 0; v < 4; ++v) {
               const int hd = G >= 2 ? (h0 + (v & 1)) : 0;
               const int64_t o = ((int64_t)b * p.Hq + (int64_t)kvh * G + hd) * p.T + t0 + tl[v];
-              if (p.acc_out) p.acc_out[o] = acc[v] >> 4;
+              if (p.acc_out) p.acc_out[o] = (acc[v] - SC_FLOAT_MAGIC) >> 4;
               if (p.deq_out) p.deq_out[o] = d[v];
             }
           }
