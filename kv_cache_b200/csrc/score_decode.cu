@@ -46,6 +46,10 @@ constexpr int SC_FLOAT_MAGIC = 0x4B400000;
 // every lane dequantises exactly four (token, head) values.
 // Persistent: CTA c owns the contiguous unit range [c*U/grid, (c+1)*U/grid) of the flattened
 // (row, tile) space.
+#ifndef KVB_SC_STAGE_PACKED_BYTES
+#define KVB_SC_STAGE_PACKED_BYTES 4096
+#endif
+
 template <int C, int G>
 struct ScoreCfg {
   static constexpr int WARPS = 8;
@@ -53,7 +57,10 @@ struct ScoreCfg {
   static constexpr int KS = C / 32;                     // k-steps of 32 channels; also packed words per lane-token
   static constexpr int TPA = 8 / G;                     // 16-token tiles that share one accumulator
   static constexpr int ITER_TOKENS = 16 * TPA;          // tokens per accumulator
-  static constexpr int TW = ITER_TOKENS > 64 ? ITER_TOKENS : 64;   // tokens per stage
+  // tokens per stage: about 4 KiB of packed codes per bulk copy (copies of 2 KiB reach only ~93 % of the
+  // streaming bandwidth that 4 KiB copies reach with the same bytes in flight)
+  static constexpr int STAGE_TOKENS = KVB_SC_STAGE_PACKED_BYTES / (C / 2);
+  static constexpr int TW = ITER_TOKENS > STAGE_TOKENS ? ITER_TOKENS : STAGE_TOKENS;
   static constexpr int IT = TW / ITER_TOKENS;
   static constexpr int TOKEN_BYTES = C / 2;
   static constexpr int PACKED_BYTES = TW * TOKEN_BYTES;
