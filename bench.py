@@ -218,7 +218,7 @@ def run_single_gpu(args, w) -> None:
                 "h2d_bytes_per_step": h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2,
                 "d2h_bytes_per_step": h_out.numel() * 2,
                 "api": "kv_cache_b200.ops.GraphedDecode.__call__ (H2D + kvb_decode_step + D2H in one CUDA graph, device-side history length)"},
-        "gpu_launches": 7 * args.steps,
+        "gpu_launches": 5 * args.steps,      # sample, scorer, final select, attend, merge per replayed step
         "roofline": {"bound": "hbm", "kernel": "score_decode_stream_kernel (candidate form)", "achieved": scorer_gbs, "peak": peak,
                      "unit": "GB/s", "frac": scorer_gbs / peak, "peak_source": peak_kind, "traffic": None,
                      "algorithmic_bytes": alg["scan"], "kernel_ms": ms_scorer,
