@@ -435,6 +435,11 @@ typedef struct kvb_decode_step_params {
    * a caller inside a graph its own scatter at a device-side position. Both or neither. */
   const void* new_key_row;
   const void* new_value_row;
+  /* 0: the selected ids (sel_idx_out, and the order in which the attention walks them) ascend, and the
+   * step is reproducible bit for bit. Non-zero: any order — the same exact set, about 3 us less per
+   * step at config 2, but the order (and with it the last bits of the fp32 accumulation) varies from
+   * run to run. */
+  int selected_any_order;
 } kvb_decode_step_params;
 
 size_t kvb_decode_step_workspace_bytes(int B, int Hq, int Hkv, int history_count, int top_k,

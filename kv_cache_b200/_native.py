@@ -48,6 +48,7 @@ class DecodeStepParams(C.Structure):
         ("workspace", _p), ("workspace_bytes", _sz),
         ("history_count_dev", _p), ("advance_history", _i),
         ("new_key_row", _p), ("new_value_row", _p),
+        ("selected_any_order", _i),
     ]
 
 

@@ -357,6 +357,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       size_t smem = (size_t)fcap * 8 + SEL_FINAL_FIXED_SMEM;
       sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
       if (sp.use_bitmap) smem += bitmap_bytes;
+      if (p->selected_any_order) { sp.order_by_index = 2; sp.use_bitmap = 0; }     // skip the ordering bitmap
       static bool attr_done[64] = {false};
       if (device < 64 && !attr_done[device]) {
         KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -40,6 +40,12 @@ def test_step_matches_oracle(cuda_device, B, Hq, Hkv, T, C, k, sink, recent):
     # running it again (now stale workspace contents) gives the same answer
     out2 = step(q, key, value, packed, scale, ch)
     assert torch.equal(out, out2)
+    # any-order selection: the same exact set, the same output within the tolerance
+    sel3 = torch.empty_like(sel)
+    out3 = ops.DecodeStep(k, protect_sink=sink, protect_recent=recent, ordered_selection=False)(
+        q, key, value, packed, scale, ch, selected_out=sel3)
+    assert torch.equal(torch.sort(sel3, dim=-1).values, sel)
+    torch.testing.assert_close(out3.float().cpu(), r["out"], rtol=RTOL, atol=ATOL)
 
 
 def test_step_equals_operator_chain(cuda_device):
