@@ -29,6 +29,10 @@ struct SampleParams {
   float* tau;                 // [R]
   int top_k;
   int cap;                    // candidate capacity per row
+  // optional: per-row words this kernel clears for the kernels after it (the candidate counter line and the
+  // failed flag), which spares the step a separate memset node
+  uint32_t* zero_count;       // [R * SC_COUNT_STRIDE] (word 0 of every row's line is the counter) or NULL
+  uint32_t* zero_failed;      // [R] or NULL
 };
 
 template <int C, int G>
@@ -42,6 +46,8 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   const int row = blockIdx.x, tid = threadIdx.x;
   pdl_launch_dependents();                      // the scorer may become resident and prepare its query codes
   pdl_wait();
+  if (q.zero_count && tid == 0) q.zero_count[(int64_t)row * SC_COUNT_STRIDE] = 0;
+  if (q.zero_failed && tid == 32) q.zero_failed[row] = 0;
   const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
   if (T <= q.cap) {                             // short rows: every token is a candidate
     if (tid == 0) q.tau[row] = -INFINITY;
@@ -210,9 +216,11 @@ static void fill_score_params(ScoreParams& sp, const void* query, int64_t q_sb, 
   sp.units_per_row = 0; sp.full_tiles = 0; sp.total_units = 0;
 }
 
-static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cudaStream_t st) {
+static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cudaStream_t st,
+                      uint32_t* zero_count = nullptr, uint32_t* zero_failed = nullptr) {
   SampleParams sq;
   sq.sp = sp; sq.tau = tau; sq.top_k = top_k; sq.cap = cap;
+  sq.zero_count = zero_count; sq.zero_failed = zero_failed;
   const int R = sp.B * sp.Hkv;
   if (sp.C == 32) return sample_launch_g<32>(sq, R, st);
   if (sp.C == 64) return sample_launch_g<64>(sq, R, st);
@@ -324,15 +332,14 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
     {
       DeviceGuard guard(device);
       if (!guard.ok) return KVB_BAD_DEVICE;
-      KVB_CHECK_CUDA(cudaMemsetAsync(ws + L.off_fcount, 0, L.fzero_bytes, st));
-      uint32_t* fcount = reinterpret_cast<uint32_t*>(ws + L.off_fcount);
+      uint32_t* fcount = reinterpret_cast<uint32_t*>(ws + L.off_fcount);      // cleared by the sample kernel
       float* ftau = reinterpret_cast<float*>(ws + L.off_ftau);
       uint64_t* fcand = reinterpret_cast<uint64_t*>(ws + L.off_fcand);
 
       ScoreParams base;
       fill_score_params(base, p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
                         p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, T_dev);
-      rc = sample_run(base, ftau, p->top_k, fcap, st);
+      rc = sample_run(base, ftau, p->top_k, fcap, st, fcount, reinterpret_cast<uint32_t*>(ws + L.off_ffailed));
       if (rc != KVB_OK) return rc;
       chain.on();                             // every later kernel of the step starts early and waits inside
 
@@ -475,12 +482,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   float* tau = reinterpret_cast<float*>(ws + L.off_tau);
   uint64_t* cand = reinterpret_cast<uint64_t*>(ws + L.off_cand);
   float* gmax = reinterpret_cast<float*>(ws + L.off_gmax);
-  KVB_CHECK_CUDA(cudaMemsetAsync(ws, 0, L.zero_bytes, st));
 
   ScoreParams base;
   fill_score_params(base, query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B,
                     Hq, Hkv, T, D, C, nullptr);
-  int rc = sample_run(base, tau, top_k, L.cap, st);
+  int rc = sample_run(base, tau, top_k, L.cap, st, count, reinterpret_cast<uint32_t*>(ws + L.off_failed));
   if (rc != KVB_OK) return rc;
   ScoreEmit emit{tau, cand, count, L.cap};
   rc = score_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq, Hkv, T,
