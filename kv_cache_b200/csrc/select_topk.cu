@@ -22,7 +22,7 @@ namespace kvb {
 constexpr int SEL_HIST_BITS = 12;
 constexpr int SEL_HIST_BINS = 1 << SEL_HIST_BITS;
 constexpr int SEL_SCAN_THREADS = 256;
-constexpr int SEL_FINAL_THREADS = 1024;
+constexpr int SEL_FINAL_THREADS = 512;            // measured best for ~3.5k on-chip candidates (barriers get cheaper, work per thread stays small)
 constexpr int SEL_MAX_K = 16384;
 constexpr int SEL_COUNT_STRIDE = 32;        // words between per-row candidate counters: one 128-byte line each,
                                             // so the atomics of different rows do not queue on one L2 line
@@ -280,6 +280,69 @@ __global__ void __launch_bounds__(SEL_SCAN_THREADS, 6) select_collect_kernel(Sel
 }
 
 // Descending bitonic sort of n (a power of two) 64-bit keys in shared memory by the whole CTA.
+// find_threshold for a shared-memory histogram that is re-used pass after pass: every thread clears the
+// bins it has read (the next pass needs no clearing loop and no barrier for it), and the barriers that only
+// protect s_tmp against the next call are dropped: the next call writes s_tmp[0..NT/32] after a barrier of
+// its own caller (the one behind the histogram atomics) and s_tmp[64..66] after two more barriers.
+template <int NT>
+__device__ __forceinline__ void find_threshold_clear(uint32_t* hist, int nbins, uint32_t need, uint32_t* s_tmp,
+                                                     uint32_t& bin_out, uint32_t& above_out, uint32_t& in_out) {
+  constexpr int MAXPER = 2048 / NT;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int per = (nbins + NT - 1) / NT;              // bins per thread, taken from the top
+  uint32_t local[MAXPER];
+  uint32_t sum = 0;
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) {
+    const int r = tid * per + j;                      // reversed bin r <-> bin nbins-1-r
+    const bool live = j < per && r < nbins;
+    local[j] = live ? hist[nbins - 1 - r] : 0u;
+    if (live) hist[nbins - 1 - r] = 0u;
+    sum += local[j];
+  }
+  uint32_t incl = sum;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += nb;
+  }
+  if (lane == 31) s_tmp[warp] = incl;
+  __syncthreads();
+  // every warp scans the (at most 32) warp totals itself: no second hand-over through shared memory
+  uint32_t w = lane < NT / 32 ? s_tmp[lane] : 0u;
+  uint32_t wi = w;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, wi, off);
+    if (lane >= off) wi += nb;
+  }
+  const uint32_t warp_excl = __shfl_sync(0xffffffffu, wi - w, warp);
+  const uint32_t excl = warp_excl + incl - sum;
+  uint32_t* s_res = s_tmp + 64;
+  if (excl < need && need <= excl + sum) {
+    uint32_t cum = excl, bin = 0, inb = 0;
+    bool found = false;
+#pragma unroll
+    for (int j = 0; j < MAXPER; ++j) {
+      if (!found) {
+        if (cum + local[j] >= need) {
+          bin = (uint32_t)(nbins - 1 - (tid * per + j));
+          inb = local[j];
+          found = true;
+        } else {
+          cum += local[j];
+        }
+      }
+    }
+    s_res[0] = bin;
+    s_res[1] = cum;
+    s_res[2] = inb;
+  }
+  __syncthreads();
+  bin_out = s_res[0];
+  above_out = s_res[1];
+  in_out = s_res[2];
+}
 template <int NT>
 __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
   for (int size = 2; size <= n; size <<= 1) {
@@ -479,12 +542,14 @@ again:
     }
   }
   // Finish the radix select inside shared memory: stop when exactly `need` elements carry the prefix.
+  if (in_prefix > need && fixed < 64) {               // the passes below clear the bins they read: zero once
+    for (int i = tid; i < 2048; i += SEL_FINAL_THREADS) s_hist[i] = 0;
+    __syncthreads();
+  }
   while (in_prefix > need && fixed < 64) {
     const int width = (64 - fixed) >= 11 ? 11 : (64 - fixed);
     const int shift = 64 - fixed - width;
     const int nb = 1 << width;
-    for (int i = tid; i < nb; i += SEL_FINAL_THREADS) s_hist[i] = 0;
-    __syncthreads();
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
       const uint64_t c = s_cand[i];
       if (fixed == 0 || (c >> (64 - fixed)) == prefix)
@@ -492,7 +557,7 @@ again:
     }
     __syncthreads();
     uint32_t d, ab, in;
-    find_threshold<SEL_FINAL_THREADS>(s_hist, nb, need, s_tmp, d, ab, in);
+    find_threshold_clear<SEL_FINAL_THREADS>(s_hist, nb, need, s_tmp, d, ab, in);
     need -= ab;
     in_prefix = in;
     prefix = (prefix << width) | d;
@@ -527,19 +592,19 @@ again:
       uint64_t pf = common_prefix;                    // (0 bits when the first select did not start from scratch)
       int fx = common_bits;
       uint32_t nd = (uint32_t)p.split_k, inp = (uint32_t)n;
+      for (int i = tid; i < 2048; i += SEL_FINAL_THREADS) s_hist[i] = 0;
+      __syncthreads();
       while (inp > nd && fx < 64) {
         const int width = (64 - fx) >= 11 ? 11 : (64 - fx);
         const int shift = 64 - fx - width;
         const int nb = 1 << width;
-        for (int i = tid; i < nb; i += SEL_FINAL_THREADS) s_hist[i] = 0;
-        __syncthreads();
         for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
           const uint64_t c = s_cand[i];
           if (fx == 0 || (c >> (64 - fx)) == pf) atomicAdd(&s_hist[(uint32_t)(c >> shift) & (uint32_t)(nb - 1)], 1u);
         }
         __syncthreads();
         uint32_t d, ab, in;
-        find_threshold<SEL_FINAL_THREADS>(s_hist, nb, nd, s_tmp, d, ab, in);
+        find_threshold_clear<SEL_FINAL_THREADS>(s_hist, nb, nd, s_tmp, d, ab, in);
         nd -= ab;
         inp = in;
         pf = (pf << width) | d;
@@ -550,13 +615,32 @@ again:
     if (tid < 3) s_count[tid] = 0;
     __syncthreads();
     const bool own = p.out_owned != nullptr;
-    for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
-      const uint64_t c = s_cand[i];
-      if (c >= kth) {
-        uint32_t pos;
-        if (split && c < kth_split) pos = (uint32_t)p.split_k + atomicAdd(&s_count[1], 1u);
-        else pos = atomicAdd(&s_count[0], 1u);
-        const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
+    // Output slots are handed out per warp (one shared-memory atomic for all takers of a warp-wide step):
+    // ballot, leader reserves, lanes take their rank inside the reservation.
+    const int lane = tid & 31;
+    const uint32_t lt = (1u << lane) - 1u;
+    auto warp_slots = [&](bool take, uint32_t* counter) -> uint32_t {
+      const uint32_t m = __ballot_sync(0xffffffffu, take);
+      uint32_t base = 0;
+      if (m) {
+        const int leader = __ffs(m) - 1;
+        if (lane == leader) base = atomicAdd(counter, (uint32_t)__popc(m));
+        base = __shfl_sync(0xffffffffu, base, leader);
+      }
+      return base + (uint32_t)__popc(m & lt);
+    };
+    const int n_round = (n + 31) & ~31;               // whole warps walk together (ballots inside)
+    for (int i = tid; i < n_round; i += SEL_FINAL_THREADS) {
+      const uint64_t c = i < n ? s_cand[i] : 0ull;
+      const bool win = i < n && c >= kth;
+      const bool first = win && !(split && c < kth_split);
+      const uint32_t pa = warp_slots(first, &s_count[0]);
+      const uint32_t pb = split ? warp_slots(win && !first, &s_count[1]) : 0u;
+      const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
+      const bool mine = own && win && (int64_t)idx >= p.own_base && (int64_t)idx < p.own_limit;
+      const uint32_t pq = own ? warp_slots(mine, &s_count[2]) : 0u;
+      if (win) {
+        const uint32_t pos = first ? pa : (uint32_t)p.split_k + pb;
         if (pos < (uint32_t)p.kk) {
           const int64_t o = (int64_t)row * out_pitch + pos;
           if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
@@ -564,10 +648,7 @@ again:
           if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(c >> 32));
           if (p.out_comp) p.out_comp[o] = (c & 0xFFFFFFFF00000000ull) | (uint64_t)(0xFFFFFFFFu - idx);
         }
-        if (own && (int64_t)idx >= p.own_base && (int64_t)idx < p.own_limit) {
-          const uint32_t q = atomicAdd(&s_count[2], 1u);
-          if (q < (uint32_t)p.kk) p.out_owned[(int64_t)row * out_pitch + q] = (int32_t)idx;
-        }
+        if (mine && pq < (uint32_t)p.kk) p.out_owned[(int64_t)row * out_pitch + pq] = (int32_t)idx;
       }
     }
     if (own && p.out_owned_count) {
@@ -819,3 +900,4 @@ extern "C" __attribute__((visibility("default"))) int kvb_select_topk(
                          hist_in, /*hist_in_workspace=*/false, /*zeroed=*/false, workspace, workspace_bytes, device,
                          reinterpret_cast<cudaStream_t>(stream));
 }
+

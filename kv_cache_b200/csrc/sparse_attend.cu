@@ -398,6 +398,11 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
   const int d = threadIdx.x;
   pdl_wait();
   const float* parts = p.ws_partial + (int64_t)row * p.nsplit * GG * PW;
+  // the first eight partial outputs are requested before the weights are known: one round trip to L2, not two
+  const float* col = parts + hd * PW + d;
+  float x0[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) x0[u] = (u < p.nsplit) ? __ldcg(col + (int64_t)u * GG * PW) : 0.0f;
   if (d < 32) {
     float m_a = -INFINITY, l_a = 0.0f, m_b = -INFINITY, l_b = 0.0f;
     if (d < p.nsplit) {
@@ -422,16 +427,9 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
   }
   __syncthreads();
   float O = 0.0f;
-  const float* col = parts + hd * PW + d;
-  int sp = 0;
-  for (; sp + 8 <= p.nsplit; sp += 8) {
-    float x[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) x[u] = __ldcg(col + (int64_t)(sp + u) * GG * PW);
-#pragma unroll
-    for (int u = 0; u < 8; ++u) O += x[u] * s_w[sp + u];
-  }
-  {
+  for (int u = 0; u < 8; ++u) O += (u < p.nsplit) ? x0[u] * s_w[u] : 0.0f;
+  for (int sp = 8; sp < p.nsplit; sp += 8) {
     float x[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) x[u] = (sp + u < p.nsplit) ? __ldcg(col + (int64_t)(sp + u) * GG * PW) : 0.0f;
