@@ -33,6 +33,10 @@ struct SampleParams {
   // failed flag), which spares the step a separate memset node
   uint32_t* zero_count;       // [R * SC_COUNT_STRIDE] (word 0 of every row's line is the counter) or NULL
   uint32_t* zero_failed;      // [R] or NULL
+  // optional: the decoded token's K and V rows (bf16 [R,128] dense), stored by this kernel as row T of the caches
+  const uint4* new_k; const uint4* new_v;
+  __nv_bfloat16* key; int64_t k_sb, k_sh, k_st;
+  __nv_bfloat16* value; int64_t v_sb, v_sh, v_st;
 };
 
 template <int C, int G>
@@ -49,6 +53,11 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   if (q.zero_count && tid == 0) q.zero_count[(int64_t)row * SC_COUNT_STRIDE] = 0;
   if (q.zero_failed && tid == 32) q.zero_failed[row] = 0;
   const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
+  if (q.new_k && tid >= 64 && tid < 96) {          // one warp: 16 lanes per row, 16 bytes per lane
+    const int l = tid - 64, rb = row / p.Hkv, rh = row - rb * p.Hkv;
+    if (l < 16) *reinterpret_cast<uint4*>(q.key + (int64_t)rb * q.k_sb + (int64_t)rh * q.k_sh + (int64_t)T * q.k_st + l * 8) = q.new_k[row * 16 + l];
+    else *reinterpret_cast<uint4*>(q.value + (int64_t)rb * q.v_sb + (int64_t)rh * q.v_sh + (int64_t)T * q.v_st + (l - 16) * 8) = q.new_v[row * 16 + l - 16];
+  }
   if (T <= q.cap) {                             // short rows: every token is a candidate
     if (tid == 0) q.tau[row] = -INFINITY;
     return;
@@ -217,10 +226,21 @@ static void fill_score_params(ScoreParams& sp, const void* query, int64_t q_sb, 
 }
 
 static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cudaStream_t st,
-                      uint32_t* zero_count = nullptr, uint32_t* zero_failed = nullptr) {
+                      uint32_t* zero_count = nullptr, uint32_t* zero_failed = nullptr,
+                      const kvb_decode_step_params* rows = nullptr) {
   SampleParams sq;
   sq.sp = sp; sq.tau = tau; sq.top_k = top_k; sq.cap = cap;
   sq.zero_count = zero_count; sq.zero_failed = zero_failed;
+  sq.new_k = nullptr; sq.new_v = nullptr; sq.key = nullptr; sq.value = nullptr;
+  sq.k_sb = sq.k_sh = sq.k_st = sq.v_sb = sq.v_sh = sq.v_st = 0;
+  if (rows && rows->new_key_row) {
+    sq.new_k = reinterpret_cast<const uint4*>(rows->new_key_row);
+    sq.new_v = reinterpret_cast<const uint4*>(rows->new_value_row);
+    sq.key = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(rows->key));
+    sq.value = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(rows->value));
+    sq.k_sb = rows->k_sb; sq.k_sh = rows->k_sh; sq.k_st = rows->k_st;
+    sq.v_sb = rows->v_sb; sq.v_sh = rows->v_sh; sq.v_st = rows->v_st;
+  }
   const int R = sp.B * sp.Hkv;
   if (sp.C == 32) return sample_launch_g<32>(sq, R, st);
   if (sp.C == 64) return sample_launch_g<64>(sq, R, st);
@@ -318,8 +338,9 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   const int32_t* T_dev = p->history_count_dev;
   if (T_dev && !fast) return KVB_BAD_SHAPE;
   if ((p->new_key_row == nullptr) != (p->new_value_row == nullptr)) return KVB_BAD_ARG;
-  if (p->new_key_row) {
-    if (p->D != 128 || !aligned_to(p->new_key_row, 16) || !aligned_to(p->new_value_row, 16)) return KVB_BAD_ALIGN;
+  if (p->new_key_row && (p->D != 128 || !aligned_to(p->new_key_row, 16) || !aligned_to(p->new_value_row, 16)))
+    return KVB_BAD_ALIGN;
+  if (p->new_key_row && !fast) {                   // (the fast path's first kernel stores the rows itself)
     DeviceGuard guard(device);
     if (!guard.ok) return KVB_BAD_DEVICE;
     store_new_rows_kernel<<<p->B * p->Hkv, 32, 0, st>>>(
@@ -339,7 +360,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       ScoreParams base;
       fill_score_params(base, p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
                         p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, T_dev);
-      rc = sample_run(base, ftau, p->top_k, fcap, st, fcount, reinterpret_cast<uint32_t*>(ws + L.off_ffailed));
+      rc = sample_run(base, ftau, p->top_k, fcap, st, fcount, reinterpret_cast<uint32_t*>(ws + L.off_ffailed), p);
       if (rc != KVB_OK) return rc;
       chain.on();                             // every later kernel of the step starts early and waits inside
 

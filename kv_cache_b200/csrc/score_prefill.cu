@@ -281,6 +281,82 @@ __global__ void __launch_bounds__(BT_WARPS * 32) block_topk_kernel(const float* 
   }
 }
 
+// The same selection for k <= 32 and rows of at most 32 * NPL elements, with the row in registers: one warp per
+// row, lane l holds elements l, l + 32, ... as order-preserving keys. The k-th largest key is found by a
+// bitwise binary search (32 steps of NPL compares and one warp sum), ties at that key are taken in index
+// order, and the winners (one per lane) are put into (score desc, index asc) order by a warp bitonic sort.
+template <int NPL>
+__global__ void __launch_bounds__(BT_WARPS * 32) block_topk_reg_kernel(const float* scores, int64_t row_stride, int64_t R,
+                                                                       int T, int k, int32_t* out_idx, float* out_scores) {
+  __shared__ uint64_t s_win[BT_WARPS][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * BT_WARPS + warp;
+  if (row >= R) return;
+  const float* src = scores + row * row_stride;
+  uint32_t key[NPL];
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    const int e = j * 32 + lane;
+    float v = e < T ? src[e] : 0.0f;
+    key[j] = (e < T && v == v) ? float_to_key(v) : 0u;          // absent and NaN: below every real score
+  }
+  const int kk = k < T ? k : T;
+  // largest K with #{key >= K} >= kk
+  uint32_t K = 0;
+#pragma unroll 1
+  for (int bit = 31; bit >= 0; --bit) {
+    const uint32_t cand = K | (1u << bit);
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) c += key[j] >= cand ? 1 : 0;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
+    if (c >= kk) K = cand;
+  }
+  // winners: every key above K, and the first (kk - that many) keys equal to K in index order
+  int above = 0;
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) above += key[j] > K ? 1 : 0;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) above += __shfl_xor_sync(0xffffffffu, above, off);
+  int ties_left = kk - above;
+  const uint32_t lt = (1u << lane) - 1u;
+  int slot_base = 0;
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    const bool gt = key[j] > K;
+    const bool eq = key[j] == K;
+    const uint32_t meq = __ballot_sync(0xffffffffu, eq);
+    const bool take_eq = eq && (int)__popc(meq & lt) < ties_left;
+    ties_left -= min(ties_left, (int)__popc(meq));
+    const bool take = gt || take_eq;
+    const uint32_t mt = __ballot_sync(0xffffffffu, take);
+    if (take) {
+      const int slot = slot_base + (int)__popc(mt & lt);
+      if (slot < 32) s_win[warp][slot] = ((uint64_t)key[j] << 32) | (uint64_t)(0xFFFFFFFFu - (uint32_t)(j * 32 + lane));
+    }
+    slot_base += (int)__popc(mt);
+  }
+  __syncwarp();
+  uint64_t c = lane < kk ? s_win[warp][lane] : 0ull;
+  // warp bitonic sort, descending
+#pragma unroll
+  for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      const uint64_t o = __shfl_xor_sync(0xffffffffu, c, stride);
+      const bool upper = (lane & stride) != 0;                   // this lane holds the higher index of the pair
+      const bool desc = (lane & size) == 0;                      // the pair's block sorts descending
+      const bool keep_max = (upper != desc);                     // lower index of a descending pair keeps the max
+      c = keep_max ? (c > o ? c : o) : (c < o ? c : o);
+    }
+  }
+  if (lane < kk) {
+    out_idx[row * kk + lane] = (int32_t)(0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull));
+    if (out_scores) out_scores[row * kk + lane] = key_to_float((uint32_t)(c >> 32));
+  }
+}
+
 template <int C, int G>
 static int prefill_launch(const PrefillParams& p0, int device, cudaStream_t st) {
   PrefillParams p = p0;
@@ -409,6 +485,15 @@ extern "C" __attribute__((visibility("default"))) int kvb_block_topk(const float
   if (R <= 0 || nblk <= 0 || k <= 0 || nblk > BT_MAX_T || row_stride < nblk) return KVB_BAD_SHAPE;
   DeviceGuard guard(device);
   if (!guard.ok) return KVB_BAD_DEVICE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (k <= 32 && nblk <= 2048) {
+    const unsigned grid = (unsigned)((R + BT_WARPS - 1) / BT_WARPS);
+    if (nblk <= 512) block_topk_reg_kernel<16><<<grid, BT_WARPS * 32, 0, st>>>(block_scores, row_stride, R, nblk, k, out_idx, out_scores);
+    else if (nblk <= 1024) block_topk_reg_kernel<32><<<grid, BT_WARPS * 32, 0, st>>>(block_scores, row_stride, R, nblk, k, out_idx, out_scores);
+    else block_topk_reg_kernel<64><<<grid, BT_WARPS * 32, 0, st>>>(block_scores, row_stride, R, nblk, k, out_idx, out_scores);
+    KVB_CHECK_CUDA(cudaGetLastError());
+    return KVB_OK;
+  }
   const size_t smem = sizeof(float) * (size_t)BT_WARPS * nblk;
   static bool attr_done[64] = {false};
   if (device < 64 && !attr_done[device]) {
