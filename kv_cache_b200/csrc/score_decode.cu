@@ -134,6 +134,30 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
     u += (ub - ua);
     const int b = row / p.Hkv, kvh = row - b * p.Hkv;
 
+    const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)kvh * p.packed_sh;
+    const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)kvh * p.scale_sh;
+
+    // Full tiles of this segment: [ta, tb); warp w takes ta + w, ta + w + WARPS, ...
+    const int ta = ua;
+    const int tb = ub < full_tiles ? ub : full_tiles;
+    const int nmy = (tb - ta - warp + WARPS - 1) / WARPS;   // <= 0 when none
+
+    auto issue = [&](int j, uint32_t slot) {
+      // lane 0 only: tile j of this warp into ring slot `slot`
+      const int64_t t0 = (int64_t)(ta + warp + j * WARPS) * TW;
+      uint8_t* dst = my_stage + (slot % NS) * STAGE_BYTES;
+      mbar_arrive_expect_tx(&my_bar[slot % NS], STAGE_BYTES);
+      bulk_g2s_evict_first(dst, packed_row + t0 * TOKEN_BYTES, PACKED_BYTES, &my_bar[slot % NS], policy);
+      bulk_g2s_evict_first(dst + PACKED_BYTES, scale_row + t0, TW * 4, &my_bar[slot % NS], policy);
+    };
+    // The first copies of the segment go out before the query is quantised (and before the wait for the
+    // kernel that produces the thresholds): the ring fills while the prologue runs.
+    if (!dead && nmy > 0 && lane == 0) {
+      fence_proxy_async_smem();                      // the slots were last read with ordinary loads
+      const int pre = nmy < NS ? nmy : NS;
+      for (int j = 0; j < pre; ++j) issue(j, ring + j);
+    }
+
     quantize_query_group<THREADS>(p, b, kvh, G, s_qv, s_qcode, s_qscale);
 
     // B fragments. Lane t4 owns packed bytes [KS*4*t4, KS*4*(t4+1)) of every token; k-step s uses
@@ -162,8 +186,6 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
 #pragma unroll
     for (int v = 0; v < HV; ++v) qs16[v] = s_qscale[(h0 + v) % G] * 0.0625f;
 
-    const uint8_t* packed_row = p.packed + (int64_t)b * p.packed_sb + (int64_t)kvh * p.packed_sh;
-    const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)kvh * p.scale_sh;
     float* gmax_row = p.gmax_out ? p.gmax_out + (int64_t)row * p.T : nullptr;
     // Everything above reads only the caller's inputs; the thresholds (and the zeroed counters) come
     // from the kernels before this one.
@@ -206,25 +228,7 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
       }
     };
 
-    // Full tiles of this segment: [ta, tb); warp w takes ta + w, ta + w + WARPS, ...
-    const int ta = ua;
-    const int tb = ub < full_tiles ? ub : full_tiles;
-    const int nmy = (tb - ta - warp + WARPS - 1) / WARPS;   // <= 0 when none
-
-    auto issue = [&](int j, uint32_t slot) {
-      // lane 0 only: tile j of this warp into ring slot `slot`
-      const int64_t t0 = (int64_t)(ta + warp + j * WARPS) * TW;
-      uint8_t* dst = my_stage + (slot % NS) * STAGE_BYTES;
-      mbar_arrive_expect_tx(&my_bar[slot % NS], STAGE_BYTES);
-      bulk_g2s_evict_first(dst, packed_row + t0 * TOKEN_BYTES, PACKED_BYTES, &my_bar[slot % NS], policy);
-      bulk_g2s_evict_first(dst + PACKED_BYTES, scale_row + t0, TW * 4, &my_bar[slot % NS], policy);
-    };
-
     if (!dead && nmy > 0) {
-      if (lane == 0) {
-        const int pre = nmy < NS ? nmy : NS;
-        for (int j = 0; j < pre; ++j) issue(j, ring + j);
-      }
       for (int j = 0; j < nmy; ++j) {
         const uint32_t slot = ring + j;
         bool ok = mbar_wait_bounded(&my_bar[slot % NS], (slot / NS) & 1u);
