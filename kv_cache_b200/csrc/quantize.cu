@@ -7,6 +7,7 @@ namespace kvb {
 constexpr int QZ_THREADS = 256;            // 8 warps, one half-warp per token => 16 tokens per pass
 constexpr int QZ_TOKENS_PER_PASS = QZ_THREADS / 16;
 constexpr int QZ_MAX_D = 256;
+constexpr int QZ_UNROLL = 4;               // tokens per half-warp per iteration, all their rows in flight at once
 constexpr int QZ_MAX_C = 128;
 
 struct QuantizeParams {
@@ -33,7 +34,7 @@ __device__ __forceinline__ int quantize_code(float x, float s) {
 template <int BPL>
 __global__ void __launch_bounds__(QZ_THREADS) quantize_pack_kernel(QuantizeParams p) {
   __shared__ int s_ch[QZ_MAX_C];
-  __shared__ __align__(16) uint16_t s_rows[QZ_TOKENS_PER_PASS][QZ_MAX_D];
+  __shared__ __align__(16) uint16_t s_rows[QZ_TOKENS_PER_PASS][QZ_UNROLL][QZ_MAX_D];
 
   const int tid = threadIdx.x;
   const int h = blockIdx.y;
@@ -48,49 +49,61 @@ __global__ void __launch_bounds__(QZ_THREADS) quantize_pack_kernel(QuantizeParam
   const __nv_bfloat16* key_row0 = p.key + (int64_t)b * p.key_sb + (int64_t)h * p.key_sh;
   uint8_t* packed_row0 = p.packed + (int64_t)b * p.packed_sb + (int64_t)h * p.packed_sh;
   float* scale_row0 = p.scale + (int64_t)b * p.scale_sb + (int64_t)h * p.scale_sh;
-  uint16_t* row = s_rows[hw];
   const int vec_per_row = p.D >> 3;
 
-  // Both half-warps of a warp run the same number of iterations (full-mask shuffles below).
-  for (int64_t t0 = (int64_t)blockIdx.x * QZ_TOKENS_PER_PASS; t0 < p.T; t0 += (int64_t)gridDim.x * QZ_TOKENS_PER_PASS) {
-    const int64_t t = t0 + hw;
-    const bool active = t < p.T;
-    if (active) {
-      const uint4* src = reinterpret_cast<const uint4*>(key_row0 + t * p.key_st);
-      for (int j = l; j < vec_per_row; j += 16) reinterpret_cast<uint4*>(row)[j] = __ldcs(src + j);
-    }
-    __syncwarp();
-
-    float x[2 * BPL];
-    float amax = 0.0f;
+  // Both half-warps of a warp run the same number of iterations (full-mask shuffles below). A half-warp
+  // takes QZ_UNROLL tokens per iteration and copies all their rows to shared memory asynchronously before it
+  // touches the first one: several 16-byte requests per lane are in flight without costing registers.
+  constexpr int U = QZ_UNROLL;
+  for (int64_t t0 = (int64_t)blockIdx.x * QZ_TOKENS_PER_PASS * U; t0 < p.T;
+       t0 += (int64_t)gridDim.x * QZ_TOKENS_PER_PASS * U) {
 #pragma unroll
-    for (int i = 0; i < 2 * BPL; ++i) {
-      const int c = 2 * byte0 + i;
-      x[i] = (active && c < p.C) ? bf16_bits_to_float(row[s_ch[c]]) : 0.0f;
-      amax = fmaxf(amax, fabsf(x[i]));
-    }
-#pragma unroll
-    for (int off = 8; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    const float sc = __fdiv_rn(fmaxf(amax, 5.9604644775390625e-08f /* 2^-24 */), 7.0f);
-
-    uint32_t word = 0;
-#pragma unroll
-    for (int j = 0; j < BPL; ++j) {
-      const int lo = quantize_code(x[2 * j], sc);
-      const int hi = quantize_code(x[2 * j + 1], sc);
-      word |= (uint32_t)((lo & 0xF) | ((hi & 0xF) << 4)) << (8 * j);
-    }
-    if (active) {
-      uint8_t* dst = packed_row0 + (p.t_dst + t) * nb + byte0;
-      if (BPL > 1 && p.wide_store && byte0 + BPL <= nb) {
-        if (BPL == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)word;
-        else *reinterpret_cast<uint32_t*>(dst) = word;
-      } else {
-#pragma unroll
-        for (int j = 0; j < BPL; ++j)
-          if (byte0 + j < nb) dst[j] = (uint8_t)(word >> (8 * j));
+    for (int u = 0; u < U; ++u) {
+      const int64_t t = t0 + (int64_t)u * QZ_TOKENS_PER_PASS + hw;
+      if (t < p.T) {
+        const uint4* src = reinterpret_cast<const uint4*>(key_row0 + t * p.key_st);
+        for (int j = l; j < vec_per_row; j += 16) cp_async_16(reinterpret_cast<uint4*>(s_rows[hw][u]) + j, src + j);
       }
-      if (l == 0) scale_row0[p.t_dst + t] = sc;
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t t = t0 + (int64_t)u * QZ_TOKENS_PER_PASS + hw;
+      const bool active = t < p.T;
+      const uint16_t* row = s_rows[hw][u];
+      float x[2 * BPL];
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 2 * BPL; ++i) {
+        const int c = 2 * byte0 + i;
+        x[i] = (active && c < p.C) ? bf16_bits_to_float(row[s_ch[c]]) : 0.0f;
+        amax = fmaxf(amax, fabsf(x[i]));
+      }
+#pragma unroll
+      for (int off = 8; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+      const float sc = __fdiv_rn(fmaxf(amax, 5.9604644775390625e-08f /* 2^-24 */), 7.0f);
+
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < BPL; ++j) {
+        const int lo = quantize_code(x[2 * j], sc);
+        const int hi = quantize_code(x[2 * j + 1], sc);
+        word |= (uint32_t)((lo & 0xF) | ((hi & 0xF) << 4)) << (8 * j);
+      }
+      if (active) {
+        uint8_t* dst = packed_row0 + (p.t_dst + t) * nb + byte0;
+        if (BPL > 1 && p.wide_store && byte0 + BPL <= nb) {
+          if (BPL == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)word;
+          else *reinterpret_cast<uint32_t*>(dst) = word;
+        } else {
+#pragma unroll
+          for (int j = 0; j < BPL; ++j)
+            if (byte0 + j < nb) dst[j] = (uint8_t)(word >> (8 * j));
+        }
+        if (l == 0) scale_row0[p.t_dst + t] = sc;
+      }
     }
     __syncwarp();
   }
@@ -122,7 +135,7 @@ static int quantize_launch(const void* key, int64_t key_sb, int64_t key_sh, int6
   p.scale = scale; p.scale_sb = scale_sb; p.scale_sh = scale_sh;
   p.T = T; p.D = D; p.C = C; p.t_dst = t_dst; p.wide_store = wide;
 
-  const int passes = ceil_div(T, QZ_TOKENS_PER_PASS);
+  const int passes = ceil_div(T, QZ_TOKENS_PER_PASS * QZ_UNROLL);
   // Enough CTAs to fill the machine several times over, each looping over a few passes.
   int64_t want = (int64_t)sm_count(device) * 8 * 4;
   int per_row = (int)((want + (int64_t)B * Hkv - 1) / ((int64_t)B * Hkv));
