@@ -1,6 +1,7 @@
-// Fused per-layer decode step: quantize-append, score (+histogram), select, final index list,
-// attend — six stream-ordered launches sharing one caller-provided workspace. Intermediate
-// tensors (group-max scores, histogram, selected ids, final list) never leave the workspace.
+// Fused per-layer decode step: threshold from a sample, candidate-emitting score, exact select, attend over
+// the implicit final list (with the quantize-append of the new row), chunk merge — five stream-ordered
+// launches sharing one caller-provided workspace (the score + histogram + select chain where the sampled
+// front end does not apply). Candidates, selected ids and attention partials never leave the workspace.
 #include "common.cuh"
 #include "score_common.cuh"
 
@@ -15,8 +16,8 @@ namespace kvb {
 // 1.75 k tokens above it in the whole row (rank ~ 112: the prediction is good to about +-10 %, so
 // both bounds hold by many standard deviations). The bounds are CHECKED, not assumed: a row whose
 // count misses them (heavy ties, adversarial layouts) is re-scored into the group-max workspace by
-// a rescue kernel and selected by the exact refinement path, so the result is always the exact
-// top-k.
+// the select kernel itself and selected by the exact refinement path, so the result is always the
+// exact top-k.
 constexpr int FS_THREADS = 512;
 constexpr int FS_RUNS = 32;                    // evenly spaced runs of sampled tokens per row
 constexpr int FS_PER_THREAD = 8;                // sampled tokens per thread for rows up to FS_LONG_ROW (4096 per row) ...
