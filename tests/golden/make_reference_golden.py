@@ -20,7 +20,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_reference_golden.py <checkout of littlexi001/kv_cache>")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "ymluo/projects/qwen3_top2_head_limit3_ppl/src"))
 import evaluate_qwen3_top2_head_limit3_ppl as ref  # noqa: E402
 
