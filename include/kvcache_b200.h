@@ -183,7 +183,8 @@ int kvb_select_topk(const float* scores, int64_t row_stride, const int32_t* payl
  *   - Problems whose workspace (kvb_select_topk_workspace_bytes(R, T, k)) exceeds the limit are
  *     refused with KVB_SCRATCH_LIMIT before anything is launched (about 50 rows at k <= 4096).
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress);
- *     make that first call outside any stream capture.
+ *     make that first call outside any stream capture. A first call whose stream is being
+ *     captured is refused with KVB_BAD_ARG before any runtime call, so the capture survives.
  *   - Nothing is allocated or freed; counters and histogram are cleared by the call itself.
  *   - All calls share the one array: two calls that may overlap on the GPU (different streams)
  *     race with each other. Serialise them on one stream or with events. */

@@ -387,12 +387,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
       if (sp.use_bitmap) smem += bitmap_bytes;
       if (p->selected_any_order) { sp.order_by_index = 2; sp.use_bitmap = 0; }     // skip the ordering bitmap
-      static bool attr_done[64] = {false};
-      if (device < 64 && !attr_done[device]) {
-        KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            (int)SEL_SMEM_LIMIT));
-        attr_done[device] = true;
-      }
+      { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
       KVB_CHECK_CUDA(launch_kernel(select_final_kernel, dim3(L.R), dim3(SEL_FINAL_THREADS), smem, st, sp));
     }
   } else {
@@ -526,12 +521,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   sp.rescue = 1; sp.rescue_sp = base;
   sp.split_k = split_k;
   const size_t smem = (size_t)L.cap * 8 + SEL_FINAL_FIXED_SMEM;
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)SEL_SMEM_LIMIT));
-    attr_done[device] = true;
-  }
+  { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
   select_final_kernel<<<L.R, SEL_FINAL_THREADS, smem, st>>>(sp);
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
@@ -569,12 +559,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(
   } else {
     sp.order_by_index = 2; sp.use_bitmap = 0;                              // exact set, arbitrary order
   }
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)SEL_SMEM_LIMIT));
-    attr_done[device] = true;
-  }
+  { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
   select_final_kernel<<<R, SEL_FINAL_THREADS, smem, reinterpret_cast<cudaStream_t>(stream)>>>(sp);
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;

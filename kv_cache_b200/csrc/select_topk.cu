@@ -14,6 +14,8 @@
 // When a row has more than CAP candidates after step 2 (heavy ties, e.g. constant scores) the
 // last kernel first refines the prefix with 11-bit passes over the row itself until the
 // candidate set fits; that path is slower but exact for any input.
+#include <atomic>
+
 #include "common.cuh"
 #include "score_common.cuh"
 
@@ -733,6 +735,20 @@ static int select_cap(int k) {
 
 constexpr size_t SEL_FINAL_FIXED_SMEM = sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 40 + 8) + 8 * SEL_MAX_SEGMENTS;
 constexpr size_t SEL_SMEM_LIMIT = 227 * 1024;
+constexpr int KVB_MAX_DEVICES = 64;              // device ordinals the per-device set-up tables cover
+
+// Opts select_final_kernel into its large dynamic shared memory once per device (the device must be
+// current). Safe to call from several host threads: the flag is atomic and the attribute call is idempotent.
+static int select_final_prepare(int device) {
+  static std::atomic<bool> done[KVB_MAX_DEVICES];
+  if (device < 0 || device >= KVB_MAX_DEVICES) return KVB_BAD_DEVICE;
+  if (!done[device].load(std::memory_order_acquire)) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)SEL_SMEM_LIMIT));
+    done[device].store(true, std::memory_order_release);
+  }
+  return KVB_OK;
+}
 
 struct SelectWorkspace {
   uint32_t* count;     // [R]      } zeroed per call, contiguous
@@ -769,7 +785,7 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   if (!scores || !workspace) return KVB_BAD_ARG;
   if (!out_idx32 && !out_idx64 && !out_scores) return KVB_BAD_ARG;
   if (R <= 0 || T <= 0 || k <= 0 || R > 65535) return KVB_BAD_SHAPE;
-  if (order != 0 && order != 1 && order != 2) return KVB_BAD_ARG;
+  if (order != 0 && order != 1) return KVB_BAD_ARG;
   const int kk = k < T ? k : T;
   if (kk > SEL_MAX_K) return KVB_BAD_SHAPE;
   if (row_stride < T) return KVB_BAD_SHAPE;
@@ -826,12 +842,7 @@ static int select_run(const float* scores, int64_t row_stride, const int32_t* pa
   else select_collect_kernel<false><<<cgrid, SEL_SCAN_THREADS, 0, st>>>(p);
   KVB_CHECK_CUDA(cudaGetLastError());
 
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)SEL_SMEM_LIMIT));
-    attr_done[device] = true;
-  }
+  { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
   select_final_kernel<<<R, SEL_FINAL_THREADS, smem, st>>>(p);
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
@@ -845,17 +856,22 @@ constexpr size_t SEL_STATIC_SCRATCH_BYTES = 4u << 20;    // 4 MiB
 static __device__ __align__(256) unsigned char g_select_static_scratch[SEL_STATIC_SCRATCH_BYTES];
 
 // Device address of the built-in scratch on `device` (which must be current); looked up on the
-// first call per device and remembered.
-static int select_static_scratch(int device, void** out) {
-  static void* cached[64] = {nullptr};
-  if (device < 0 || device >= 64) return KVB_BAD_DEVICE;
-  if (!cached[device]) {
-    void* ptr = nullptr;
+// first call per device and remembered. The lookup is a runtime call that is not allowed while
+// `st` is being captured into a graph: in that case nothing is called and KVB_BAD_ARG comes back,
+// so the capture stays valid (make one call outside capture first).
+static int select_static_scratch(int device, cudaStream_t st, void** out) {
+  static std::atomic<void*> cached[KVB_MAX_DEVICES];
+  if (device < 0 || device >= KVB_MAX_DEVICES) return KVB_BAD_DEVICE;
+  void* ptr = cached[device].load(std::memory_order_acquire);
+  if (!ptr) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) return KVB_CUDA_ERROR;
+    if (cap != cudaStreamCaptureStatusNone) return KVB_BAD_ARG;
     const cudaError_t e = cudaGetSymbolAddress(&ptr, g_select_static_scratch);
     if (e != cudaSuccess || ptr == nullptr) return KVB_CUDA_ERROR;
-    cached[device] = ptr;
+    cached[device].store(ptr, std::memory_order_release);
   }
-  *out = cached[device];
+  *out = ptr;
   return KVB_OK;
 }
 
@@ -876,7 +892,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_select_topk_static(
   DeviceGuard guard(device);
   if (!guard.ok) return KVB_BAD_DEVICE;
   void* scratch = nullptr;
-  const int rc = select_static_scratch(device, &scratch);
+  const int rc = select_static_scratch(device, reinterpret_cast<cudaStream_t>(stream), &scratch);
   if (rc != KVB_OK) return rc;
   // select_run clears the counters and the histogram itself (memset nodes, no allocation); the
   // candidate area needs no clearing because only the counted prefix is ever read.

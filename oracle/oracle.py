@@ -33,8 +33,14 @@ TWO_M24 = 2.0 ** -24
 
 def choose_channels(key: torch.Tensor, num_channels: int) -> torch.Tensor:
     """Per KV head the C channels with the largest mean |K| over (B, T); ties -> lower channel;
-    ascending int32 [Hkv, C]."""
-    mean_abs = key.float().abs().mean(dim=(0, 2))
+    ascending int32 [Hkv, C]. The mean is taken in fp64: a sum of bf16 magnitudes is exact there for
+    any realistic cache (8-bit mantissas, 53-bit accumulator), so the result does not depend on the
+    order of summation and "equal means" is a well-defined notion."""
+    B, Hkv, T, D = key.shape
+    total = torch.zeros((Hkv, D), dtype=torch.float64)
+    for t0 in range(0, T, 65536):                                      # bounded temporaries
+        total += key[:, :, t0:t0 + 65536].to(torch.float64).abs().sum(dim=(0, 2))
+    mean_abs = total / max(1, B * T)
     order = torch.sort(mean_abs, dim=-1, descending=True, stable=True).indices[:, :num_channels]
     return torch.sort(order, dim=-1).values.to(torch.int32)
 
@@ -135,11 +141,12 @@ def attend_fp32(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, ind
     if Hi == Hkv:
         idx = idx.repeat_interleave(G, dim=1)
         ok = ok.repeat_interleave(G, dim=1)
-    kr = key.repeat_interleave(G, dim=1).float()
-    vr = value.repeat_interleave(G, dim=1).float()
-    gi = idx[..., None].expand(-1, -1, -1, D)
-    ks = torch.gather(kr, 2, gi)
-    vs = torch.gather(vr, 2, gi)
+    # rows are gathered from the un-repeated cache (head h reads KV head h // G): same values as
+    # repeating K/V to the query heads first, without the G-fold copy of the whole cache
+    bi = torch.arange(B)[:, None, None]
+    hi = (torch.arange(Hq) // G)[None, :, None]
+    ks = key[bi, hi, idx].float()                                   # [B,Hq,S,D]
+    vs = value[bi, hi, idx].float()
     s = torch.einsum("bhd,bhsd->bhs", query.float(), ks) * scaling
     if mask_rows is not None:
         s = s + torch.gather(mask_rows.float()[:, None, :].expand(-1, Hq, -1), -1, idx)
@@ -314,9 +321,11 @@ def candidate_count(candidate_fraction: float, history_count: int) -> int:
 
 
 def qabs_candidate_attention(query_states, key_states, value_states, attention_mask, scaling, dim_count,
-                             candidate_fraction, always_keep_self=True, protect_sink=0, protect_recent=0):
+                             candidate_fraction, always_keep_self=True, protect_sink=0, protect_recent=0,
+                             append_protected=False):
     """EVAL:4400-4502 (_qabs_candidate_attention_forward, torch branches) preceded by the K/V
     repeat of the dispatcher (EVAL:6248-6251): the reference's own CPU path for one decode step.
+    ``append_protected`` is the ``...appendattn`` form of the mode (EVAL:4451-4458).
     query [B,Hq,1,D], key/value [B,Hkv,Tk,D] -> [B,1,Hq,D]."""
     if key_states.shape[1] != query_states.shape[1]:
         rep = query_states.shape[1] // key_states.shape[1]
@@ -333,7 +342,7 @@ def qabs_candidate_attention(query_states, key_states, value_states, attention_m
     partial, _ = qabs_partial_scores(q_raw, key_states[:, :, :history, :], d_s)
     _, cand = torch.topk(partial, k=requested, dim=-1, largest=True)
     fidx, fvalid = final_indices_from_selected(cand, torch.ones_like(cand, dtype=torch.bool), history, key_count,
-                                               always_keep_self, protect_sink, protect_recent)
+                                               always_keep_self, protect_sink, protect_recent, append_protected)
     return attention_from_final_indices(query_states, key_states, value_states, attention_mask, fidx, fvalid, scaling)
 
 

@@ -68,9 +68,8 @@ def test_reference_decode_step_restated(case):
     mode = str(GOLD["ds_modes"][case])
     sink, recent = GOLD["ds_protect"][case].tolist()
     dims, frac = GOLD[f"ds_{case}_params"].tolist()
-    if mode.endswith("appendattn"):
-        pytest.skip("append variant is covered by the index-builder golden cases")
-    out = oracle.qabs_candidate_attention(q, k, v, None, q.shape[-1] ** -0.5, int(dims), frac, True, sink, recent)
+    out = oracle.qabs_candidate_attention(q, k, v, None, q.shape[-1] ** -0.5, int(dims), frac, True, sink, recent,
+                                          append_protected=mode.endswith("appendattn"))
     want = bf16(GOLD[f"ds_{case}_out"])
     assert torch.equal(out.view(torch.int16), want.view(torch.int16))
 

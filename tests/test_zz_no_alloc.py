@@ -4,14 +4,15 @@ It exists for hosts that must not allocate device memory where they call the lib
 stream-ordered region, under an embedding runtime that owns all allocation, with the memory budget
 already spent): its workspace is a fixed array inside the library image. The test drives it through
 the C ABI twice in a row — the array keeps the previous call's contents, so the second call proves
-that stale scratch does no harm — and checks every output bit for bit against kvb_select_topk.
-Collected last on purpose; it must pass on its own and after the rest of the suite."""
+that stale scratch does no harm — and checks every output bit for bit against kvb_select_topk
+and against the CPU oracle's select. Collected last on purpose; it must pass on its own and after the rest of the suite."""
 import ctypes
 
 import pytest
 import torch
 
 from kv_cache_b200 import _native
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -59,6 +60,13 @@ def test_static_select_matches_workspace_select_on_two_calls_in_a_row(cuda_devic
             torch.cuda.synchronize()
             for a, b in zip(got, want):
                 assert torch.equal(a, b)
+            # and against the oracle: (score desc, index asc) order, or the same set by ascending index
+            o_idx, o_val = oracle.select(scores.cpu(), k)
+            if order == 1:
+                by_index = torch.sort(o_idx, dim=-1)
+                o_idx, o_val = by_index.values, torch.gather(o_val, -1, by_index.indices)
+            assert torch.equal(got[1].cpu(), o_idx + 7)
+            assert torch.equal(got[2].cpu(), o_val)
 
 
 def test_static_select_refuses_what_does_not_fit(cuda_device):
