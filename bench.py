@@ -1,33 +1,38 @@
 #!/usr/bin/env python
 """Benchmark of the retrieval-sparse decode attention step (one layer).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c0|c1|c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c0|c1|c3|c4]
 
 Metric: K tokens scored+attended per second = B * T * steps / seconds / 1e3 for one layer's
 decode step (score all T cached int4 keys, select top-k per KV head, attend over the selected
 rows, append the new token to the int4 cache). One JSON line is printed by rank 0.
 
   value     whole step, inputs resident in HBM, CUDA-graph replay, CUDA events
-  e2e       the same step through the Python operator (kv_cache_b200.ops.DecodeStep) with the
+  e2e       the same step through the Python operator (ops.GraphedDecode / sharded step) with the
             step's inputs (query, new K/V row) copied from pinned host memory and the output
             copied back, every step, inside the timed region. The KV cache itself is device
             state (it is what "cache" means), like weights in a training step.
   roofline  the dominant kernel (the int4 scorer): algorithmic bytes / CUDA-event time of that
             kernel alone, against the measured HBM copy bandwidth in MEASURED_PEAKS.json
+  parity    after the timed region (untimed): one seeded (batch row, KV head) of the very outputs
+            the timed graph wrote is recomputed by the CPU oracle; ids must be equal, outputs in tolerance
+  secondary (--gpus 1, default workload) config 4 on one GPU through the sharded step as a world of
+            one, config 3 (chunked-prefill block scoring, both tcgen05 encodings) and the bulk quantizer
   cpu_baseline  the reference's torch CPU op chain for this step (oracle port), timed on this
             box's host cores on one batch row of the same workload
 
---impl reference times only that CPU chain (all host threads) and prints the same line shape.
+--gpus N > 1 (under torchrun) runs config 4 sequence-sharded over N ranks (strong scaling; the N = 1
+point of the same workload is `secondary.c4_n1` of the --gpus 1 line, or `--gpus 1 --workload c4`).
+--impl reference times only the CPU chain (all host threads) and prints the same line shape.
 """
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 from pathlib import Path
 
@@ -39,15 +44,16 @@ import torch  # noqa: E402
 
 from kv_cache_b200.benchutil import METRIC, UNIT, ClockSampler, hbm_peak  # noqa: E402
 
+DTYPE = "int4xint8->int32 scores, bf16 attention (fp32 accumulate)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one score_decode_stream_kernel launch at config 2 with
+# batch 4 (ncu capture summarised in profiles/): the traffic of a full launch is that times batch / 4
+# (the kernel streams every row exactly once, so its traffic is proportional to the rows).
+SCORER_DRAM_BYTES_BATCH4_C2 = 151.10e6 + 4.08e6
+
 
 # ------------------------------------------------------------------------------------------
-# CPU arm (reference op chain restated in oracle/)
+# CPU arm and the parity checker (the only users of oracle/ outside tests/ and the smoke check)
 # ------------------------------------------------------------------------------------------
-
-def reference_mode_params(w) -> tuple[int, float]:
-    """The reference mode string for this workload is qabs{C}cand{100k/T}attn (EVAL:748-754)."""
-    return w.channels, w.top_k / w.context
-
 
 def cpu_reference_sample(w, steps: int, warmup: int) -> dict:
     """Times the reference's torch CPU chain (EVAL:6248-6251 + EVAL:4400-4502, restated in
@@ -56,6 +62,7 @@ def cpu_reference_sample(w, steps: int, warmup: int) -> dict:
     from kv_cache_b200 import inputs
     from oracle import oracle
 
+    torch.set_num_threads(os.cpu_count() or 1)          # torchrun exports OMP_NUM_THREADS=1
     T = min(w.context, 131072)
     ws = inputs.Workload(w.name, 1, w.q_heads, w.kv_heads, w.head_dim, T, w.channels,
                          max(1, round(w.top_k * T / w.context)), w.seed)
@@ -89,7 +96,8 @@ def run_reference_arm(args, w) -> None:
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp32 scores / bf16 attention (CPU)", "data": "synthetic",
+        "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None,
+        "dtype": "fp32 scores / bf16 attention (CPU)", "data": "synthetic",
         "config": {"workload": w.name, "sample": base["sample"]},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -98,8 +106,33 @@ def run_reference_arm(args, w) -> None:
     print(json.dumps(line), flush=True)
 
 
+def oracle_parity(w, row: tuple[int, int], key_row: torch.Tensor, value_row: torch.Tensor, query: torch.Tensor,
+                  ch: torch.Tensor, sel: torch.Tensor, out: torch.Tensor) -> dict:
+    """Untimed check of one (batch row, KV head) of the outputs the timed graph wrote against the CPU oracle
+    (oracle.decode_step on that row's whole K/V): the selected ids must be the oracle's set, the G output
+    heads within 2e-2 relative / 1e-2 absolute. ``key_row`` / ``value_row``: ``[1,1,T+1,D]`` on any device."""
+    from oracle import oracle
+
+    b, h = row
+    G = w.q_heads // w.kv_heads
+    r = oracle.decode_step(query[b:b + 1, h * G:(h + 1) * G].cpu(), key_row.cpu(), value_row.cpu(), ch[h:h + 1].cpu(),
+                           w.top_k)
+    want = torch.sort(r["selected"][0, 0]).values
+    got = torch.sort(sel[b, h].cpu().long()).values
+    o = out[b, 0, h * G:(h + 1) * G].float().cpu()
+    ref = r["out"][0, 0]
+    err = (o - ref).abs()
+    return {"row": [b, h], "indices_equal": bool(torch.equal(want, got)), "max_abs_err": float(err.max()),
+            "within_tolerance": bool((err <= 1e-2 + 2e-2 * ref.abs()).all()), "tolerance": "2e-2 rel / 1e-2 abs",
+            "checker": "oracle.decode_step on the whole row (CPU), against the outputs of the timed graph"}
+
+
+def parity_row(w) -> tuple[int, int]:
+    return (w.seed * 7 + 3) % w.batch, (w.seed * 5 + 1) % w.kv_heads
+
+
 # ------------------------------------------------------------------------------------------
-# GPU arm, one GPU
+# GPU arm, one GPU, un-sharded step
 # ------------------------------------------------------------------------------------------
 
 def event_time_ms(fn, iters: int, stream) -> float:
@@ -114,8 +147,8 @@ def event_time_ms(fn, iters: int, stream) -> float:
     return start.elapsed_time(end) / iters
 
 
-def run_single_gpu(args, w) -> None:
-    from kv_cache_b200 import inputs, ops
+def run_single_gpu(args, w, with_secondary: bool) -> None:
+    from kv_cache_b200 import _native, inputs, ops
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
@@ -133,10 +166,11 @@ def run_single_gpu(args, w) -> None:
     # any-order selection: the exact top-k set without the ordering pass (see kvb_decode_step_params)
     step = ops.DecodeStep(k, ordered_selection=False)
     out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16, device=dev)
+    sel = torch.empty((B, Hkv, min(k, T)), dtype=torch.int32, device=dev)
     stream = torch.cuda.Stream(dev)
 
     def run_step():
-        step(query, key, value, packed, scale, ch, out=out)
+        step(query, key, value, packed, scale, ch, out=out, selected_out=sel)
 
     with torch.cuda.stream(stream):
         for _ in range(3):
@@ -158,9 +192,9 @@ def run_single_gpu(args, w) -> None:
         nrep = max(4, min(400, int(1000.0 / max(ms_step * args.steps, 1e-3))))
         repeats = [ms_step] + [event_time_ms(graph.replay, args.steps, stream) for _ in range(nrep)]
         ms_step = statistics.median(repeats)
+        out_timed, sel_timed = out.clone(), sel.clone()         # what the timed graph wrote
 
         # dominant kernel alone: the scorer in the form the step uses (candidate emission), same stream
-        from kv_cache_b200 import _native
         lib = _native.lib()
         cap = lib.kvb_candidate_capacity(k)
         _, _, tau = ops.score_candidates(query, packed, scale, ch, T, k)
@@ -195,6 +229,12 @@ def run_single_gpu(args, w) -> None:
             h_out = gd()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
         h_q, h_k, h_v = gd.h_query, gd.h_key_row, gd.h_value_row
+        e2e_equal = bool(torch.equal(h_out.cpu(), out_timed.cpu())) if step.ordered_selection else None
+
+    b_chk, h_chk = parity_row(w)
+    parity = oracle_parity(w, (b_chk, h_chk), key[b_chk:b_chk + 1, h_chk:h_chk + 1], value[b_chk:b_chk + 1, h_chk:h_chk + 1],
+                           query, ch, sel_timed, out_timed)
+    e2e_err = (h_out.float() - out_timed.float().cpu()).abs().max().item()
 
     tokens = B * T
     peak, peak_kind = hbm_peak()
@@ -205,15 +245,33 @@ def run_single_gpu(args, w) -> None:
         l2_note = "working set of %d MiB fits the 126 MB L2: a latency figure, not a bandwidth one" % (alg["total"] >> 20)
     scorer_gbs = alg["scan"] / (ms_scorer * 1e-3) / 1e9
     step_gbs = alg["total"] / (ms_step * 1e-3) / 1e9
+    traffic = None
+    if w.name.startswith("c2_"):
+        traffic = SCORER_DRAM_BYTES_BATCH4_C2 * B / 4.0
     cpu = None
     if not args.no_cpu_baseline:
         cpu = cpu_reference_sample(w, 2, 1)
 
+    secondary = None
+    if with_secondary:
+        secondary = {}
+        w4 = inputs.WORKLOADS["c4"]
+        r4 = measure_sharded(w4, max(5, args.steps // 2), 3, dev)
+        a4 = w4.algorithmic_bytes()
+        secondary["c4_n1"] = {
+            "workload": w4.name, "ms_per_step": r4["ms_step"], "value": w4.batch * w4.context / (r4["ms_step"] * 1e-3) / 1e3,
+            "unit": UNIT, "e2e_ms_per_step": r4["e2e_ms"], "whole_step_frac": a4["total"] / (r4["ms_step"] * 1e-3) / 1e9 / peak,
+            "path": "kvb_sharded_decode_step as a world of one (the code the N >= 2 lines run), CUDA graph replay",
+            "parity": r4["parity"]}
+        torch.cuda.empty_cache()
+        secondary["c3"] = measure_prefill(2, 4096, max(3, args.steps // 4), 3, dev)
+        torch.cuda.empty_cache()
+        secondary["bulk_quantize"] = measure_quantize(dev)
+
     line = {
         "metric": METRIC, "value": tokens / (ms_step * 1e-3) / 1e3, "unit": UNIT, "n_gpus": 1,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int4xint8->int32 scores, bf16 attention (fp32 accumulate)",
-        "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
         "config": {"workload": w.name, "batch": B, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "context": T,
                    "partial_channels": C, "top_k": k, "l2": l2_note,
                    "launch": "CUDA graph replay of kvb_decode_step (selected ids in any order)", "setup_s": round(setup_s, 1),
@@ -221,27 +279,193 @@ def run_single_gpu(args, w) -> None:
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e3, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h_q.numel() * 2 + h_k.numel() * 2 + h_v.numel() * 2,
-                "d2h_bytes_per_step": h_out.numel() * 2,
+                "d2h_bytes_per_step": h_out.numel() * 2, "max_abs_diff_vs_timed_output": e2e_err,
                 "api": "kv_cache_b200.ops.GraphedDecode.__call__ (H2D + kvb_decode_step + D2H in one CUDA graph, device-side history length)"},
         "gpu_launches": 5 * args.steps,      # sample, scorer, final select, attend, merge per replayed step
         "roofline": {"bound": "hbm", "kernel": "score_decode_stream_kernel (candidate form)", "achieved": scorer_gbs, "peak": peak,
-                     "unit": "GB/s", "frac": scorer_gbs / peak, "peak_source": peak_kind, "traffic": None,
+                     "unit": "GB/s", "frac": scorer_gbs / peak, "peak_source": peak_kind, "traffic": traffic,
+                     "traffic_source": None if traffic is None else "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at batch 4, scaled by batch / 4",
                      "algorithmic_bytes": alg["scan"], "kernel_ms": ms_scorer,
                      "whole_step": {"algorithmic_bytes": alg["total"], "achieved": step_gbs, "frac": step_gbs / peak}},
+        "parity": parity,
         "cpu_baseline": cpu,
     }
+    if secondary is not None:
+        line["secondary"] = secondary
+    if e2e_equal is not None:
+        line["e2e"]["equal_to_timed_output"] = e2e_equal
     print(json.dumps(line), flush=True)
 
 
-def run_prefill_gpu(args) -> None:
-    """Config 3: chunked-prefill block scoring, 4096 queries x 131072 keys, batch 2, Qwen3-8B shapes.
-    A step = per-token query quantisation + int8 block scoring + top-32 blocks per (b, KV head, query)."""
-    import dataclasses
+# ------------------------------------------------------------------------------------------
+# sequence-sharded step (config 4): N ranks under torchrun, or a world of one
+# ------------------------------------------------------------------------------------------
+
+def measure_sharded(w, steps: int, warmup: int, dev: torch.device) -> dict:
+    """Times the sharded step of workload ``w`` on the ranks of the default process group (a world of one
+    without it): CUDA-graph replays, CUDA events, max over ranks; then the end-to-end form (the step's
+    inputs copied from pinned host memory and the output copied back inside one graph, the host waiting
+    every step); then, on rank 0, the parity check of the timed outputs against the un-sharded oracle."""
+    import torch.distributed as dist
+    from kv_cache_b200 import inputs
+    from kv_cache_b200.sharded import ShardedSparseDecode, make_shard
+
+    on = dist.is_available() and dist.is_initialized()
+    rank = dist.get_rank() if on else 0
+    world = dist.get_world_size() if on else 1
+    B, Hq, Hkv, D, T, k = w.batch, w.q_heads, w.kv_heads, w.head_dim, w.context, w.top_k
+    t_setup = time.perf_counter()
+    s = make_shard(w, rank, world, dev)
+    setup_s = time.perf_counter() - t_setup
+    key, value, query, ch, packed, scale, t0, t_local = (s[n] for n in ("key", "value", "query", "ch", "packed", "scale",
+                                                                         "t0", "t_local"))
+    eng = ShardedSparseDecode(k, total_tokens=T)
+    graph, (out, sel) = eng.capture(query, key, value, packed, scale, ch, t_local, t0)
+    one_call = bool(eng._fast)
+    stream = torch.cuda.Stream(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, warmup)):
+            graph.replay()
+        stream.synchronize()
+        sampler = ClockSampler(dev.index or 0)
+        if rank == 0:
+            sampler.start()
+        barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        nrep = max(1, int(800.0 / max(0.3 * steps, 1e-3)))            # the better part of a second of timed work
+        start.record(stream)
+        for _ in range(steps * nrep):
+            graph.replay()
+        end.record(stream)
+        barrier()
+        torch.cuda.synchronize()
+        ms_step = max_over_ranks(start.elapsed_time(end) / (steps * nrep))
+        clocks = sampler.stop() if rank == 0 else None
+        out_timed, sel_timed = out.clone(), sel.clone()
+
+        # end to end: one graph = H2D of the step's inputs, the step, D2H of the output
+        nq, nkv = query.numel(), B * Hkv * D
+        h_in = torch.empty((nq + 2 * nkv,), dtype=torch.bfloat16).pin_memory()
+        h_in[:nq].copy_(query.reshape(-1))
+        h_in[nq:nq + nkv].copy_(key[:, :, t_local].reshape(-1))
+        h_in[nq + nkv:].copy_(value[:, :, t_local].reshape(-1))
+        d_in = torch.empty(h_in.shape, dtype=torch.bfloat16, device=dev)
+        d_q = d_in[:nq].view(B, Hq, D)
+        h_out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_body():
+            d_in.copy_(h_in, non_blocking=True)
+            key[:, :, t_local].copy_(d_in[nq:nq + nkv].view(B, Hkv, D))
+            value[:, :, t_local].copy_(d_in[nq + nkv:].view(B, Hkv, D))
+            o, _ = eng.step(d_q, key, value, packed, scale, ch, t_local, t0)
+            h_out.copy_(o, non_blocking=True)
+
+        e2e_body()
+        stream.synchronize()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=stream):
+            e2e_body()
+
+        def e2e_step():
+            g2.replay()
+            stream.synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        tw = time.perf_counter()
+        for _ in range(steps):
+            e2e_step()
+        e2e_ms = max_over_ranks((time.perf_counter() - tw) * 1e3 / steps)
+
+    parity = None
+    if rank == 0:
+        b_chk, h_chk = parity_row(w)
+        kb, vb = inputs.make_kv(w, dev, 0, T + 1, batch_rows=range(b_chk, b_chk + 1))      # the row's shards, all of them
+        parity = oracle_parity(w, (b_chk, h_chk), kb[:, h_chk:h_chk + 1], vb[:, h_chk:h_chk + 1], query, ch, sel_timed,
+                               out_timed)
+        parity["e2e_max_abs_diff_vs_timed_output"] = (h_out.float() - out_timed.float().cpu()).abs().max().item()
+        del kb, vb
+    barrier()
+    graph = g2 = None
+    eng.close()
+    return dict(ms_step=ms_step, e2e_ms=e2e_ms, clocks=clocks, parity=parity, world=world, rank=rank, one_call=one_call,
+                setup_s=setup_s, h2d=h_in.numel() * 2, d2h=h_out.numel() * 2, timed_steps=steps * nrep)
+
+
+def run_sharded(args, w) -> None:
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    under_torchrun = "WORLD_SIZE" in os.environ and int(os.environ["WORLD_SIZE"]) > 1
+    if under_torchrun and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    r = measure_sharded(w, args.steps, args.warmup, dev)
+    world = r["world"]
+    if rank == 0:
+        B, Hq, Hkv, D, T, Cc, k = w.batch, w.q_heads, w.kv_heads, w.head_dim, w.context, w.channels, w.top_k
+        ms_step, e2e_ms = r["ms_step"], r["e2e_ms"]
+        tokens = B * T
+        alg = w.algorithmic_bytes()
+        peak, peak_kind = hbm_peak()
+        cpu = None if args.no_cpu_baseline else cpu_reference_sample(w, 2, 1)
+        line = {
+            "metric": METRIC, "value": tokens / (ms_step * 1e-3) / 1e3, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+            "config": {"workload": w.name, "batch": B, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "context": T,
+                       "partial_channels": Cc, "top_k": k, "sharding": f"sequence/{world}",
+                       "exchange": ("no collective in the step: candidate prefixes and LSE partials are stored into "
+                                    "peer memory over NVLink under step-numbered flags (kvb_sharded_decode_step)")
+                       if r["one_call"] else "2 all-gathers per step (candidates, LSE partials)",
+                       "launch": "CUDA graph replay of the 7-kernel step", "timed_steps": r["timed_steps"],
+                       "l2": "inputs larger than L2 (scan stream %d MiB per rank)" % ((alg["scan"] // world) >> 20),
+                       "setup_s": round(r["setup_s"], 1)},
+            "clocks": r["clocks"],
+            "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e3, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
+                    "api": "kv_cache_b200.sharded.ShardedSparseDecode.step inside one CUDA graph with the H2D copy of "
+                           "the step's inputs and the D2H copy of its output; the host waits every step"},
+            "gpu_launches": 7 * args.steps * world,
+            "roofline": {"bound": "hbm", "kernel": "whole sharded step, per rank", "achieved":
+                         alg["total"] / world / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg["total"] / world / (ms_step * 1e-3) / 1e9 / peak, "peak_source": peak_kind,
+                         "traffic": None, "algorithmic_bytes": alg["total"] // world},
+            "parity": r["parity"],
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------
+# config 3 (chunked-prefill block scoring) and the bulk quantizer
+# ------------------------------------------------------------------------------------------
+
+def measure_prefill(B: int, Tq: int, steps: int, warmup: int, dev: torch.device) -> dict:
+    """Config 3: Tq queries x 131072 keys, Qwen3-8B shapes. A step = per-token query quantisation + int8 block
+    scoring + top-32 blocks per (b, KV head, query); the scorer is also timed alone in both tcgen05 encodings."""
     from kv_cache_b200 import inputs, ops
 
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    B, Hq, Hkv, D, Tq, Tk, C, top_blocks = args.batch or 2, 32, 8, 128, args.queries, 131072, 64, 32
+    Hq, Hkv, D, Tk, C, top_blocks = 32, 8, 128, 131072, 64, 32
     w = inputs.Workload("c3_qwen3-8b_prefill_b%d_tq%d_tk131072_c64_blk64_top32" % (B, Tq), B, Hq, Hkv, D, Tk, C, 0, seed=3)
     key, _ = inputs.make_kv(w, dev, 0, Tk)
     ch = ops.choose_channels(key, C)
@@ -258,29 +482,62 @@ def run_prefill_gpu(args) -> None:
             bs = ops.score_prefill_blocks(qc, qs, packed, scale, Tk)
             return ops.block_topk(bs, top_blocks), qc, qs
 
-        for _ in range(max(3, args.warmup)):
+        for _ in range(max(3, warmup)):
             idx, qc, qs = step()
         sampler = ClockSampler(dev.index or 0)
         sampler.start()
-        ms_step = event_time_ms(step, args.steps, stream)
-        ms_score = event_time_ms(lambda: ops.score_prefill_blocks(qc, qs, packed, scale, Tk), args.steps, stream)
+        ms_step = event_time_ms(step, steps, stream)
+        kernel_ms = {e: event_time_ms(lambda e=e: ops.score_prefill_blocks(qc, qs, packed, scale, Tk, engine=e), steps, stream)
+                     for e in ("f16", "i8")}
         clocks = sampler.stop()
     ops_total = 2.0 * B * Hq * Tq * Tk * C
+    best = min(kernel_ms, key=kernel_ms.get)
+    return {"workload": w.name, "ms_per_step": ms_step, "tops": ops_total / (ms_step * 1e-3) / 1e12,
+            "engine": "f16 (default: the same integers as fp16 operands, fp32 accumulators in tensor memory; "
+                      "i8 = int8 operands, int32 accumulators; identical bits)",
+            "kernel_ms": kernel_ms, "kernel_tops": {e: ops_total / (v * 1e-3) / 1e12 for e, v in kernel_ms.items()},
+            "frac_of_nominal_int8_peak": ops_total / (kernel_ms[best] * 1e-3) / 1e12 / 4500.0, "clocks": clocks,
+            "int8_ops": ops_total, "steps": steps}
+
+
+def run_prefill_gpu(args) -> None:
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B = args.batch or 2
+    r = measure_prefill(B, args.queries, args.steps, args.warmup, dev)
     line = {
-        "metric": "int8 TOPS, chunked-prefill block scoring", "value": ops_total / (ms_step * 1e-3) / 1e12,
-        "unit": "TOPS", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+        "metric": "int8 TOPS, chunked-prefill block scoring", "value": r["tops"],
+        "unit": "TOPS", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": r["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4->int8, int32 accumulate",
         "data": "synthetic",
-        "config": {"workload": w.name, "batch": B, "q_heads": Hq, "kv_heads": Hkv, "queries": Tq, "keys": Tk,
-                   "partial_channels": C, "block": 64, "top_blocks": top_blocks},
-        "clocks": clocks, "gpu_launches": 3 * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "score_prefill_tc_kernel (tcgen05, engine %s)" % os.environ.get("KVB_PREFILL_ENGINE", "f16"),
-                     "achieved": ops_total / (ms_score * 1e-3) / 1e12,
-                     "peak": 4500.0, "unit": "TOPS", "frac": ops_total / (ms_score * 1e-3) / 1e12 / 4500.0,
-                     "peak_source": "nominal dense int8 (no measured int8 peak on this pool)", "kernel_ms": ms_score,
+        "config": {"workload": r["workload"], "batch": B, "q_heads": 32, "kv_heads": 8, "queries": args.queries,
+                   "keys": 131072, "partial_channels": 64, "block": 64, "top_blocks": 32, "engine": r["engine"]},
+        "clocks": r["clocks"], "gpu_launches": 3 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "score_prefill_tc_kernel (tcgen05)",
+                     "achieved": max(r["kernel_tops"].values()), "peak": 4500.0, "unit": "TOPS",
+                     "frac": r["frac_of_nominal_int8_peak"],
+                     "peak_source": "nominal dense int8 (no measured int8 peak on this pool)", "kernel_ms": r["kernel_ms"],
                      "note": "K = 64: every accumulator element is drained from tensor memory after only 64 MACs; the kernel is bound by that drain and the per-element scale+max, not by the MMAs"},
     }
     print(json.dumps(line), flush=True)
+
+
+def measure_quantize(dev: torch.device) -> dict:
+    """Bulk quantize/pack of 4 GiB of bf16 K (config 2's cache of one layer), CUDA events."""
+    from kv_cache_b200 import ops
+
+    B, Hkv, T, D, C = 16, 8, 131072, 128, 64
+    key = torch.empty((B, Hkv, T, D), dtype=torch.bfloat16, device=dev).normal_()
+    ch = torch.arange(0, 2 * C, 2, dtype=torch.int32, device=dev).repeat(Hkv, 1)
+    packed, scale = ops.alloc_side_cache(B, Hkv, T, C, dev)
+    stream = torch.cuda.current_stream(dev)
+    for _ in range(3):
+        ops.quantize(key, ch, out=(packed, scale))
+    ms = event_time_ms(lambda: ops.quantize(key, ch, out=(packed, scale)), 10, stream)
+    nbytes = B * Hkv * T * (2 * D + C // 2 + 4)
+    peak, _ = hbm_peak()
+    return {"ms": ms, "bytes": nbytes, "gb_per_s": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak,
+            "what": "kvb_quantize_pack over bf16 K [16,8,131072,128] -> int4 codes on 64 channels + fp32 scales"}
 
 
 def main() -> None:
@@ -291,6 +548,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the config 4 / config 3 / quantizer block of the default run")
     ap.add_argument("--queries", type=int, default=4096, help="query chunk length of the prefill workload (c3)")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's batch (smaller device footprint for profiler captures)")
@@ -307,18 +565,16 @@ def main() -> None:
         return
     w = inputs.WORKLOADS[name]
     if args.batch:
-        import dataclasses
         w = dataclasses.replace(w, batch=args.batch, name=f"{w.name}_batch{args.batch}")
     if args.impl == "reference":
         run_reference_arm(args, w)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
-    if args.gpus == 1:
-        run_single_gpu(args, w)
+    if args.gpus == 1 and name != "c4":
+        run_single_gpu(args, w, with_secondary=(args.workload is None and not args.batch and not args.no_secondary))
     else:
-        from kv_cache_b200 import sharded
-        sharded.bench_main(args, w)
+        run_sharded(args, w)
 
 
 if __name__ == "__main__":

@@ -7,7 +7,7 @@
  *   - validates shapes, strides and alignment on the host and returns a kvb_status
  *     BEFORE anything is launched when they are wrong,
  *   - never allocates, never frees, never synchronises the device, never throws
- *     (the one exception, kvb_device_status, says so).
+ *     (the exceptions, kvb_device_status and kvb_exchange_alloc / _free, say so).
  *
  * Tensor naming: B batch, Hq query heads, Hkv KV heads, G = Hq / Hkv, D head dim (128),
  * T cached ("history") tokens, C partial channels (even, <= 128), k top-k, S length of a
@@ -318,6 +318,74 @@ int kvb_merge_candidates(const uint64_t* gathered, int N, int R, int kk, int top
                          int prefix_k, int32_t* out_idx,
                          int64_t own_base, int64_t own_limit, int32_t* out_owned, int32_t* out_owned_count,
                          int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Sequence-sharded decode step without a collective call (no counterpart in the reference, which
+ * has no sharding). Rank r of `world` owns the history tokens [id_offset, id_offset + t_local) of
+ * every sequence (bf16 K/V rows and the int4 side cache); query, channel list and the decoded
+ * token's K/V row are replicated. One call enqueues the whole step on `stream`:
+ *   phase 1  sample -> candidate scorer -> exact local top-k; the last kernel stores its
+ *            min(top_k, 8192/world) best (score, global id) composites per (batch, KV head) into
+ *            EVERY rank's exchange buffer with ordinary 8-byte stores over NVLink and then raises a
+ *            per-(source rank, row) flag there (st.release.sys);
+ *   phase 2  global merge: waits for the `world` flags of its row (bounded polling), selects the
+ *            global top-k from its LOCAL buffer with the acceptance test of kvb_merge_candidates
+ *            (a row that fails it reads the ranks' whole lists with plain loads from their
+ *            memory), compacts the winners this rank owns; attention over those rows; the chunk
+ *            merge stores the un-normalised (o, m, l) of every (batch, head) into every rank's
+ *            buffer and raises a second flag;
+ *   phase 3  waits for the `world` partial flags and combines them by log-sum-exp into `out`
+ *            (the same bits on every rank).
+ * The flags carry a step number kept in the exchange buffer, so the same call sequence can be
+ * captured once in a CUDA graph and replayed. Every wait gives up after wait_polls polls (0 = a few
+ * seconds' worth), sets KVB_TIMEOUT in the device status word and lets the kernel return. Only plain
+ * loads and stores touch peer memory.
+ *
+ * All ranks must call with the same B, Hq, Hkv, top_k, world and take the same number of steps.
+ * Needs the streaming scorer configuration (C in {32,64,128}, G in {1,2,4,8}, aligned side cache),
+ * 3 * top_k <= 16384 and top_k <= t_local on every rank; otherwise KVB_BAD_SHAPE and the caller
+ * composes the step from the operators above around its own all-gathers.
+ *
+ * Exchange buffers. kvb_exchange_alloc / kvb_exchange_free are the only entry points of this
+ * library that allocate device memory (cudaMalloc / cudaFree, zero-filled, synchronising): call
+ * them at set-up. Each rank allocates kvb_sharded_exchange_bytes(...) bytes, publishes the 64-byte
+ * handle to its peers (any host transport), and maps theirs with kvb_exchange_open (CUDA IPC with
+ * lazy peer access; the owning device may differ from `device`). exchange[r] in the parameters is
+ * rank r's buffer as mapped in the calling process; exchange[rank] is the local allocation.
+ *
+ * `phases` (bit 0, 1, 2 = phase 1, 2, 3; 7 = the whole step) exists so that several ranks can be
+ * stepped from ONE process on one GPU, phase by phase (all ranks' phase 1, then all ranks' phase
+ * 2, ...): kernels that wait for each other must never be queued behind one another on one GPU.
+ * ------------------------------------------------------------------------------------- */
+typedef struct kvb_sharded_step_params {
+  const void* query;  int64_t q_sb, q_sh;                 /* bf16 [B,Hq,D]                         */
+  const void* key;    int64_t k_sb, k_sh, k_st;           /* bf16 [B,Hkv,t_local+1,D]: the shard's   */
+  const void* value;  int64_t v_sb, v_sh, v_st;           /* rows, then the decoded token's row     */
+  const uint8_t* packed; int64_t packed_sb, packed_sh;    /* int4 cache of the shard's rows         */
+  const float* scale;    int64_t scale_sb, scale_sh;
+  const int32_t* channel_idx;                             /* int32 [Hkv,C]                          */
+  int B, Hq, Hkv, D, C;
+  int t_local;                                            /* history tokens this rank owns          */
+  int64_t id_offset;                                      /* global id of local row 0               */
+  int64_t total_tokens;                                   /* global history length                  */
+  int top_k;
+  int rank, world;
+  float scaling;
+  void* out;                                              /* bf16 [B,1,Hq,D] (phase 3)              */
+  int32_t* sel_idx_out;                                   /* int32 [B*Hkv,top_k] global ids, any order, or NULL */
+  void* workspace; size_t workspace_bytes;                /* kvb_sharded_step_workspace_bytes       */
+  void* exchange[8]; size_t exchange_bytes;               /* see above                              */
+  int phases;
+  unsigned wait_polls;
+} kvb_sharded_step_params;
+
+size_t kvb_sharded_exchange_bytes(int B, int Hq, int Hkv, int top_k, int world);
+size_t kvb_sharded_step_workspace_bytes(int B, int Hq, int Hkv, int t_local, int top_k);
+int kvb_exchange_alloc(size_t bytes, int device, void** out_ptr, void* out_handle /* 64 bytes */);
+int kvb_exchange_open(const void* handle /* 64 bytes */, int device, void** out_ptr);
+int kvb_exchange_close(void* ptr, int device);
+int kvb_exchange_free(void* ptr, int device);
+int kvb_sharded_decode_step(const kvb_sharded_step_params* p, int device, void* stream);
 
 /* Combine N shard partials [N,B,Hq,D+2] (layout of out_partial above) into bf16 [B,1,Hq,D]:
  * o = sum_r e^{m_r-m} o_r / sum_r e^{m_r-m} l_r, shards with l == 0 ignored. No reference

@@ -52,6 +52,27 @@ class DecodeStepParams(C.Structure):
     ]
 
 
+class ShardedStepParams(C.Structure):
+    """Mirror of struct kvb_sharded_step_params."""
+
+    _fields_ = [
+        ("query", _p), ("q_sb", _i64), ("q_sh", _i64),
+        ("key", _p), ("k_sb", _i64), ("k_sh", _i64), ("k_st", _i64),
+        ("value", _p), ("v_sb", _i64), ("v_sh", _i64), ("v_st", _i64),
+        ("packed", _p), ("packed_sb", _i64), ("packed_sh", _i64),
+        ("scale", _p), ("scale_sb", _i64), ("scale_sh", _i64),
+        ("channel_idx", _p),
+        ("B", _i), ("Hq", _i), ("Hkv", _i), ("D", _i), ("C", _i),
+        ("t_local", _i), ("id_offset", _i64), ("total_tokens", _i64),
+        ("top_k", _i), ("rank", _i), ("world", _i),
+        ("scaling", _f),
+        ("out", _p), ("sel_idx_out", _p),
+        ("workspace", _p), ("workspace_bytes", _sz),
+        ("exchange", _p * 8), ("exchange_bytes", _sz),
+        ("phases", _i), ("wait_polls", C.c_uint),
+    ]
+
+
 # name -> (restype, argtypes); every symbol declared in include/kvcache_b200.h
 SIGNATURES = {
     "kvb_version": (_i, []),
@@ -85,6 +106,13 @@ SIGNATURES = {
     "kvb_shard_candidates": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
                                   _i, _i, _i, _i, _i, _i, _i, _i, _i64, _p, _p, _sz, _i, _p]),
     "kvb_merge_candidates": (_i, [_p, _i, _i, _i, _i, _i64, _i, _p, _i64, _i64, _p, _p, _i, _p]),
+    "kvb_sharded_exchange_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "kvb_sharded_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "kvb_exchange_alloc": (_i, [_sz, _i, C.POINTER(_p), _p]),
+    "kvb_exchange_open": (_i, [_p, _i, C.POINTER(_p)]),
+    "kvb_exchange_close": (_i, [_p, _i]),
+    "kvb_exchange_free": (_i, [_p, _i]),
+    "kvb_sharded_decode_step": (_i, [C.POINTER(ShardedStepParams), _i, _p]),
     "kvb_lse_merge": (_i, [_p, _i, _i, _i, _i, _p, _i, _p]),
     "kvb_quantize_query_tokens": (_i, [_p, _i64, _i64, _i64, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     "kvb_score_prefill_blocks": (_i, [_p, _p, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),

@@ -6,10 +6,15 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
 
 #include "../../include/kvcache_b200.h"
 
 namespace kvb {
+
+constexpr int KVB_MAX_DEVICES = 64;              // device ordinals the per-device set-up tables cover
 
 // ---- host side -------------------------------------------------------------------------
 
@@ -44,14 +49,26 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Number of SMs of a device (cached per device ordinal).
 inline int sm_count(int device) {
-  static int cached[64] = {0};
-  if (device < 0 || device >= 64) return 148;
-  if (cached[device] == 0) {
-    int n = 0;
+  static std::atomic<int> cached[KVB_MAX_DEVICES];
+  if (device < 0 || device >= KVB_MAX_DEVICES) return 148;
+  int n = cached[device].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
-    cached[device] = n;
+    cached[device].store(n, std::memory_order_relaxed);
   }
-  return cached[device];
+  return n;
+}
+
+// Opts `kern` into `bytes` of dynamic shared memory once per device (which must be current). `done` is the
+// call site's own table of KVB_MAX_DEVICES flags; concurrent first calls only repeat an idempotent attribute call.
+template <typename K>
+static inline int ensure_dynamic_smem(K kern, std::atomic<bool>* done, int device, size_t bytes) {
+  if (device < 0 || device >= KVB_MAX_DEVICES) return KVB_BAD_DEVICE;
+  if (!done[device].load(std::memory_order_acquire)) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    done[device].store(true, std::memory_order_release);
+  }
+  return KVB_OK;
 }
 
 // Sticky device status word. The library is built as ONE translation unit (kvcache_b200.cu
@@ -169,6 +186,67 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+
+// ---- exchange between the ranks of a sequence-sharded step (plain loads/stores over NVLink) ------
+// A rank publishes data into a buffer that lives in ANOTHER rank's memory (mapped into this process),
+// then raises a flag there; the consumer polls its own local flag and reads its own local memory.
+// Flags carry the step number, so nothing is ever cleared.
+constexpr int KVB_MAX_RANKS = 8;
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait for *flag == want: gives up after `limit` polls, records KVB_TIMEOUT in the sticky status
+// word and returns false; the caller must then finish without using the data the flag guards.
+__device__ __forceinline__ bool wait_flag_bounded(const uint32_t* flag, uint32_t want, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (ld_acquire_sys_u32(flag) == want) return true;
+    __nanosleep(128);
+  }
+  atomicExch(&g_device_status, (int)KVB_TIMEOUT);
+  return false;
+}
+constexpr uint32_t KVB_DEFAULT_WAIT_POLLS = 1u << 22;       // a few seconds at ~1 us per poll
+
+// Producer side of the candidate exchange (local top-k kernel): the `prefix` best composites of every row
+// go to slot [rank, row, 0..prefix) of every rank's inbox, then flag [rank, row] of that rank is set.
+struct PeerPush {
+  int n = 0;                              // ranks; 0 = no exchange
+  int rank = 0;
+  int prefix = 0;                         // entries per (rank, row) slot
+  uint64_t* inbox[KVB_MAX_RANKS] = {};    // rank q's inbox  uint64 [n, R, prefix]
+  uint32_t* flags[KVB_MAX_RANKS] = {};    // rank q's flags  uint32 [n, R]
+  const uint32_t* epoch = nullptr;        // this rank's step counter
+};
+// Consumer side (global merge kernel): waits for flags [s, row] == epoch for every rank s, then reads the
+// local inbox; `full[s]` is rank s's whole local list uint64 [R, full_len] (peer memory, read only when the
+// prefixes cannot decide a row).
+struct PeerWait {
+  int n = 0;
+  const uint32_t* flags = nullptr;        // local, uint32 [n, R]
+  const uint32_t* epoch = nullptr;
+  uint32_t limit = KVB_DEFAULT_WAIT_POLLS;
+  const uint64_t* full[KVB_MAX_RANKS] = {};
+  int full_len = 0;
+};
+// The same for the attention partials fp32 [n, B*Hq, D+2], one flag per (rank, batch, query head).
+struct PartialPush {
+  int n = 0, rank = 0;
+  float* inbox[KVB_MAX_RANKS] = {};
+  uint32_t* flags[KVB_MAX_RANKS] = {};
+  const uint32_t* epoch = nullptr;
+};
+struct PartialWait {
+  int n = 0;
+  const uint32_t* flags = nullptr;        // local, uint32 [n, B*Hq]
+  const uint32_t* epoch = nullptr;
+  uint32_t limit = KVB_DEFAULT_WAIT_POLLS;
+};
 
 // ---- programmatic dependent launch ------------------------------------------------------------
 // Inside a chain of kernels on one stream the next kernel may be made resident while the current

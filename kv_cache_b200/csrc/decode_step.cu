@@ -21,9 +21,14 @@ namespace kvb {
 constexpr int FS_THREADS = 512;
 constexpr int FS_RUNS = 32;                    // evenly spaced runs of sampled tokens per row
 constexpr int FS_PER_THREAD = 8;                // sampled tokens per thread for rows up to FS_LONG_ROW (4096 per row) ...
-constexpr int FS_PER_THREAD_LONG = 16;          // ... and beyond it (8192 per row), loaded four at a time
+constexpr int FS_PER_THREAD_LONG = 16;          // ... beyond it (8192 per row) ...
+constexpr int FS_PER_THREAD_MAX = 32;           // ... and beyond twice that (16384 per row); loaded four at a time
 constexpr int FS_LONG_ROW = 262144;
-__host__ __device__ inline int fs_per_thread(int T) { return T > FS_LONG_ROW ? FS_PER_THREAD_LONG : FS_PER_THREAD; }
+// (the sample stays at least 1/64 of the row up to a million tokens, so the rank that sets the threshold stays
+// near 1.75 k / 64 and its relative spread near 10 %)
+__host__ __device__ inline int fs_per_thread(int T) {
+  return T > 2 * FS_LONG_ROW ? FS_PER_THREAD_MAX : (T > FS_LONG_ROW ? FS_PER_THREAD_LONG : FS_PER_THREAD);
+}
 
 struct SampleParams {
   ScoreParams sp;             // query / packed / scale / channels / shapes (outputs unused)
@@ -38,6 +43,7 @@ struct SampleParams {
   const uint4* new_k; const uint4* new_v;
   __nv_bfloat16* key; int64_t k_sb, k_sh, k_st;
   __nv_bfloat16* value; int64_t v_sb, v_sh, v_st;
+  uint32_t* step_counter = nullptr;   // optional: CTA 0 adds one (the step number of the sequence-sharded exchange)
 };
 
 template <int C, int G>
@@ -51,6 +57,7 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   const int row = blockIdx.x, tid = threadIdx.x;
   pdl_launch_dependents();                      // the scorer may become resident and prepare its query codes
   pdl_wait();
+  if (q.step_counter && row == 0 && tid == 33) *q.step_counter += 1;
   if (q.zero_count && tid == 0) q.zero_count[(int64_t)row * SC_COUNT_STRIDE] = 0;
   if (q.zero_failed && tid == 32) q.zero_failed[row] = 0;
   const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
@@ -117,7 +124,7 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
     s_qhi[hd][w] = (int)hi;
   }
   __syncthreads();
-  float v[FS_PER_THREAD_LONG];
+  float v[FS_PER_THREAD_MAX];
 #pragma unroll 1
   for (int e0 = 0; e0 < per_thread; e0 += 4) {
     load_batch(e0, wv, ks);
@@ -228,10 +235,11 @@ static void fill_score_params(ScoreParams& sp, const void* query, int64_t q_sb, 
 
 static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cudaStream_t st,
                       uint32_t* zero_count = nullptr, uint32_t* zero_failed = nullptr,
-                      const kvb_decode_step_params* rows = nullptr) {
+                      const kvb_decode_step_params* rows = nullptr, uint32_t* step_counter = nullptr) {
   SampleParams sq;
   sq.sp = sp; sq.tau = tau; sq.top_k = top_k; sq.cap = cap;
   sq.zero_count = zero_count; sq.zero_failed = zero_failed;
+  sq.step_counter = step_counter;
   sq.new_k = nullptr; sq.new_v = nullptr; sq.key = nullptr; sq.value = nullptr;
   sq.k_sb = sq.k_sh = sq.k_st = sq.v_sb = sq.v_sh = sq.v_st = 0;
   if (rows && rows->new_key_row) {
@@ -475,56 +483,6 @@ extern "C" __attribute__((visibility("default"))) size_t kvb_shard_candidates_wo
                                                                                               int top_k) {
   if (B <= 0 || Hkv <= 0 || T <= 0 || top_k <= 0) return 0;
   return kvb::shard_layout(B, Hkv, T, top_k).bytes;
-}
-
-extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
-    const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
-    const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
-    int D, int C, int top_k, int split_k, int64_t id_offset, uint64_t* out_comp, void* workspace,
-    size_t workspace_bytes, int device, void* stream) {
-  using namespace kvb;
-  if (!query || !packed || !scale || !channel_idx || !out_comp || !workspace) return KVB_BAD_ARG;
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || top_k <= 0 || split_k < 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
-  if (id_offset < 0 || id_offset + T > 0x7fffffffLL) return KVB_BAD_SHAPE;
-  if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
-  const ShardLayout L = shard_layout(B, Hkv, T, top_k);
-  if (workspace_bytes < L.bytes) return KVB_WORKSPACE_TOO_SMALL;
-  if (!fast_front_ok(C, Hq / Hkv, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, T, L.kk, L.cap))
-    return KVB_BAD_SHAPE;
-  DeviceGuard guard(device);
-  if (!guard.ok) return KVB_BAD_DEVICE;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-  uint32_t* count = reinterpret_cast<uint32_t*>(ws + L.off_count);
-  float* tau = reinterpret_cast<float*>(ws + L.off_tau);
-  uint64_t* cand = reinterpret_cast<uint64_t*>(ws + L.off_cand);
-  float* gmax = reinterpret_cast<float*>(ws + L.off_gmax);
-
-  ScoreParams base;
-  fill_score_params(base, query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B,
-                    Hq, Hkv, T, D, C, nullptr);
-  int rc = sample_run(base, tau, top_k, L.cap, st, count, reinterpret_cast<uint32_t*>(ws + L.off_failed));
-  if (rc != KVB_OK) return rc;
-  ScoreEmit emit{tau, cand, count, L.cap};
-  rc = score_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B, Hq, Hkv, T,
-                 D, C, nullptr, nullptr, nullptr, nullptr, &emit, nullptr, device, st);
-  if (rc != KVB_OK) return rc;
-  SelectParams sp;
-  sp.scores = gmax; sp.row_stride = T; sp.payload = nullptr;
-  sp.R = L.R; sp.T = T; sp.k = top_k; sp.kk = L.kk; sp.idx_offset = id_offset;
-  sp.out_idx32 = nullptr; sp.out_idx64 = nullptr; sp.out_scores = nullptr; sp.out_comp = out_comp;
-  sp.hist = nullptr; sp.cand = cand; sp.cand_count = count; sp.cap = L.cap;
-  sp.tokens_per_cta = 0; sp.thresholds = nullptr;
-  sp.order_by_index = 2; sp.use_bitmap = 0;
-  sp.from_candidates = 1; sp.row_failed = nullptr; sp.T_dev = nullptr;
-  sp.gather = nullptr; sp.gather_n = 0; sp.gather_len = 0; sp.gather_stride = 0;
-  sp.rescue = 1; sp.rescue_sp = base;
-  sp.split_k = split_k;
-  const size_t smem = (size_t)L.cap * 8 + SEL_FINAL_FIXED_SMEM;
-  { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
-  select_final_kernel<<<L.R, SEL_FINAL_THREADS, smem, st>>>(sp);
-  KVB_CHECK_CUDA(cudaGetLastError());
-  return KVB_OK;
 }
 
 extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(

@@ -7,6 +7,7 @@
 #include "select_topk.cu"
 #include "sparse_attend.cu"
 #include "decode_step.cu"
+#include "sharded_step.cu"
 #include "score_prefill_tc.cu"
 #include "score_prefill.cu"
 #include "qabs_fp32.cu"

@@ -422,11 +422,8 @@ static int score_stream_launch(const ScoreParams& p0, int device, cudaStream_t s
   p.total_units = (int64_t)p.B * p.Hkv * p.units_per_row;
   const size_t smem = score_stream_smem_bytes<C, G, NS, MODE>();
   auto kern = score_decode_stream_kernel<C, G, NS, MODE>;
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_done[device] = true;
-  }
+  static std::atomic<bool> attr_done[KVB_MAX_DEVICES];
+  { const int arc = ensure_dynamic_smem(kern, attr_done, device, (size_t)smem); if (arc != KVB_OK) return arc; }
   int per_sm = (int)((227 * 1024) / (smem + 1024));
   if (per_sm < 1) per_sm = 1;
   if (per_sm > 2) per_sm = 2;

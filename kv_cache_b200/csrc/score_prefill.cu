@@ -495,12 +495,8 @@ extern "C" __attribute__((visibility("default"))) int kvb_block_topk(const float
     return KVB_OK;
   }
   const size_t smem = sizeof(float) * (size_t)BT_WARPS * nblk;
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(block_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)(sizeof(float) * BT_WARPS * BT_MAX_T)));
-    attr_done[device] = true;
-  }
+  static std::atomic<bool> attr_done[KVB_MAX_DEVICES];
+  { const int arc = ensure_dynamic_smem(block_topk_kernel, attr_done, device, (size_t)(sizeof(float) * BT_WARPS * BT_MAX_T)); if (arc != KVB_OK) return arc; }
   block_topk_kernel<<<(unsigned)((R + BT_WARPS - 1) / BT_WARPS), BT_WARPS * 32, smem,
                       reinterpret_cast<cudaStream_t>(stream)>>>(block_scores, row_stride, R, nblk, k, out_idx, out_scores);
   KVB_CHECK_CUDA(cudaGetLastError());

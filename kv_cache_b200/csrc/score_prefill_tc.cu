@@ -492,11 +492,8 @@ static int prefill_tc_launch(const PrefillTcParams& p, int device, cudaStream_t 
   using Cfg = TcCfg<C, KIND>;
   static_assert(Cfg::BYTES <= 227 * 1024, "shared memory budget");
   auto kern = score_prefill_tc_kernel<C, G, KIND>;
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::BYTES));
-    attr_done[device] = true;
-  }
+  static std::atomic<bool> attr_done[KVB_MAX_DEVICES];
+  { const int arc = ensure_dynamic_smem(kern, attr_done, device, (size_t)Cfg::BYTES); if (arc != KVB_OK) return arc; }
   constexpr int QCTA = TC_QT * (128 / G);
   dim3 grid(ceil_div(p.Tq, QCTA), p.B * p.Hkv);
   kern<<<grid, TC_THREADS, Cfg::BYTES, st>>>(p);

@@ -14,8 +14,6 @@
 // When a row has more than CAP candidates after step 2 (heavy ties, e.g. constant scores) the
 // last kernel first refines the prefix with 11-bit passes over the row itself until the
 // candidate set fits; that path is slower but exact for any input.
-#include <atomic>
-
 #include "common.cuh"
 #include "score_common.cuh"
 
@@ -74,6 +72,13 @@ struct SelectParams {
   int32_t* out_owned_count = nullptr;
   int64_t own_base = 0, own_limit = 0;
   int common_start = 1;       // start the on-chip select below the common key prefix of the candidates
+  // Sequence-sharded step without a collective: the local top-k kernel PUSHES its best entries into every
+  // rank's inbox (push.n > 0, unordered output with split_k == push.prefix or push.prefix >= kk); the merge
+  // kernel WAITS for all ranks' flags (wait.n > 0) and then selects from its local inbox (`gather`, rows
+  // gather_pitch apart), falling back to the ranks' whole lists (wait.full) for a row its prefixes cannot decide.
+  int gather_pitch = 0;       // row pitch of a segment in `gather`; 0 = gather_len
+  PeerPush push;
+  PeerWait wait;
 };
 
 __device__ __forceinline__ uint32_t element_index(const SelectParams& p, int row, int64_t t) {
@@ -364,14 +369,17 @@ __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
 // One CTA per row: candidates -> exact k-th composite -> the k winners in the requested order.
 __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectParams pin) {
   // the row length (and with it the count to select) may live on the device
-  SelectParams p = pin;
+  // (the parameters stay in constant memory: a modifiable copy would live on the thread's stack because
+  // the rank tables are indexed at run time; only the two values that can change are held in registers)
+  const SelectParams& p = pin;
   const int out_pitch = pin.kk;                         // rows of the outputs stay kk_max apart
+  int rT = pin.T, rkk = pin.kk;
   pdl_launch_dependents();
   pdl_wait();
   if (p.T_dev) {
     const int t = *p.T_dev;
-    p.T = t < pin.T ? t : pin.T;
-    p.kk = p.k < p.T ? p.k : p.T;
+    rT = t < pin.T ? t : pin.T;
+    rkk = p.k < rT ? p.k : rT;
   }
   extern __shared__ __align__(16) uint8_t sel_smem[];
   uint64_t* s_cand = reinterpret_cast<uint64_t*>(sel_smem);                     // [cap]
@@ -383,14 +391,37 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
+  const bool peer = p.wait.n > 0;
+  uint32_t epoch = 0;
+  if (p.push.n > 0) epoch = *p.push.epoch;
+  if (peer) {
+    // every rank's best entries for this row must have landed in the local inbox
+    // (the arrival word lives in the dynamic area: this kernel may ask for all the shared memory there is,
+    // which leaves no room for a static variable)
+    epoch = *p.wait.epoch;
+    volatile uint32_t* s_arrived = s_count + 7;
+    if (tid == 0) *s_arrived = 1;
+    __syncthreads();
+    if (tid < p.wait.n && !wait_flag_bounded(p.wait.flags + (int64_t)tid * p.R + row, epoch, p.wait.limit)) *s_arrived = 0;
+    __syncthreads();
+    const bool arrived = *s_arrived != 0;
+    __syncthreads();
+    if (!arrived) {                                     // gave up (status word set): this row selects nothing
+      if (tid == 0 && p.out_owned_count) p.out_owned_count[row] = 0;
+      return;
+    }
+  }
   const float* src = p.scores ? p.scores + (int64_t)row * p.row_stride : nullptr;
   const bool gathered = p.gather_n > 0;
-  const int64_t n_src = gathered ? (int64_t)p.gather_n * p.gather_len : (int64_t)p.T;     // elements of the row
+  const int gpitch = p.gather_pitch > 0 ? p.gather_pitch : p.gather_len;
+  const int64_t n_src = gathered ? (int64_t)p.gather_n * p.gather_len : (int64_t)rT;     // elements of the row
   // composite of element t of this row, whatever the source
   auto load_comp = [&](int64_t t) -> uint64_t {
     if (gathered) {
       const int64_t seg = t / p.gather_len;
-      return __ldcg(p.gather + seg * p.gather_stride + (int64_t)row * p.gather_len + (t - seg * p.gather_len));
+      const int64_t off = (int64_t)row * p.gather_len + (t - seg * p.gather_len);
+      // whole lists: a slice of the all-gathered buffer, or (peer exchange) the list in rank seg's own memory
+      return peer ? __ldcg(p.wait.full[seg] + off) : __ldcg(p.gather + seg * p.gather_stride + off);
     }
     return make_composite(src[t], element_index(p, row, t));
   };
@@ -403,9 +434,9 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   bool have_candidates;
   uint64_t kth;
   const uint64_t* cand = p.cand ? p.cand + (int64_t)row * p.cap : nullptr;
-  bool prefix_mode = gathered && p.gather_prefix > 0 && p.gather_prefix < p.gather_len &&
+  bool prefix_mode = gathered && p.gather_prefix > 0 && (peer || p.gather_prefix < p.gather_len) &&
                      p.gather_n <= SEL_MAX_SEGMENTS && (int64_t)p.gather_n * p.gather_prefix <= (int64_t)p.cap &&
-                     (int64_t)p.gather_n * p.gather_prefix >= (int64_t)p.kk;
+                     (int64_t)p.gather_n * p.gather_prefix >= (int64_t)rkk;
 again:
   if (prefix_mode) {
     // The best gather_prefix entries of every segment, all on chip; the smallest of each prefix is kept
@@ -415,12 +446,12 @@ again:
     n = p.gather_n * p.gather_prefix;
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
       const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
-      const uint64_t c = __ldcg(p.gather + (int64_t)seg * p.gather_stride + (int64_t)row * p.gather_len + j);
+      const uint64_t c = __ldcg(p.gather + (int64_t)seg * p.gather_stride + (int64_t)row * gpitch + j);
       s_cand[i] = c;
       atomicMin(&s_segmin[seg], (unsigned long long)c);
     }
     __syncthreads();
-    prefix = 0; fixed = 0; need = (uint32_t)p.kk; in_prefix = (uint32_t)n;
+    prefix = 0; fixed = 0; need = (uint32_t)rkk; in_prefix = (uint32_t)n;
     have_candidates = true;
   } else if (gathered) {
     // All-gathered shard lists: up to gather_n * gather_len composites, far more than fit on chip. The
@@ -428,14 +459,14 @@ again:
     // i.i.d. shard lists under the capacity) and then collects the survivors.
     // (Dropping everything below "max over segments of the segment minimum" is exact but useless here:
     // each shard's worst entry lies far below the global k-th one.)
-    prefix = 0; fixed = 0; need = (uint32_t)p.kk; in_prefix = (uint32_t)n_src;
+    prefix = 0; fixed = 0; need = (uint32_t)rkk; in_prefix = (uint32_t)n_src;
     have_candidates = false;
   } else if (p.from_candidates) {
-    prefix = 0; fixed = 0; need = (uint32_t)p.kk;
+    prefix = 0; fixed = 0; need = (uint32_t)rkk;
     bool failed = p.row_failed != nullptr && p.row_failed[row] != 0;
     if (p.rescue && !failed) {
       const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
-      if (have < (uint32_t)p.kk || have > (uint32_t)p.cap) {
+      if (have < (uint32_t)rkk || have > (uint32_t)p.cap) {
         // the sampled threshold missed its bounds for this row: score the whole row again, exactly
         const ScoreParams& sp = p.rescue_sp;
         float* r_qv = reinterpret_cast<float*>(s_cand);                    // scratch inside the (still unused) candidate area
@@ -444,7 +475,7 @@ again:
         const int rb = row / sp.Hkv, rg = row - rb * sp.Hkv;
         quantize_query_group<SEL_FINAL_THREADS>(sp, rb, rg, sp.G, r_qv, r_qcode, r_qscale);
         float* dst = const_cast<float*>(src);
-        for (int64_t t = tid; t < p.T; t += SEL_FINAL_THREADS)
+        for (int64_t t = tid; t < rT; t += SEL_FINAL_THREADS)
           dst[t] = score_token_plain<SC_MAX_G>(sp, sp.G, rb, rg, t, r_qcode, r_qscale);
         __syncthreads();
         failed = true;
@@ -452,7 +483,7 @@ again:
     }
     have_candidates = !failed;
     if (failed) {
-      in_prefix = (uint32_t)p.T;
+      in_prefix = (uint32_t)rT;
     } else {
       const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
       n = (int)(have < (uint32_t)p.cap ? have : (uint32_t)p.cap);
@@ -462,7 +493,7 @@ again:
     }
   } else {
     const uint4 thr = p.thresholds[row];
-    prefix = thr.x; fixed = SEL_HIST_BITS; need = (uint32_t)p.kk - thr.y; in_prefix = thr.z;
+    prefix = thr.x; fixed = SEL_HIST_BITS; need = (uint32_t)rkk - thr.y; in_prefix = thr.z;
     have_candidates = thr.y + thr.z <= (uint32_t)p.cap;
     if (have_candidates) {
       n = (int)(thr.y + thr.z);
@@ -474,7 +505,7 @@ again:
   }
   if (!have_candidates) {
     // Too many candidates share the prefix (or none were prepared): refine over the row itself.
-    while ((uint32_t)p.kk - need + in_prefix > (uint32_t)p.cap && fixed < 64) {
+    while ((uint32_t)rkk - need + in_prefix > (uint32_t)p.cap && fixed < 64) {
       const int width = (64 - fixed) >= 11 ? 11 : (64 - fixed);
       const int shift = 64 - fixed - width;
       const int nb = 1 << width;
@@ -571,7 +602,8 @@ again:
     // itself no winner-beating value (<= kth), nothing behind it can be a winner. Otherwise start over
     // on the whole segments.
     bool ok = true;
-    for (int sgm = 0; sgm < p.gather_n; ++sgm) ok = ok && (s_segmin[sgm] <= kth);
+    if (p.gather_prefix < p.gather_len)                 // (a prefix that is the whole list hides nothing)
+      for (int sgm = 0; sgm < p.gather_n; ++sgm) ok = ok && (s_segmin[sgm] <= kth);
     if (!ok) {
       prefix_mode = false;
       n = 0;
@@ -588,7 +620,7 @@ again:
     // Unordered output: the winners in whatever order the threads meet them (the SET is exact); with
     // split_k the split_k best of them come first.
     uint64_t kth_split = ~0ull;
-    const bool split = p.split_k > 0 && p.split_k < p.kk;
+    const bool split = p.split_k > 0 && p.split_k < rkk;
     if (split) {
       // a second radix select over the same on-chip candidates, for rank split_k
       uint64_t pf = common_prefix;                    // (0 bits when the first select did not start from scratch)
@@ -643,25 +675,39 @@ again:
       const uint32_t pq = own ? warp_slots(mine, &s_count[2]) : 0u;
       if (win) {
         const uint32_t pos = first ? pa : (uint32_t)p.split_k + pb;
-        if (pos < (uint32_t)p.kk) {
+        if (pos < (uint32_t)rkk) {
           const int64_t o = (int64_t)row * out_pitch + pos;
           if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
           if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
           if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(c >> 32));
-          if (p.out_comp) p.out_comp[o] = (c & 0xFFFFFFFF00000000ull) | (uint64_t)(0xFFFFFFFFu - idx);
+          const uint64_t cg = (c & 0xFFFFFFFF00000000ull) | (uint64_t)(0xFFFFFFFFu - idx);
+          if (p.out_comp) p.out_comp[o] = cg;
+          if (p.push.n > 0 && pos < (uint32_t)p.push.prefix) {
+            const int64_t slot = ((int64_t)p.push.rank * p.R + row) * p.push.prefix + pos;
+            for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot] = cg;
+          }
         }
-        if (mine && pq < (uint32_t)p.kk) p.out_owned[(int64_t)row * out_pitch + pq] = (int32_t)idx;
+        if (mine && pq < (uint32_t)rkk) p.out_owned[(int64_t)row * out_pitch + pq] = (int32_t)idx;
       }
     }
     if (own && p.out_owned_count) {
       __syncthreads();
-      if (tid == 0) p.out_owned_count[row] = (int32_t)(s_count[2] < (uint32_t)p.kk ? s_count[2] : (uint32_t)p.kk);
+      if (tid == 0) p.out_owned_count[row] = (int32_t)(s_count[2] < (uint32_t)rkk ? s_count[2] : (uint32_t)rkk);
+    }
+    if (p.push.n > 0) {
+      // every thread's stores (local list and the ranks' inboxes) precede the barrier; one thread per rank
+      // then makes them visible system-wide and raises this row's flag there
+      __syncthreads();
+      if (tid < p.push.n) {
+        __threadfence_system();
+        st_release_sys_u32(p.push.flags[tid] + (int64_t)p.push.rank * p.R + row, epoch);
+      }
     }
     return;
   }
   if (p.use_bitmap) {
     // Ascending-index output: one bit per token of the row, read out in order.
-    const int words = (p.T + 31) >> 5;
+    const int words = (rT + 31) >> 5;
     for (int i = tid; i < words; i += SEL_FINAL_THREADS) s_bitmap[i] = 0;
     __syncthreads();
     for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
@@ -686,7 +732,7 @@ again:
         const int bit = __ffs(bits) - 1;
         bits &= bits - 1;
         const uint32_t local = (uint32_t)(w0 + j) * 32u + (uint32_t)bit;
-        if (pos < (uint32_t)p.kk) {
+        if (pos < (uint32_t)rkk) {
           const int64_t o = (int64_t)row * out_pitch + pos;
           const uint32_t idx = local + id_add;
           if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
@@ -715,7 +761,7 @@ again:
   for (int i = n + tid; i < n2; i += SEL_FINAL_THREADS) s_cand[i] = 0;
   __syncthreads();
   bitonic_sort_desc<SEL_FINAL_THREADS>(s_cand, n2);
-  for (int i = tid; i < p.kk; i += SEL_FINAL_THREADS) {
+  for (int i = tid; i < rkk; i += SEL_FINAL_THREADS) {
     uint64_t c = s_cand[i];
     if (p.order_by_index) c = ((c & 0xFFFFFFFFull) << 32) | (c >> 32);
     const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
@@ -735,19 +781,12 @@ static int select_cap(int k) {
 
 constexpr size_t SEL_FINAL_FIXED_SMEM = sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 40 + 8) + 8 * SEL_MAX_SEGMENTS;
 constexpr size_t SEL_SMEM_LIMIT = 227 * 1024;
-constexpr int KVB_MAX_DEVICES = 64;              // device ordinals the per-device set-up tables cover
 
 // Opts select_final_kernel into its large dynamic shared memory once per device (the device must be
 // current). Safe to call from several host threads: the flag is atomic and the attribute call is idempotent.
 static int select_final_prepare(int device) {
   static std::atomic<bool> done[KVB_MAX_DEVICES];
-  if (device < 0 || device >= KVB_MAX_DEVICES) return KVB_BAD_DEVICE;
-  if (!done[device].load(std::memory_order_acquire)) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(select_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)SEL_SMEM_LIMIT));
-    done[device].store(true, std::memory_order_release);
-  }
-  return KVB_OK;
+  return ensure_dynamic_smem(select_final_kernel, done, device, SEL_SMEM_LIMIT);
 }
 
 struct SelectWorkspace {

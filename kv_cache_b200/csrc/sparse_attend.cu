@@ -90,6 +90,7 @@ struct AttendParams {
   const int32_t* T_dev;
   int top_k, protect_sink, protect_recent, keep_self;
   int advance_history;        // the merge kernel adds one to *T_dev when everything else is done
+  PartialPush ppush;          // sequence-sharded step: the merged (o, m, l) of every head goes to all ranks' inboxes
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -447,26 +448,57 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
       op[AT_D + 1] = L;
     }
   }
+  if (p.ppush.n > 0) {
+    const uint32_t epoch = *p.ppush.epoch;
+    const int64_t bh = (int64_t)b * p.Hq + head;
+    const int64_t o = ((int64_t)p.ppush.rank * p.B * p.Hq + bh) * PW;
+    for (int q = 0; q < p.ppush.n; ++q) {
+      float* op = p.ppush.inbox[q] + o;
+      op[d] = O;
+      if (d == 0) {
+        op[AT_D] = M;
+        op[AT_D + 1] = L;
+      }
+    }
+    __syncthreads();
+    if (d < p.ppush.n) {
+      __threadfence_system();
+      st_release_sys_u32(p.ppush.flags[d] + (int64_t)p.ppush.rank * p.B * p.Hq + bh, epoch);
+    }
+  }
 }
 
 // Combine N shard partials into the final bf16 output: grid B*Hq, 128 threads (one per dim).
-__global__ void __launch_bounds__(AT_THREADS) lse_merge_kernel(const float* partials, int N, int BH, __nv_bfloat16* out) {
+// With `wait` the partials are an inbox that the ranks fill over NVLink: the CTA first waits (bounded) for
+// every rank's flag of its (batch, head).
+__global__ void __launch_bounds__(AT_THREADS) lse_merge_kernel(const float* partials, int N, int BH, __nv_bfloat16* out,
+                                                               PartialWait wait) {
   constexpr int PW = AT_D + 2;
   const int bh = blockIdx.x, d = threadIdx.x;
+  pdl_wait();
+  if (wait.n > 0) {
+    __shared__ int s_arrived;
+    const uint32_t epoch = *wait.epoch;
+    if (d == 0) s_arrived = 1;
+    __syncthreads();
+    if (d < wait.n && !wait_flag_bounded(wait.flags + (int64_t)d * BH + bh, epoch, wait.limit)) s_arrived = 0;
+    __syncthreads();
+    if (!s_arrived) return;                             // gave up (status word set): the output keeps its old contents
+  }
   float M = -INFINITY;
   for (int r = 0; r < N; ++r) {
     const float* ps = partials + ((int64_t)r * BH + bh) * PW;
-    if (ps[AT_D + 1] > 0.0f) M = fmaxf(M, ps[AT_D]);
+    if (__ldcg(ps + AT_D + 1) > 0.0f) M = fmaxf(M, __ldcg(ps + AT_D));
   }
   float L = 0.0f, O = 0.0f;
   if (M != -INFINITY) {
     for (int r = 0; r < N; ++r) {
       const float* ps = partials + ((int64_t)r * BH + bh) * PW;
-      const float l = ps[AT_D + 1];
+      const float l = __ldcg(ps + AT_D + 1);
       if (l > 0.0f) {
-        const float w = __expf(ps[AT_D] - M);
+        const float w = __expf(__ldcg(ps + AT_D) - M);
         L += l * w;
-        O += ps[d] * w;
+        O += __ldcg(ps + d) * w;
       }
     }
   }
@@ -530,11 +562,8 @@ template <int GG>
 static int attend_launch(const AttendParams& p, int device, cudaStream_t st) {
   const size_t smem = (size_t)AT_WARPS * AT_WARP_SMEM;
   auto kern = sparse_attend_kernel<GG>;
-  static bool attr_done[64] = {false};
-  if (device < 64 && !attr_done[device]) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_done[device] = true;
-  }
+  static std::atomic<bool> attr_done[KVB_MAX_DEVICES];
+  { const int arc = ensure_dynamic_smem(kern, attr_done, device, smem); if (arc != KVB_OK) return arc; }
   const int tasks = p.B * p.Hi * p.nsplit;
   KVB_CHECK_CUDA(launch_kernel(kern, dim3(ceil_div(tasks, AT_WARPS)), dim3(AT_THREADS), smem, st, p));
   KVB_CHECK_CUDA(cudaGetLastError());
@@ -566,10 +595,10 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
                       const float* mask, int64_t mask_sb,
                       int B, int Hq, int Hkv, int Hi, int Tk, int D, int S, float scaling, void* out,
                       float* out_partial, uint32_t* ws_counter, float* ws_partial, bool counters_zeroed, int device,
-                      cudaStream_t st) {
+                      cudaStream_t st, const PartialPush* ppush = nullptr) {
   if (!query || !key || !value || !ws_counter || !ws_partial) return KVB_BAD_ARG;
   if (list.implicit ? (!list.selected && list.kk > 0) : !list.indices) return KVB_BAD_ARG;
-  if (!out && !out_partial) return KVB_BAD_ARG;
+  if (!out && !out_partial && !ppush) return KVB_BAD_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hi <= 0 || Tk <= 0 || S <= 0) return KVB_BAD_SHAPE;
   if (D != AT_D || (Hq % Hkv) || (Hi != Hkv && Hi != Hq)) return KVB_BAD_SHAPE;
   const int GG = Hq / Hi;
@@ -604,6 +633,7 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
   p.ws_counter = ws_counter;
   p.ws_partial = ws_partial;
   p.nsplit = plan.nsplit; p.tiles_per_split = plan.tiles_per_split;
+  if (ppush) p.ppush = *ppush;
 
   (void)counters_zeroed;   // the chunk merge is its own launch: no arrival counters to clear
   switch (GG) {
@@ -676,7 +706,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_lse_merge(const float*
   DeviceGuard guard(device);
   if (!guard.ok) return KVB_BAD_DEVICE;
   lse_merge_kernel<<<B * Hq, AT_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      partials, N, B * Hq, reinterpret_cast<__nv_bfloat16*>(out));
+      partials, N, B * Hq, reinterpret_cast<__nv_bfloat16*>(out), PartialWait{});
   KVB_CHECK_CUDA(cudaGetLastError());
   return KVB_OK;
 }

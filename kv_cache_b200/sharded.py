@@ -1,37 +1,37 @@
 """Sequence-sharded sparse decode: the KV cache of every sequence is split along the token axis
-across the ranks of one node (one process per GPU, torch.distributed / NCCL).
+across the ranks of one node (one process per GPU, torch.distributed for the set-up plumbing).
 
 Rank r owns history tokens [r*T/N, (r+1)*T/N) (bf16 K/V and the int4 side cache); the query, the
 channel list and the K/V row of the token being decoded are replicated. One decode step:
 
-  1. local  : int4 score of the shard, local top-k per KV head -> (score, GLOBAL token id) lists
-  2. gather : ONE all-gather of the packed (score, id) lists            [N, 2, B*Hkv, kk] int32
-  3. merge  : every rank selects the global top-k from the N lists with the same rule
+  1. local  : int4 score of the shard, exact local top-k per KV head -> (score, GLOBAL token id) lists;
+              the best 8192/N entries per row go straight into every rank's exchange buffer
+  2. merge  : every rank selects the global top-k from the N lists with the same rule
               (score desc, id asc): identical result on every rank, independent of rank order
-  4. attend : each rank attends to the selected ids it owns (the last rank also to the decoded
-              token) and emits un-normalised partials (o, m, l)
-  5. gather : ONE all-gather of the partials [N, B, Hq, D+2], log-sum-exp combine on every rank
+  3. attend : each rank attends to the selected ids it owns (the last rank also to the decoded
+              token) and sends its un-normalised partial (o, m, l) to every rank
+  4. combine: log-sum-exp merge of the N partials on every rank
 
-Both collectives move at most a few MiB: they are latency-bound, never bandwidth-bound. Remote
-data always lands in local memory through the collective before a kernel reads it.
+On GPUs the whole step is ONE library call (kvb_sharded_decode_step): seven kernel launches, no
+collective. Data moves between ranks by ordinary stores into peer memory over NVLink (exchange
+buffers mapped once at set-up through CUDA IPC) guarded by flags that carry the step number; all
+device-side waits are bounded. The call sequence is captured once in a CUDA graph and replayed.
 
-The reference (littlexi001/kv_cache) has no sharded path; the single-GPU operators it composes
-are those of kv_cache_b200.ops. The compute backend is pluggable so that the rank/plumbing logic
-can be exercised on CPU ranks (gloo) with a checker backend; the default backend is the CUDA one
-and has no fallback.
+The reference (littlexi001/kv_cache) has no sharded path; the single-GPU operators it composes are
+those of kv_cache_b200.ops. Shapes the one-call step does not take (top_k above a shard's length,
+non-streaming scorer configurations) and CPU ranks (gloo, with a checker backend standing in for the
+device stages) run the same four stages composed from operators around two all-gathers.
 """
 from __future__ import annotations
 
-import json
-import os
-import statistics
-import time
+import ctypes as C
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 
-from . import ops
+from . import _native, ops
+from ._native import ShardedStepParams, check
 
 
 def shard_bounds(total_tokens: int, world: int, rank: int) -> tuple[int, int]:
@@ -49,8 +49,78 @@ def _all_gather(t: torch.Tensor, world: int, group) -> torch.Tensor:
     return out.view(world, *t.shape)
 
 
+class PeerExchange:
+    """This rank's exchange buffer (zero-filled device memory allocated by the library) and the
+    buffers of all peers mapped into this process. ``ptrs[r]`` is rank r's buffer as seen from here."""
+
+    def __init__(self, nbytes: int, device: torch.device, rank: int = 0, world: int = 1, group=None):
+        lib = _native.lib()
+        self.device = device.index if device.index is not None else torch.cuda.current_device()
+        self.nbytes, self.rank, self.world = int(nbytes), rank, world
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        check(lib.kvb_exchange_alloc(self.nbytes, self.device, C.byref(ptr), handle), "kvb_exchange_alloc")
+        self.local = ptr.value
+        self.ptrs: list[int] = [0] * world
+        self.ptrs[rank] = self.local
+        if world > 1:
+            handles: list = [None] * world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            for r in range(world):
+                if r != rank:
+                    peer = C.c_void_p()
+                    check(lib.kvb_exchange_open(handles[r], self.device, C.byref(peer)), "kvb_exchange_open")
+                    self.ptrs[r] = peer.value
+            dist.barrier(group=group)           # nobody steps before every mapping exists
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees the local one. Call on every rank, after the last step
+        has completed everywhere (the caller synchronises and barriers first)."""
+        lib = _native.lib()
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank and p:
+                lib.kvb_exchange_close(p, self.device)
+        if self.local:
+            lib.kvb_exchange_free(self.local, self.device)
+        self.local, self.ptrs = 0, []
+
+
+def sharded_decode_step(query: torch.Tensor, key_local: torch.Tensor, value_local: torch.Tensor, packed: torch.Tensor,
+                        scale: torch.Tensor, channel_idx: torch.Tensor, t_local: int, id_offset: int, total_tokens: int,
+                        top_k: int, rank: int, world: int, exchange_ptrs: list[int], exchange_bytes: int,
+                        workspace: torch.Tensor, out: Optional[torch.Tensor], selected_out: Optional[torch.Tensor] = None,
+                        scaling: Optional[float] = None, phases: int = 7, wait_polls: int = 0) -> int:
+    """Thin call of ``kvb_sharded_decode_step`` on the current stream; returns the status code."""
+    query = ops._query3(query)
+    B, Hq, D = query.shape
+    Hkv = key_local.shape[1]
+    C_ = int(channel_idx.shape[-1])
+    ops._check_side_cache(packed, scale, C_)
+    key_local, value_local = ops._rows_contiguous(key_local), ops._rows_contiguous(value_local)
+    p = ShardedStepParams()
+    p.query, p.q_sb, p.q_sh = query.data_ptr(), query.stride(0), query.stride(1)
+    p.key, p.k_sb, p.k_sh, p.k_st = key_local.data_ptr(), key_local.stride(0), key_local.stride(1), key_local.stride(2)
+    p.value, p.v_sb, p.v_sh, p.v_st = (value_local.data_ptr(), value_local.stride(0), value_local.stride(1),
+                                       value_local.stride(2))
+    p.packed, p.packed_sb, p.packed_sh = packed.data_ptr(), packed.stride(0), packed.stride(1)
+    p.scale, p.scale_sb, p.scale_sh = scale.data_ptr(), scale.stride(0), scale.stride(1)
+    p.channel_idx = channel_idx.data_ptr()
+    p.B, p.Hq, p.Hkv, p.D, p.C = B, Hq, Hkv, D, C_
+    p.t_local, p.id_offset, p.total_tokens = int(t_local), int(id_offset), int(total_tokens)
+    p.top_k, p.rank, p.world = int(top_k), int(rank), int(world)
+    p.scaling = float(D) ** -0.5 if scaling is None else float(scaling)
+    p.out = ops._ptr(out)
+    p.sel_idx_out = ops._ptr(selected_out)
+    p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    for r in range(world):
+        p.exchange[r] = exchange_ptrs[r]
+    p.exchange_bytes = int(exchange_bytes)
+    p.phases, p.wait_polls = int(phases), int(wait_polls)
+    return _native.lib().kvb_sharded_decode_step(C.byref(p), ops._dev(query), ops._stream(query.device))
+
+
 class CudaBackend:
-    """The four device stages of a sharded step on kv_cache_b200.ops."""
+    """The four device stages of a sharded step composed from kv_cache_b200.ops (the form used around
+    all-gathers when the one-call step does not take the shape)."""
 
     def local_candidates(self, query, packed, scale, channel_idx, t_local: int, k: int, id_offset: int):
         r = ops.score(query, packed, scale, channel_idx, t_local, want_acc=False, want_deq=False, want_hist=True)
@@ -75,65 +145,61 @@ class CudaBackend:
 
 
 class ShardedSparseDecode:
-    """One layer's sharded decode step. All ranks of ``group`` call ``step`` collectively."""
+    """One layer's sharded decode step. All ranks of ``group`` call ``step`` collectively. Without an
+    initialised process group it is a world of one (the same code path, exchange buffers local)."""
 
     def __init__(self, top_k: int, group: Optional[dist.ProcessGroup] = None, backend=None,
-                 total_tokens: Optional[int] = None):
+                 total_tokens: Optional[int] = None, wait_polls: int = 0):
         self.top_k = int(top_k)
         self.group = group
         self.backend = backend if backend is not None else CudaBackend()
-        self.rank = dist.get_rank(group)
-        self.world = dist.get_world_size(group)
-        self.total_tokens = total_tokens      # global history length: enables the one-kernel merge (ascending ids)
+        on = dist.is_available() and dist.is_initialized()
+        self.rank = dist.get_rank(group) if on else 0
+        self.world = dist.get_world_size(group) if on else 1
+        self.total_tokens = total_tokens      # global history length: needed by the one-call step
+        self.wait_polls = int(wait_polls)
         self._fast: Optional[bool] = None     # agreed by all ranks on the first step
         self._ws: Optional[torch.Tensor] = None
+        self._out: Optional[torch.Tensor] = None
+        self._sel: Optional[torch.Tensor] = None
+        self.exchange: Optional[PeerExchange] = None
 
-    def _fast_step(self, query, key_local, value_local, packed, scale, channel_idx, t_local, id_offset, scaling):
-        """Front end and merge as single C calls: sampled-threshold candidate scorer -> exact local
-        top-k as composites -> ONE all-gather -> one-kernel global merge. Returns None when this
-        configuration has no candidate front end."""
-        N = self.world
-        B, Hkv = key_local.shape[0], key_local.shape[1]
-        mark = self._mark
-        mark("start")
-        # Every shard puts its 8192/N best candidates first: the merge then works on those prefixes alone
-        # (all on chip) whenever that is provably the global answer, which it is unless one shard holds far
-        # more than its share of the winners.
-        prefix = min(self.top_k, 8192 // N) if N > 1 else 0
-        comp = ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset, self._ws,
-                                    split_k=prefix)
-        if comp is None:
-            return None
-        mark("local top-k")
-        gathered = _all_gather(comp, N, self.group) if N > 1 else comp[None]
-        mark("all-gather candidates")
-        # the merge also hands this rank the winners it owns, compacted: the attention walks only those
-        sel, owned, owned_count = ops.merge_candidates(gathered, self.top_k, self.total_tokens, prefix_k=prefix,
-                                                       own=(id_offset, id_offset + t_local))
-        sel = sel.view(B, Hkv, -1)
-        mark("global merge")
-        part = ops.attend_selected(query, key_local, value_local, owned.view(B, Hkv, -1), t_local, id_base=id_offset,
-                                   keep_self=self.rank == N - 1, scaling=scaling, return_partial=True,
-                                   selected_count=owned_count)
-        mark("attend owned rows")
-        parts = _all_gather(part, N, self.group) if N > 1 else part[None]
-        mark("all-gather partials")
-        out = self.backend.combine(parts)
-        mark("LSE combine")
-        return out, sel
+    def close(self) -> None:
+        if self.exchange is not None:
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            self.exchange.close()
+            self.exchange = None
 
-    def _mark(self, name: str) -> None:
-        """Stage timing hook: records a CUDA event when ``self.stage_events`` is a list (eager runs only)."""
-        ev = getattr(self, "stage_events", None)
-        if ev is not None:
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
-            ev.append((name, e))
+    def _prepare_fast(self, query, key_local, packed, scale, channel_idx, t_local: int, id_offset: int) -> bool:
+        """Decides, identically on all ranks, whether the one-call step applies, and sets it up."""
+        q3 = ops._query3(query)
+        B, Hq, D = q3.shape
+        Hkv = key_local.shape[1]
+        lib = _native.lib()
+        ok = isinstance(self.backend, CudaBackend) and q3.is_cuda and self.total_tokens is not None
+        if ok:
+            # a dry call of phase 1's checks: kvb_shard_candidates refuses what the front end cannot take
+            ok = self.top_k <= t_local and self.world <= 8 and D == 128 and lib.kvb_candidate_capacity(self.top_k) > 0
+            ok = ok and ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset) is not None
+        if self.world > 1:
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=query.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            ok = bool(flag.item())
+        if ok:
+            dev = q3.device
+            need = lib.kvb_sharded_step_workspace_bytes(B, Hq, Hkv, t_local, self.top_k)
+            self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
+            self._out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16, device=dev)
+            self._sel = torch.empty((B, Hkv, self.top_k), dtype=torch.int32, device=dev)
+            xbytes = lib.kvb_sharded_exchange_bytes(B, Hq, Hkv, self.top_k, self.world)
+            self.exchange = PeerExchange(xbytes, dev, self.rank, self.world, self.group)
+        return ok
 
     def capture(self, *args, **kwargs):
-        """Captures one step (collectives included) into a CUDA graph after two eager warm-up steps;
-        returns ``(graph, outputs)``: replaying the graph refreshes ``outputs`` in place. All ranks
-        must capture and replay together."""
+        """Captures one step into a CUDA graph after two eager warm-up steps; returns ``(graph, outputs)``:
+        replaying the graph refreshes ``outputs`` in place. All ranks must capture and replay together."""
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream):
             for _ in range(2):
@@ -150,23 +216,19 @@ class ShardedSparseDecode:
              scaling: Optional[float] = None):
         """``key_local`` / ``value_local`` hold this rank's ``t_local`` history rows followed by the
         row of the decoded token (``[B,Hkv,t_local+1,D]``); ``id_offset`` is the global id of local
-        row 0. Returns ``(out [B,1,Hq,D] bf16, selected int32 [B,Hkv,k] global ids)``, the same on
-        every rank."""
+        row 0. Returns ``(out [B,1,Hq,D] bf16, selected int32 [B,Hkv,k] global ids)``, the same set on
+        every rank (ascending from the composed form, in no particular order from the one-call step)."""
         be, N = self.backend, self.world
         B, Hkv = key_local.shape[0], key_local.shape[1]
         if self._fast is None:
-            # every rank must take the same path (the paths issue different collectives): agree once
-            ok = (isinstance(be, CudaBackend) and self.total_tokens is not None and self.top_k <= t_local
-                  and ops.shard_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset) is not None)
-            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=query.device)
-            if N > 1:
-                dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
-            self._fast = bool(flag.item())
-            if self._fast:
-                need = ops._native.lib().kvb_shard_candidates_workspace_bytes(B, Hkv, t_local + 1, self.top_k)
-                self._ws = torch.empty(need, dtype=torch.uint8, device=query.device)
+            self._fast = self._prepare_fast(query, key_local, packed, scale, channel_idx, t_local, id_offset)
         if self._fast:
-            return self._fast_step(query, key_local, value_local, packed, scale, channel_idx, t_local, id_offset, scaling)
+            rc = sharded_decode_step(query, key_local, value_local, packed, scale, channel_idx, t_local, id_offset,
+                                     self.total_tokens, self.top_k, self.rank, N, self.exchange.ptrs,
+                                     self.exchange.nbytes, self._ws, self._out, self._sel, scaling,
+                                     wait_polls=self.wait_polls)
+            check(rc, "kvb_sharded_decode_step")
+            return self._out, self._sel
         sc, idx = be.local_candidates(query, packed, scale, channel_idx, t_local, self.top_k, id_offset)
         R, kk = sc.shape
         # pack (score bits, id) into one buffer so that a single all-gather carries both
@@ -180,9 +242,13 @@ class ShardedSparseDecode:
                 kk_all = [kk] * N
             kk_max = max(kk_all)
             if kk < kk_max:
-                pad = torch.empty((2, R, kk_max - kk), dtype=torch.int32, device=mine.device)
+                # padding entries: the lowest possible score and ids no real token has, distinct within the row
+                # (the select requires unique ids) and across ranks
+                npad = kk_max - kk
+                pad = torch.empty((2, R, npad), dtype=torch.int32, device=mine.device)
                 pad[0] = torch.tensor(float("-inf")).view(torch.int32).item()
-                pad[1] = torch.iinfo(torch.int32).max
+                top = torch.iinfo(torch.int32).max - self.rank * kk_max
+                pad[1] = (top - torch.arange(npad, device=mine.device, dtype=torch.int64)).to(torch.int32)
                 mine = torch.cat((mine, pad), dim=2).contiguous()
             gathered = _all_gather(mine, N, self.group)                 # [N, 2, R, kk_max]
             sel = be.merge(gathered[:, 0].view(torch.float32), gathered[:, 1], self.top_k)
@@ -201,24 +267,14 @@ class ShardedSparseDecode:
         return be.combine(parts), sel
 
 
-# ------------------------------------------------------------------------------------------
-# benchmark entry (called by bench.py under torchrun for --gpus N > 1)
-# ------------------------------------------------------------------------------------------
-
-def bench_main(args, w) -> None:
+def make_shard(w, rank: int, world: int, dev: torch.device):
+    """This rank's slice of workload ``w``: K/V rows [t0, t1) plus the decoded token's row, the query, the
+    channel list (identical on all ranks: mean |K| summed over the shards) and the int4 side cache."""
     from . import inputs
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=dev)
-    B, Hq, Hkv, D, T, C, k = w.batch, w.q_heads, w.kv_heads, w.head_dim, w.context, w.channels, w.top_k
+    B, Hkv, D, T, C_ = w.batch, w.kv_heads, w.head_dim, w.context, w.channels
     t0, t1 = shard_bounds(T, world, rank)
     t_local = t1 - t0
-
     key = torch.empty((B, Hkv, t_local + 1, D), dtype=torch.bfloat16, device=dev)
     value = torch.empty_like(key)
     for b in range(B):                                           # one batch row at a time: bounded temporaries
@@ -227,131 +283,14 @@ def bench_main(args, w) -> None:
         ks, vs = inputs.make_kv(w, dev, T, T + 1, batch_rows=range(b, b + 1))
         key[b, :, t_local:], value[b, :, t_local:] = ks[0], vs[0]
     query = inputs.make_query(w, dev)
-    # channel choice must be identical on all ranks: mean |K| summed over the shards
-    tot = key[:, :, :t_local].float().abs().sum(dim=(0, 2), dtype=torch.float64) if t_local <= 65536 else sum(
-        key[:, :, s:s + 65536].float().abs().sum(dim=(0, 2), dtype=torch.float64) for s in range(0, t_local, 65536))
-    dist.all_reduce(tot)
-    order = torch.sort(tot, dim=-1, descending=True, stable=True).indices[:, :C]
+    tot = torch.zeros((Hkv, D), dtype=torch.float64, device=dev)
+    for s in range(0, t_local, 65536):
+        tot += key[:, :, s:min(s + 65536, t_local)].float().abs().sum(dim=(0, 2), dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tot)
+    order = torch.sort(tot, dim=-1, descending=True, stable=True).indices[:, :C_]
     ch = torch.sort(order, dim=-1).values.to(torch.int32).contiguous()
-    packed, scale = ops.alloc_side_cache(B, Hkv, t_local + 1, C, dev)
+    packed, scale = ops.alloc_side_cache(B, Hkv, t_local + 1, C_, dev)
     ops.quantize(key[:, :, :t_local], ch, out=(packed, scale))
     torch.cuda.synchronize()
-
-    eng = ShardedSparseDecode(k, total_tokens=T)
-    stream = torch.cuda.Stream(dev)
-
-    def run():
-        return eng.step(query, key, value, packed, scale, ch, t_local, t0)
-
-    from .benchutil import METRIC, UNIT, ClockSampler, hbm_peak
-
-    # The step is captured into a CUDA graph (kernels and both NCCL all-gathers). A capture failure is
-    # fatal on purpose: falling back on one rank only would leave the ranks issuing different collectives.
-    graph = None
-    if os.environ.get("KVB_SHARDED_EAGER") == "1":
-        launch = "eager Python step"
-    else:
-        graph, (out, sel) = eng.capture(query, key, value, packed, scale, ch, t_local, t0)
-        run = graph.replay
-        launch = "CUDA graph replay (kernels and both NCCL all-gathers captured)"
-
-    if os.environ.get("KVB_SHARDED_STAGES") == "1":
-        # per-stage device times of eager steps (host launch gaps included), printed by rank 0 to stderr
-        import sys
-        acc: dict = {}
-        for it in range(25):
-            eng.stage_events = []
-            eng.step(query, key, value, packed, scale, ch, t_local, t0)
-            torch.cuda.synchronize()
-            ev = eng.stage_events
-            if it >= 5:
-                for (n0, e0), (n1, e1) in zip(ev, ev[1:]):
-                    acc.setdefault(n1, []).append(e0.elapsed_time(e1) * 1e3)
-        eng.stage_events = None
-        if rank == 0:
-            print("stage medians (us): " + ", ".join(f"{n}={statistics.median(v):.1f}" for n, v in acc.items()), file=sys.stderr)
-
-    with torch.cuda.stream(stream):
-        for _ in range(max(3, args.warmup)):
-            run()
-        stream.synchronize()
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
-        dist.barrier()
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        nrep = max(1, int(1000.0 / max(0.3 * args.steps, 1e-3)))     # about a second of timed work
-        start.record(stream)
-        for _ in range(args.steps * nrep):
-            run()
-        end.record(stream)
-        dist.barrier()
-        torch.cuda.synchronize()
-        ms = torch.tensor([start.elapsed_time(end) / (args.steps * nrep)], dtype=torch.float64, device=dev)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        clocks = sampler.stop() if rank == 0 else None
-
-        # end to end: the step's inputs from pinned host memory, the output back to the host
-        h_q = torch.empty_like(query, device="cpu").pin_memory()
-        h_q.copy_(query)
-        h_kv = torch.empty((2, B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory()
-        h_kv[0].copy_(key[:, :, t_local:])
-        h_kv[1].copy_(value[:, :, t_local:])
-        h_out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16).pin_memory()
-        d_q = torch.empty_like(query)
-
-        def e2e_step():
-            d_q.copy_(h_q, non_blocking=True)
-            key[:, :, t_local:].copy_(h_kv[0], non_blocking=True)
-            value[:, :, t_local:].copy_(h_kv[1], non_blocking=True)
-            o, _ = eng.step(d_q, key, value, packed, scale, ch, t_local, t0)
-            h_out.copy_(o, non_blocking=True)
-            stream.synchronize()
-
-        for _ in range(3):
-            e2e_step()
-        dist.barrier()
-        tw = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
-        e2e = torch.tensor([(time.perf_counter() - tw) * 1e3 / args.steps], dtype=torch.float64, device=dev)
-        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
-
-    if rank == 0:
-        ms_step, e2e_ms = float(ms.item()), float(e2e.item())
-        tokens = B * T
-        alg = w.algorithmic_bytes()
-        peak, peak_kind = hbm_peak()
-        line = {
-            "metric": METRIC, "value": tokens / (ms_step * 1e-3) / 1e3, "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None,
-            "dtype": "int4xint8->int32 scores, bf16 attention (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": w.name, "batch": B, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "context": T,
-                       "partial_channels": C, "top_k": k, "sharding": f"sequence/{world}",
-                       "collectives": "2 NCCL all-gathers per step (candidates, LSE partials)", "launch": launch,
-                       "l2": "inputs larger than L2 (scan stream %d MiB per rank)" % ((alg["scan"] // world) >> 20)},
-            "clocks": clocks,
-            "e2e": {"value": tokens / (e2e_ms * 1e-3) / 1e3, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": (h_q.numel() + h_kv.numel()) * 2, "d2h_bytes_per_step": h_out.numel() * 2,
-                    "api": "kv_cache_b200.sharded.ShardedSparseDecode.step"},
-            "gpu_launches": 9 * args.steps * world,
-            "roofline": {"bound": "hbm", "kernel": "whole sharded step, per rank", "achieved":
-                         alg["total"] / world / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                         "frac": alg["total"] / world / (ms_step * 1e-3) / 1e9 / peak, "peak_source": peak_kind,
-                         "traffic": None, "algorithmic_bytes": alg["total"] // world},
-            "cpu_baseline": None,
-        }
-        print(json.dumps(line), flush=True)
-    # Teardown: drop the captured graph (it references the communicator) before anything else, and leave
-    # without tearing the process group down: destroying a communicator that a captured graph used
-    # has been seen to block forever, and the process is about to exit anyway.
-    graph = None
-    run = None
-    torch.cuda.synchronize()
-    dist.barrier()
-    import sys
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+    return dict(key=key, value=value, query=query, ch=ch, packed=packed, scale=scale, t0=t0, t_local=t_local)

@@ -24,7 +24,7 @@ def _long_case(dev, T, seed):
     return w, query, key, value, ch, packed, scale
 
 
-@pytest.mark.parametrize("T", [262144, 262145, 524288])
+@pytest.mark.parametrize("T", [262144, 262145, 524288, 1048576])
 def test_decode_step_and_shard_candidates_on_long_rows(cuda_device, T):
     k = 4096
     w, q, key, value, ch, packed, scale = _long_case(cuda_device, T, seed=T % 1000)

@@ -1,12 +1,8 @@
 """The CUDA backend of the sharded step on one GPU: a world of one, and the per-shard stages run
 for every shard of a two-way split inside one process (what each rank would compute), merged
 exactly as the ranks would."""
-import os
-import socket
-
 import pytest
 import torch
-import torch.distributed as dist
 
 from kv_cache_b200 import ops
 from kv_cache_b200.sharded import CudaBackend, ShardedSparseDecode, shard_bounds
@@ -39,22 +35,159 @@ def test_two_shards_emulated_in_one_process(cuda_device):
 
 
 def test_world_of_one(cuda_device):
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=0, world_size=1)
+    """No process group: the one-call step with local exchange buffers (the configuration-4-on-one-GPU path)."""
+    T, k = 20000, 128
+    w, q, key, value = make_case(cuda_device, batch=1, q_heads=4, kv_heads=2, context=T, channels=32)
+    ch = ops.choose_channels(key[:, :, :T], 32)
+    packed, scale = ops.quantize(key[:, :, :T], ch)
+    eng = ShardedSparseDecode(k, total_tokens=T)
     try:
-        T, k = 2000, 128
-        w, q, key, value = make_case(cuda_device, batch=1, q_heads=4, kv_heads=2, context=T, channels=32)
-        ch = ops.choose_channels(key[:, :, :T], 32)
-        packed, scale = ops.quantize(key[:, :, :T], ch)
-        out, sel = ShardedSparseDecode(k).step(q, key, value, packed, scale, ch, T, 0)
         want = oracle.decode_step(*cpu(q, key, value, ch), k)
-        assert torch.equal(sel.cpu().long(), torch.sort(want["selected"], dim=-1).values)
-        torch.testing.assert_close(out.float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
+        for _ in range(3):                                      # the step number advances, nothing is cleared in between
+            out, sel = eng.step(q, key, value, packed, scale, ch, T, 0)
+            assert eng._fast
+            assert torch.equal(torch.sort(sel.cpu().long(), dim=-1).values, torch.sort(want["selected"], dim=-1).values)
+            torch.testing.assert_close(out.float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
     finally:
-        dist.destroy_process_group()
+        eng.close()
+
+
+def test_world_of_one_composed_form(cuda_device):
+    """top_k above the shard length: the step composed from operators (the form used around all-gathers)."""
+    T, k = 100, 128
+    w, q, key, value = make_case(cuda_device, batch=1, q_heads=4, kv_heads=2, context=T, channels=32)
+    ch = ops.choose_channels(key[:, :, :T], 32)
+    packed, scale = ops.quantize(key[:, :, :T], ch)
+    eng = ShardedSparseDecode(k, total_tokens=T)
+    out, sel = eng.step(q, key, value, packed, scale, ch, T, 0)
+    assert not eng._fast
+    want = oracle.decode_step(*cpu(q, key, value, ch), k)
+    assert torch.equal(sel.cpu().long(), torch.sort(want["selected"], dim=-1).values)
+    torch.testing.assert_close(out.float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
+
+
+class _EmulatedRanks:
+    """N ranks of the one-call sharded step inside ONE process on one GPU: every rank has its own exchange
+    buffer and workspace, and the phases are run rank after rank (all phase 1, then all phase 2, then all
+    phase 3), so no kernel ever waits for one queued behind it."""
+
+    def __init__(self, dev, q, key, value, ch, T, k, N, wait_polls=0):
+        from kv_cache_b200 import _native
+        from kv_cache_b200.sharded import PeerExchange
+
+        lib = _native.lib()
+        B, Hq = q.shape[0], q.shape[1]
+        Hkv = key.shape[1]
+        self.N, self.k, self.T, self.q, self.ch, self.wait_polls = N, k, T, q, ch, wait_polls
+        self.xbytes = lib.kvb_sharded_exchange_bytes(B, Hq, Hkv, k, N)
+        self.ex = [PeerExchange(self.xbytes, dev) for _ in range(N)]
+        self.ptrs = [e.local for e in self.ex]
+        self.shards = []
+        for r in range(N):
+            t0, t1 = shard_bounds(T, N, r)
+            tl = t1 - t0
+            k_loc = torch.cat((key[:, :, t0:t1], key[:, :, T:]), dim=2).contiguous()
+            v_loc = torch.cat((value[:, :, t0:t1], value[:, :, T:]), dim=2).contiguous()
+            packed, scale = ops.quantize(k_loc[:, :, :tl], ch)
+            ws = torch.empty(lib.kvb_sharded_step_workspace_bytes(B, Hq, Hkv, tl, k), dtype=torch.uint8, device=dev)
+            out = torch.zeros((B, 1, Hq, 128), dtype=torch.bfloat16, device=dev)
+            sel = torch.zeros((B, Hkv, k), dtype=torch.int32, device=dev)
+            self.shards.append(dict(k=k_loc, v=v_loc, packed=packed, scale=scale, tl=tl, t0=t0, ws=ws, out=out, sel=sel))
+
+    def phase(self, r, phases):
+        from kv_cache_b200.sharded import sharded_decode_step
+
+        s = self.shards[r]
+        return sharded_decode_step(self.q, s["k"], s["v"], s["packed"], s["scale"], self.ch, s["tl"], s["t0"], self.T,
+                                   self.k, r, self.N, self.ptrs, self.xbytes, s["ws"], s["out"], s["sel"],
+                                   phases=phases, wait_polls=self.wait_polls)
+
+    def step(self):
+        for ph in (1, 2, 4):
+            for r in range(self.N):
+                assert self.phase(r, ph) == 0
+
+    def close(self):
+        torch.cuda.synchronize()
+        for e in self.ex:
+            e.close()
+
+
+@pytest.mark.parametrize("N,T,k", [(2, 24000, 512), (4, 40000, 1024), (8, 80000, 256), (3, 30001, 4000)])
+def test_one_call_step_emulated_ranks(cuda_device, N, T, k):
+    """The step that runs across GPUs, with all ranks' buffers on one device: pushed candidate prefixes, flags,
+    the merge on the inbox, owned-row attention, pushed partials, the combine. Every rank must hold the
+    un-sharded oracle's selection and output, step after step."""
+    w, q, key, value = make_case(cuda_device, batch=2, q_heads=8, kv_heads=2, context=T, channels=64, seed=N + 40)
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    want = oracle.decode_step(*cpu(q, key, value, ch), k)
+    want_sel = torch.sort(want["selected"], dim=-1).values
+    em = _EmulatedRanks(cuda_device, q, key, value, ch, T, k, N)
+    try:
+        for it in range(3):
+            em.step()
+            for r in range(N):
+                s = em.shards[r]
+                assert torch.equal(torch.sort(s["sel"].cpu().long(), dim=-1).values, want_sel), (it, r)
+                torch.testing.assert_close(s["out"].float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
+            assert all(torch.equal(em.shards[0]["out"], em.shards[r]["out"]) for r in range(N))     # the same bits everywhere
+    finally:
+        em.close()
+
+
+def test_one_call_step_when_one_shard_holds_every_winner(cuda_device):
+    """All large keys live in shard 0: the prefixes cannot decide the rows, so the merge must read the ranks'
+    whole lists (the path that crosses NVLink with plain loads on a real node)."""
+    N, T, k = 8, 64000, 2048
+    w, q, key, value = make_case(cuda_device, batch=1, q_heads=8, kv_heads=2, context=T, channels=64, seed=77)
+    key = key.clone()
+    key[:, :, T // N:T] *= 0.01                                  # shards 1.. are far below shard 0
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    want = oracle.decode_step(*cpu(q, key, value, ch), k)
+    want_sel = torch.sort(want["selected"], dim=-1).values
+    assert int((want["selected"] < T // N).sum()) > 2 * (8192 // N)        # more winners in shard 0 than a prefix holds
+    em = _EmulatedRanks(cuda_device, q, key, value, ch, T, k, N)
+    try:
+        em.step()
+        for r in range(N):
+            assert torch.equal(torch.sort(em.shards[r]["sel"].cpu().long(), dim=-1).values, want_sel)
+            torch.testing.assert_close(em.shards[r]["out"].float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
+    finally:
+        em.close()
+
+
+def test_bounded_wait_gives_up_cleanly(cuda_device):
+    """Rank 1 never runs phase 1, so rank 0's merge waits for a flag that nothing raises: with a poll limit of
+    64 the kernels must return, the status word must say KVB_TIMEOUT, and the device must stay usable."""
+    import ctypes
+    from kv_cache_b200 import _native
+
+    N, T, k = 2, 24000, 256
+    w, q, key, value = make_case(cuda_device, batch=1, q_heads=4, kv_heads=2, context=T, channels=32, seed=3)
+    ch = ops.choose_channels(key[:, :, :T], 32)
+    em = _EmulatedRanks(cuda_device, q, key, value, ch, T, k, N, wait_polls=64)
+    lib = _native.lib()
+    st = ctypes.c_int(-1)
+    try:
+        assert lib.kvb_device_status(0, ctypes.byref(st)) == 0 and st.value == 0
+        assert em.phase(0, 1) == 0
+        assert em.phase(0, 2) == 0                               # waits for rank 1's flag, gives up after 64 polls
+        assert em.phase(0, 4) == 0                               # and for rank 1's partial
+        torch.cuda.synchronize()
+        assert lib.kvb_device_status(0, ctypes.byref(st)) == 0 and st.value == 5          # KVB_TIMEOUT, then cleared
+        assert lib.kvb_device_status(0, ctypes.byref(st)) == 0 and st.value == 0
+        # the context is alive: bring rank 1 level (its step counter is one behind) and run a full, correct step
+        assert em.phase(1, 1) == 0
+        em.step()
+        torch.cuda.synchronize()
+        want = oracle.decode_step(*cpu(q, key, value, ch), k)
+        for r in range(N):
+            assert torch.equal(torch.sort(em.shards[r]["sel"].cpu().long(), dim=-1).values,
+                               torch.sort(want["selected"], dim=-1).values)
+            torch.testing.assert_close(em.shards[r]["out"].float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
+        assert lib.kvb_device_status(0, ctypes.byref(st)) == 0 and st.value == 0
+    finally:
+        em.close()
 
 
 @pytest.mark.parametrize("N,T,k", [(2, 24000, 512), (4, 40000, 1024), (8, 80000, 256)])
