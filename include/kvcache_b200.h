@@ -448,7 +448,8 @@ int kvb_block_topk(const float* block_scores, int64_t row_stride, int64_t R, int
  *   in fp32 (torch form: EVAL:4443-4446). key is a [B,Hk,T,D] VIEW with element strides
  *   k_sb/k_sh/k_st/k_sd (token-major: k_sd = 1; dim-major storage: k_st = 1); Hk may be the number
  *   of KV heads (head h reads KV head h / (H/Hk)) or H (keys repeated, as the reference passes them).
- *   query bf16 [B,H,D] dense, out fp32 [B,H,T] dense.
+ *   query [B,H,D] dense, out fp32 [B,H,T] dense. elem_type is the type of query and key elements:
+ *   0 = bf16, 1 = fp16, 2 = fp32 (the three types the reference dispatches over, QCK:430-458).
  * kvb_qabs_candidate_full_scores replaces candidate_full_scores (QCK:668-691, kernel QCK:160-216):
  *   out[b,h,t] = scaling * q.k over all D channels where current | previous_candidate |
  *   previous_final (uint8 [B,H,T]; the previous_* may be NULL) or t < protect_sink or
@@ -457,14 +458,14 @@ int kvb_block_topk(const float* block_scores, int64_t row_stride, int64_t R, int
 int kvb_qabs_partial_scores(const void* query, const void* key,
                             int64_t k_sb, int64_t k_sh, int64_t k_st, int64_t k_sd,
                             const int64_t* dim_indices, int dim_count, float* out,
-                            int B, int H, int Hk, int T, int D, int device, void* stream);
+                            int B, int H, int Hk, int T, int D, int elem_type, int device, void* stream);
 
 int kvb_qabs_candidate_full_scores(const void* query, const void* key,
                                    int64_t k_sb, int64_t k_sh, int64_t k_st,
                                    const uint8_t* current, const uint8_t* previous_candidate,
                                    const uint8_t* previous_final, int protect_sink, int protect_recent,
                                    float scaling, float* out,
-                                   int B, int H, int Hk, int T, int D, int device, void* stream);
+                                   int B, int H, int Hk, int T, int D, int elem_type, int device, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused decode step for one layer: quantize-append of the new K row, score, select,

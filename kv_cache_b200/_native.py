@@ -119,9 +119,9 @@ SIGNATURES = {
     "kvb_score_prefill_blocks_engine": (_i, [_p, _p, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _i,
                                              _i, _p]),
     "kvb_block_topk": (_i, [_p, _i64, _i64, _i, _i, _p, _p, _i, _p]),
-    "kvb_qabs_partial_scores": (_i, [_p, _p, _i64, _i64, _i64, _i64, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "kvb_qabs_partial_scores": (_i, [_p, _p, _i64, _i64, _i64, _i64, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     "kvb_qabs_candidate_full_scores": (_i, [_p, _p, _i64, _i64, _i64, _p, _p, _p, _i, _i, _f, _p,
-                                            _i, _i, _i, _i, _i, _i, _p]),
+                                            _i, _i, _i, _i, _i, _i, _i, _p]),
     "kvb_decode_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i, _i]),
     "kvb_decode_step": (_i, [C.POINTER(DecodeStepParams), _i, _p]),
 }

@@ -4,7 +4,9 @@ ymluo/projects/qwen3_top2_head_limit3_ppl/src/evaluate_qwen3_top2_head_limit3_pp
 The reference installs ``_limited_eager_attention_forward`` (EVAL:6236-6931) as the HF "eager"
 attention function (``install_qwen3_attention_patch``, EVAL:6934-6944) and steers it with the
 ``attention_mode(...)`` context manager (EVAL:6947-7075). This module keeps those two entry
-points and the mode mini-language for the path this package implements:
+points — ``attention_mode`` with the reference's complete parameter list, so the evaluator's own
+call with 29 positional arguments (EVAL:7236-7266) binds — and the mode mini-language for the path
+this package implements:
 
     baseline                       dense attention (the original HF eager function)
     qabs{C}cand{P}attn             C partial channels, top ceil(P% * T) tokens  (EVAL:748-754, 4400-4502)
@@ -13,11 +15,19 @@ points and the mode mini-language for the path this package implements:
 with the int4 scorer and GQA-group selection in place of the reference's fp32 per-head scoring.
 Unlike the reference dispatcher, K/V are NOT repeated to the query heads (EVAL:6248-6251 copies
 them G times every layer, every step). Any other mode string raises: there is no fallback.
+
+State. The reference opens one ``with attention_mode(...)`` per decoded token (EVAL:7236), so the
+int4 side caches cannot live in the ``with`` block: they live in a module-level
+``SparseDecodeState`` (or one the caller passes as ``sparse_state=``) and are extended by one row
+per step. A layer's side cache is dropped when the calls that pass through the patched function
+stop being a continuation of what it has seen (a new prefill, another batch shape or device), or
+by ``reset_sparse_state()``.
 """
 from __future__ import annotations
 
 import math
 import re
+import sys
 from contextlib import contextmanager
 from dataclasses import dataclass, field
 from typing import Any, Optional
@@ -59,57 +69,98 @@ class LayerSideCache:
     channel_idx: torch.Tensor
     packed: torch.Tensor
     scale: torch.Tensor
-    count: int = 0                      # tokens quantized so far
-    key_ptr: int = 0                    # identity of the K storage last seen (detects a new sequence)
+    count: int = 0                      # rows quantized so far
+    seen: int = 0                       # key rows of this sequence that have passed through the patched function
+    calibrated_at: int = 0              # history length the channel choice was made from
+    fixed_channels: bool = False        # the caller supplied the channel list: never re-chosen
 
 
 @dataclass
 class SparseDecodeState:
-    """Per-model state of the sparse path: one side cache and one fused-step object per layer."""
+    """Per-model state of the sparse path: one int4 side cache per layer and one fused-step object
+    (with its workspace) per selection policy."""
     layers: dict[int, LayerSideCache] = field(default_factory=dict)
     steps: dict[tuple, ops.DecodeStep] = field(default_factory=dict)
     growth: int = 4096                  # capacity headroom (tokens) when a side cache is (re)allocated
+    # The static channel set is chosen from the keys that exist at a layer's first sparse call. When that
+    # call comes early (token-by-token evaluation from the first token) the choice rests on a handful of
+    # rows, so it is made again, once, when the history first reaches this many tokens (the prefix is then
+    # re-quantized, a few hundred rows).
+    calibration_tokens: int = 256
+    channel_lists: dict[int, torch.Tensor] = field(default_factory=dict)    # optional per-layer int32 [Hkv,C] from the caller
+    bulk_quantized_rows: int = 0        # rows ever sent through the bulk quantizer (tests read this)
 
     def reset(self) -> None:
         self.layers.clear()
+
+    def observe(self, layer_idx: int, key_count: int, query_count: int) -> None:
+        """Called for every attention call that does NOT take the sparse path (baseline mode, prefill
+        chunks): keeps a layer's side cache only while those calls continue the sequence it belongs to."""
+        sc = self.layers.get(layer_idx)
+        if sc is None:
+            return
+        if key_count - query_count == sc.seen:
+            sc.seen = key_count                          # same sequence, rows pending for the next sparse call
+        else:
+            del self.layers[layer_idx]
 
     def side_cache(self, layer_idx: int, key_states: torch.Tensor, history: int, channels: int) -> LayerSideCache:
         B, Hkv = key_states.shape[0], key_states.shape[1]
         sc = self.layers.get(layer_idx)
         stale = (sc is None or sc.packed.shape[0] != B or sc.packed.shape[1] != Hkv
-                 or sc.channel_idx.shape[-1] != channels or sc.count > history
-                 or sc.packed.device != key_states.device)
+                 or sc.channel_idx.shape[-1] != channels or sc.packed.device != key_states.device
+                 or sc.seen != history or sc.count > history)
+        given = self.channel_lists.get(layer_idx)
+        if not stale and not sc.fixed_channels and sc.calibrated_at < self.calibration_tokens <= history:
+            stale = True                                 # the one re-calibration (see calibration_tokens)
         if stale:
-            ch = ops.choose_channels(key_states[:, :, :history], channels)
+            if given is not None:
+                ch = given.to(device=key_states.device, dtype=torch.int32).contiguous()
+            else:
+                ch = ops.choose_channels(key_states[:, :, :history], channels)
             packed, scale = ops.alloc_side_cache(B, Hkv, history + 1 + self.growth, channels, key_states.device)
-            sc = LayerSideCache(ch, packed, scale, 0)
+            sc = LayerSideCache(ch, packed, scale, 0, history, history, given is not None)
             self.layers[layer_idx] = sc
         elif sc.packed.shape[2] < history + 1:
             packed, scale = ops.alloc_side_cache(B, Hkv, history + 1 + self.growth, channels, key_states.device)
             packed[:, :, : sc.count].copy_(sc.packed[:, :, : sc.count])
             scale[:, :, : sc.count].copy_(sc.scale[:, :, : sc.count])
             sc.packed, sc.scale = packed, scale
-        if sc.count < history:          # first decode step after a prefill: bulk quantize the new rows
+        if sc.count < history:          # rows that arrived outside the sparse path (prefill): bulk quantize them
             ops.quantize(key_states[:, :, sc.count:history], sc.channel_idx, out=(sc.packed, sc.scale), t_dst=sc.count)
+            self.bulk_quantized_rows += history - sc.count
             sc.count = history
         return sc
 
-    def step(self, top_k: int, sink: int, recent: int, keep_self: bool, append: bool) -> ops.DecodeStep:
-        key = (top_k, sink, recent, keep_self, append)
+    def step(self, sink: int, recent: int, keep_self: bool, append: bool) -> ops.DecodeStep:
+        """One fused-step object (one workspace) per policy; the candidate count is passed per call."""
+        key = (sink, recent, keep_self, append)
         st = self.steps.get(key)
         if st is None:
-            st = ops.DecodeStep(top_k, sink, recent, keep_self, append_protected=append, append_self=True)
+            st = ops.DecodeStep(1, sink, recent, keep_self, append_protected=append, append_self=True)
             self.steps[key] = st
         return st
 
 
 # Process-global mode, as in the reference (EVAL:55-97): set by attention_mode(), read by the forward.
 _ACTIVE_MODE = "baseline"
+_ACTIVE_TOP_FRACTION = 0.02
 _ACTIVE_ALWAYS_KEEP_SELF = True
 _ACTIVE_PROTECT_SINK_TOKENS = 0
 _ACTIVE_PROTECT_RECENT_TOKENS = 0
 _ACTIVE_STATE: Optional[SparseDecodeState] = None
+_DEFAULT_STATE = SparseDecodeState()
 _ORIGINAL_EAGER_ATTENTION_FORWARD = None
+
+
+def reset_sparse_state() -> None:
+    """Drops every int4 side cache of the module-level state (call between unrelated sequences when the
+    patched function cannot see the change, e.g. two prompts of which the second is prefilled elsewhere)."""
+    _DEFAULT_STATE.reset()
+
+
+def default_sparse_state() -> SparseDecodeState:
+    return _DEFAULT_STATE
 
 
 def sparse_eager_attention_forward(module: torch.nn.Module, query_states: torch.Tensor, key_states: torch.Tensor,
@@ -120,9 +171,13 @@ def sparse_eager_attention_forward(module: torch.nn.Module, query_states: torch.
     if scaling is None:
         scaling = float(getattr(module, "scaling", 1.0 / math.sqrt(query_states.shape[-1])))
     mode = _ACTIVE_MODE
+    state = _ACTIVE_STATE if _ACTIVE_STATE is not None else _DEFAULT_STATE
+    layer_idx = int(getattr(module, "layer_idx", 0))
+    key_count = key_states.shape[-2]
     if mode == "baseline":
         if _ORIGINAL_EAGER_ATTENTION_FORWARD is None:
             raise RuntimeError("baseline mode needs install_qwen3_attention_patch() to have captured the HF function")
+        state.observe(layer_idx, key_count, query_states.shape[2])
         return _ORIGINAL_EAGER_ATTENTION_FORWARD(module, query_states, key_states, value_states, attention_mask,
                                                  scaling=scaling, dropout=dropout, **kwargs)
     params = parse_qabs_partial_rerank_params(mode)
@@ -132,23 +187,19 @@ def sparse_eager_attention_forward(module: torch.nn.Module, query_states: torch.
     if query_states.shape[2] != 1:
         # same contract as EVAL:4413-4414
         raise RuntimeError("qabs candidate-attention mode requires token-by-token eval; set --eval_chunk_size 1.")
-    key_count = key_states.shape[-2]
     if key_count <= 1:                  # EVAL:4415-4417
+        state.observe(layer_idx, key_count, 1)
         out = value_states[:, :, -1:, :].transpose(1, 2)
         rep = query_states.shape[1] // value_states.shape[1]
         return out.repeat_interleave(rep, dim=2).contiguous(), None
-    state = _ACTIVE_STATE
-    if state is None:
-        raise RuntimeError("sparse modes must run inside `with attention_mode(...)`")
     history = key_count - 1
-    layer_idx = int(getattr(module, "layer_idx", 0))
     top_k = candidate_count(fraction, history)
     sc = state.side_cache(layer_idx, key_states, history, min(max(2, channels + (channels & 1)), key_states.shape[-1]))
-    step = state.step(top_k, _ACTIVE_PROTECT_SINK_TOKENS, _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_ALWAYS_KEEP_SELF,
+    step = state.step(_ACTIVE_PROTECT_SINK_TOKENS, _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_ALWAYS_KEEP_SELF,
                       mode.endswith("appendattn"))
     out = step(query_states, key_states, value_states, sc.packed, sc.scale, sc.channel_idx, scaling=scaling,
-               attention_mask=attention_mask)
-    sc.count = key_count                # the fused step appended the current token's row
+               attention_mask=attention_mask, top_k=top_k)
+    sc.count = sc.seen = key_count      # the fused step appended the current token's row
     return out, None
 
 
@@ -179,26 +230,49 @@ def uninstall_qwen3_attention_patch() -> None:
     _ORIGINAL_EAGER_ATTENTION_FORWARD = None
 
 
+def install_qabs_cuda_kernels_alias() -> None:
+    """Makes ``from qabs_cuda_kernels import ...`` (the top-level import inside the evaluator's
+    ``_maybe_cuda_*`` hooks, EVAL:3794, 3826, 3862, 3901) resolve to this package's module with the same four
+    callables, so those hooks reach the sm_100a library without an edit of the evaluator."""
+    from . import qabs_cuda_kernels
+
+    sys.modules["qabs_cuda_kernels"] = qabs_cuda_kernels
+
+
 @contextmanager
 def attention_mode(mode: str, top_fraction: float = 0.02, max_heads_per_token: int = 3, always_keep_self: bool = True,
                    protect_sink_tokens: int = 0, protect_recent_tokens: int = 0, load_stats: Any = None,
-                   sparse_state: Optional[SparseDecodeState] = None, **reference_kwargs: Any):
-    """Same leading parameters as the reference's ``attention_mode`` (EVAL:6947-6955). The state
-    objects and switches of modes this package does not implement are accepted and ignored so that
-    existing call sites keep working; ``sparse_state`` carries the int4 side caches across ``with``
-    blocks (a fresh one is created when omitted)."""
-    global _ACTIVE_MODE, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS, _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE
+                   obs_state: Any = None, obs_mass_state: Any = None, obs_hybrid_state: Any = None,
+                   reuse_state: Any = None, knorm_state: Any = None, block_route_state: Any = None,
+                   ksign_state: Any = None, kdom_state: Any = None, brep_state: Any = None,
+                   sparq_mean_state: Any = None, candidate_stats: Any = None, reuse_overlap_stats: Any = None,
+                   qabs_fast_path: bool = False, qabs_cuda_final_kernel: bool = False,
+                   qabs_cuda_candidate_kernel: bool = False, qabs_cuda_reuse_select_kernel: bool = False,
+                   qabs_profile_stats: Any = None, qabs_candidate_selection: str = "topk",
+                   qabs_threshold_sample_size: int = 256, full_head_map_path: str = "",
+                   full_layer_map_path: str = "", layer_budget_map_path: str = "", *,
+                   sparse_state: Optional[SparseDecodeState] = None):
+    """The reference's ``attention_mode`` with its parameter list in its order (EVAL:6947-6976), so that
+    existing call sites — positional or by keyword — keep working. Used here: ``mode``, ``top_fraction``,
+    ``always_keep_self``, ``protect_sink_tokens``, ``protect_recent_tokens``; the state objects and switches
+    of modes this package does not implement are accepted and ignored (the CUDA-kernel switches are moot:
+    the library is always the path). ``sparse_state`` (keyword only, not in the reference) replaces the
+    module-level state that carries the int4 side caches from one ``with`` block to the next.
+    Yields the state in use."""
+    global _ACTIVE_MODE, _ACTIVE_TOP_FRACTION, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS
+    global _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE
     if mode != "baseline" and parse_qabs_partial_rerank_params(mode) is None:
         raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}[append]attn'; got mode {mode!r}")
-    previous = (_ACTIVE_MODE, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS, _ACTIVE_PROTECT_RECENT_TOKENS,
-                _ACTIVE_STATE)
+    previous = (_ACTIVE_MODE, _ACTIVE_TOP_FRACTION, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS,
+                _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE)
     _ACTIVE_MODE = mode
+    _ACTIVE_TOP_FRACTION = float(top_fraction)
     _ACTIVE_ALWAYS_KEEP_SELF = bool(always_keep_self)
     _ACTIVE_PROTECT_SINK_TOKENS = max(0, int(protect_sink_tokens))
     _ACTIVE_PROTECT_RECENT_TOKENS = max(0, int(protect_recent_tokens))
-    _ACTIVE_STATE = sparse_state if sparse_state is not None else SparseDecodeState()
+    _ACTIVE_STATE = sparse_state if sparse_state is not None else _DEFAULT_STATE
     try:
         yield _ACTIVE_STATE
     finally:
-        (_ACTIVE_MODE, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS, _ACTIVE_PROTECT_RECENT_TOKENS,
-         _ACTIVE_STATE) = previous
+        (_ACTIVE_MODE, _ACTIVE_TOP_FRACTION, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS,
+         _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE) = previous

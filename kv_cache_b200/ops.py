@@ -559,9 +559,10 @@ class DecodeStep:
         self.append_self = bool(append_self)
         self._ws: Optional[torch.Tensor] = None
 
-    def workspace(self, B: int, Hq: int, Hkv: int, history_count: int, device) -> torch.Tensor:
+    def workspace(self, B: int, Hq: int, Hkv: int, history_count: int, device, top_k: Optional[int] = None) -> torch.Tensor:
         need = _native.lib().kvb_decode_step_workspace_bytes(
-            B, Hq, Hkv, history_count, self.top_k, self.protect_sink, self.protect_recent, int(self.keep_self))
+            B, Hq, Hkv, history_count, self.top_k if top_k is None else top_k, self.protect_sink, self.protect_recent,
+            int(self.keep_self))
         if self._ws is None or self._ws.numel() < need or self._ws.device != torch.device(device):
             # headroom so that a growing history does not reallocate every step
             self._ws = torch.empty(int(need * 1.25) + 4096, dtype=torch.uint8, device=device)
@@ -572,9 +573,12 @@ class DecodeStep:
                  attention_mask: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  selected_out: Optional[torch.Tensor] = None, history_dev: Optional[torch.Tensor] = None,
                  advance_history: bool = False,
-                 new_rows: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+                 new_rows: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                 top_k: Optional[int] = None) -> torch.Tensor:
         """``key``/``value`` hold history+1 rows (the last is the token being decoded); the side
-        cache holds the history rows. Returns bf16 ``[B,1,Hq,D]``.
+        cache holds the history rows. Returns bf16 ``[B,1,Hq,D]``. ``top_k`` overrides the count given at
+        construction for this call (a policy whose count follows the history length keeps ONE step object
+        and one workspace).
 
         With ``history_dev`` (int32 device tensor of one element) the history length is read on
         the device and ``key``/``value`` are the whole cache (capacity rows): the same launch
@@ -594,7 +598,8 @@ class DecodeStep:
         key = _rows_contiguous(key)
         value = _rows_contiguous(value)
         dev = query.device
-        ws = self.workspace(B, Hq, Hkv, T, dev)
+        k_now = self.top_k if top_k is None else int(top_k)
+        ws = self.workspace(B, Hq, Hkv, T, dev, k_now)
         if out is None:
             out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16, device=dev)
         mask = _mask_rows(attention_mask, B, key_count)
@@ -608,7 +613,7 @@ class DecodeStep:
         p.mask, p.mask_sb = (_ptr(mask), 0 if mask is None else mask.stride(0))
         p.B, p.Hq, p.Hkv, p.D, p.C = B, Hq, Hkv, D, C_
         p.history_count = T
-        p.top_k = self.top_k
+        p.top_k = k_now
         p.protect_sink, p.protect_recent = self.protect_sink, self.protect_recent
         p.keep_self, p.append_protected = int(self.keep_self), int(self.append_protected)
         p.append_self = int(self.append_self)

@@ -62,3 +62,32 @@ def test_candidate_full_scores_and_final_attention(cuda_device):
     out = qck.final_attention(q, k, v, idx, valid, D ** -0.5)
     ref = oracle.attention_from_final_indices(q.cpu()[:, :, None, :], k.cpu(), v.cpu(), None, idx.cpu(), valid.cpu(), D ** -0.5)
     torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=2e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_the_four_callables_take_fp32_and_fp16_like_the_reference(cuda_device, dtype):
+    """The reference's extension is compiled for float, half and bfloat16 (QCK:430-458)."""
+    g = torch.Generator(device=cuda_device).manual_seed(8)
+    B, H, Hk, T, D = 2, 4, 2, 257, 128
+    q = torch.randn(B, H, D, generator=g, device=cuda_device).to(dtype)
+    k = torch.randn(B, Hk, T, D, generator=g, device=cuda_device).to(dtype)
+    v = torch.randn(B, Hk, T, D, generator=g, device=cuda_device).to(dtype)
+    rep = k.repeat_interleave(H // Hk, dim=1)
+    want, qdim = oracle.qabs_partial_scores(q.cpu(), rep.cpu(), 16)
+    got = qck.partial_scores(q, k, 16)
+    torch.testing.assert_close(got.cpu(), want, rtol=1e-4, atol=1e-3)
+    got_dm = qck.partial_scores_dim_major(q, rep.transpose(2, 3).contiguous(), qdim.to(cuda_device))
+    torch.testing.assert_close(got_dm.cpu(), want, rtol=1e-4, atol=1e-3)
+    cur = torch.rand(B, H, T, generator=g, device=cuda_device) > 0.8
+    full = qck.candidate_full_scores(q, k, cur, None, None, 2, 3, D ** -0.5)
+    want_full = oracle.qabs_candidate_full_scores(q.cpu(), rep.cpu(), cur.cpu(), None, None, 2, 3, D ** -0.5)
+    fin = ~torch.isinf(want_full)
+    assert torch.equal(torch.isinf(full.cpu()), ~fin)
+    torch.testing.assert_close(full.cpu()[fin], want_full[fin], rtol=1e-4, atol=1e-3)
+    idx = torch.randint(0, T, (B, H, 33), generator=g, device=cuda_device)
+    valid = torch.rand(B, H, 33, generator=g, device=cuda_device) > 0.2
+    out = qck.final_attention(q, k, v, idx, valid, D ** -0.5)
+    assert out.dtype == dtype and out.shape == (B, 1, H, D)
+    ref, _, _ = oracle.attend_fp32(q.cpu().to(torch.bfloat16), k.cpu().to(torch.bfloat16), v.cpu().to(torch.bfloat16),
+                                   idx.cpu(), valid.cpu(), D ** -0.5)
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-2, atol=1e-2)
