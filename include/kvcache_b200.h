@@ -319,6 +319,61 @@ int kvb_merge_candidates(const uint64_t* gathered, int N, int R, int kk, int top
                          int64_t own_base, int64_t own_limit, int32_t* out_owned, int32_t* out_owned_count,
                          int device, void* stream);
 
+/* Stages 2 and 3 in one call: the exact top-k token ids per (batch, KV head) straight from the int4 cache
+ * (sampled threshold -> candidate-emitting scorer -> exact finish; the chain of kvb_shard_candidates with ids
+ * instead of composites). It stands where the reference runs its partial scoring followed by torch.topk
+ * (EVAL:4435-4448) when only the candidate ids are wanted (the rerank modes). out_idx int32
+ * [B*Hkv, min(top_k,T)], ascending when `ascending` != 0 and the row's bitmap fits on chip (T up to ~600K),
+ * otherwise in no particular order; same shape limits and workspace as kvb_shard_candidates. */
+int kvb_score_select(const void* query, int64_t q_sb, int64_t q_sh,
+                     const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                     const float* scale, int64_t scale_sb, int64_t scale_sh,
+                     const int32_t* channel_idx,
+                     int B, int Hq, int Hkv, int T, int D, int C, int top_k, int ascending,
+                     int32_t* out_idx, void* workspace, size_t workspace_bytes,
+                     int device, void* stream);
+
+/* Exact rerank of a candidate union given as id LISTS: replaces candidate_full_scores (QCK:668-691, kernel
+ * QCK:160-216: three dense bool masks [B,H,T] in, a dense fp32 [B,H,T] row out) followed by torch.topk
+ * (EVAL:4297-4302), i.e. the core of the reference's rerank / reuse modes (EVAL:4147-4311) and of its
+ * "top2" modes (EVAL:4704-4720).
+ *   list0 / list1 / list2   int32 [R, n_i] token ids (current candidates; previous candidates; previous final
+ *                           set; list1, list2 may be NULL), R = B * Hi list rows with Hi = Hkv (one list per KV
+ *                           head, shared by its G query heads) or Hq (one per query head, the reference's form).
+ *                           count_i int32 [R] or NULL: row r uses its first count_i[r] entries. Ids outside
+ *                           [0, history_count) (-1 padding, ids of a longer past) are ignored; duplicates within
+ *                           and across the lists are merged.
+ *   force_sink / force_recent  additionally put [0, force_sink) and [history_count - force_recent, history_count)
+ *                           into the union (the reference's lagged modes, EVAL:4209-4214); 0 = off.
+ *   score                   max over the query heads that share the list of (q . k) in fp32 over all D channels,
+ *                           times `scaling`, plus mask[b, token] (fp32 [B, >= history_count] or NULL).
+ *   out_idx                 int32 [R, keep]: the min(keep, |union|) best ids by (score desc, id asc), written in
+ *                           ASCENDING id order, the rest of the row -1; out_count int32 [R] how many.
+ * Limits: n0 + n1 + n2 + forced <= 16384, history_count small enough for two on-chip bitmaps (about 600K
+ * tokens), D = 128; otherwise KVB_BAD_SHAPE. workspace >= kvb_rerank_union_workspace_bytes(R, n0+n1+n2+forced). */
+size_t kvb_rerank_union_workspace_bytes(int R, int max_union);
+
+int kvb_rerank_union(const void* query, int64_t q_sb, int64_t q_sh,
+                     const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+                     const int32_t* list0, int n0, const int32_t* count0,
+                     const int32_t* list1, int n1, const int32_t* count1,
+                     const int32_t* list2, int n2, const int32_t* count2,
+                     int force_sink, int force_recent,
+                     const float* mask, int64_t mask_sb,
+                     int B, int Hq, int Hkv, int Hi, int history_count, int D, float scaling, int keep,
+                     int32_t* out_idx, int32_t* out_count,
+                     void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/* Final keep set of the rerank modes as a list: the given ids, plus the protected ranges [0, force_sink) and
+ * [history_count - force_recent, history_count) (EVAL:4306-4311), each token then widened to its aligned block
+ * of block_size tokens (_expand_history_keep_to_aligned_blocks, EVAL:2914-2922; block_size 1 = no widening),
+ * de-duplicated, in ascending order. list int32 [R, n] with optional per-row count; ids outside
+ * [0, history_count) are ignored. out_idx int32 [R, out_cap] (entries beyond out_cap are dropped, the unused
+ * tail is -1), out_count int32 [R]. history_count / block_size up to about 1.8 M bits (on-chip bitmap). */
+int kvb_expand_final(const int32_t* list, int n, const int32_t* count, int R, int history_count,
+                     int force_sink, int force_recent, int block_size,
+                     int32_t* out_idx, int out_cap, int32_t* out_count, int device, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Sequence-sharded decode step without a collective call (no counterpart in the reference, which
  * has no sharding). Rank r of `world` owns the history tokens [id_offset, id_offset + t_local) of

@@ -106,6 +106,12 @@ SIGNATURES = {
     "kvb_shard_candidates": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
                                   _i, _i, _i, _i, _i, _i, _i, _i, _i64, _p, _p, _sz, _i, _p]),
     "kvb_merge_candidates": (_i, [_p, _i, _i, _i, _i, _i64, _i, _p, _i64, _i64, _p, _p, _i, _p]),
+    "kvb_score_select": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p,
+                              _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _sz, _i, _p]),
+    "kvb_rerank_union_workspace_bytes": (_sz, [_i, _i]),
+    "kvb_rerank_union": (_i, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i, _p, _p, _i, _p, _p, _i, _p, _i, _i,
+                              _p, _i64, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p, _sz, _i, _p]),
+    "kvb_expand_final": (_i, [_p, _i, _p, _i, _i, _i, _i, _i, _p, _i, _p, _i, _p]),
     "kvb_sharded_exchange_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "kvb_sharded_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "kvb_exchange_alloc": (_i, [_sz, _i, C.POINTER(_p), _p]),

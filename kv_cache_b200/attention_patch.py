@@ -11,8 +11,13 @@ this package implements:
     baseline                       dense attention (the original HF eager function)
     qabs{C}cand{P}attn             C partial channels, top ceil(P% * T) tokens  (EVAL:748-754, 4400-4502)
     qabs{C}cand{P}appendattn       same, protected ranges appended instead of filtered (EVAL:2985-3022)
+    qabs{C}cand{P}top2attn         candidates, exact q.k on them, the best ceil(top_fraction * T)  (EVAL:4650-4766)
+    qabs{C}cand{P}reuse            candidates + the previous step's candidates and final set, exact q.k on the
+      [2set|final][blk{N}]         union, the best ceil(top_fraction * T), protected ranges forced in, optional
+                                   widening to aligned blocks of N tokens (EVAL:3991-4397, 1596-1759, 2914-2922)
 
-with the int4 scorer and GQA-group selection in place of the reference's fp32 per-head scoring.
+with the int4 scorer and GQA-group selection in place of the reference's fp32 per-head scoring: one
+candidate list, one exact rerank (maximum of q.k over the group's query heads) and one final list per KV head.
 Unlike the reference dispatcher, K/V are NOT repeated to the query heads (EVAL:6248-6251 copies
 them G times every layer, every step). Any other mode string raises: there is no fallback.
 
@@ -36,16 +41,29 @@ import torch
 
 from . import ops
 
-_QABS_RE = re.compile(r"qabs(\d+)cand(\d+(?:p\d+)?)(appendattn|attn)")
+_QABS_RE = re.compile(r"qabs(\d+)cand(\d+(?:p\d+)?)(appendattn|top2attn|attn|reuse(?:2set|final)?(?:blk(\d+))?)")
 
 
 def parse_qabs_partial_rerank_params(mode: str) -> Optional[tuple[int, float]]:
-    """``(channels, candidate_fraction)`` of a ``qabs{C}cand{P}[append]attn`` mode string, else None.
-    ``P`` is a percentage with ``p`` as the decimal point (``6p25`` = 6.25 %), as in EVAL:748-754."""
+    """``(channels, candidate_fraction)`` of a ``qabs{C}cand{P}...`` mode string this package implements, else
+    None. ``P`` is a percentage with ``p`` as the decimal point (``6p25`` = 6.25 %), as in EVAL:748-754."""
     m = _QABS_RE.fullmatch(mode)
     if not m:
         return None
     return int(m.group(1)), float(m.group(2).replace("p", ".")) / 100.0
+
+
+def parse_mode_kind(mode: str) -> Optional[tuple[str, int]]:
+    """``(kind, block_size)``: kind is ``attn``, ``appendattn``, ``top2attn`` or ``reuse`` / ``reuse2set`` /
+    ``reusefinal`` (EVAL:955-960: which previous sets join the union); block_size from a ``blk{N}`` suffix, else 1."""
+    m = _QABS_RE.fullmatch(mode)
+    if not m:
+        return None
+    tail = m.group(3)
+    block = int(m.group(4)) if m.group(4) else 1
+    if tail.startswith("reuse"):
+        tail = tail.split("blk")[0]
+    return tail, max(1, block)
 
 
 def candidate_count(candidate_fraction: float, history_count: int) -> int:
@@ -76,6 +94,16 @@ class LayerSideCache:
 
 
 @dataclass
+class LayerReuse:
+    """What a reuse mode carries from one decode step of a layer to the next (the list form of the two masks in
+    ReuseCandidateState.previous_layer, EVAL:1725-1745)."""
+    query_token: int
+    candidate: torch.Tensor             # int32 [B,Hkv,n]   this step's own candidates
+    final: torch.Tensor                 # int32 [B,Hkv,m]   kept set incl. protected ranges, -1 padded
+    final_count: torch.Tensor           # int32 [B,Hkv]
+
+
+@dataclass
 class SparseDecodeState:
     """Per-model state of the sparse path: one int4 side cache per layer and one fused-step object
     (with its workspace) per selection policy."""
@@ -89,9 +117,11 @@ class SparseDecodeState:
     calibration_tokens: int = 256
     channel_lists: dict[int, torch.Tensor] = field(default_factory=dict)    # optional per-layer int32 [Hkv,C] from the caller
     bulk_quantized_rows: int = 0        # rows ever sent through the bulk quantizer (tests read this)
+    reuse: dict[int, LayerReuse] = field(default_factory=dict)
 
     def reset(self) -> None:
         self.layers.clear()
+        self.reuse.clear()
 
     def observe(self, layer_idx: int, key_count: int, query_count: int) -> None:
         """Called for every attention call that does NOT take the sparse path (baseline mode, prefill
@@ -182,7 +212,7 @@ def sparse_eager_attention_forward(module: torch.nn.Module, query_states: torch.
                                                  scaling=scaling, dropout=dropout, **kwargs)
     params = parse_qabs_partial_rerank_params(mode)
     if params is None:
-        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}[append]attn'; got mode {mode!r}")
+        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}' + attn | appendattn | top2attn | reuse[2set|final][blkN]; got mode {mode!r}")
     channels, fraction = params
     if query_states.shape[2] != 1:
         # same contract as EVAL:4413-4414
@@ -195,12 +225,50 @@ def sparse_eager_attention_forward(module: torch.nn.Module, query_states: torch.
     history = key_count - 1
     top_k = candidate_count(fraction, history)
     sc = state.side_cache(layer_idx, key_states, history, min(max(2, channels + (channels & 1)), key_states.shape[-1]))
+    kind, block = parse_mode_kind(mode)
+    if kind == "top2attn" or kind.startswith("reuse"):
+        return _rerank_forward(state, layer_idx, sc, kind, block, top_k, query_states, key_states, value_states,
+                               attention_mask, scaling), None
     step = state.step(_ACTIVE_PROTECT_SINK_TOKENS, _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_ALWAYS_KEEP_SELF,
                       mode.endswith("appendattn"))
     out = step(query_states, key_states, value_states, sc.packed, sc.scale, sc.channel_idx, scaling=scaling,
                attention_mask=attention_mask, top_k=top_k)
     sc.count = sc.seen = key_count      # the fused step appended the current token's row
     return out, None
+
+
+def _rerank_forward(state: SparseDecodeState, layer_idx: int, sc: LayerSideCache, kind: str, block: int, cand_k: int,
+                    query_states, key_states, value_states, attention_mask, scaling: float) -> torch.Tensor:
+    """The rerank modes as lists: int4 candidates -> (union with the previous step's lists) -> exact q.k ->
+    top ceil(top_fraction * T) -> protected ranges / block widening -> attention over the final list."""
+    key_count = key_states.shape[-2]
+    history = key_count - 1
+    sink, recent = _ACTIVE_PROTECT_SINK_TOKENS, _ACTIVE_PROTECT_RECENT_TOKENS
+    cand = ops.score_select(query_states, sc.packed, sc.scale, sc.channel_idx, history, cand_k)
+    ops.quantize_append(key_states[:, :, history], sc.channel_idx, sc.packed, sc.scale, history)
+    sc.count = sc.seen = key_count
+    keep_full = max(1, math.ceil(_ACTIVE_TOP_FRACTION * history))
+    if kind == "top2attn":
+        keep = min(cand_k, keep_full)                      # EVAL:4676
+        kept, cnt = ops.rerank_union(query_states, key_states, [cand], history, keep, scaling=scaling,
+                                     attention_mask=attention_mask)
+        selected, count = kept, cnt
+    else:
+        keep = min(history, keep_full)                     # EVAL:4269-4270
+        prev = state.reuse.get(layer_idx)
+        if prev is not None and (prev.query_token != history - 1 or prev.candidate.shape[:2] != cand.shape[:2]
+                                 or prev.candidate.device != cand.device):
+            prev = None                                    # not the step before this one (EVAL:1653-1655)
+        lists = [cand, prev.candidate if prev is not None and kind != "reusefinal" else None,
+                 prev.final if prev is not None and kind != "reuse2set" else None]
+        counts = [None, None, prev.final_count if lists[2] is not None else None]
+        kept, cnt = ops.rerank_union(query_states, key_states, lists, history, keep, counts=counts, scaling=scaling)
+        final, fcnt = ops.expand_final(kept, history, count=cnt, force_sink=sink, force_recent=recent, block_size=block)
+        state.reuse[layer_idx] = LayerReuse(history, cand, final, fcnt)
+        selected, count = (final, fcnt) if block > 1 else (kept, cnt)
+    return ops.attend_selected(query_states, key_states, value_states, selected, history, protect_sink=sink,
+                               protect_recent=recent, keep_self=_ACTIVE_ALWAYS_KEEP_SELF, scaling=scaling,
+                               attention_mask=attention_mask, selected_count=count.reshape(-1))
 
 
 def install_qwen3_attention_patch() -> None:
@@ -262,7 +330,7 @@ def attention_mode(mode: str, top_fraction: float = 0.02, max_heads_per_token: i
     global _ACTIVE_MODE, _ACTIVE_TOP_FRACTION, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS
     global _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE
     if mode != "baseline" and parse_qabs_partial_rerank_params(mode) is None:
-        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}[append]attn'; got mode {mode!r}")
+        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}' + attn | appendattn | top2attn | reuse[2set|final][blkN]; got mode {mode!r}")
     previous = (_ACTIVE_MODE, _ACTIVE_TOP_FRACTION, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS,
                 _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE)
     _ACTIVE_MODE = mode

@@ -8,6 +8,7 @@
 #include "sparse_attend.cu"
 #include "decode_step.cu"
 #include "sharded_step.cu"
+#include "rerank.cu"
 #include "score_prefill_tc.cu"
 #include "score_prefill.cu"
 #include "qabs_fp32.cu"

@@ -76,6 +76,7 @@ struct SelectParams {
   // rank's inbox (push.n > 0, unordered output with split_k == push.prefix or push.prefix >= kk); the merge
   // kernel WAITS for all ranks' flags (wait.n > 0) and then selects from its local inbox (`gather`, rows
   // gather_pitch apart), falling back to the ranks' whole lists (wait.full) for a row its prefixes cannot decide.
+  int out_pitch = 0;          // row pitch of the outputs; 0 = kk
   int gather_pitch = 0;       // row pitch of a segment in `gather`; 0 = gather_len
   PeerPush push;
   PeerWait wait;
@@ -372,7 +373,7 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   // (the parameters stay in constant memory: a modifiable copy would live on the thread's stack because
   // the rank tables are indexed at run time; only the two values that can change are held in registers)
   const SelectParams& p = pin;
-  const int out_pitch = pin.kk;                         // rows of the outputs stay kk_max apart
+  const int out_pitch = pin.out_pitch > 0 ? pin.out_pitch : pin.kk;     // rows of the outputs stay kk_max apart
   int rT = pin.T, rkk = pin.kk;
   pdl_launch_dependents();
   pdl_wait();
@@ -725,6 +726,13 @@ again:
       if (w0 + j < words) cnt += (uint32_t)__popc(s_bitmap[w0 + j]);
     uint32_t total;
     uint32_t pos = block_exclusive_scan<SEL_FINAL_THREADS>(cnt, s_tmp, total);
+    // a row with fewer candidates than kk: report how many it got and mark the unused tail
+    if (p.out_owned_count && !p.out_owned) {
+      const uint32_t got = total < (uint32_t)rkk ? total : (uint32_t)rkk;
+      if (tid == 0) p.out_owned_count[row] = (int32_t)got;
+      if (p.out_idx32)
+        for (uint32_t i = got + tid; i < (uint32_t)out_pitch; i += SEL_FINAL_THREADS) p.out_idx32[(int64_t)row * out_pitch + i] = -1;
+    }
     for (int j = 0; j < per; ++j) {
       if (w0 + j >= words) break;
       uint32_t bits = s_bitmap[w0 + j];

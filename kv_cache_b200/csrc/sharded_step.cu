@@ -74,8 +74,9 @@ static int shard_candidates_run(const void* query, int64_t q_sb, int64_t q_sh, c
                                 const int32_t* channel_idx, int B, int Hq, int Hkv, int T, int D, int C, int top_k,
                                 int split_k, int64_t id_offset, uint64_t* out_comp, void* workspace,
                                 size_t workspace_bytes, const PeerPush* push, uint32_t* step_counter,
-                                ChainLaunchScope* chain, int device, cudaStream_t st) {
-  if (!query || !packed || !scale || !channel_idx || !out_comp || !workspace) return KVB_BAD_ARG;
+                                ChainLaunchScope* chain, int device, cudaStream_t st, int32_t* out_idx = nullptr,
+                                bool ascending = false) {
+  if (!query || !packed || !scale || !channel_idx || (!out_comp && !out_idx) || !workspace) return KVB_BAD_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || T <= 0 || top_k <= 0 || split_k < 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
   if (id_offset < 0 || id_offset + T > 0x7fffffffLL) return KVB_BAD_SHAPE;
   if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
@@ -105,7 +106,7 @@ static int shard_candidates_run(const void* query, int64_t q_sb, int64_t q_sh, c
   SelectParams sp;
   sp.scores = gmax; sp.row_stride = T; sp.payload = nullptr;
   sp.R = L.R; sp.T = T; sp.k = top_k; sp.kk = L.kk; sp.idx_offset = id_offset;
-  sp.out_idx32 = nullptr; sp.out_idx64 = nullptr; sp.out_scores = nullptr; sp.out_comp = out_comp;
+  sp.out_idx32 = out_idx; sp.out_idx64 = nullptr; sp.out_scores = nullptr; sp.out_comp = out_comp;
   sp.hist = nullptr; sp.cand = cand; sp.cand_count = count; sp.cap = L.cap;
   sp.tokens_per_cta = 0; sp.thresholds = nullptr;
   sp.order_by_index = 2; sp.use_bitmap = 0;
@@ -114,7 +115,11 @@ static int shard_candidates_run(const void* query, int64_t q_sb, int64_t q_sh, c
   sp.rescue = 1; sp.rescue_sp = base;
   sp.split_k = split_k;
   if (push) sp.push = *push;
-  const size_t smem = (size_t)L.cap * 8 + SEL_FINAL_FIXED_SMEM;
+  size_t smem = (size_t)L.cap * 8 + SEL_FINAL_FIXED_SMEM;
+  const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
+  if (ascending && !out_comp && smem + bitmap_bytes <= SEL_SMEM_LIMIT) {      // ids in ascending order (on-chip bitmap)
+    sp.order_by_index = 1; sp.use_bitmap = 1; smem += bitmap_bytes;
+  }
   { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
   KVB_CHECK_CUDA(launch_kernel(select_final_kernel, dim3(L.R), dim3(SEL_FINAL_THREADS), smem, st, sp));
   return KVB_OK;
@@ -130,6 +135,17 @@ extern "C" __attribute__((visibility("default"))) int kvb_shard_candidates(
   return kvb::shard_candidates_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx,
                                    B, Hq, Hkv, T, D, C, top_k, split_k, id_offset, out_comp, workspace, workspace_bytes,
                                    nullptr, nullptr, nullptr, device, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_score_select(
+    const void* query, int64_t q_sb, int64_t q_sh, const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, const int32_t* channel_idx, int B, int Hq, int Hkv, int T,
+    int D, int C, int top_k, int ascending, int32_t* out_idx, void* workspace, size_t workspace_bytes, int device,
+    void* stream) {
+  if (!out_idx) return KVB_BAD_ARG;
+  return kvb::shard_candidates_run(query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx,
+                                   B, Hq, Hkv, T, D, C, top_k, 0, 0, nullptr, workspace, workspace_bytes, nullptr, nullptr,
+                                   nullptr, device, reinterpret_cast<cudaStream_t>(stream), out_idx, ascending != 0);
 }
 
 // ---- exchange buffers: the only entry points of the library that allocate -------------------------------

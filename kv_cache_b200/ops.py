@@ -426,6 +426,99 @@ def shard_candidates(query: torch.Tensor, packed: torch.Tensor, scale: torch.Ten
     return out
 
 
+def score_select(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
+                 history_count: int, top_k: int, ascending: bool = True,
+                 workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Stages 2 and 3 in one call: the exact top-``k`` token ids per (batch, KV head) from the int4 cache, int32
+    ``[B,Hkv,min(k,T)]`` (ascending when asked and the history is short enough for the on-chip bitmap). Falls
+    back to ``score`` + ``select`` for configurations without the candidate front end."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    Hkv = packed.shape[1]
+    C_ = int(channel_idx.shape[-1])
+    _check_side_cache(packed, scale, C_)
+    T = int(history_count)
+    dev = query.device
+    lib = _native.lib()
+    kk = min(int(top_k), T)
+    need = lib.kvb_shard_candidates_workspace_bytes(B, Hkv, T, int(top_k))
+    ws = workspace if workspace is not None and workspace.numel() >= need else torch.empty(need, dtype=torch.uint8, device=dev)
+    out = torch.empty((B, Hkv, kk), dtype=torch.int32, device=dev)
+    rc = lib.kvb_score_select(
+        query.data_ptr(), query.stride(0), query.stride(1), packed.data_ptr(), packed.stride(0), packed.stride(1),
+        scale.data_ptr(), scale.stride(0), scale.stride(1), channel_idx.data_ptr(), B, Hq, Hkv, T, D, C_, int(top_k),
+        int(ascending), out.data_ptr(), ws.data_ptr(), ws.numel(), _dev(query), _stream(dev))
+    if rc == 1:          # KVB_BAD_SHAPE: no candidate front end for this shape
+        r = score(query, packed, scale, channel_idx, T, want_acc=False, want_deq=False, want_hist=True)
+        return select(r.gmax, top_k, hist=r.hist, index_dtype=torch.int32, order="index" if ascending else "score")
+    check(rc, "kvb_score_select")
+    return out
+
+
+def rerank_union(query: torch.Tensor, key: torch.Tensor, lists, history_count: int, keep: int, *,
+                 counts=None, scaling: Optional[float] = None, attention_mask: Optional[torch.Tensor] = None,
+                 force_sink: int = 0, force_recent: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Exact rerank of the union of up to three id lists (current candidates, previous candidates, previous
+    final set; the reference's rerank / reuse modes, EVAL:4147-4311, with lists in place of its ``[B,H,T]``
+    masks). ``lists``: int32 ``[B,Hi,n_i]`` tensors (``None`` entries allowed after the first), ``Hi`` = KV heads
+    (one list per GQA group, scored by the maximum over its query heads) or query heads. Returns
+    ``(ids int32 [B,Hi,keep] ascending, -1 padded; count int32 [B,Hi])`` — the ``min(keep, |union|)`` best by
+    (exact score desc, id asc)."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    key = _rows_contiguous(key)
+    Hkv = key.shape[1]
+    lists = list(lists) + [None] * (3 - len(lists))
+    counts = list(counts) + [None] * (3 - len(counts)) if counts is not None else [None] * 3
+    if lists[0] is None:
+        raise RuntimeError("the first list (current candidates) is required")
+    Hi = lists[0].shape[1]
+    dev = query.device
+    ls = [None if l is None else l.to(torch.int32).contiguous() for l in lists]
+    cs = [None if c is None else c.to(torch.int32).contiguous() for c in counts]
+    for l in ls:
+        if l is not None and (l.dim() != 3 or l.shape[0] != B or l.shape[1] != Hi):
+            raise RuntimeError("lists must be [B,Hi,n] with the same Hi")
+    ns = [0 if l is None else int(l.shape[2]) for l in ls]
+    if scaling is None:
+        scaling = float(D) ** -0.5
+    mask = _mask_rows(attention_mask, B, int(history_count))
+    lib = _native.lib()
+    total = min(int(history_count), sum(ns) + int(force_sink) + int(force_recent))
+    ws_bytes = lib.kvb_rerank_union_workspace_bytes(B * Hi, total)
+    if ws_bytes == 0:
+        raise RuntimeError("kvb_rerank_union: the candidate union is too large (more than 16384 entries)")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    out = torch.empty((B, Hi, int(keep)), dtype=torch.int32, device=dev)
+    cnt = torch.empty((B, Hi), dtype=torch.int32, device=dev)
+    check(lib.kvb_rerank_union(
+        query.data_ptr(), query.stride(0), query.stride(1), key.data_ptr(), key.stride(0), key.stride(1), key.stride(2),
+        ls[0].data_ptr(), ns[0], _ptr(cs[0]), _ptr(ls[1]), ns[1], _ptr(cs[1]), _ptr(ls[2]), ns[2], _ptr(cs[2]),
+        int(force_sink), int(force_recent), _ptr(mask), 0 if mask is None else mask.stride(0),
+        B, Hq, Hkv, Hi, int(history_count), D, float(scaling), int(keep), out.data_ptr(), cnt.data_ptr(),
+        ws.data_ptr(), ws_bytes, _dev(query), _stream(dev)), "kvb_rerank_union")
+    return out, cnt
+
+
+def expand_final(ids: torch.Tensor, history_count: int, *, count: Optional[torch.Tensor] = None, force_sink: int = 0,
+                 force_recent: int = 0, block_size: int = 1, capacity: Optional[int] = None):
+    """The keep set of the rerank modes as a list: ``ids`` (int32 ``[..., n]``, -1 / out-of-range entries
+    ignored) plus the protected ranges (EVAL:4306-4311), widened to aligned blocks of ``block_size`` tokens
+    (EVAL:2914-2922), de-duplicated and ascending. Returns ``(ids int32 [..., capacity] -1 padded, count)``."""
+    lead, n = ids.shape[:-1], ids.shape[-1]
+    l2 = ids.reshape(-1, n).to(torch.int32).contiguous()
+    R = l2.shape[0]
+    c2 = None if count is None else count.reshape(-1).to(torch.int32).contiguous()
+    if capacity is None:
+        capacity = min(int(history_count), (n + int(force_sink) + int(force_recent)) * max(1, int(block_size)))
+    out = torch.empty((R, int(capacity)), dtype=torch.int32, device=ids.device)
+    cnt = torch.empty((R,), dtype=torch.int32, device=ids.device)
+    check(_native.lib().kvb_expand_final(l2.data_ptr(), n, _ptr(c2), R, int(history_count), int(force_sink),
+                                         int(force_recent), int(block_size), out.data_ptr(), int(capacity), cnt.data_ptr(),
+                                         _dev(ids), _stream(ids.device)), "kvb_expand_final")
+    return out.reshape(*lead, int(capacity)), cnt.reshape(*lead)
+
+
 def merge_candidates(gathered: torch.Tensor, top_k: int, id_range: int, prefix_k: int = 0,
                      own: Optional[tuple[int, int]] = None):
     """Global top-``k`` token ids (int32 ``[R, k']``) from all-gathered composite lists int64 ``[N,R,kk]``.

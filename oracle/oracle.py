@@ -179,6 +179,37 @@ def decode_step(query, key, value, channel_idx, top_k, *, protect_sink=0, protec
                 selected=sel, selected_scores=sel_scores, final_indices=fidx, final_valid=fvalid, out=out, m=m, l=l)
 
 
+def reuse_decode_step(query, key, value, channel_idx, candidate_k, keep, *, prev_candidate=None, prev_final=None,
+                      protect_sink=0, protect_recent=0, keep_self=True, block_size=1, scaling=None, mask_rows=None):
+    """The rerank / reuse step of this project on the int4 path (parity unpinned for the int4 part; the union /
+    exact-score / top-keep / protected-range / block stages follow the reference, see rerank_union and
+    qabs_reuse_step): per KV head, candidates = int4 group-max top-candidate_k; union with the previous step's
+    candidate and final lists; exact rerank with the group maximum of q.k; keep the best `keep`; final set =
+    kept + protected ranges, widened to blocks; attention over final + self. Lists are int tensors [B,Hkv,n]
+    (-1 padded). Returns dict(candidates, kept, kept_count, final (list of lists per row), out)."""
+    B, Hq, D = query.shape
+    Hkv, Tk = key.shape[1], key.shape[2]
+    T = Tk - 1
+    scaling = D ** -0.5 if scaling is None else scaling
+    codes, _, kscale = quantize_pack(key[:, :, :T], channel_idx)
+    qcode, qscale = quantize_query(query, channel_idx)
+    _, _, gmax = score(qcode, qscale, codes, kscale)
+    cand, _ = select(gmax, candidate_k)
+    kept, kept_count = rerank_union(query, key, [cand, prev_candidate, prev_final], T, keep, scaling, mask_rows=mask_rows)
+    final = expand_final(kept, T, counts=kept_count, force_sink=protect_sink, force_recent=protect_recent,
+                         block_size=block_size)
+    S = max(len(f) for f in final) + (1 if keep_self else 0)
+    idx = torch.zeros((B, Hkv, S), dtype=torch.long)
+    valid = torch.zeros((B, Hkv, S), dtype=torch.bool)
+    for r, f in enumerate(final):
+        b, g = divmod(r, Hkv)
+        row = f + ([T] if keep_self else [])
+        idx[b, g, :len(row)] = torch.tensor(row, dtype=torch.long)
+        valid[b, g, :len(row)] = True
+    out, _, _ = attend_fp32(query, key, value, idx, valid, scaling, mask_rows)
+    return dict(candidates=cand, kept=kept, kept_count=kept_count, final=final, out=out)
+
+
 def quantize_query_tokens(query: torch.Tensor, channel_idx: torch.Tensor):
     """query bf16 [B,Hq,Tq,D] -> per-token qcode int8 [B,Hq,Tq,C], qscale fp32 [B,Hq,Tq]."""
     B, Hq, Tq, D = query.shape
@@ -231,6 +262,69 @@ def lse_merge(partials: torch.Tensor) -> torch.Tensor:
     O = (o * w[..., None]).sum(0)
     out = torch.where(L[..., None] > 0, O / L.clamp_min(1e-30)[..., None], torch.zeros_like(O))
     return out[:, None, :, :]
+
+
+def rerank_union(query, key, lists, history_count, keep, scaling, counts=None, mask_rows=None, force_sink=0,
+                 force_recent=0):
+    """List form of the reference's exact rerank (the candidate union of EVAL:4186-4214, the exact scores of
+    QCK:160-216 / EVAL:4287-4295, the top-keep of EVAL:4297-4302) with the tie rule of this project:
+    per list row, the union of the ids in ``lists`` (int [B,Hi,n_i], entries outside [0, history_count)
+    ignored, optional per-row counts) and of the forced ranges; score = max over the query heads sharing the
+    list of fp32 q.k, times scaling, plus mask; the min(keep, |union|) best by (score desc, id asc), returned
+    ascending and -1 padded with their count. query [B,Hq,D], key [B,Hkv,>=history_count,D]."""
+    B, Hq, D = query.shape
+    Hkv = key.shape[1]
+    Hi = lists[0].shape[1]
+    GG, G = Hq // Hi, Hq // Hkv
+    out = torch.full((B, Hi, keep), -1, dtype=torch.int64)
+    cnt = torch.zeros((B, Hi), dtype=torch.int64)
+    qf, kf = query.float(), key.float()
+    for b in range(B):
+        for hi in range(Hi):
+            ids = set()
+            for li, l in enumerate(lists):
+                if l is None:
+                    continue
+                n = l.shape[2] if counts is None or counts[li] is None else int(counts[li][b, hi])
+                ids.update(int(x) for x in l[b, hi, :n].tolist() if 0 <= int(x) < history_count)
+            ids.update(range(min(force_sink, history_count)))
+            ids.update(range(max(0, history_count - force_recent), history_count) if force_recent > 0 else ())
+            if not ids:
+                continue
+            u = torch.tensor(sorted(ids), dtype=torch.long)
+            heads = range(hi * GG, (hi + 1) * GG)
+            kv = (hi * GG) // G
+            sc = torch.stack([kf[b, kv, u] @ qf[b, h] for h in heads]).amax(0) * scaling
+            if mask_rows is not None:
+                sc = sc + mask_rows[b, u].float()
+            order = torch.sort(sc + 0.0, descending=True, stable=True).indices[:keep]          # u ascending: ties -> lower id
+            win = torch.sort(u[order]).values
+            out[b, hi, :win.numel()] = win
+            cnt[b, hi] = win.numel()
+    return out, cnt
+
+
+def expand_final(ids, history_count, counts=None, force_sink=0, force_recent=0, block_size=1):
+    """ids (any int tensor [..., n], out-of-range ignored) plus the protected ranges (EVAL:4306-4311), widened to
+    aligned blocks (EVAL:2914-2922): list of sorted python lists, one per leading row."""
+    flat = ids.reshape(-1, ids.shape[-1])
+    res = []
+    for r in range(flat.shape[0]):
+        n = flat.shape[1] if counts is None else int(counts.reshape(-1)[r])
+        keep = torch.zeros(history_count, dtype=torch.bool)
+        good = [int(x) for x in flat[r, :n].tolist() if 0 <= int(x) < history_count]
+        keep[good] = True
+        if force_sink > 0:
+            keep[:min(force_sink, history_count)] = True
+        if force_recent > 0:
+            keep[max(0, history_count - force_recent):] = True
+        if block_size > 1:
+            pad = (-history_count) % block_size
+            padded = F.pad(keep, (0, pad), value=False)
+            blk = padded.view(-1, block_size).any(dim=-1, keepdim=True).expand(-1, block_size).reshape(-1)
+            keep = blk[:history_count]
+        res.append(torch.nonzero(keep).flatten().tolist())
+    return res
 
 
 # ==========================================================================================
@@ -344,6 +438,129 @@ def qabs_candidate_attention(query_states, key_states, value_states, attention_m
     fidx, fvalid = final_indices_from_selected(cand, torch.ones_like(cand, dtype=torch.bool), history, key_count,
                                                always_keep_self, protect_sink, protect_recent, append_protected)
     return attention_from_final_indices(query_states, key_states, value_states, attention_mask, fidx, fvalid, scaling)
+
+
+def indices_from_keep_mask(keep: torch.Tensor):
+    """EVAL:2896-2911 (_indices_from_keep_mask): bool [B,H,T] -> padded indices (DESCENDING positions, as the
+    reference's topk over positions yields) and their validity."""
+    counts = keep.sum(dim=-1)
+    max_selected = int(counts.max().item()) if counts.numel() else 0
+    if max_selected <= 0:
+        empty = torch.zeros((*keep.shape[:-1], 0), dtype=torch.long)
+        return empty, torch.zeros_like(empty, dtype=torch.bool)
+    positions = torch.arange(keep.shape[-1], dtype=torch.long).view(1, 1, -1).expand_as(keep)
+    masked = torch.where(keep, positions, torch.full_like(positions, -1))
+    indices = torch.topk(masked, k=max_selected, dim=-1, largest=True).values
+    return indices.clamp_min(0), indices >= 0
+
+
+def expand_keep_to_aligned_blocks(keep: torch.Tensor, block_size: Optional[int]) -> torch.Tensor:
+    """EVAL:2914-2922 (_expand_history_keep_to_aligned_blocks)."""
+    if block_size is None or block_size <= 1 or keep.shape[-1] <= 1:
+        return keep
+    history_count = int(keep.shape[-1])
+    pad = (-history_count) % int(block_size)
+    padded = F.pad(keep, (0, pad), value=False) if pad else keep
+    blk = padded.view(*padded.shape[:-1], -1, int(block_size)).any(dim=-1, keepdim=True)
+    return blk.expand(*blk.shape[:-1], int(block_size)).reshape(*padded.shape[:-1], padded.shape[-1])[..., :history_count]
+
+
+def _pad_mask(mask: Optional[torch.Tensor], history_count: int) -> Optional[torch.Tensor]:
+    """EVAL:1603-1624 (ReuseCandidateState.previous_layer_masks): cut or zero-pad a stored mask to the new length."""
+    if mask is None:
+        return None
+    if mask.shape[-1] > history_count:
+        mask = mask[..., :history_count]
+    if mask.shape[-1] < history_count:
+        mask = F.pad(mask, (0, history_count - mask.shape[-1]), value=False)
+    return mask
+
+
+def qabs_reuse_step(query_states, key_states, value_states, scaling, dim_count, candidate_fraction, top_fraction,
+                    prev_candidate=None, prev_final=None, protect_sink=0, protect_recent=0, always_keep_self=True,
+                    use_prev_candidate=True, use_prev_final=True, block_size=None):
+    """EVAL:3991-4397 (_qabs_reuse_fast_attention_forward, torch branches, 'qabs{D}cand{C}reuse[2set|final][blkN]')
+    preceded by the K/V repeat of the dispatcher (EVAL:6248-6251): per head, current candidates = partial score
+    >= the requested-th largest (EVAL:3987-3989), union with the previous step's candidate and final masks
+    (EVAL:4186-4196), exact q.k on the union (EVAL:4287-4295), top ceil(top_fraction * T) (EVAL:4297-4302),
+    protected ranges forced in (EVAL:4306-4311), optional block widening (EVAL:4314-4316), attention over the
+    final list (EVAL:4364-4396). Returns (out [B,1,Hq,D], current candidate mask, final mask), the two masks being
+    what the reference stores for the next step (EVAL:4352-4362)."""
+    if key_states.shape[1] != query_states.shape[1]:
+        rep = query_states.shape[1] // key_states.shape[1]
+        key_states = key_states.repeat_interleave(rep, dim=1)
+        value_states = value_states.repeat_interleave(rep, dim=1)
+    B, H, _, D = query_states.shape
+    key_count = key_states.shape[-2]
+    history = key_count - 1
+    q_raw = query_states[:, :, 0, :]
+    k_history = key_states[:, :, :history, :]
+    d_s = min(max(1, dim_count), D)
+    requested = candidate_count(candidate_fraction, history)
+    partial, _ = qabs_partial_scores(q_raw, k_history, d_s)
+    threshold = torch.topk(partial, k=requested, dim=-1, largest=True).values[:, :, -1:]
+    current = partial >= threshold
+    union = current.clone()
+    pc, pf = _pad_mask(prev_candidate, history), _pad_mask(prev_final, history)
+    if pc is not None and use_prev_candidate:
+        union |= pc
+    if pf is not None and use_prev_final:
+        union |= pf
+    cand_idx, cand_valid = indices_from_keep_mask(union)
+    gather = cand_idx[:, :, :, None].expand(-1, -1, -1, D)
+    cand_keys = torch.gather(k_history, 2, gather)
+    cand_scores = torch.matmul(query_states[:, :, 0:1, :], cand_keys.transpose(2, 3)).squeeze(2) * scaling
+    cand_scores = cand_scores.masked_fill(~cand_valid, torch.finfo(cand_scores.dtype).min)
+    keep_count = min(min(history, max(1, math.ceil(top_fraction * history))), cand_scores.shape[-1])
+    _, pos = torch.topk(cand_scores, k=keep_count, dim=-1, largest=True)
+    sel_idx = torch.gather(cand_idx, -1, pos)
+    sel_valid = torch.gather(cand_valid, -1, pos)
+    final = torch.zeros_like(current)
+    final.scatter_(-1, sel_idx, sel_valid)
+    if protect_sink > 0:
+        final[:, :, :min(protect_sink, history)] = True
+    if protect_recent > 0:
+        final[:, :, max(0, history - protect_recent):history] = True
+    if block_size is not None:
+        final = expand_keep_to_aligned_blocks(final, block_size)
+        sel_idx, sel_valid = indices_from_keep_mask(final)
+    fidx, fvalid = final_indices_from_selected(sel_idx, sel_valid, history, key_count, always_keep_self, protect_sink,
+                                               protect_recent)
+    out = attention_from_final_indices(query_states, key_states, value_states, None, fidx, fvalid, scaling)
+    return out, current, final
+
+
+def qabs_top2_step(query_states, key_states, value_states, attention_mask, scaling, dim_count, candidate_fraction,
+                   top_fraction, protect_sink=0, protect_recent=0, always_keep_self=True):
+    """EVAL:4650-4766 (_qabs_candidate_top2_attention_forward, plain 'qabs{D}cand{C}top2attn') after the K/V repeat
+    of the dispatcher: top candidates by partial score, exact q.k (+ mask) on them, the best
+    min(candidates, ceil(top_fraction * T)) per head, attention over the final list. Returns (out, selected ids)."""
+    if key_states.shape[1] != query_states.shape[1]:
+        rep = query_states.shape[1] // key_states.shape[1]
+        key_states = key_states.repeat_interleave(rep, dim=1)
+        value_states = value_states.repeat_interleave(rep, dim=1)
+    B, H, _, D = query_states.shape
+    key_count = key_states.shape[-2]
+    history = key_count - 1
+    cc = candidate_count(candidate_fraction, history)
+    final_per_head = min(cc, max(1, math.ceil(top_fraction * history)))
+    q_raw = query_states[:, :, 0, :]
+    k_history = key_states[:, :, :history, :]
+    partial, _ = qabs_partial_scores(q_raw, k_history, min(max(1, dim_count), D))
+    _, cand = torch.topk(partial, k=cc, dim=-1, largest=True)
+    cand_keys = torch.gather(k_history, 2, cand[:, :, :, None].expand(-1, -1, -1, D))
+    scores = torch.matmul(query_states[:, :, 0:1, :], cand_keys.transpose(2, 3)).squeeze(2) * scaling
+    if attention_mask is not None:
+        mask_row = attention_mask[:, :, 0, :history]
+        if mask_row.shape[1] == 1 and H != 1:
+            mask_row = mask_row.expand(-1, H, -1)
+        scores = scores + torch.gather(mask_row, -1, cand)
+    _, pos = torch.topk(scores, k=final_per_head, dim=-1, largest=True)
+    sel = torch.gather(cand, -1, pos)
+    fidx, fvalid = final_indices_from_selected(sel, torch.ones_like(sel, dtype=torch.bool), history, key_count,
+                                               always_keep_self, protect_sink, protect_recent)
+    out = attention_from_final_indices(query_states, key_states, value_states, attention_mask, fidx, fvalid, scaling)
+    return out, sel
 
 
 def qabs_candidate_full_scores(query, key_history, current, previous_candidate, previous_final, protect_sink,

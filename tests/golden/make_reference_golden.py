@@ -11,6 +11,9 @@ evaluate_qwen3_top2_head_limit3_ppl.py):
   _qabs_attention_from_final_indices  EVAL:4612-4647 (torch branch)
   _limited_eager_attention_forward    EVAL:6236 -> _qabs_candidate_attention_forward EVAL:4400-4502
   parse_qabs_partial_rerank_params    EVAL:748-754
+  _qabs_reuse_fast_attention_forward  EVAL:3991-4397 with ReuseCandidateState EVAL:1596-1759 (three consecutive
+                                      decode steps; fp32 tensors holding bf16-representable values)
+  _qabs_candidate_top2_attention_forward EVAL:4650-4766
 """
 from __future__ import annotations
 
@@ -108,6 +111,50 @@ def main() -> None:
     k_sel = torch.gather(k_hist.float(), -1, qdim[:, :, None, :].expand(-1, -1, Tk - 1, -1))
     out["ps_scores"] = (k_sel * q_sel[:, :, None, :]).sum(-1).numpy()
     out["ps_qdim"] = qdim.numpy()
+
+    # ---- rerank + reuse over three consecutive steps (EVAL:3991-4397) and the top-2 % mode (EVAL:4650-4766) ----
+    # fp32 tensors whose values are exactly representable in bf16: the reference then forms its exact scores in
+    # fp32 (no bf16 rounding of q.k, hence no rounding ties at the cut), and a bf16 kernel sees the same numbers.
+    B, Hq, Hkv, D, T0 = 2, 8, 2, 128, 300
+    G = Hq // Hkv
+    rq = torch.randn(3, B, Hq, 1, D).to(torch.bfloat16).float()
+    rk = (torch.randn(B, Hkv, T0 + 3, D) * torch.exp(0.7 * torch.randn(1, Hkv, 1, D))).to(torch.bfloat16).float()
+    rv = torch.randn(B, Hkv, T0 + 3, D).to(torch.bfloat16).float()
+    out["ru_q"], out["ru_k"], out["ru_v"] = bits(rq.to(torch.bfloat16)), bits(rk.to(torch.bfloat16)), bits(rv.to(torch.bfloat16))
+    ru_mode, ru_top, ru_sink, ru_recent = "qabs16cand12p5reuse", 0.05, 2, 3
+    out["ru_mode"] = np.array([ru_mode])
+    out["ru_params"] = np.array([ru_top, ru_sink, ru_recent, T0])
+    state = ref.ReuseCandidateState()
+    for step in range(3):
+        kc = T0 + 1 + step
+        with ref.attention_mode(ru_mode, ru_top, 3, True, ru_sink, ru_recent, None, reuse_state=state, qabs_fast_path=True):
+            o, w = ref._limited_eager_attention_forward(_M(), rq[step], rk[:, :, :kc], rv[:, :, :kc], None, scaling=D ** -0.5)
+        assert w is None
+        rec = state.previous_layer[0]
+        assert rec["query_token"] == kc - 1
+        out[f"ru_{step}_candidate"] = rec["candidate"].numpy()          # bool [B,Hq,history]: this step's own candidates
+        out[f"ru_{step}_final"] = rec["final"].numpy()                  # bool [B,Hq,history]: kept set incl. protected ranges
+        out[f"ru_{step}_out"] = o.numpy()
+        # the cut must not sit on a near-tie (summation order differs between implementations)
+        hist = kc - 1
+        kr_ = rk[:, :, :hist].repeat_interleave(G, dim=1)
+        exact = torch.einsum("bhd,bhtd->bht", rq[step][:, :, 0], kr_) * D ** -0.5
+        keep = min(hist, max(1, __import__("math").ceil(ru_top * hist)))
+        union = torch.from_numpy(out[f"ru_{step}_candidate"]).clone()
+        if step > 0:
+            pc = torch.from_numpy(out[f"ru_{step - 1}_candidate"])
+            pf = torch.from_numpy(out[f"ru_{step - 1}_final"])
+            union[..., : pc.shape[-1]] |= pc | pf
+        srt = torch.sort(exact.masked_fill(~union, float("-inf")), dim=-1, descending=True).values
+        assert float((srt[..., keep - 1] - srt[..., keep]).min()) > 1e-4, "near-tie at the cut: change the seed"
+
+    t2_mode, t2_top = "qabs16cand12p5top2attn", 0.03
+    kc = T0 + 1
+    with ref.attention_mode(t2_mode, t2_top, 3, True, 2, 3, None, qabs_fast_path=True):
+        o, w = ref._limited_eager_attention_forward(_M(), rq[0], rk[:, :, :kc], rv[:, :, :kc], None, scaling=D ** -0.5)
+    out["t2_mode"] = np.array([t2_mode])
+    out["t2_params"] = np.array([t2_top, 2, 3])
+    out["t2_out"] = o.numpy()
 
     np.savez_compressed(OUT, **out)
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.1f} KiB), {len(out)} arrays")

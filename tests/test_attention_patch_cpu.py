@@ -11,8 +11,15 @@ def test_mode_strings_parse_like_the_reference():
     assert ap.parse_qabs_partial_rerank_params("qabs32cand6p25attn") == (32, 0.0625)
     assert ap.parse_qabs_partial_rerank_params("qabs64cand1p5625attn") == (64, 0.015625)
     assert ap.parse_qabs_partial_rerank_params("qabs8cand25appendattn") == (8, 0.25)
-    assert ap.parse_qabs_partial_rerank_params("qabs8cand3reuse") is None
+    assert ap.parse_qabs_partial_rerank_params("qabs8cand3reuse") == (8, 0.03)
+    assert ap.parse_qabs_partial_rerank_params("qabs8cand3keep") is None
     assert ap.parse_qabs_partial_rerank_params("baseline") is None
+    assert ap.parse_mode_kind("qabs8cand3reuse") == ("reuse", 1)
+    assert ap.parse_mode_kind("qabs8cand3reuse2setblk16") == ("reuse2set", 16)
+    assert ap.parse_mode_kind("qabs8cand3reusefinal") == ("reusefinal", 1)
+    assert ap.parse_mode_kind("qabs8cand3top2attn") == ("top2attn", 1)
+    assert ap.parse_mode_kind("qabs8cand3appendattn") == ("appendattn", 1)
+    assert ap.parse_mode_kind("qabs8cand3attn") == ("attn", 1)
 
 
 def test_candidate_count_and_mode_for_round_trip():

@@ -79,3 +79,66 @@ def test_candidate_count_rule():
     assert oracle.candidate_count(0.015625, 131072) == 2048
     assert oracle.candidate_count(0.5, 1) == 1
     assert oracle.candidate_count(0.0, 10) == 1
+
+
+def _f32(a):
+    return bf16(a).float()
+
+
+def test_reuse_steps_restated_against_the_reference():
+    """Three consecutive steps of the reference's rerank + reuse mode (EVAL:3991-4397): the masks it stores for
+    the next step and its outputs, from the oracle's restatement fed with its own previous masks."""
+    q, k, v = _f32(GOLD["ru_q"]), _f32(GOLD["ru_k"]), _f32(GOLD["ru_v"])
+    top, sink, recent, T0 = GOLD["ru_params"].tolist()
+    sink, recent, T0 = int(sink), int(recent), int(T0)
+    dims, frac = 16, 0.125
+    assert str(GOLD["ru_mode"][0]) == "qabs16cand12p5reuse"
+    pc = pf = None
+    for step in range(3):
+        kc = T0 + 1 + step
+        out, cur, fin = oracle.qabs_reuse_step(q[step], k[:, :, :kc], v[:, :, :kc], 128 ** -0.5, dims, frac, top, pc, pf,
+                                               sink, recent)
+        assert torch.equal(cur, torch.from_numpy(GOLD[f"ru_{step}_candidate"]))
+        assert torch.equal(fin, torch.from_numpy(GOLD[f"ru_{step}_final"]))
+        torch.testing.assert_close(out, torch.from_numpy(GOLD[f"ru_{step}_out"]), rtol=1e-5, atol=1e-6)
+        pc, pf = cur, fin
+
+
+def test_top2_step_restated_against_the_reference():
+    q, k, v = _f32(GOLD["ru_q"]), _f32(GOLD["ru_k"]), _f32(GOLD["ru_v"])
+    top, sink, recent = GOLD["t2_params"].tolist()
+    T0 = int(GOLD["ru_params"][3])
+    out, sel = oracle.qabs_top2_step(q[0], k[:, :, :T0 + 1], v[:, :, :T0 + 1], None, 128 ** -0.5, 16, 0.125, top,
+                                     int(sink), int(recent))
+    torch.testing.assert_close(out, torch.from_numpy(GOLD["t2_out"]), rtol=1e-5, atol=1e-6)
+    assert sel.shape[-1] == 9                                            # min(38 candidates, ceil(0.03 * 300))
+
+
+def test_list_rerank_equals_the_mask_form():
+    """oracle.rerank_union (lists, this project's tie rule) against the reference's mask form on the recorded
+    steps: per query head, the kept ids plus the protected ranges are exactly the reference's final mask."""
+    q, k = _f32(GOLD["ru_q"]), _f32(GOLD["ru_k"])
+    top, sink, recent, T0 = GOLD["ru_params"].tolist()
+    sink, recent, T0 = int(sink), int(recent), int(T0)
+    import math
+    for step in range(3):
+        hist = T0 + step
+        keep = min(hist, max(1, math.ceil(top * hist)))
+        masks = [torch.from_numpy(GOLD[f"ru_{step}_candidate"])]
+        if step:
+            masks += [torch.from_numpy(GOLD[f"ru_{step - 1}_candidate"]), torch.from_numpy(GOLD[f"ru_{step - 1}_final"])]
+        lists = []
+        for m in masks:
+            n = int(m.sum(-1).max())
+            ids = torch.full((*m.shape[:2], n), -1, dtype=torch.long)
+            for b in range(m.shape[0]):
+                for h in range(m.shape[1]):
+                    nz = torch.nonzero(m[b, h]).flatten()
+                    ids[b, h, :nz.numel()] = nz
+            lists.append(ids)
+        kept, cnt = oracle.rerank_union(q[step][:, :, 0], k[:, :, :hist], lists, hist, keep, 128 ** -0.5)
+        final = oracle.expand_final(kept, hist, counts=cnt, force_sink=sink, force_recent=recent)
+        want = torch.from_numpy(GOLD[f"ru_{step}_final"])
+        for r, f in enumerate(final):
+            b, h = divmod(r, want.shape[1])
+            assert f == torch.nonzero(want[b, h]).flatten().tolist()
