@@ -374,6 +374,40 @@ int kvb_expand_final(const int32_t* list, int n, const int32_t* count, int R, in
                      int force_sink, int force_recent, int block_size,
                      int32_t* out_idx, int out_cap, int32_t* out_count, int device, void* stream);
 
+/* SparQ-style mean-value correction (the reference's "sparqfast" mode,
+ * _sparq_fast_attention_output_for_query, EVAL:2646-2722, with its running mean of V, EVAL:2006-2016):
+ * the exact attention over the selected tokens is blended with the mean of V by the softmax mass alpha that
+ * the selected tokens carry under the APPROXIMATE logits. Here those logits are the dequantised int4 partial
+ * scores of the side cache, s[b,h,t] = deq[b,h,t] / sqrt(D * |q_sel|_1 / |q|_1) (+ mask[b,t]), q_sel = the
+ * query on the layer's channel list (EVAL:2683-2686 for the scale), softmax over all T cached tokens.
+ *   kvb_sparq_alpha         alpha fp32 [B*Hq] = sum over the ids in `selected` (int32 [B*Hkv, kk], optional
+ *                           per-row sel_count, ids outside [0,T) ignored) of softmax_h(s)[id]. One streaming
+ *                           pass over the int4 cache plus a re-score of the selected rows; C a multiple of 8,
+ *                           G <= 8. workspace >= kvb_sparq_alpha_workspace_bytes(B, Hq, T).
+ *   kvb_attend_selected_blend  kvb_attend_selected (no protected ranges, local ids) whose output is
+ *                           value_mean + alpha * (attention - value_mean); value_mean fp32 [B,Hkv,D] dense is
+ *                           the caller's running mean of V over all Tk rows. */
+size_t kvb_sparq_alpha_workspace_bytes(int B, int Hq, int T);
+
+int kvb_sparq_alpha(const void* query, int64_t q_sb, int64_t q_sh,
+                    const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                    const float* scale, int64_t scale_sb, int64_t scale_sh,
+                    const int32_t* channel_idx, const float* mask, int64_t mask_sb,
+                    const int32_t* selected, int kk, const int32_t* sel_count,
+                    int B, int Hq, int Hkv, int T, int D, int C,
+                    float* alpha, void* workspace, size_t workspace_bytes, int device, void* stream);
+
+int kvb_attend_selected_blend(const void* query, int64_t q_sb, int64_t q_sh,
+                              const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+                              const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st,
+                              const int32_t* selected, int kk, const int32_t* sel_count,
+                              int history_count, int keep_self,
+                              const float* mask, int64_t mask_sb,
+                              const float* alpha, const float* value_mean,
+                              int B, int Hq, int Hkv, int Tk, int D, float scaling,
+                              void* out, void* workspace, size_t workspace_bytes,
+                              int device, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Sequence-sharded decode step without a collective call (no counterpart in the reference, which
  * has no sharding). Rank r of `world` owns the history tokens [id_offset, id_offset + t_local) of

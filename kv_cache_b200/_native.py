@@ -111,6 +111,11 @@ SIGNATURES = {
     "kvb_rerank_union_workspace_bytes": (_sz, [_i, _i]),
     "kvb_rerank_union": (_i, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i, _p, _p, _i, _p, _p, _i, _p, _i, _i,
                               _p, _i64, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p, _sz, _i, _p]),
+    "kvb_sparq_alpha_workspace_bytes": (_sz, [_i, _i, _i]),
+    "kvb_sparq_alpha": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p, _p, _i64, _p, _i, _p,
+                             _i, _i, _i, _i, _i, _i, _p, _p, _sz, _i, _p]),
+    "kvb_attend_selected_blend": (_i, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _p, _i, _p,
+                                       _i, _i, _p, _i64, _p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _sz, _i, _p]),
     "kvb_expand_final": (_i, [_p, _i, _p, _i, _i, _i, _i, _i, _p, _i, _p, _i, _p]),
     "kvb_sharded_exchange_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "kvb_sharded_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

@@ -15,6 +15,9 @@ this package implements:
     qabs{C}cand{P}reuse            candidates + the previous step's candidates and final set, exact q.k on the
       [2set|final][blk{N}]         union, the best ceil(top_fraction * T), protected ranges forced in, optional
                                    widening to aligned blocks of N tokens (EVAL:3991-4397, 1596-1759, 2914-2922)
+    sparqfast{C}cand{P}            top ceil(P% * keys) of ALL keys (the decoded token included), exact attention
+                                   over them blended with the running mean of V by the softmax mass they carry
+                                   under the approximate logits (EVAL:2646-2722, 2006-2016)
 
 with the int4 scorer and GQA-group selection in place of the reference's fp32 per-head scoring: one
 candidate list, one exact rerank (maximum of q.k over the group's query heads) and one final list per KV head.
@@ -48,6 +51,17 @@ def parse_qabs_partial_rerank_params(mode: str) -> Optional[tuple[int, float]]:
     """``(channels, candidate_fraction)`` of a ``qabs{C}cand{P}...`` mode string this package implements, else
     None. ``P`` is a percentage with ``p`` as the decimal point (``6p25`` = 6.25 %), as in EVAL:748-754."""
     m = _QABS_RE.fullmatch(mode)
+    if not m:
+        return None
+    return int(m.group(1)), float(m.group(2).replace("p", ".")) / 100.0
+
+
+_SPARQ_RE = re.compile(r"sparqfast(\d+)cand(\d+(?:p\d+)?)")
+
+
+def parse_sparq_params(mode: str) -> Optional[tuple[int, float]]:
+    """``(channels, candidate_fraction)`` of ``sparqfast{C}cand{P}`` (EVAL:892-898), else None."""
+    m = _SPARQ_RE.fullmatch(mode)
     if not m:
         return None
     return int(m.group(1)), float(m.group(2).replace("p", ".")) / 100.0
@@ -110,6 +124,8 @@ class SparseDecodeState:
     layers: dict[int, LayerSideCache] = field(default_factory=dict)
     steps: dict[tuple, ops.DecodeStep] = field(default_factory=dict)
     growth: int = 4096                  # capacity headroom (tokens) when a side cache is (re)allocated
+    capacity_hint: int = 0              # allocate side caches for at least this many tokens (the capacity of a
+                                        # pre-allocated KV cache): no re-allocation during a decode
     # The static channel set is chosen from the keys that exist at a layer's first sparse call. When that
     # call comes early (token-by-token evaluation from the first token) the choice rests on a handful of
     # rows, so it is made again, once, when the history first reaches this many tokens (the prefix is then
@@ -118,10 +134,29 @@ class SparseDecodeState:
     channel_lists: dict[int, torch.Tensor] = field(default_factory=dict)    # optional per-layer int32 [Hkv,C] from the caller
     bulk_quantized_rows: int = 0        # rows ever sent through the bulk quantizer (tests read this)
     reuse: dict[int, LayerReuse] = field(default_factory=dict)
+    value_means: dict[int, tuple[int, torch.Tensor]] = field(default_factory=dict)    # layer -> (rows, fp32 [B,Hkv,D])
 
     def reset(self) -> None:
         self.layers.clear()
         self.reuse.clear()
+        self.value_means.clear()
+
+    def value_mean(self, layer_idx: int, value_states: torch.Tensor) -> torch.Tensor:
+        """Mean of V over all key rows, fp32 ``[B,Hkv,D]``, kept per layer and updated by the one new row when the
+        call continues the previous one (SparQMeanState.value_mean, EVAL:2006-2016)."""
+        key_count = value_states.shape[2]
+        prev = self.value_means.get(layer_idx)
+        if prev is not None and prev[0] == key_count - 1 and prev[1].shape[:2] == value_states.shape[:2] \
+                and prev[1].device == value_states.device:
+            mean = (prev[1] * float(key_count - 1) + value_states[:, :, -1, :].float()) / float(key_count)
+        else:
+            mean = torch.zeros((*value_states.shape[:2], value_states.shape[-1]), dtype=torch.float32,
+                               device=value_states.device)
+            for t0 in range(0, key_count, 65536):                        # bounded fp32 temporaries
+                mean += value_states[:, :, t0:t0 + 65536].float().sum(dim=2)
+            mean /= float(key_count)
+        self.value_means[layer_idx] = (key_count, mean)
+        return mean
 
     def observe(self, layer_idx: int, key_count: int, query_count: int) -> None:
         """Called for every attention call that does NOT take the sparse path (baseline mode, prefill
@@ -148,7 +183,8 @@ class SparseDecodeState:
                 ch = given.to(device=key_states.device, dtype=torch.int32).contiguous()
             else:
                 ch = ops.choose_channels(key_states[:, :, :history], channels)
-            packed, scale = ops.alloc_side_cache(B, Hkv, history + 1 + self.growth, channels, key_states.device)
+            packed, scale = ops.alloc_side_cache(B, Hkv, max(history + 1 + self.growth, self.capacity_hint), channels,
+                                                 key_states.device)
             sc = LayerSideCache(ch, packed, scale, 0, history, history, given is not None)
             self.layers[layer_idx] = sc
         elif sc.packed.shape[2] < history + 1:
@@ -210,9 +246,14 @@ def sparse_eager_attention_forward(module: torch.nn.Module, query_states: torch.
         state.observe(layer_idx, key_count, query_states.shape[2])
         return _ORIGINAL_EAGER_ATTENTION_FORWARD(module, query_states, key_states, value_states, attention_mask,
                                                  scaling=scaling, dropout=dropout, **kwargs)
+    sparq = parse_sparq_params(mode)
+    if sparq is not None:
+        if query_states.shape[2] != 1:
+            raise RuntimeError("SparQ fast mode requires token-by-token eval; set --eval_chunk_size 1.")   # EVAL:6359-6360
+        return _sparq_forward(state, layer_idx, sparq, query_states, key_states, value_states, attention_mask, scaling), None
     params = parse_qabs_partial_rerank_params(mode)
     if params is None:
-        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}' + attn | appendattn | top2attn | reuse[2set|final][blkN]; got mode {mode!r}")
+        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}' + attn | appendattn | top2attn | reuse[2set|final][blkN], 'sparqfast{{C}}cand{{P}}'; got mode {mode!r}")
     channels, fraction = params
     if query_states.shape[2] != 1:
         # same contract as EVAL:4413-4414
@@ -235,6 +276,29 @@ def sparse_eager_attention_forward(module: torch.nn.Module, query_states: torch.
                attention_mask=attention_mask, top_k=top_k)
     sc.count = sc.seen = key_count      # the fused step appended the current token's row
     return out, None
+
+
+def _sparq_forward(state: SparseDecodeState, layer_idx: int, params: tuple[int, float], query_states, key_states,
+                   value_states, attention_mask, scaling: float) -> torch.Tensor:
+    """``sparqfast{C}cand{P}``: every key row (the decoded token's too) is in the int4 cache; the best
+    ceil(P * keys) per KV head are attended exactly and the result is blended with the running mean of V."""
+    channels, fraction = params
+    key_count = key_states.shape[-2]
+    channels = min(max(8, (channels + 7) // 8 * 8), key_states.shape[-1])
+    if key_count <= 1:
+        state.observe(layer_idx, key_count, 1)
+        rep = query_states.shape[1] // value_states.shape[1]
+        return value_states[:, :, -1:, :].transpose(1, 2).repeat_interleave(rep, dim=2).contiguous()
+    history = key_count - 1
+    sc = state.side_cache(layer_idx, key_states, history, channels)
+    ops.quantize_append(key_states[:, :, history], sc.channel_idx, sc.packed, sc.scale, history)
+    sc.count = sc.seen = key_count
+    cand_k = min(key_count, max(1, math.ceil(fraction * key_count)))       # EVAL:2661
+    sel = ops.score_select(query_states, sc.packed, sc.scale, sc.channel_idx, key_count, cand_k)
+    alpha = ops.sparq_alpha(query_states, sc.packed, sc.scale, sc.channel_idx, key_count, sel, attention_mask=attention_mask)
+    vmean = state.value_mean(layer_idx, value_states)
+    return ops.attend_selected_blend(query_states, key_states, value_states, sel, key_count, alpha, vmean, keep_self=False,
+                                     scaling=scaling, attention_mask=attention_mask)
 
 
 def _rerank_forward(state: SparseDecodeState, layer_idx: int, sc: LayerSideCache, kind: str, block: int, cand_k: int,
@@ -329,8 +393,8 @@ def attention_mode(mode: str, top_fraction: float = 0.02, max_heads_per_token: i
     Yields the state in use."""
     global _ACTIVE_MODE, _ACTIVE_TOP_FRACTION, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS
     global _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE
-    if mode != "baseline" and parse_qabs_partial_rerank_params(mode) is None:
-        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}' + attn | appendattn | top2attn | reuse[2set|final][blkN]; got mode {mode!r}")
+    if mode != "baseline" and parse_qabs_partial_rerank_params(mode) is None and parse_sparq_params(mode) is None:
+        raise RuntimeError(f"kv_cache_b200 implements 'baseline' and 'qabs{{C}}cand{{P}}' + attn | appendattn | top2attn | reuse[2set|final][blkN], 'sparqfast{{C}}cand{{P}}'; got mode {mode!r}")
     previous = (_ACTIVE_MODE, _ACTIVE_TOP_FRACTION, _ACTIVE_ALWAYS_KEEP_SELF, _ACTIVE_PROTECT_SINK_TOKENS,
                 _ACTIVE_PROTECT_RECENT_TOKENS, _ACTIVE_STATE)
     _ACTIVE_MODE = mode

@@ -9,6 +9,7 @@
 #include "decode_step.cu"
 #include "sharded_step.cu"
 #include "rerank.cu"
+#include "sparq.cu"
 #include "score_prefill_tc.cu"
 #include "score_prefill.cu"
 #include "qabs_fp32.cu"

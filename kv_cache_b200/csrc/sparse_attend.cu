@@ -91,6 +91,9 @@ struct AttendParams {
   int top_k, protect_sink, protect_recent, keep_self;
   int advance_history;        // the merge kernel adds one to *T_dev when everything else is done
   PartialPush ppush;          // sequence-sharded step: the merged (o, m, l) of every head goes to all ranks' inboxes
+  // optional mean-value blend (SparQ): out = mean + alpha * (attention - mean)
+  const float* blend_alpha;   // fp32 [B*Hq] or NULL
+  const float* blend_mean;    // fp32 [B,Hkv,D] dense
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -438,7 +441,15 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
     for (int u = 0; u < 8; ++u) O += (sp + u < p.nsplit) ? x[u] * s_w[sp + u] : 0.0f;
   }
   const float M = s_ml[0], L = s_ml[1];
-  if (p.out) p.out[((int64_t)b * p.Hq + head) * AT_D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+  if (p.out) {
+    float res = L > 0.0f ? O / L : 0.0f;
+    if (p.blend_alpha) {
+      const float a = p.blend_alpha[(int64_t)b * p.Hq + head];
+      const float vm = p.blend_mean[((int64_t)b * p.Hkv + head / p.G) * AT_D + d];
+      res = fmaf(a, res - vm, vm);
+    }
+    p.out[((int64_t)b * p.Hq + head) * AT_D + d] = __float2bfloat16_rn(res);
+  }
   if (p.advance_history && p.T_dev && blockIdx.x == 0 && d == 0) *const_cast<int32_t*>(p.T_dev) += 1;
   if (p.out_partial) {
     float* op = p.out_partial + ((int64_t)b * p.Hq + head) * PW;
@@ -595,7 +606,8 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
                       const float* mask, int64_t mask_sb,
                       int B, int Hq, int Hkv, int Hi, int Tk, int D, int S, float scaling, void* out,
                       float* out_partial, uint32_t* ws_counter, float* ws_partial, bool counters_zeroed, int device,
-                      cudaStream_t st, const PartialPush* ppush = nullptr) {
+                      cudaStream_t st, const PartialPush* ppush = nullptr, const float* blend_alpha = nullptr,
+                      const float* blend_mean = nullptr) {
   if (!query || !key || !value || !ws_counter || !ws_partial) return KVB_BAD_ARG;
   if (list.implicit ? (!list.selected && list.kk > 0) : !list.indices) return KVB_BAD_ARG;
   if (!out && !out_partial && !ppush) return KVB_BAD_ARG;
@@ -634,6 +646,7 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
   p.ws_partial = ws_partial;
   p.nsplit = plan.nsplit; p.tiles_per_split = plan.tiles_per_split;
   if (ppush) p.ppush = *ppush;
+  p.blend_alpha = blend_alpha; p.blend_mean = blend_mean;
 
   (void)counters_zeroed;   // the chunk merge is its own launch: no arrival counters to clear
   switch (GG) {
@@ -666,17 +679,20 @@ extern "C" __attribute__((visibility("default"))) int kvb_sparse_attend(
                     /*counters_zeroed=*/false, device, reinterpret_cast<cudaStream_t>(stream));
 }
 
-extern "C" __attribute__((visibility("default"))) int kvb_attend_selected(
+namespace kvb {
+static int attend_selected_impl(
     const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
     const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st, const int32_t* selected, int kk,
     const int32_t* sel_count, int64_t id_base,
     int history_count, int protect_sink, int protect_recent, int keep_self, int append_protected, const float* mask,
     int64_t mask_sb, int B, int Hq, int Hkv, int Tk, int D, float scaling, void* out, float* out_partial,
-    void* workspace, size_t workspace_bytes, int device, void* stream) {
-  using namespace kvb;
+    void* workspace, size_t workspace_bytes, const float* blend_alpha, const float* blend_mean, int device,
+    void* stream) {
   if (!workspace || (!selected && kk > 0)) return KVB_BAD_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || kk < 0 || history_count < 0 || (Hq % Hkv)) return KVB_BAD_SHAPE;
   if (Tk < history_count + (keep_self ? 1 : 0)) return KVB_BAD_SHAPE;
+  if ((blend_alpha == nullptr) != (blend_mean == nullptr)) return KVB_BAD_ARG;
+  if (blend_alpha && !out) return KVB_BAD_ARG;
   if (!aligned_to(workspace, 256)) return KVB_BAD_ALIGN;
   const FinalLayout f = final_layout(kk, history_count, protect_sink, protect_recent, keep_self);
   if (f.S <= 0) return KVB_BAD_SHAPE;
@@ -695,7 +711,34 @@ extern "C" __attribute__((visibility("default"))) int kvb_attend_selected(
                     B, Hq, Hkv, Hkv, keep_self ? history_count + 1 : history_count, D, f.S, scaling, out, out_partial,
                     reinterpret_cast<uint32_t*>(workspace),
                     reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plan.counter_bytes),
-                    /*counters_zeroed=*/false, device, reinterpret_cast<cudaStream_t>(stream));
+                    /*counters_zeroed=*/false, device, reinterpret_cast<cudaStream_t>(stream), nullptr, blend_alpha,
+                    blend_mean);
+}
+}  // namespace kvb
+
+extern "C" __attribute__((visibility("default"))) int kvb_attend_selected(
+    const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+    const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st, const int32_t* selected, int kk,
+    const int32_t* sel_count, int64_t id_base,
+    int history_count, int protect_sink, int protect_recent, int keep_self, int append_protected, const float* mask,
+    int64_t mask_sb, int B, int Hq, int Hkv, int Tk, int D, float scaling, void* out, float* out_partial,
+    void* workspace, size_t workspace_bytes, int device, void* stream) {
+  return kvb::attend_selected_impl(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, selected, kk,
+                                   sel_count, id_base, history_count, protect_sink, protect_recent, keep_self,
+                                   append_protected, mask, mask_sb, B, Hq, Hkv, Tk, D, scaling, out, out_partial,
+                                   workspace, workspace_bytes, nullptr, nullptr, device, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_attend_selected_blend(
+    const void* query, int64_t q_sb, int64_t q_sh, const void* key, int64_t k_sb, int64_t k_sh, int64_t k_st,
+    const void* value, int64_t v_sb, int64_t v_sh, int64_t v_st, const int32_t* selected, int kk,
+    const int32_t* sel_count, int history_count, int keep_self, const float* mask, int64_t mask_sb,
+    const float* alpha, const float* value_mean, int B, int Hq, int Hkv, int Tk, int D, float scaling, void* out,
+    void* workspace, size_t workspace_bytes, int device, void* stream) {
+  if (!alpha || !value_mean || !out) return KVB_BAD_ARG;
+  return kvb::attend_selected_impl(query, q_sb, q_sh, key, k_sb, k_sh, k_st, value, v_sb, v_sh, v_st, selected, kk,
+                                   sel_count, 0, history_count, 0, 0, keep_self, 0, mask, mask_sb, B, Hq, Hkv, Tk, D,
+                                   scaling, out, nullptr, workspace, workspace_bytes, alpha, value_mean, device, stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int kvb_lse_merge(const float* partials, int N, int B, int Hq, int D, void* out, int device,

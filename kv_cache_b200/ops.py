@@ -398,6 +398,68 @@ def attend_selected(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
     return part if return_partial else out
 
 
+def sparq_alpha(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
+                history_count: int, selected: torch.Tensor, *, selected_count: Optional[torch.Tensor] = None,
+                attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Softmax mass, under the approximate (int4 partial) logits, of the tokens in ``selected`` (int32
+    ``[B,Hkv,kk]``) among all ``history_count`` cached tokens: fp32 ``[B,Hq]`` (the alpha of the reference's
+    SparQ blend, EVAL:2720-2722)."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    Hkv = packed.shape[1]
+    C_ = int(channel_idx.shape[-1])
+    _check_side_cache(packed, scale, C_)
+    T = int(history_count)
+    dev = query.device
+    selected = selected.to(torch.int32).contiguous()
+    cnt = None if selected_count is None else selected_count.reshape(-1).to(torch.int32).contiguous()
+    mask = _mask_rows(attention_mask, B, T)
+    lib = _native.lib()
+    ws = torch.empty(max(256, lib.kvb_sparq_alpha_workspace_bytes(B, Hq, T)), dtype=torch.uint8, device=dev)
+    alpha = torch.empty((B, Hq), dtype=torch.float32, device=dev)
+    check(lib.kvb_sparq_alpha(
+        query.data_ptr(), query.stride(0), query.stride(1), packed.data_ptr(), packed.stride(0), packed.stride(1),
+        scale.data_ptr(), scale.stride(0), scale.stride(1), channel_idx.data_ptr(), _ptr(mask),
+        0 if mask is None else mask.stride(0), selected.data_ptr(), int(selected.shape[-1]), _ptr(cnt),
+        B, Hq, Hkv, T, D, C_, alpha.data_ptr(), ws.data_ptr(), ws.numel(), _dev(query), _stream(dev)), "kvb_sparq_alpha")
+    return alpha
+
+
+def attend_selected_blend(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, selected: torch.Tensor,
+                          history_count: int, alpha: torch.Tensor, value_mean: torch.Tensor, *, keep_self: bool = False,
+                          scaling: Optional[float] = None, attention_mask: Optional[torch.Tensor] = None,
+                          selected_count: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``value_mean + alpha * (attention over selected - value_mean)`` (``torch.lerp(mean, exact, alpha)`` of
+    EVAL:2722) in one attention call: ``alpha`` fp32 ``[B,Hq]``, ``value_mean`` fp32 ``[B,Hkv,D]``."""
+    query = _query3(query)
+    B, Hq, D = query.shape
+    Hkv, Tk = key.shape[1], key.shape[2]
+    key = _rows_contiguous(key)
+    value = _rows_contiguous(value)
+    selected = selected.to(torch.int32).contiguous()
+    kk = selected.shape[2]
+    cnt = None if selected_count is None else selected_count.reshape(-1).to(torch.int32).contiguous()
+    if scaling is None:
+        scaling = float(D) ** -0.5
+    dev = query.device
+    mask = _mask_rows(attention_mask, B, Tk)
+    alpha = alpha.to(torch.float32).contiguous()
+    value_mean = value_mean.to(torch.float32).contiguous()
+    lib = _native.lib()
+    S = lib.kvb_final_index_count(kk, history_count, 0, 0, int(keep_self))
+    ws = torch.empty(max(lib.kvb_sparse_attend_workspace_bytes(B, Hq, Hkv, S), 256), dtype=torch.uint8, device=dev)
+    out = torch.empty((B, 1, Hq, D), dtype=torch.bfloat16, device=dev)
+    check(lib.kvb_attend_selected_blend(
+        query.data_ptr(), query.stride(0), query.stride(1),
+        key.data_ptr(), key.stride(0), key.stride(1), key.stride(2),
+        value.data_ptr(), value.stride(0), value.stride(1), value.stride(2),
+        selected.data_ptr(), kk, _ptr(cnt), int(history_count), int(keep_self), _ptr(mask),
+        0 if mask is None else mask.stride(0), alpha.data_ptr(), value_mean.data_ptr(),
+        B, Hq, Hkv, Tk, D, float(scaling), out.data_ptr(), ws.data_ptr(), ws.numel(), _dev(query), _stream(dev)),
+        "kvb_attend_selected_blend")
+    return out
+
+
 def shard_candidates(query: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, channel_idx: torch.Tensor,
                      history_count: int, top_k: int, id_offset: int = 0,
                      workspace: Optional[torch.Tensor] = None, split_k: int = 0) -> Optional[torch.Tensor]:

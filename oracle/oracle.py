@@ -210,6 +210,95 @@ def reuse_decode_step(query, key, value, channel_idx, candidate_k, keep, *, prev
     return dict(candidates=cand, kept=kept, kept_count=kept_count, final=final, out=out)
 
 
+def sparq_alpha(query, deq, selected, channel_idx, mask_rows=None):
+    """alpha[b,h] = softmax mass, over all T tokens, of the ids in selected[b, h // G] under the logits
+    deq[b,h,t] / sqrt(D * |q_sel|_1 / |q|_1) (+ mask): the blend weight of EVAL:2683-2686, 2720-2722 with the
+    dequantised int4 partial score as the approximate logit."""
+    B, Hq, D = query.shape
+    Hkv = channel_idx.shape[0]
+    G = Hq // Hkv
+    T = deq.shape[-1]
+    qf = query.float()
+    idx = channel_idx.long().repeat_interleave(G, dim=0)[None].expand(B, Hq, -1)
+    sel_abs = torch.gather(qf, -1, idx).abs().sum(-1).clamp_min(1.0e-6)
+    all_abs = qf.abs().sum(-1).clamp_min(1.0e-6)
+    ds = torch.sqrt(D * sel_abs / all_abs)
+    logits = deq.double() / ds[..., None].double()
+    if mask_rows is not None:
+        logits = logits + mask_rows[:, None, :T].double()
+    w = torch.softmax(logits, dim=-1)
+    alpha = torch.zeros((B, Hq), dtype=torch.float64)
+    for b in range(B):
+        for h in range(Hq):
+            ids = [int(x) for x in selected[b, h // G].tolist() if 0 <= int(x) < T]
+            alpha[b, h] = w[b, h, sorted(set(ids))].sum()
+    return alpha.float()
+
+
+def sparq_decode_step(query, key, value, channel_idx, top_k, *, scaling=None, mask_rows=None):
+    """The mean-value-corrected step of this project on the int4 path (parity unpinned for the int4 part): ALL
+    key rows (the decoded token's included) are quantized and scored, the top-k per KV head (group max, lower
+    id on ties) are attended exactly, alpha from sparq_alpha, out = mean(V) + alpha * (exact - mean(V)) with the
+    mean over all key rows in fp32 (EVAL:2646-2722 with the int4 logits). Returns dict(selected, alpha, vmean, out)."""
+    B, Hq, D = query.shape
+    Tk = key.shape[2]
+    scaling = D ** -0.5 if scaling is None else scaling
+    codes, _, kscale = quantize_pack(key, channel_idx)
+    qcode, qscale = quantize_query(query, channel_idx)
+    _, deq, gmax = score(qcode, qscale, codes, kscale)
+    sel, _ = select(gmax, top_k)
+    alpha = sparq_alpha(query, deq, sel, channel_idx, mask_rows)
+    exact, _, _ = attend_fp32(query, key, value, sel, None, scaling, mask_rows)
+    G = Hq // key.shape[1]
+    vmean = value.float().mean(dim=2)                                   # [B,Hkv,D]
+    vm = vmean.repeat_interleave(G, dim=1)[:, None]                     # [B,1,Hq,D]
+    out = vm + alpha[:, None, :, None] * (exact - vm)
+    return dict(selected=sel, alpha=alpha, vmean=vmean, out=out)
+
+
+def sparq_fast_step(query_states, key_states, value_states, attention_mask, scaling, dim_count, candidate_fraction,
+                    value_mean=None):
+    """EVAL:2646-2722 (_sparq_fast_attention_output_for_query, torch branches, one query token) after the K/V
+    repeat of the dispatcher (EVAL:6248-6251): approximate logits from the dim_count channels with the largest
+    |q| per head, softmax over all keys, exact attention over the top ceil(fraction * keys) of them, blended
+    with the mean of V by the approximate mass they carry. query [B,H,1,D] -> [B,1,H,D]."""
+    if key_states.shape[1] != query_states.shape[1]:
+        rep = query_states.shape[1] // key_states.shape[1]
+        key_states = key_states.repeat_interleave(rep, dim=1)
+        value_states = value_states.repeat_interleave(rep, dim=1)
+    B, H, _, D = query_states.shape
+    key_count = key_states.shape[-2]
+    d_s = min(max(1, dim_count), D)
+    cc = min(key_count, max(1, math.ceil(candidate_fraction * key_count)))
+    q = query_states[:, :, 0:1, :]
+    abs_q = q.float().abs()
+    abs_q_hat, dim_indices = torch.topk(abs_q, k=d_s, dim=-1, largest=True, sorted=False)
+    q_sel = torch.gather(q.float(), -1, dim_indices)
+    k_sel = torch.gather(key_states.float(), -1, dim_indices.expand(B, H, key_count, d_s))
+    approx = torch.matmul(q_sel, k_sel.transpose(2, 3))
+    divscale = torch.sqrt(torch.tensor(float(D)) * abs_q_hat.sum(-1, keepdim=True).clamp_min(1.0e-6)
+                          / abs_q.sum(-1, keepdim=True).clamp_min(1.0e-6))
+    approx = approx / divscale
+    mask_row = None
+    if attention_mask is not None:
+        mask_row = attention_mask[:, :, 0:1, :key_count]
+        if mask_row.shape[1] == 1 and H != 1:
+            mask_row = mask_row.expand(-1, H, -1, -1)
+        approx = approx + mask_row
+    w = F.softmax(approx, dim=-1, dtype=torch.float32)
+    mass, top = torch.topk(w, k=cc, dim=-1, largest=True, sorted=False)
+    gi = top[..., None].expand(B, H, 1, cc, D).squeeze(2)
+    sk, sv = torch.gather(key_states, 2, gi), torch.gather(value_states, 2, gi)
+    exact_scores = torch.matmul(q, sk.transpose(2, 3)) * scaling
+    if mask_row is not None:
+        exact_scores = exact_scores + torch.gather(mask_row, -1, top)
+    exact = torch.matmul(F.softmax(exact_scores, dim=-1, dtype=torch.float32).to(q.dtype), sv)
+    if value_mean is None:
+        value_mean = value_states.float().mean(dim=2, keepdim=True).to(value_states.dtype)
+    alpha = mass.sum(-1, keepdim=True).to(q.dtype)
+    return torch.lerp(value_mean, exact, alpha).transpose(1, 2).contiguous()
+
+
 def quantize_query_tokens(query: torch.Tensor, channel_idx: torch.Tensor):
     """query bf16 [B,Hq,Tq,D] -> per-token qcode int8 [B,Hq,Tq,C], qscale fp32 [B,Hq,Tq]."""
     B, Hq, Tq, D = query.shape

@@ -14,6 +14,7 @@ evaluate_qwen3_top2_head_limit3_ppl.py):
   _qabs_reuse_fast_attention_forward  EVAL:3991-4397 with ReuseCandidateState EVAL:1596-1759 (three consecutive
                                       decode steps; fp32 tensors holding bf16-representable values)
   _qabs_candidate_top2_attention_forward EVAL:4650-4766
+  _sparq_fast_attention_output_for_query EVAL:2646-2722 with SparQMeanState.value_mean EVAL:2006-2016 (two steps)
 """
 from __future__ import annotations
 
@@ -155,6 +156,17 @@ def main() -> None:
     out["t2_mode"] = np.array([t2_mode])
     out["t2_params"] = np.array([t2_top, 2, 3])
     out["t2_out"] = o.numpy()
+
+    # ---- SparQ fast mode with its running mean of V, two consecutive steps (EVAL:2646-2722, 2006-2016) ----
+    sq_mode = "sparqfast16cand12p5"
+    out["sq_mode"] = np.array([sq_mode])
+    sq_state = ref.SparQMeanState()
+    for step in range(2):
+        kc = T0 + 1 + step
+        with ref.attention_mode(sq_mode, 0.02, 3, True, 0, 0, None, sparq_mean_state=sq_state, qabs_fast_path=True):
+            o, w = ref._limited_eager_attention_forward(_M(), rq[step], rk[:, :, :kc], rv[:, :, :kc], None, scaling=D ** -0.5)
+        out[f"sq_{step}_out"] = o.numpy()
+        out[f"sq_{step}_vmean"] = sq_state.previous_layer[0]["mean"].numpy()
 
     np.savez_compressed(OUT, **out)
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.1f} KiB), {len(out)} arrays")

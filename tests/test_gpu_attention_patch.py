@@ -220,3 +220,48 @@ def test_config_1_sized_step_all_28_layers_resident(cuda_device):
         want = oracle.decode_step(q[b:b + 1].cpu(), key[b:b + 1].cpu(), value[b:b + 1].cpu(), ch.cpu(), k)
         torch.testing.assert_close(outs[layer][b:b + 1].float().cpu(), want["out"], rtol=2e-2, atol=1e-2)
         assert torch.equal(state.layers[layer].packed[b:b + 1, :, :T].cpu(), want["packed"])
+
+
+def test_preallocated_cache_decodes_without_copying_the_cache(cuda_device):
+    """A Qwen3-0.6B-shaped model (28 layers) decoded token by token through PreallocatedCache under the sparse
+    mode, one `with` block per token as the reference's loop does: K/V buffers, int4 side caches and the step
+    workspace keep their storage for the whole decode, the prefix is quantized once, and the logits equal
+    those of the same decode through the stock DynamicCache."""
+    pytest.importorskip("transformers")
+    from transformers import DynamicCache, Qwen3Config, Qwen3ForCausalLM
+    from kv_cache_b200.cache import PreallocatedCache
+
+    torch.manual_seed(2)
+    cfg = Qwen3Config(vocab_size=1024, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28,
+                      num_attention_heads=16, num_key_value_heads=8, head_dim=128, max_position_embeddings=40960,
+                      rope_theta=1e6, rms_norm_eps=1e-6, attn_implementation="eager")
+    model = Qwen3ForCausalLM(cfg).to(cuda_device, torch.bfloat16).eval()
+    ap.install_qwen3_attention_patch()
+    try:
+        ids = torch.randint(0, 1024, (2, 1200), device=cuda_device)
+        steps = [torch.randint(0, 1024, (2, 1), device=cuda_device) for _ in range(4)]
+        mode = "qabs32cand6p25attn"
+
+        def decode(cache, state):
+            logits = []
+            with torch.inference_mode():
+                with ap.attention_mode("baseline", sparse_state=state):
+                    out = model(input_ids=ids, past_key_values=cache, use_cache=True)
+                for tok in steps:
+                    with ap.attention_mode(mode, 0.02, 3, True, 4, 16, None, sparse_state=state):
+                        out = model(input_ids=tok, past_key_values=out.past_key_values, use_cache=True)
+                    logits.append(out.logits.float().clone())
+            return logits
+
+        ref_logits = decode(DynamicCache(config=cfg), ap.SparseDecodeState())
+        state = ap.SparseDecodeState(capacity_hint=2048)
+        cache = PreallocatedCache(num_layers=28, capacity=2048)
+        got = decode(cache, state)
+        for a, b in zip(got, ref_logits):
+            torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-3)
+        assert cache.reallocations == 0 and cache.get_seq_length() == 1204
+        assert state.bulk_quantized_rows == 28 * 1200                      # every layer's prefix, once
+        assert all(state.layers[l].packed.shape[2] >= 2048 and state.layers[l].count == 1204 for l in range(28))
+        assert len(state.steps) == 1                                       # one step object (one workspace) for the policy
+    finally:
+        ap.uninstall_qwen3_attention_patch()

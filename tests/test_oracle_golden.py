@@ -142,3 +142,22 @@ def test_list_rerank_equals_the_mask_form():
         for r, f in enumerate(final):
             b, h = divmod(r, want.shape[1])
             assert f == torch.nonzero(want[b, h]).flatten().tolist()
+
+
+def test_sparq_fast_steps_restated_against_the_reference():
+    """Two consecutive steps of the reference's SparQ fast mode with its running mean of V (EVAL:2646-2722,
+    2006-2016): the oracle's restatement, fed the incrementally updated mean, reproduces the recorded outputs."""
+    q, k, v = _f32(GOLD["ru_q"]), _f32(GOLD["ru_k"]), _f32(GOLD["ru_v"])
+    T0 = int(GOLD["ru_params"][3])
+    G = q.shape[2] // k.shape[1]
+    mean = None
+    for step in range(2):
+        kc = T0 + 1 + step
+        vr = v[:, :, :kc].repeat_interleave(G, dim=1)
+        if mean is None:
+            mean = vr.float().mean(dim=2, keepdim=True)                                   # EVAL:2014
+        else:
+            mean = (mean * float(kc - 1) + vr[:, :, -1:, :].float()) / float(kc)           # EVAL:2011-2012
+        torch.testing.assert_close(mean, torch.from_numpy(GOLD[f"sq_{step}_vmean"]), rtol=1e-6, atol=1e-7)
+        out = oracle.sparq_fast_step(q[step], k[:, :, :kc], v[:, :, :kc], None, 128 ** -0.5, 16, 0.125, value_mean=mean)
+        torch.testing.assert_close(out, torch.from_numpy(GOLD[f"sq_{step}_out"]), rtol=1e-5, atol=1e-6)
