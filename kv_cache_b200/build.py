@@ -7,6 +7,8 @@ The library lands in kv_cache_b200/_lib/libkvcache_b200.so; nothing is installed
 """
 from __future__ import annotations
 
+import fcntl
+import hashlib
 import os
 import shutil
 import subprocess
@@ -43,27 +45,54 @@ def sources() -> list[Path]:
     return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "kvcache_b200.h"])
 
 
+STAMP_PATH = LIB_DIR / "libkvcache_b200.srchash"
+
+
+def source_hash() -> str:
+    """Hash of every source the library is built from (content, not modification times: a copy of the tree
+    to another machine must not look stale)."""
+    h = hashlib.sha256()
+    for s in sources():
+        h.update(s.name.encode())
+        h.update(s.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
 def is_stale() -> bool:
-    if not LIB_PATH.exists():
+    if not LIB_PATH.exists() or not STAMP_PATH.exists():
         return True
-    built = LIB_PATH.stat().st_mtime
-    return any(s.stat().st_mtime > built for s in sources())
+    return STAMP_PATH.read_text().strip() != source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compiles the library when its sources changed. Safe when several processes (the ranks of one node) call
+    it at once: one holds a file lock and builds into a temporary file that is renamed into place, the others
+    wait for the lock and find the library fresh."""
     if not force and not is_stale():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    extra = os.environ.get("KVB_NVCC_EXTRA", "").split()       # e.g. -D switches for experiments
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-o", str(LIB_PATH), str(UNITY)]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-        print(" ".join(cmd), flush=True)
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
-    if verbose:
-        print(res.stderr)
+    with open(LIB_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not is_stale():
+                return LIB_PATH
+            digest = source_hash()
+            tmp = LIB_DIR / f".libkvcache_b200.{os.getpid()}.so.tmp"
+            cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(tmp), str(UNITY)]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+                print(" ".join(cmd), flush=True)
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+            if verbose:
+                print(res.stderr)
+            os.replace(tmp, LIB_PATH)
+            STAMP_PATH.write_text(digest + "\n")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 

@@ -53,3 +53,21 @@ def test_quantize_edge_values(cuda_device):
     _, packed_o, scale_o = oracle.quantize_pack(key.cpu(), ch.cpu())
     assert torch.equal(packed.cpu(), packed_o)
     assert torch.equal(scale.cpu(), scale_o)
+
+
+def test_every_bf16_magnitude_as_the_row_maximum(cuda_device):
+    """The kernel forms scale = absmax / 7 and the codes without the division routine; the row maximum can only
+    be a bf16 value, so all 32640 finite positive magnitudes are tried as the maximum of a row (with neighbours
+    at fixed fractions of it, among them exact rounding boundaries) and every scale and code must equal the
+    oracle's IEEE arithmetic."""
+    mags = torch.arange(1, 0x7F80, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)          # all finite positive bf16
+    T = mags.numel()
+    key = torch.zeros((1, 1, T, 128), dtype=torch.bfloat16)
+    fr = torch.tensor([1.0, -1.0, 0.5, -0.5, 0.25, 0.75, 3 / 14, 5 / 14, 1 / 14, 13 / 14, 9 / 14, 11 / 14, 0.0, 1 / 7, 2 / 7, 6 / 7])
+    key[0, 0, :, :16] = (mags.float()[:, None] * fr[None, :]).to(torch.bfloat16)
+    key[0, 0, :, 16:64] = (mags.float()[:, None] * torch.linspace(-1, 1, 48)[None, :]).to(torch.bfloat16)
+    ch = torch.arange(64, dtype=torch.int32).view(1, 64)
+    packed, scale = ops.quantize(key.to(cuda_device), ch.to(cuda_device))
+    _, packed_o, scale_o = oracle.quantize_pack(key, ch)
+    assert torch.equal(scale.cpu(), scale_o)
+    assert torch.equal(packed.cpu(), packed_o)
