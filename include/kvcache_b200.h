@@ -500,8 +500,8 @@ int kvb_lse_merge(const float* partials, int N, int B, int Hq, int D, void* out,
  *   query of the chunk. C in {32,64,128}, G in {1,2,4,8}; packed/scale aligned as for the
  *   streaming decode scorer. block_scores fp32 [B,Hkv,Tq,ceil(Tk/64)] dense; -0 stored as +0.
  *   kvb_score_prefill_blocks_engine is the same with the implementation chosen by the caller
- *   (all give identical bits): 0 = automatic (tensor-memory path; the environment variable
- *   KVB_PREFILL_ENGINE = mma | i8 | f16 overrides it), 1 = warp-level int8 MMA, 2 = tcgen05
+ *   (all give identical bits): 0 = automatic (the tensor-memory path with the fp16 encoding where the
+ *   shape allows it), 1 = warp-level int8 MMA, 2 = tcgen05
  *   kind::i8 with int32 accumulators in tensor memory, 3 = tcgen05 kind::f16 with the integer
  *   codes carried exactly as fp16 values and fp32 accumulators.
  * kvb_block_topk: per row of block scores ([R,nblk], nblk <= 4096) the min(k,nblk) best blocks

@@ -262,10 +262,7 @@ static thread_local bool t_chain_launch = false;
 struct ChainLaunchScope {
   bool prev;
   ChainLaunchScope() : prev(t_chain_launch) {}
-  void on() {
-    static const bool disabled = [] { const char* e = getenv("KVB_NO_CHAIN_LAUNCH"); return e && e[0] == '1'; }();
-    t_chain_launch = !disabled;
-  }
+  void on() { t_chain_launch = true; }
   ~ChainLaunchScope() { t_chain_launch = prev; }
 };
 

@@ -389,7 +389,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       sp.from_candidates = 1; sp.row_failed = nullptr; sp.T_dev = T_dev;
       sp.out_comp = nullptr; sp.gather = nullptr; sp.gather_n = 0; sp.gather_len = 0; sp.gather_stride = 0;
       sp.rescue = 1; sp.rescue_sp = base;          // rows that miss [kk, cap] are re-scored inside the kernel
-      { static const bool off = [] { const char* e = getenv("KVB_NO_COMMON_PREFIX"); return e && e[0] == '1'; }(); sp.common_start = off ? 0 : 1; }
       const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
       size_t smem = (size_t)fcap * 8 + SEL_FINAL_FIXED_SMEM;
       sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;

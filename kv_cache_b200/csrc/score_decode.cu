@@ -46,9 +46,7 @@ constexpr int SC_FLOAT_MAGIC = 0x4B400000;
 // every lane dequantises exactly four (token, head) values.
 // Persistent: CTA c owns the contiguous unit range [c*U/grid, (c+1)*U/grid) of the flattened
 // (row, tile) space.
-#ifndef KVB_SC_STAGE_PACKED_BYTES
-#define KVB_SC_STAGE_PACKED_BYTES 4096
-#endif
+constexpr int SC_STAGE_PACKED_BYTES = 4096;
 
 template <int C, int G>
 struct ScoreCfg {
@@ -59,7 +57,7 @@ struct ScoreCfg {
   static constexpr int ITER_TOKENS = 16 * TPA;          // tokens per accumulator
   // tokens per stage: about 4 KiB of packed codes per bulk copy (copies of 2 KiB reach only ~93 % of the
   // streaming bandwidth that 4 KiB copies reach with the same bytes in flight)
-  static constexpr int STAGE_TOKENS = KVB_SC_STAGE_PACKED_BYTES / (C / 2);
+  static constexpr int STAGE_TOKENS = SC_STAGE_PACKED_BYTES / (C / 2);
   static constexpr int TW = ITER_TOKENS > STAGE_TOKENS ? ITER_TOKENS : STAGE_TOKENS;
   static constexpr int IT = TW / ITER_TOKENS;
   static constexpr int TOKEN_BYTES = C / 2;

@@ -406,18 +406,6 @@ extern "C" __attribute__((visibility("default"))) int kvb_quantize_query_tokens(
 namespace kvb {
 
 // engine: 0 = automatic, 1 = mma.sync int8 (score_prefill_kernel), 2 = tcgen05 kind::i8, 3 = tcgen05 kind::f16.
-static int prefill_engine_default() {
-  static const int e = [] {
-    const char* v = getenv("KVB_PREFILL_ENGINE");
-    if (!v) return 0;
-    if (!strcmp(v, "mma")) return 1;
-    if (!strcmp(v, "i8")) return 2;
-    if (!strcmp(v, "f16")) return 3;
-    return 0;
-  }();
-  return e;
-}
-
 static int prefill_blocks_run(const int8_t* qcode, const float* qscale, const uint8_t* packed, int64_t packed_sb,
                               int64_t packed_sh, const float* scale, int64_t scale_sb, int64_t scale_sh, int B, int Hq,
                               int Hkv, int Tq, int Tk, int C, int block_size, float* block_scores, int engine,
@@ -435,7 +423,6 @@ static int prefill_blocks_run(const int8_t* qcode, const float* qscale, const ui
   if (!guard.ok) return KVB_BAD_DEVICE;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int G = Hq / Hkv;
-  if (engine == 0) engine = prefill_engine_default();
   if (engine == 0) engine = 3;                      // tensor-memory path, fp16 encoding of the integer codes
   if (engine >= 2) {
     PrefillTcParams t;

@@ -281,33 +281,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
       }
       return v;
     };
-    // Block maximum of 16 accumulator columns against their key scales: two columns per packed fp32
-    // multiply (each half rounded to nearest, as a scalar multiply) and per 3-input maximum.
+    // Block maximum of 16 accumulator columns against their key scales: one rounded fp32 multiply per column
+    // (the scales come from shared memory four at a time, the same address for every lane) and one 3-input
+    // maximum per two columns, on two independent chains. Nothing is packed or unpacked: the accumulator
+    // registers of the tensor-memory load are used as they are.
     auto chunk_max = [&](const uint32_t* v, const float* ks, float m) -> float {
       float ma = m, mb = -INFINITY;
 #pragma unroll
       for (int c = 0; c < TC_CHW; c += 4) {
-        const ulonglong2 kk = *reinterpret_cast<const ulonglong2*>(ks + c);      // scales of columns c..c+3
-        uint64_t x01, x23, p01, p23;
-        float a0, a1, a2, a3;
+        const float4 kk = *reinterpret_cast<const float4*>(ks + c);              // scales of columns c..c+3
+        float x0, x1, x2, x3;
         if constexpr (KIND == 0) {
           // exact int -> float (|acc| < 2^22): bits of 1.5 * 2^23 + acc, minus 1.5 * 2^23
-          const uint32_t i0 = v[c] + 0x4B400000u, i1 = v[c + 1] + 0x4B400000u;
-          const uint32_t i2 = v[c + 2] + 0x4B400000u, i3 = v[c + 3] + 0x4B400000u;
-          uint64_t y01, y23;
-          const uint64_t bias = 0xCB400000CB400000ull;                           // (-12582912.0f, -12582912.0f)
-          asm("mov.b64 %0, {%1, %2};" : "=l"(y01) : "r"(i0), "r"(i1));
-          asm("mov.b64 %0, {%1, %2};" : "=l"(y23) : "r"(i2), "r"(i3));
-          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(x01) : "l"(y01), "l"(bias));
-          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(x23) : "l"(y23), "l"(bias));
+          x0 = __uint_as_float(v[c] + 0x4B400000u) - 12582912.0f;
+          x1 = __uint_as_float(v[c + 1] + 0x4B400000u) - 12582912.0f;
+          x2 = __uint_as_float(v[c + 2] + 0x4B400000u) - 12582912.0f;
+          x3 = __uint_as_float(v[c + 3] + 0x4B400000u) - 12582912.0f;
         } else {
-          asm("mov.b64 %0, {%1, %2};" : "=l"(x01) : "r"(v[c]), "r"(v[c + 1]));
-          asm("mov.b64 %0, {%1, %2};" : "=l"(x23) : "r"(v[c + 2]), "r"(v[c + 3]));
+          x0 = __uint_as_float(v[c]); x1 = __uint_as_float(v[c + 1]);
+          x2 = __uint_as_float(v[c + 2]); x3 = __uint_as_float(v[c + 3]);
         }
-        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p01) : "l"(x01), "l"(kk.x));
-        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p23) : "l"(x23), "l"(kk.y));
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(p01));
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(a2), "=f"(a3) : "l"(p23));
+        const float a0 = __fmul_rn(x0, kk.x), a1 = __fmul_rn(x1, kk.y);
+        const float a2 = __fmul_rn(x2, kk.z), a3 = __fmul_rn(x3, kk.w);
         asm("max.f32 %0, %0, %1, %2;" : "+f"(ma) : "f"(a0), "f"(a1));
         asm("max.f32 %0, %0, %1, %2;" : "+f"(mb) : "f"(a2), "f"(a3));
       }
@@ -453,7 +448,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
       for (int u = 0; u < U; ++u) {
         const int i = i0 + u;
         if (i >= ntiles) break;
-        constexpr int dummy = 0; (void)dummy;
         const int s = u % BSTAGES, a = u & 1;                          // constants after unrolling (U is even and a multiple of BSTAGES)
         const uint32_t use_b = round * (U / BSTAGES) + (uint32_t)(u / BSTAGES);   // n-th use of operand stage s
         const uint32_t use_a = round * (U / 2) + (uint32_t)(u / 2);               // n-th use of accumulator stage a

@@ -367,6 +367,55 @@ __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
   }
 }
 
+// Copies n 64-bit entries from global to shared memory with eight loads of every thread in flight at once
+// (a plain strided loop leaves one dependent L2 round trip per iteration on the critical path of the CTA).
+template <int NT>
+__device__ __forceinline__ void load_list_to_smem(uint64_t* dst, const uint64_t* src, int n) {
+  for (int i0 = 0; i0 < n; i0 += NT * 8) {
+    uint64_t v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * NT + (int)threadIdx.x;
+      v[u] = i < n ? __ldcg(src + i) : 0ull;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * NT + (int)threadIdx.x;
+      if (i < n) dst[i] = v[u];
+    }
+  }
+}
+
+// Exclusive prefix sums of TWO values per thread over the CTA with the barriers of one scan; also the totals.
+// s_warp needs 2 * (NT/32 + 1) words. Ends with a barrier.
+template <int NT>
+__device__ __forceinline__ void block_exclusive_scan2(uint32_t va, uint32_t vb, uint32_t* s_warp, uint32_t& ea,
+                                                      uint32_t& eb, uint32_t& ta, uint32_t& tb) {
+  constexpr int NW = NT / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t ia = va, ib = vb;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t na = __shfl_up_sync(0xffffffffu, ia, off), nb = __shfl_up_sync(0xffffffffu, ib, off);
+    if (lane >= off) { ia += na; ib += nb; }
+  }
+  if (lane == 31) { s_warp[warp] = ia; s_warp[NW + 1 + warp] = ib; }
+  __syncthreads();
+  // every warp scans the (at most 32) warp totals itself
+  uint32_t wa = lane < NW ? s_warp[lane] : 0u, wb = lane < NW ? s_warp[NW + 1 + lane] : 0u;
+  uint32_t sa = wa, sb = wb;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t na = __shfl_up_sync(0xffffffffu, sa, off), nb = __shfl_up_sync(0xffffffffu, sb, off);
+    if (lane >= off) { sa += na; sb += nb; }
+  }
+  ea = __shfl_sync(0xffffffffu, sa - wa, warp) + ia - va;
+  eb = __shfl_sync(0xffffffffu, sb - wb, warp) + ib - vb;
+  ta = __shfl_sync(0xffffffffu, sa, 31);
+  tb = __shfl_sync(0xffffffffu, sb, 31);
+  __syncthreads();
+}
+
 // One CTA per row: candidates -> exact k-th composite -> the k winners in the requested order.
 __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectParams pin) {
   // the row length (and with it the count to select) may live on the device
@@ -445,11 +494,22 @@ again:
     for (int i = tid; i < p.gather_n; i += SEL_FINAL_THREADS) s_segmin[i] = ~0ull;
     __syncthreads();
     n = p.gather_n * p.gather_prefix;
-    for (int i = tid; i < n; i += SEL_FINAL_THREADS) {
-      const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
-      const uint64_t c = __ldcg(p.gather + (int64_t)seg * p.gather_stride + (int64_t)row * gpitch + j);
-      s_cand[i] = c;
-      atomicMin(&s_segmin[seg], (unsigned long long)c);
+    for (int i0 = 0; i0 < n; i0 += SEL_FINAL_THREADS * 8) {          // eight loads of every thread in flight
+      uint64_t v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * SEL_FINAL_THREADS + tid;
+        const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
+        v[u] = i < n ? __ldcg(p.gather + (int64_t)seg * p.gather_stride + (int64_t)row * gpitch + j) : 0ull;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * SEL_FINAL_THREADS + tid;
+        if (i < n) {
+          s_cand[i] = v[u];
+          if (p.gather_prefix < p.gather_len) atomicMin(&s_segmin[i / p.gather_prefix], (unsigned long long)v[u]);
+        }
+      }
     }
     __syncthreads();
     prefix = 0; fixed = 0; need = (uint32_t)rkk; in_prefix = (uint32_t)n;
@@ -489,7 +549,7 @@ again:
       const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
       n = (int)(have < (uint32_t)p.cap ? have : (uint32_t)p.cap);
       in_prefix = (uint32_t)n;
-      for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
+      load_list_to_smem<SEL_FINAL_THREADS>(s_cand, cand, n);
       __syncthreads();
     }
   } else {
@@ -500,7 +560,7 @@ again:
       n = (int)(thr.y + thr.z);
       const uint32_t have = p.cand_count[(int64_t)row * SEL_COUNT_STRIDE];
       if ((uint32_t)n > have) n = (int)have;            // cannot happen; keeps reads in bounds
-      for (int i = tid; i < n; i += SEL_FINAL_THREADS) s_cand[i] = __ldcg(cand + i);
+      load_list_to_smem<SEL_FINAL_THREADS>(s_cand, cand, n);
       __syncthreads();
     }
   }
@@ -647,35 +707,38 @@ again:
       }
       kth_split = fx >= 64 ? pf : (fx == 0 ? 0ull : (pf << (64 - fx)));
     }
-    if (tid < 3) s_count[tid] = 0;
-    __syncthreads();
     const bool own = p.out_owned != nullptr;
-    // Output slots are handed out per warp (one shared-memory atomic for all takers of a warp-wide step):
-    // ballot, leader reserves, lanes take their rank inside the reservation.
-    const int lane = tid & 31;
-    const uint32_t lt = (1u << lane) - 1u;
-    auto warp_slots = [&](bool take, uint32_t* counter) -> uint32_t {
-      const uint32_t m = __ballot_sync(0xffffffffu, take);
-      uint32_t base = 0;
-      if (m) {
-        const int leader = __ffs(m) - 1;
-        if (lane == leader) base = atomicAdd(counter, (uint32_t)__popc(m));
-        base = __shfl_sync(0xffffffffu, base, leader);
+    // Output positions come from prefix sums, not from atomics: a thread owns the entries tid, tid + NT, ...
+    // (at most cap / NT <= 32 of them), notes in three bit masks which of them win, win among the split_k
+    // best, and win inside the owned id range; two block scans then give every thread the start of its run
+    // in each of the (up to) three output lists, and a second walk over the same entries writes them.
+    uint32_t m_first = 0, m_second = 0, m_mine = 0;
+    {
+      int j = 0;
+      for (int i = tid; i < n; i += SEL_FINAL_THREADS, ++j) {
+        const uint64_t c = s_cand[i];
+        const bool win = c >= kth;
+        const bool first = win && !(split && c < kth_split);
+        const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
+        const bool mine = own && win && (int64_t)idx >= p.own_base && (int64_t)idx < p.own_limit;
+        m_first |= (first ? 1u : 0u) << j;
+        m_second |= ((win && !first) ? 1u : 0u) << j;
+        m_mine |= (mine ? 1u : 0u) << j;
       }
-      return base + (uint32_t)__popc(m & lt);
-    };
-    const int n_round = (n + 31) & ~31;               // whole warps walk together (ballots inside)
-    for (int i = tid; i < n_round; i += SEL_FINAL_THREADS) {
-      const uint64_t c = i < n ? s_cand[i] : 0ull;
-      const bool win = i < n && c >= kth;
-      const bool first = win && !(split && c < kth_split);
-      const uint32_t pa = warp_slots(first, &s_count[0]);
-      const uint32_t pb = split ? warp_slots(win && !first, &s_count[1]) : 0u;
-      const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
-      const bool mine = own && win && (int64_t)idx >= p.own_base && (int64_t)idx < p.own_limit;
-      const uint32_t pq = own ? warp_slots(mine, &s_count[2]) : 0u;
-      if (win) {
-        const uint32_t pos = first ? pa : (uint32_t)p.split_k + pb;
+    }
+    uint32_t pa, pb, pq = 0, ta, tb, tq = 0, unused_e, unused_t;
+    block_exclusive_scan2<SEL_FINAL_THREADS>((uint32_t)__popc(m_first), (uint32_t)__popc(m_second), s_tmp, pa, pb, ta, tb);
+    if (own) block_exclusive_scan2<SEL_FINAL_THREADS>((uint32_t)__popc(m_mine), 0u, s_tmp, pq, unused_e, tq, unused_t);
+    (void)ta; (void)tb; (void)unused_e; (void)unused_t;
+    if (tid == 0) s_count[2] = tq;
+    {
+      int j = 0;
+      for (int i = tid; i < n; i += SEL_FINAL_THREADS, ++j) {
+        const bool first = (m_first >> j) & 1u, second = (m_second >> j) & 1u, mine = (m_mine >> j) & 1u;
+        if (!(first || second)) continue;
+        const uint64_t c = s_cand[i];
+        const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
+        const uint32_t pos = first ? pa++ : (uint32_t)p.split_k + pb++;
         if (pos < (uint32_t)rkk) {
           const int64_t o = (int64_t)row * out_pitch + pos;
           if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
@@ -688,7 +751,10 @@ again:
             for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot] = cg;
           }
         }
-        if (mine && pq < (uint32_t)rkk) p.out_owned[(int64_t)row * out_pitch + pq] = (int32_t)idx;
+        if (mine) {
+          if (pq < (uint32_t)rkk) p.out_owned[(int64_t)row * out_pitch + pq] = (int32_t)idx;
+          ++pq;
+        }
       }
     }
     if (own && p.out_owned_count) {
