@@ -504,6 +504,17 @@ int kvb_lse_merge(const float* partials, int N, int B, int Hq, int D, void* out,
  *   shape allows it), 1 = warp-level int8 MMA, 2 = tcgen05
  *   kind::i8 with int32 accumulators in tensor memory, 3 = tcgen05 kind::f16 with the integer
  *   codes carried exactly as fp16 values and fp32 accumulators.
+ * Pre-widened key operands. A chunked prefill scores every chunk of queries against the same keys, so the
+ *   int4 -> tensor-core operand conversion can be paid once per cache instead of once per CTA:
+ *   kvb_prefill_operand_bytes(B, Hkv, key_capacity, C, engine) is the size of a buffer holding the operands of
+ *   key_capacity tokens per (batch, KV head): [B*Hkv][ceil(key_capacity/128)][128*C*es] bytes, es = 2 for
+ *   engine 0/3 (fp16 values of the codes), 1 for engine 2 (int8 bytes 16*code); each tile of 128 tokens is
+ *   stored in the 8-row x 16-byte core-matrix order the tensor core reads from shared memory, so a CTA
+ *   fetches a tile with ONE bulk copy. kvb_widen_keys writes the tiles that hold tokens first_token .. Tk-1
+ *   (tokens at or beyond Tk inside the last tile become zero rows); after an append call it again with
+ *   first_token = the old Tk. kvb_score_prefill_blocks_widened is kvb_score_prefill_blocks_engine reading
+ *   those operands (same engine number as they were widened for); identical bits. operands must be
+ *   128-byte aligned. No reference counterpart.
  * kvb_block_topk: per row of block scores ([R,nblk], nblk <= 4096) the min(k,nblk) best blocks
  *   ordered by (score desc, block asc); out_idx int32 [R,kk], out_scores fp32 [R,kk] or NULL.
  * ------------------------------------------------------------------------------------- */
@@ -523,6 +534,18 @@ int kvb_score_prefill_blocks_engine(const int8_t* qcode, const float* qscale,
                                     const float* scale, int64_t scale_sb, int64_t scale_sh,
                                     int B, int Hq, int Hkv, int Tq, int Tk, int C, int block_size,
                                     float* block_scores, int engine, int device, void* stream);
+
+size_t kvb_prefill_operand_bytes(int B, int Hkv, int key_capacity, int C, int engine);
+
+int kvb_widen_keys(const uint8_t* packed, int64_t packed_sb, int64_t packed_sh,
+                   int B, int Hkv, int Tk, int key_capacity, int C, int engine, int first_token,
+                   void* operands, size_t operand_bytes, int device, void* stream);
+
+int kvb_score_prefill_blocks_widened(const int8_t* qcode, const float* qscale,
+                                     const void* operands, size_t operand_bytes, int key_capacity,
+                                     const float* scale, int64_t scale_sb, int64_t scale_sh,
+                                     int B, int Hq, int Hkv, int Tq, int Tk, int C, int block_size,
+                                     float* block_scores, int engine, int device, void* stream);
 
 int kvb_block_topk(const float* block_scores, int64_t row_stride, int64_t R, int nblk, int k,
                    int32_t* out_idx, float* out_scores, int device, void* stream);

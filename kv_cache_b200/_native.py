@@ -129,6 +129,10 @@ SIGNATURES = {
     "kvb_score_prefill_blocks": (_i, [_p, _p, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _i, _p]),
     "kvb_score_prefill_blocks_engine": (_i, [_p, _p, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _i,
                                              _i, _p]),
+    "kvb_prefill_operand_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "kvb_widen_keys": (_i, [_p, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _sz, _i, _p]),
+    "kvb_score_prefill_blocks_widened": (_i, [_p, _p, _p, _sz, _i, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _i,
+                                              _i, _p]),
     "kvb_block_topk": (_i, [_p, _i64, _i64, _i, _i, _p, _p, _i, _p]),
     "kvb_qabs_partial_scores": (_i, [_p, _p, _i64, _i64, _i64, _i64, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     "kvb_qabs_candidate_full_scores": (_i, [_p, _p, _i64, _i64, _i64, _p, _p, _p, _i, _i, _f, _p,

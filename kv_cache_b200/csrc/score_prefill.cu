@@ -464,6 +464,59 @@ extern "C" __attribute__((visibility("default"))) int kvb_score_prefill_blocks_e
                                  Tk, C, block_size, block_scores, engine, device, stream);
 }
 
+extern "C" __attribute__((visibility("default"))) size_t kvb_prefill_operand_bytes(int B, int Hkv, int key_capacity,
+                                                                                    int C, int engine) {
+  if (B <= 0 || Hkv <= 0 || key_capacity <= 0 || (C != 32 && C != 64 && C != 128)) return 0;
+  if (engine != 0 && engine != 2 && engine != 3) return 0;
+  return (size_t)B * Hkv * kvb::ceil_div(key_capacity, kvb::TC_NTILE) * kvb::prefill_operand_tile_bytes(C, engine == 2 ? 0 : 1);
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_widen_keys(
+    const uint8_t* packed, int64_t packed_sb, int64_t packed_sh, int B, int Hkv, int Tk, int key_capacity, int C,
+    int engine, int first_token, void* operands, size_t operand_bytes, int device, void* stream) {
+  using namespace kvb;
+  if (!packed || !operands) return KVB_BAD_ARG;
+  if (B <= 0 || Hkv <= 0 || Tk <= 0 || key_capacity < Tk || first_token < 0) return KVB_BAD_SHAPE;
+  if (C != 32 && C != 64 && C != 128) return KVB_BAD_SHAPE;
+  if (engine != 0 && engine != 2 && engine != 3) return KVB_BAD_ARG;
+  if ((int64_t)B * Hkv > 65535) return KVB_BAD_SHAPE;
+  if (!aligned_to(packed, 16) || (packed_sb % 16) || (packed_sh % 16) || !aligned_to(operands, 128)) return KVB_BAD_ALIGN;
+  if (operand_bytes < kvb_prefill_operand_bytes(B, Hkv, key_capacity, C, engine)) return KVB_WORKSPACE_TOO_SMALL;
+  DeviceGuard guard(device);
+  if (!guard.ok) return KVB_BAD_DEVICE;
+  return prefill_widen_run(packed, packed_sb, packed_sh, B, Hkv, Tk, C, engine == 2 ? 0 : 1,
+                           ceil_div(key_capacity, TC_NTILE), first_token / TC_NTILE,
+                           reinterpret_cast<uint8_t*>(operands), reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" __attribute__((visibility("default"))) int kvb_score_prefill_blocks_widened(
+    const int8_t* qcode, const float* qscale, const void* operands, size_t operand_bytes, int key_capacity,
+    const float* scale, int64_t scale_sb, int64_t scale_sh, int B, int Hq, int Hkv, int Tq, int Tk, int C,
+    int block_size, float* block_scores, int engine, int device, void* stream) {
+  using namespace kvb;
+  if (!qcode || !qscale || !operands || !scale || !block_scores) return KVB_BAD_ARG;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Tq <= 0 || Tk <= 0 || (Hq % Hkv) || key_capacity < Tk) return KVB_BAD_SHAPE;
+  if (block_size != PF_BLOCK) return KVB_BAD_SHAPE;
+  if (C != 32 && C != 64 && C != 128) return KVB_BAD_SHAPE;
+  if (engine != 0 && engine != 2 && engine != 3) return KVB_BAD_ARG;
+  if ((int64_t)B * Hkv > 65535) return KVB_BAD_SHAPE;
+  if (!aligned_to(qcode, 8) || !aligned_to(operands, 128) || !aligned_to(scale, 16) || (scale_sb % 4) || (scale_sh % 4))
+    return KVB_BAD_ALIGN;
+  if (operand_bytes < kvb_prefill_operand_bytes(B, Hkv, key_capacity, C, engine)) return KVB_WORKSPACE_TOO_SMALL;
+  DeviceGuard guard(device);
+  if (!guard.ok) return KVB_BAD_DEVICE;
+  PrefillTwParams pw;
+  pw.base.qcode = qcode; pw.base.qscale = qscale;
+  pw.base.packed = nullptr; pw.base.packed_sb = 0; pw.base.packed_sh = 0;
+  pw.base.scale = scale; pw.base.scale_sb = scale_sb; pw.base.scale_sh = scale_sh;
+  pw.base.out = block_scores;
+  pw.base.B = B; pw.base.Hq = Hq; pw.base.Hkv = Hkv; pw.base.Tq = Tq; pw.base.Tk = Tk;
+  pw.base.nblk = ceil_div(Tk, PF_BLOCK);
+  pw.operands = reinterpret_cast<const uint8_t*>(operands);
+  pw.cap_tiles = ceil_div(key_capacity, TC_NTILE);
+  return prefill_tw_run(pw, C, Hq / Hkv, engine == 2 ? 0 : 1, device, reinterpret_cast<cudaStream_t>(stream));
+}
+
 extern "C" __attribute__((visibility("default"))) int kvb_block_topk(const float* block_scores, int64_t row_stride,
                                                                       int64_t R, int nblk, int k, int32_t* out_idx,
                                                                       float* out_scores, int device, void* stream) {

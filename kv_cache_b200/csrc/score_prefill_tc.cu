@@ -30,11 +30,14 @@
 #include "common.cuh"
 
 #include <cuda_fp16.h>
+#ifdef KVB_EXP_PROFILE
+#include <cstdio>
+#endif
 
 namespace kvb {
 
 constexpr int TC_EPI_WARPS = 16;                   // four per TMEM lane quadrant: one (tile, block) unit each
-constexpr int TC_PROD_WARPS = 4;
+constexpr int TC_PROD_WARPS = 4;                   // 1, 2 or 4 (128 tokens per tile are split over them)
 constexpr int TC_WARPS = TC_EPI_WARPS + TC_PROD_WARPS + 1;
 constexpr int TC_THREADS = TC_WARPS * 32;
 constexpr int TC_NTILE = 128;                      // key tokens per MMA tile (two 64-token blocks)
@@ -42,6 +45,7 @@ constexpr int TC_QT = 2;                           // 128-row accumulator tiles 
 constexpr int TC_ASTAGES = 2;                      // accumulator stages in tensor memory
 constexpr int TC_TMEM_COLS = TC_ASTAGES * TC_QT * TC_NTILE;   // 512: all of it
 constexpr int TC_CHW = 16;                         // accumulator columns per tensor-memory load
+constexpr bool TC_DOUBLE_BUFFER = TC_CHW <= 32;    // two loads alternate in registers when they fit
 constexpr int TC_LBO = 128;                        // bytes between core matrices along K
 
 struct PrefillTcParams {
@@ -89,49 +93,98 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         : "memory");
   }
 }
-// 32 consecutive accumulator columns of this thread's TMEM lane
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+// TcLd<N>::ld reads N consecutive accumulator columns of this thread's TMEM lane; TcLd<N>::wait waits for
+// every tcgen05.ld of this thread. The registers of the load are passed through the wait statement so that
+// no use of them can be scheduled ahead of it.
+template <int N>
+struct TcLd;
+template <>
+struct TcLd<16> {
+  static __device__ __forceinline__ void ld(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {"
+      "%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15"
+      "}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr)
       : "memory");
-}
-// Waits for every tcgen05.ld of this thread. The registers of the load are passed through the statement
-// so that no use of them can be scheduled ahead of the wait.
-__device__ __forceinline__ void tc_wait_ld32(uint32_t* v) {
-  asm volatile(
+  }
+  static __device__ __forceinline__ void wait(uint32_t* v) {
+    asm volatile(
       "tcgen05.wait::ld.sync.aligned;"
-      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
-        "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]),
-        "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]),
-        "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+        "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
       :
       : "memory");
-}
-// 16-column forms of the two above
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+  }
+};
+template <>
+struct TcLd<32> {
+  static __device__ __forceinline__ void ld(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {"
+      "%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+      "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31"
+      "}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+        "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+        "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld16(uint32_t* v) {
-  asm volatile(
+  }
+  static __device__ __forceinline__ void wait(uint32_t* v) {
+    asm volatile(
       "tcgen05.wait::ld.sync.aligned;"
-      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
-        "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+        "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+        "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]),
+        "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]),
+        "+r"(v[30]), "+r"(v[31])
       :
       : "memory");
-}
+  }
+};
+template <>
+struct TcLd<64> {
+  static __device__ __forceinline__ void ld(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {"
+      "%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+      "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, "
+      "%42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, "
+      "%62, %63"
+      "}, [%64];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+        "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+        "=r"(v[30]), "=r"(v[31]), "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]),
+        "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]),
+        "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]), "=r"(v[49]), "=r"(v[50]),
+        "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]),
+        "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+      : "r"(taddr)
+      : "memory");
+  }
+  static __device__ __forceinline__ void wait(uint32_t* v) {
+    asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+        "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+        "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]),
+        "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]),
+        "+r"(v[30]), "+r"(v[31]), "+r"(v[32]), "+r"(v[33]), "+r"(v[34]), "+r"(v[35]), "+r"(v[36]),
+        "+r"(v[37]), "+r"(v[38]), "+r"(v[39]), "+r"(v[40]), "+r"(v[41]), "+r"(v[42]), "+r"(v[43]),
+        "+r"(v[44]), "+r"(v[45]), "+r"(v[46]), "+r"(v[47]), "+r"(v[48]), "+r"(v[49]), "+r"(v[50]),
+        "+r"(v[51]), "+r"(v[52]), "+r"(v[53]), "+r"(v[54]), "+r"(v[55]), "+r"(v[56]), "+r"(v[57]),
+        "+r"(v[58]), "+r"(v[59]), "+r"(v[60]), "+r"(v[61]), "+r"(v[62]), "+r"(v[63])
+      :
+      : "memory");
+  }
+};
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -172,6 +225,181 @@ struct TcCfg {
   static constexpr int BYTES = OFF_MISC + 16;
 };
 
+// The packed int4 codes of one token (W = C/8 words, two's complement nibbles) as one operand row in the
+// core-matrix layout: 16-byte chunk c of the row goes to dst + c * TC_LBO. `dst` may be shared or global.
+//   KIND 0: chunk c = words 2c, 2c+1 -> bytes 16*code in the order (even, odd, even, odd channels);
+//   KIND 1: chunk c = word c -> 8 halves (4 even channels, 4 odd), built as 1024 + (code + 8) by byte
+//           permutation and brought to the signed code by one exact half2 subtraction.
+template <int C, int KIND>
+__device__ __forceinline__ void tc_widen_token(const uint32_t* words, uint8_t* dst) {
+  constexpr int W = C / 8;
+  if constexpr (KIND == 0) {
+#pragma unroll
+    for (int c = 0; c < W / 2; ++c) {
+      const uint32_t w0 = words[2 * c], w1 = words[2 * c + 1];
+      *reinterpret_cast<uint4*>(dst + c * TC_LBO) =
+          make_uint4((w0 << 4) & 0xF0F0F0F0u, w0 & 0xF0F0F0F0u, (w1 << 4) & 0xF0F0F0F0u, w1 & 0xF0F0F0F0u);
+    }
+  } else {
+    const __half2 bias = __floats2half2_rn(1032.0f, 1032.0f);
+#pragma unroll
+    for (int c = 0; c < W; ++c) {
+      const uint32_t x = words[c] ^ 0x88888888u;    // two's complement nibble -> code + 8
+      const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
+      uint32_t hh[4];
+      hh[0] = __byte_perm(lo, 0x64u, 0x4140);       // halves 1024 + (code + 8) of bytes 0, 1
+      hh[1] = __byte_perm(lo, 0x64u, 0x4342);
+      hh[2] = __byte_perm(hi, 0x64u, 0x4140);
+      hh[3] = __byte_perm(hi, 0x64u, 0x4342);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&hh[j]), bias);
+        hh[j] = *reinterpret_cast<const uint32_t*>(&r);
+      }
+      *reinterpret_cast<uint4*>(dst + c * TC_LBO) = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+    }
+  }
+}
+
+// Maximum of N accumulator columns against their key scales, continued from m: one rounded fp32 multiply per
+// column (the scales come from shared memory four at a time, the same address for every lane) and one
+// 3-input maximum per two columns, on two independent chains. The accumulator registers of the
+// tensor-memory load are used as they are; int32 accumulators are converted exactly (|acc| < 2^22) through
+// the bits of 1.5 * 2^23 + acc.
+template <int KIND, int N>
+__device__ __forceinline__ float tc_chunk_max(const uint32_t* v, const float* ks, float m) {
+  float ma = m, mb = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < N; c += 4) {
+#ifdef KVB_EXP_NOKS
+    const float4 kk = *reinterpret_cast<const float4*>(ks);
+#else
+    const float4 kk = *reinterpret_cast<const float4*>(ks + c);
+#endif
+    float x0, x1, x2, x3;
+    if constexpr (KIND == 0) {
+      x0 = __uint_as_float(v[c] + 0x4B400000u) - 12582912.0f;
+      x1 = __uint_as_float(v[c + 1] + 0x4B400000u) - 12582912.0f;
+      x2 = __uint_as_float(v[c + 2] + 0x4B400000u) - 12582912.0f;
+      x3 = __uint_as_float(v[c + 3] + 0x4B400000u) - 12582912.0f;
+    } else {
+      x0 = __uint_as_float(v[c]); x1 = __uint_as_float(v[c + 1]);
+      x2 = __uint_as_float(v[c + 2]); x3 = __uint_as_float(v[c + 3]);
+    }
+    const float a0 = __fmul_rn(x0, kk.x), a1 = __fmul_rn(x1, kk.y);
+    const float a2 = __fmul_rn(x2, kk.z), a3 = __fmul_rn(x3, kk.w);
+    asm("max.f32 %0, %0, %1, %2;" : "+f"(ma) : "f"(a0), "f"(a1));
+    asm("max.f32 %0, %0, %1, %2;" : "+f"(mb) : "f"(a2), "f"(a3));
+  }
+  return fmaxf(ma, mb);
+}
+
+// A tiles: row r of tile qt = query q0 + qt*QPT + r / G, head r % G (the heads of a query are neighbouring
+// rows, hence neighbouring TMEM lanes of one epilogue warp); K order inside each group of 8 channels is
+// (even channels, odd channels), the order in which the widened key words deliver them.
+template <int C, int G, int KIND, class Cfg>
+__device__ __forceinline__ void tc_fill_a_tiles(const PrefillTcParams& p, uint8_t* s_a, int b, int kvh, int q0, int tid,
+                                                int nthreads) {
+  constexpr int QPT = 128 / G;
+  constexpr int W = C / 8;
+  for (int item = tid; item < TC_QT * 128 * W; item += nthreads) {
+    const int w = item % W;
+    const int r = (item / W) % 128;
+    const int qt = item / (W * 128);
+    const int qi = r / G, hd = r - qi * G;
+    const int q = q0 + qt * QPT + qi;
+    uint32_t ev = 0, od = 0;
+    if (q < p.Tq) {
+      const int64_t rowoff = ((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q;
+      const uint2 x = *reinterpret_cast<const uint2*>(p.qcode + rowoff * C + 8 * w);
+      ev = __byte_perm(x.x, x.y, 0x6420);          // channels 8w + 0,2,4,6
+      od = __byte_perm(x.x, x.y, 0x7531);          // channels 8w + 1,3,5,7
+    }
+    uint8_t* tile = s_a + qt * Cfg::A_TILE + (r >> 3) * Cfg::SBO + (r & 7) * 16;
+    if constexpr (KIND == 0) {
+      *reinterpret_cast<uint2*>(tile + (w >> 1) * TC_LBO + (w & 1) * 8) = make_uint2(ev, od);
+    } else {
+      uint32_t h[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t src = i == 0 ? ev : od;
+        const __half2 lo = __floats2half2_rn((float)(int8_t)(src & 0xFF), (float)(int8_t)((src >> 8) & 0xFF));
+        const __half2 hi = __floats2half2_rn((float)(int8_t)((src >> 16) & 0xFF), (float)(int8_t)(src >> 24));
+        h[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
+        h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+      *reinterpret_cast<uint4*>(tile + w * TC_LBO) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+  }
+}
+
+// The MMA issuer (one thread). Its instruction stream is the serial part of the whole CTA, so it is kept
+// short: descriptors differ from a base only in their address field (low word, no carry into the other
+// fields below 256 KiB), the tile loop is unrolled over the operand ring and the two accumulator stages so
+// that every index is a constant, and barrier addresses are plain integers.
+template <int KIND, class Cfg>
+__device__ __forceinline__ void tc_issue_tiles(uint8_t* s_a, uint8_t* s_b, uint64_t* b_full, uint64_t* b_empty,
+                                               uint64_t* acc_full, uint64_t* acc_empty, uint64_t* all_done,
+                                               volatile uint32_t* s_dead, uint32_t tmem_base, int ntiles) {
+  constexpr int BSTAGES = Cfg::BSTAGES;
+#ifdef KVB_EXP_PROFILE
+  long long g_prof_mma[2] = {0, 0};
+#endif
+  {
+    const uint32_t idesc = tc_instr_desc<KIND>(128, TC_NTILE);
+    const uint64_t a_desc0 = tc_smem_desc(smem_u32(s_a), TC_LBO, Cfg::SBO);
+    const uint64_t b_desc0 = tc_smem_desc(smem_u32(s_b), TC_LBO, Cfg::SBO);
+    const uint32_t a_lo = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
+    const uint32_t b_lo = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
+    auto desc = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
+    constexpr int U = (BSTAGES % 2 == 0) ? BSTAGES : 2 * BSTAGES;      // tiles per unrolled round
+    bool dead = false;
+    uint32_t round = 0;                                               // i0 / U
+    for (int i0 = 0; i0 < ntiles && !dead; i0 += U, ++round) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u;
+        if (i >= ntiles) break;
+        const int s = u % BSTAGES, a = u & 1;                          // constants after unrolling (U is even and a multiple of BSTAGES)
+        const uint32_t use_b = round * (U / BSTAGES) + (uint32_t)(u / BSTAGES);   // n-th use of operand stage s
+        const uint32_t use_a = round * (U / 2) + (uint32_t)(u / 2);               // n-th use of accumulator stage a
+#ifdef KVB_EXP_PROFILE
+        const long long c0 = clock64();
+#endif
+        bool ok = mbar_wait_bounded(&b_full[s], use_b & 1u);
+#ifdef KVB_EXP_PROFILE
+        const long long c1 = clock64();
+#endif
+        ok = ok && mbar_wait_bounded(&acc_empty[a], (use_a & 1u) ^ 1u);
+#ifdef KVB_EXP_PROFILE
+        const long long c2 = clock64();
+        g_prof_mma[0] += c1 - c0; g_prof_mma[1] += c2 - c1;
+#endif
+        if (!ok) { *s_dead = 1; dead = true; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int qt = 0; qt < TC_QT; ++qt) {
+          const uint32_t d = tmem_base + (uint32_t)(a * TC_QT * TC_NTILE + qt * TC_NTILE);
+#pragma unroll
+          for (int k = 0; k < Cfg::KSTEPS; ++k) {
+            const uint64_t ad = desc(a_lo + (uint32_t)((qt * Cfg::A_TILE + k * 2 * TC_LBO) >> 4), a_hi);
+            const uint64_t bd = desc(b_lo + (uint32_t)((s * Cfg::B_STAGE + k * 2 * TC_LBO) >> 4), b_hi);
+            tc_mma<KIND>(d, ad, bd, idesc, k > 0 ? 1u : 0u);
+          }
+        }
+        tc_commit(&b_empty[s]);                     // the stage may be overwritten once these MMAs have read it
+        tc_commit(&acc_full[a]);
+      }
+    }
+    tc_commit(all_done);
+    mbar_wait_bounded(all_done, 0);                 // nothing of this CTA is still in flight in the tensor core
+#ifdef KVB_EXP_PROFILE
+    if (blockIdx.x == 0 && blockIdx.y == 0)
+      printf("mma: wait b_full %lld wait acc_empty %lld per tile (ntiles %d)\n", g_prof_mma[0] / ntiles, g_prof_mma[1] / ntiles, ntiles);
+#endif
+  }
+}
+
 template <int C, int G, int KIND>
 __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(PrefillTcParams p) {
   using Cfg = TcCfg<C, KIND>;
@@ -210,38 +438,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
     tc_relinquish();
   }
 
-  // ---- A tiles: row r of tile qt = query q0 + qt*QPT + r / G, head r % G (the heads of a query are
-  // neighbouring rows, hence neighbouring TMEM lanes of one epilogue warp); K order inside each group of
-  // 8 channels is (even channels, odd channels), the order in which the widened key words deliver them.
-  for (int item = tid; item < TC_QT * 128 * W; item += TC_THREADS) {
-    const int w = item % W;
-    const int r = (item / W) % 128;
-    const int qt = item / (W * 128);
-    const int qi = r / G, hd = r - qi * G;
-    const int q = q0 + qt * QPT + qi;
-    uint32_t ev = 0, od = 0;
-    if (q < p.Tq) {
-      const int64_t rowoff = ((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q;
-      const uint2 x = *reinterpret_cast<const uint2*>(p.qcode + rowoff * C + 8 * w);
-      ev = __byte_perm(x.x, x.y, 0x6420);          // channels 8w + 0,2,4,6
-      od = __byte_perm(x.x, x.y, 0x7531);          // channels 8w + 1,3,5,7
-    }
-    uint8_t* tile = s_a + qt * Cfg::A_TILE + (r >> 3) * Cfg::SBO + (r & 7) * 16;
-    if constexpr (KIND == 0) {
-      *reinterpret_cast<uint2*>(tile + (w >> 1) * TC_LBO + (w & 1) * 8) = make_uint2(ev, od);
-    } else {
-      uint32_t h[4];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const uint32_t src = i == 0 ? ev : od;
-        const __half2 lo = __floats2half2_rn((float)(int8_t)(src & 0xFF), (float)(int8_t)((src >> 8) & 0xFF));
-        const __half2 hi = __floats2half2_rn((float)(int8_t)((src >> 16) & 0xFF), (float)(int8_t)(src >> 24));
-        h[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
-        h[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
-      }
-      *reinterpret_cast<uint4*>(tile + w * TC_LBO) = make_uint4(h[0], h[1], h[2], h[3]);
-    }
-  }
+  tc_fill_a_tiles<C, G, KIND, Cfg>(p, s_a, b, kvh, q0, tid, TC_THREADS);
   fence_proxy_async_smem();                         // the tensor core reads shared memory through the async proxy
   tc_fence_before();
   __syncthreads();
@@ -281,35 +478,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
       }
       return v;
     };
-    // Block maximum of 16 accumulator columns against their key scales: one rounded fp32 multiply per column
-    // (the scales come from shared memory four at a time, the same address for every lane) and one 3-input
-    // maximum per two columns, on two independent chains. Nothing is packed or unpacked: the accumulator
-    // registers of the tensor-memory load are used as they are.
     auto chunk_max = [&](const uint32_t* v, const float* ks, float m) -> float {
-      float ma = m, mb = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < TC_CHW; c += 4) {
-        const float4 kk = *reinterpret_cast<const float4*>(ks + c);              // scales of columns c..c+3
-        float x0, x1, x2, x3;
-        if constexpr (KIND == 0) {
-          // exact int -> float (|acc| < 2^22): bits of 1.5 * 2^23 + acc, minus 1.5 * 2^23
-          x0 = __uint_as_float(v[c] + 0x4B400000u) - 12582912.0f;
-          x1 = __uint_as_float(v[c + 1] + 0x4B400000u) - 12582912.0f;
-          x2 = __uint_as_float(v[c + 2] + 0x4B400000u) - 12582912.0f;
-          x3 = __uint_as_float(v[c + 3] + 0x4B400000u) - 12582912.0f;
-        } else {
-          x0 = __uint_as_float(v[c]); x1 = __uint_as_float(v[c + 1]);
-          x2 = __uint_as_float(v[c + 2]); x3 = __uint_as_float(v[c + 3]);
-        }
-        const float a0 = __fmul_rn(x0, kk.x), a1 = __fmul_rn(x1, kk.y);
-        const float a2 = __fmul_rn(x2, kk.z), a3 = __fmul_rn(x3, kk.w);
-        asm("max.f32 %0, %0, %1, %2;" : "+f"(ma) : "f"(a0), "f"(a1));
-        asm("max.f32 %0, %0, %1, %2;" : "+f"(mb) : "f"(a2), "f"(a3));
-      }
-      return fmaxf(ma, mb);
+      return tc_chunk_max<KIND, TC_CHW>(v, ks, m);
     };
-    constexpr int NCH = TC_NTILE / TC_CHW;          // chunks per tile: 8
-    constexpr int CPB = 64 / TC_CHW;                // chunks per 64-token block: 4
+    constexpr int NCH = TC_NTILE / TC_CHW;          // chunks per tile
+    constexpr int CPB = 64 / TC_CHW;                // chunks per 64-token block
     const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(par * TC_QT * TC_NTILE + qt * TC_NTILE);
     float4 k_cur = load_ks(par), k_next = load_ks(par + 2);
     int buf = 0;
@@ -322,22 +495,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
       if (*s_dead) break;
       if (!mbar_wait_bounded(&acc_full[par], (uint32_t)(i >> 1) & 1u)) { *s_dead = 1; break; }
       tc_fence_after();
-      uint32_t va[TC_CHW], vb[TC_CHW];
-      tc_ld16(tbase, va);
       float m = -INFINITY, m0 = 0.0f;
+      if constexpr (TC_DOUBLE_BUFFER) {
+        uint32_t va[TC_CHW], vb[TC_CHW];
+        TcLd<TC_CHW>::ld(tbase, va);
 #pragma unroll
-      for (int ch = 0; ch < NCH; ++ch) {
-        uint32_t* cur = (ch & 1) ? vb : va;
-        uint32_t* nxt = (ch & 1) ? va : vb;
-        tc_wait_ld16(cur);
-        if (ch + 1 < NCH) {
-          tc_ld16(tbase + (uint32_t)((ch + 1) * TC_CHW), nxt);
-        } else {                                    // the whole tile is in registers: the stage may be refilled
-          tc_fence_before();
-          mbar_arrive(&acc_empty[par]);
+        for (int ch = 0; ch < NCH; ++ch) {
+          uint32_t* cur = (ch & 1) ? vb : va;
+          uint32_t* nxt = (ch & 1) ? va : vb;
+          TcLd<TC_CHW>::wait(cur);
+          if (ch + 1 < NCH) {
+            TcLd<TC_CHW>::ld(tbase + (uint32_t)((ch + 1) * TC_CHW), nxt);
+          } else {                                  // the whole tile is in registers: the stage may be refilled
+            tc_fence_before();
+            mbar_arrive(&acc_empty[par]);
+          }
+          m = chunk_max(cur, ksb + ch * TC_CHW, m);
+          if (ch == CPB - 1) { m0 = m; m = -INFINITY; }
         }
-        m = chunk_max(cur, ksb + ch * TC_CHW, m);
-        if (ch == CPB - 1) { m0 = m; m = -INFINITY; }
+      } else {
+        // one wide load at a time: the other epilogue warps of the scheduler cover its latency
+        uint32_t v[TC_CHW];
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          TcLd<TC_CHW>::ld(tbase + (uint32_t)(ch * TC_CHW), v);
+          TcLd<TC_CHW>::wait(v);
+          if (ch + 1 == NCH) {
+            tc_fence_before();
+            mbar_arrive(&acc_empty[par]);
+          }
+          m = chunk_max(v, ksb + ch * TC_CHW, m);
+          if (ch == CPB - 1) { m0 = m; m = -INFINITY; }
+        }
       }
       // x -> fl(x * qscale) is monotone for qscale > 0: scale the block maxima only; then the group maximum
       // over the G heads of the query, which are G neighbouring lanes
@@ -361,24 +550,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
     }
   } else if (warp < TC_EPI_WARPS + TC_PROD_WARPS) {
     // =============================== producers ===============================
-    const int pt = tid - TC_EPI_WARPS * 32;         // 0..127: token of the tile
-    uint32_t bufA[W], bufB[W], bufC[W], bufD[W];
-    auto load_tile = [&](int tile, uint32_t (&buf)[W]) {
-      const int64_t t = (int64_t)tile * TC_NTILE + pt;
-      if (tile < ntiles && t < p.Tk) {
-        const uint4* src = reinterpret_cast<const uint4*>(packed_row + t * (C / 2));
+    // thread pt widens tokens pt, pt + 32 * TC_PROD_WARPS, ... of every tile
+    constexpr int PTHREADS = TC_PROD_WARPS * 32;
+    constexpr int TPT = TC_NTILE / PTHREADS;        // tokens per producer thread
+    constexpr int PW = W * TPT;
+    const int pt = tid - TC_EPI_WARPS * 32;
+    uint32_t bufA[PW], bufB[PW], bufC[PW], bufD[PW];
+    auto load_tile = [&](int tile, uint32_t (&buf)[PW]) {
 #pragma unroll
-        for (int x = 0; x < W / 4; ++x) {
-          const uint4 u = __ldg(src + x);
-          buf[4 * x] = u.x; buf[4 * x + 1] = u.y; buf[4 * x + 2] = u.z; buf[4 * x + 3] = u.w;
+      for (int h = 0; h < TPT; ++h) {
+        const int64_t t = (int64_t)tile * TC_NTILE + pt + h * PTHREADS;
+        if (tile < ntiles && t < p.Tk) {
+          const uint4* src = reinterpret_cast<const uint4*>(packed_row + t * (C / 2));
+#pragma unroll
+          for (int x = 0; x < W / 4; ++x) {
+            const uint4 u = __ldg(src + x);
+            buf[h * W + 4 * x] = u.x; buf[h * W + 4 * x + 1] = u.y;
+            buf[h * W + 4 * x + 2] = u.z; buf[h * W + 4 * x + 3] = u.w;
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < W; ++x) buf[h * W + x] = 0;
         }
-      } else {
-#pragma unroll
-        for (int x = 0; x < W; ++x) buf[x] = 0;
       }
     };
     bool dead = false;
-    auto store_tile = [&](int i, const uint32_t (&buf)[W]) {
+    auto store_tile = [&](int i, const uint32_t (&buf)[PW]) {
       const int s = i % BSTAGES;
       if (!dead) {
         const bool ok = mbar_wait_bounded(&b_empty[s], ((uint32_t)(i / BSTAGES) & 1u) ^ 1u);
@@ -386,32 +583,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
       }
       if (*s_dead) dead = true;
       if (dead) return;
-      uint8_t* dst = s_b + s * Cfg::B_STAGE + (pt >> 3) * Cfg::SBO + (pt & 7) * 16;
-      if constexpr (KIND == 0) {
 #pragma unroll
-        for (int c = 0; c < W / 2; ++c) {           // 16-byte chunk c = words 2c, 2c+1 -> (even, odd, even, odd)
-          const uint32_t w0 = buf[2 * c], w1 = buf[2 * c + 1];
-          *reinterpret_cast<uint4*>(dst + c * TC_LBO) =
-              make_uint4((w0 << 4) & 0xF0F0F0F0u, w0 & 0xF0F0F0F0u, (w1 << 4) & 0xF0F0F0F0u, w1 & 0xF0F0F0F0u);
-        }
-      } else {
-        const __half2 bias = __floats2half2_rn(1032.0f, 1032.0f);
-#pragma unroll
-        for (int c = 0; c < W; ++c) {               // chunk c = word c -> 8 halves (4 even channels, 4 odd)
-          const uint32_t x = buf[c] ^ 0x88888888u;  // two's complement nibble -> code + 8
-          const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
-          uint32_t h[4];
-          h[0] = __byte_perm(lo, 0x64u, 0x4140);    // halves 1024 + (code + 8) of bytes 0, 1
-          h[1] = __byte_perm(lo, 0x64u, 0x4342);
-          h[2] = __byte_perm(hi, 0x64u, 0x4140);
-          h[3] = __byte_perm(hi, 0x64u, 0x4342);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h[j]), bias);
-            h[j] = *reinterpret_cast<const uint32_t*>(&r);
-          }
-          *reinterpret_cast<uint4*>(dst + c * TC_LBO) = make_uint4(h[0], h[1], h[2], h[3]);
-        }
+      for (int h = 0; h < TPT; ++h) {
+        const int tok = pt + h * PTHREADS;
+        uint8_t* dst = s_b + s * Cfg::B_STAGE + (tok >> 3) * Cfg::SBO + (tok & 7) * 16;
+        tc_widen_token<C, KIND>(buf + h * W, dst);
       }
       fence_proxy_async_smem();
       mbar_arrive(&b_full[s]);
@@ -430,52 +606,251 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
     }
   } else if (lane == 0) {
     // =============================== MMA issuer ===============================
-    // One thread feeds the tensor core; its instruction stream is the serial part of the whole CTA, so it
-    // is kept short: descriptors differ from a base only in their address field (low word, no carry into
-    // the other fields below 256 KiB), the tile loop is unrolled over the operand ring and the two
-    // accumulator stages so that every index is a constant, and barrier addresses are plain integers.
-    const uint32_t idesc = tc_instr_desc<KIND>(128, TC_NTILE);
-    const uint64_t a_desc0 = tc_smem_desc(smem_u32(s_a), TC_LBO, Cfg::SBO);
-    const uint64_t b_desc0 = tc_smem_desc(smem_u32(s_b), TC_LBO, Cfg::SBO);
-    const uint32_t a_lo = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
-    const uint32_t b_lo = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
-    auto desc = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
-    constexpr int U = (BSTAGES % 2 == 0) ? BSTAGES : 2 * BSTAGES;      // tiles per unrolled round
-    bool dead = false;
-    uint32_t round = 0;                                               // i0 / U
-    for (int i0 = 0; i0 < ntiles && !dead; i0 += U, ++round) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int i = i0 + u;
-        if (i >= ntiles) break;
-        const int s = u % BSTAGES, a = u & 1;                          // constants after unrolling (U is even and a multiple of BSTAGES)
-        const uint32_t use_b = round * (U / BSTAGES) + (uint32_t)(u / BSTAGES);   // n-th use of operand stage s
-        const uint32_t use_a = round * (U / 2) + (uint32_t)(u / 2);               // n-th use of accumulator stage a
-        bool ok = mbar_wait_bounded(&b_full[s], use_b & 1u);
-        ok = ok && mbar_wait_bounded(&acc_empty[a], (use_a & 1u) ^ 1u);
-        if (!ok) { *s_dead = 1; dead = true; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int qt = 0; qt < TC_QT; ++qt) {
-          const uint32_t d = tmem_base + (uint32_t)(a * TC_QT * TC_NTILE + qt * TC_NTILE);
-#pragma unroll
-          for (int k = 0; k < Cfg::KSTEPS; ++k) {
-            const uint64_t ad = desc(a_lo + (uint32_t)((qt * Cfg::A_TILE + k * 2 * TC_LBO) >> 4), a_hi);
-            const uint64_t bd = desc(b_lo + (uint32_t)((s * Cfg::B_STAGE + k * 2 * TC_LBO) >> 4), b_hi);
-            tc_mma<KIND>(d, ad, bd, idesc, k > 0 ? 1u : 0u);
-          }
-        }
-        tc_commit(&b_empty[s]);                     // the stage may be overwritten once these MMAs have read it
-        tc_commit(&acc_full[a]);
-      }
-    }
-    tc_commit(all_done);
-    mbar_wait_bounded(all_done, 0);                 // nothing of this CTA is still in flight in the tensor core
+    tc_issue_tiles<KIND, Cfg>(s_a, s_b, b_full, b_empty, acc_full, acc_empty, all_done, s_dead, tmem_base, ntiles);
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == TC_WARPS - 1) {
+    tc_fence_after();
+    tc_dealloc(tmem_base, TC_TMEM_COLS);
+  }
+}
+
+// ====================================================================================================
+// Second form: the key operands are widened ONCE into global memory (prefill_widen_kernel), already in the
+// core-matrix layout, one contiguous B_STAGE block per tile of 128 tokens, and every CTA fetches a tile with
+// one bulk copy issued by one thread. That frees the four conversion warps and their issue slots, and the
+// registers they held go to the epilogue: 18 warps, 16 of them epilogue warps that ALL drain every tile
+// (warp = TMEM lane quadrant x row tile x 64-column half = one block of one row tile), so an accumulator
+// stage is released after two 32-column loads per warp instead of eight 16-column loads, and the tensor
+// core is given the stage back four times sooner. The 64 CTAs of one (batch, KV head) read the same
+// operand stream at the same pace, so it comes from L2.
+constexpr int TW_EPI_WARPS = 16;
+constexpr int TW_WARPS = TW_EPI_WARPS + 2;        // + the bulk-copy thread's warp + the MMA warp
+constexpr int TW_THREADS = TW_WARPS * 32;
+constexpr int TW_CHW = 32;                        // accumulator columns per tensor-memory load
+
+template <int C, int KIND>
+struct TwCfg {
+  using Base = TcCfg<C, KIND>;
+  static constexpr int SBO = Base::SBO;
+  static constexpr int KSTEPS = Base::KSTEPS;
+  static constexpr int A_TILE = Base::A_TILE;
+  static constexpr int B_STAGE = Base::B_STAGE;
+  static constexpr int FIT = (200 * 1024 - TC_QT * A_TILE) / B_STAGE;
+  static constexpr int BSTAGES = FIT >= 8 ? 8 : (FIT & ~1);                 // even, at most 8
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + TC_QT * A_TILE;
+  static constexpr int OFF_KS = OFF_B + BSTAGES * B_STAGE;                  // [epilogue warps][2][64] key scales
+  static constexpr int OFF_BAR = OFF_KS + TW_EPI_WARPS * 2 * 64 * 4;
+  static constexpr int NBAR = 2 * BSTAGES + 2 * TC_ASTAGES + 1;
+  static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;
+  static constexpr int BYTES = OFF_MISC + 16;
+};
+
+// operands: [B*Hkv][cap_tiles][B_STAGE]; tokens at or beyond Tk are zero rows. The tiles first_tile ..
+// ceil(Tk/128)-1 are written (a grown cache re-widens only its last, partly filled tile and the new ones).
+template <int C, int KIND>
+__global__ void __launch_bounds__(TC_NTILE) prefill_widen_kernel(const uint8_t* __restrict__ packed, int64_t packed_sb,
+                                                                 int64_t packed_sh, int Hkv, int Tk, int cap_tiles,
+                                                                 int first_tile, uint8_t* __restrict__ operands) {
+  using Cfg = TcCfg<C, KIND>;
+  constexpr int W = C / 8;
+  const int tile = first_tile + blockIdx.x, bh = blockIdx.y, pt = threadIdx.x;
+  const int b = bh / Hkv, kvh = bh - b * Hkv;
+  const int64_t t = (int64_t)tile * TC_NTILE + pt;
+  uint32_t words[W];
+  if (t < Tk) {
+    const uint4* src = reinterpret_cast<const uint4*>(packed + (int64_t)b * packed_sb + (int64_t)kvh * packed_sh + t * (C / 2));
+#pragma unroll
+    for (int x = 0; x < W / 4; ++x) {
+      const uint4 u = __ldg(src + x);
+      words[4 * x] = u.x; words[4 * x + 1] = u.y; words[4 * x + 2] = u.z; words[4 * x + 3] = u.w;
+    }
+  } else {
+#pragma unroll
+    for (int x = 0; x < W; ++x) words[x] = 0;
+  }
+  uint8_t* dst = operands + ((int64_t)bh * cap_tiles + tile) * Cfg::B_STAGE + (pt >> 3) * Cfg::SBO + (pt & 7) * 16;
+  tc_widen_token<C, KIND>(words, dst);
+}
+
+struct PrefillTwParams {
+  PrefillTcParams base;       // packed is unused
+  const uint8_t* operands;    // see prefill_widen_kernel
+  int cap_tiles;
+};
+
+template <int C, int G, int KIND>
+__global__ void __launch_bounds__(TW_THREADS, 1) score_prefill_tw_kernel(PrefillTwParams pw) {
+  using Cfg = TwCfg<C, KIND>;
+  const PrefillTcParams& p = pw.base;
+  constexpr int QPT = 128 / G;
+  constexpr int QCTA = TC_QT * QPT;
+  constexpr int BSTAGES = Cfg::BSTAGES;
+  extern __shared__ __align__(1024) uint8_t tc_smem[];
+  uint8_t* s_a = tc_smem + Cfg::OFF_A;
+  uint8_t* s_b = tc_smem + Cfg::OFF_B;
+  float* s_ks = reinterpret_cast<float*>(tc_smem + Cfg::OFF_KS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tc_smem + Cfg::OFF_BAR);
+  uint64_t* b_full = bars;                          // [BSTAGES] bulk copy landed (transaction bytes)
+  uint64_t* b_empty = bars + BSTAGES;               // [BSTAGES] MMA -> copy thread (commit)
+  uint64_t* acc_full = bars + 2 * BSTAGES;          // [ASTAGES] MMA -> epilogue (commit)
+  uint64_t* acc_empty = acc_full + TC_ASTAGES;      // [ASTAGES] one arrival per epilogue warp
+  uint64_t* all_done = acc_empty + TC_ASTAGES;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tc_smem + Cfg::OFF_MISC);
+  volatile uint32_t* s_dead = s_tmem + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.Hkv, kvh = bh - b * p.Hkv;
+  const int q0 = blockIdx.x * QCTA;
+  const int ntiles = (p.Tk + TC_NTILE - 1) / TC_NTILE;
+
+  if (tid == 0) {
+    for (int s = 0; s < BSTAGES; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+    for (int a = 0; a < TC_ASTAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TW_EPI_WARPS); }
+    mbar_init(all_done, 1);
+    *s_dead = 0;
+    fence_mbar_init();
+  }
+  if (warp == TW_WARPS - 1) {
+    tc_alloc(s_tmem, TC_TMEM_COLS);
+    tc_relinquish();
+  }
+  tc_fill_a_tiles<C, G, KIND, Cfg>(p, s_a, b, kvh, q0, tid, TW_THREADS);
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+  const float* scale_row = p.scale + (int64_t)b * p.scale_sb + (int64_t)kvh * p.scale_sh;
+
+  if (warp < TW_EPI_WARPS) {
+    // =============================== epilogue ===============================
+    // warp -> TMEM lane quadrant (warp % 4, fixed by the hardware), row tile qt, column half: the warp
+    // reads columns [64*half, 64*half + 64) of row tile qt of EVERY tile = block 2*i + half.
+    const int quad = warp & 3, qt = (warp >> 2) & 1, half = warp >> 3;
+    const int row = quad * 32 + lane;
+    const int qi = row / G, hd = row - qi * G;
+    const int q = q0 + qt * QPT + qi;
+    const float qs = q < p.Tq ? p.qscale[((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q] : 0.0f;
+    float* out_row = p.out + (((int64_t)b * p.Hkv + kvh) * p.Tq + (q < p.Tq ? q : 0)) * p.nblk;
+    const bool writer = hd == 0 && q < p.Tq;
+    float* my_ks = s_ks + warp * 2 * 64;
+    // Key scales of the warp's 64 tokens of a tile: lane l fetches tokens 2l, 2l+1; dead tokens get NaN,
+    // which never wins a max. Fetched two tiles ahead.
+    auto load_ks = [&](int tile) -> float2 {
+      const float nan = __int_as_float(0x7fc00000);
+      float2 v = make_float2(nan, nan);
+      const int64_t t = (int64_t)tile * TC_NTILE + half * 64 + 2 * lane;
+      if (tile < ntiles) {
+        if (t + 1 < p.Tk) {
+          v = *reinterpret_cast<const float2*>(scale_row + t);
+        } else if (t < p.Tk) {
+          v.x = scale_row[t];
+        }
+        if constexpr (KIND == 0) { v.x *= 0.0625f; v.y *= 0.0625f; }
+      }
+      return v;
+    };
+    // TMEM address of the warp's columns in accumulator stage a
+    auto tcol = [&](int a) -> uint32_t {
+      return tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * TC_QT * TC_NTILE + qt * TC_NTILE + half * 64);
+    };
+    float2 k_cur = load_ks(0), k_next = load_ks(1);
+    uint32_t va[TW_CHW], vb[TW_CHW];
+    bool live = ntiles > 0;
+    if (live) {
+      if (!mbar_wait_bounded(&acc_full[0], 0u)) { *s_dead = 1; live = false; }
+    }
+    if (live) {
+      tc_fence_after();
+      TcLd<TW_CHW>::ld(tcol(0), va);
+    }
+#ifdef KVB_EXP_PROFILE
+    long long pf[5] = {0, 0, 0, 0, 0};
+    long long pc = clock64();
+#define PF_MARK(k) { const long long now = clock64(); pf[k] += now - pc; pc = now; }
+#else
+#define PF_MARK(k)
+#endif
+    for (int i = 0; live && i < ntiles; ++i) {
+      const int a = i & 1;
+      float* ksb = my_ks + a * 64;
+      *reinterpret_cast<float2*>(ksb + 2 * lane) = k_cur;
+      k_cur = k_next;
+      k_next = load_ks(i + 2);
+      __syncwarp();
+      PF_MARK(0)
+      TcLd<TW_CHW>::wait(va);
+      PF_MARK(1)
+      TcLd<TW_CHW>::ld(tcol(a) + TW_CHW, vb);
+      float m = tc_chunk_max<KIND, TW_CHW>(va, ksb, -INFINITY);
+      PF_MARK(2)
+      TcLd<TW_CHW>::wait(vb);
+      PF_MARK(1)
+      // the warp's 64 columns are in registers: its share of the stage may be refilled
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[a]);
+      if (i + 1 < ntiles) {                         // next tile's first half in flight while this one is finished
+        if (*s_dead || !mbar_wait_bounded(&acc_full[a ^ 1], (uint32_t)((i + 1) >> 1) & 1u)) {
+          *s_dead = 1;
+          live = false;
+        } else {
+          tc_fence_after();
+          TcLd<TW_CHW>::ld(tcol(a ^ 1), va);
+        }
+      }
+      PF_MARK(3)
+      m = tc_chunk_max<KIND, TW_CHW>(vb, ksb + TW_CHW, m);
+      PF_MARK(2)
+      // x -> fl(x * qscale) is monotone for qscale > 0: scale the block maximum only; then the group
+      // maximum over the G heads of the query, which are G neighbouring lanes
+      float r0 = __fmul_rn(m, qs);
+#pragma unroll
+      for (int off = 1; off < G; off <<= 1) r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, off));
+      const int blk = 2 * i + half;
+      if (writer && blk < p.nblk) {
+        if (r0 == 0.0f) r0 = 0.0f;                  // -0 -> +0
+        out_row[blk] = r0;
+      }
+      PF_MARK(4)
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#ifdef KVB_EXP_PROFILE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 5 || warp == 15))
+      printf("epi warp %d per tile: ks/sync %lld wait_ld %lld compute %lld arrive+acc_full %lld finalize %lld\n", warp,
+             pf[0] / ntiles, pf[1] / ntiles, pf[2] / ntiles, pf[3] / ntiles, pf[4] / ntiles);
+#endif
+  } else if (warp == TW_EPI_WARPS) {
+    // =============================== operand copies ===============================
+    if (lane == 0) {
+      const uint8_t* src = pw.operands + (int64_t)bh * pw.cap_tiles * Cfg::B_STAGE;
+      int issued = 0;
+      for (int i = 0; i < ntiles; ++i) {
+        const int s = i % BSTAGES;
+        if (*s_dead) break;
+        if (!mbar_wait_bounded(&b_empty[s], ((uint32_t)(i / BSTAGES) & 1u) ^ 1u)) { *s_dead = 1; break; }
+        mbar_arrive_expect_tx(&b_full[s], (uint32_t)Cfg::B_STAGE);
+        bulk_g2s(s_b + s * Cfg::B_STAGE, src + (int64_t)i * Cfg::B_STAGE, (uint32_t)Cfg::B_STAGE, &b_full[s]);
+        ++issued;
+      }
+      // no copy of this CTA may still be writing shared memory when the CTA leaves: wait (bounded) for the
+      // copies that can be outstanding, the last BSTAGES ones
+      for (int j = issued > BSTAGES ? issued - BSTAGES : 0; j < issued; ++j)
+        mbar_wait_bounded(&b_full[j % BSTAGES], (uint32_t)(j / BSTAGES) & 1u, 1u << 16);
+    }
+  } else if (lane == 0) {
+    // =============================== MMA issuer ===============================
+    tc_issue_tiles<KIND, Cfg>(s_a, s_b, b_full, b_empty, acc_full, acc_empty, all_done, s_dead, tmem_base, ntiles);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == TW_WARPS - 1) {
     tc_fence_after();
     tc_dealloc(tmem_base, TC_TMEM_COLS);
   }
@@ -516,6 +891,74 @@ static int prefill_tc_run(const PrefillTcParams& p, int C, int G, int kind, int 
     if (C == 32) return prefill_tc_dispatch_g<32, 1>(p, G, device, st);
     if (C == 64) return prefill_tc_dispatch_g<64, 1>(p, G, device, st);
     if (C == 128) return prefill_tc_dispatch_g<128, 1>(p, G, device, st);
+  }
+  return KVB_BAD_SHAPE;
+}
+
+
+template <int C, int G, int KIND>
+static int prefill_tw_launch(const PrefillTwParams& pw, int device, cudaStream_t st) {
+  using Cfg = TwCfg<C, KIND>;
+  static_assert(Cfg::BYTES <= 227 * 1024, "shared memory budget");
+  static_assert(Cfg::BSTAGES >= 2, "operand ring");
+  auto kern = score_prefill_tw_kernel<C, G, KIND>;
+  static std::atomic<bool> attr_done[KVB_MAX_DEVICES];
+  { const int arc = ensure_dynamic_smem(kern, attr_done, device, (size_t)Cfg::BYTES); if (arc != KVB_OK) return arc; }
+  constexpr int QCTA = TC_QT * (128 / G);
+  dim3 grid(ceil_div(pw.base.Tq, QCTA), pw.base.B * pw.base.Hkv);
+  kern<<<grid, TW_THREADS, Cfg::BYTES, st>>>(pw);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  return KVB_OK;
+}
+
+template <int C, int KIND>
+static int prefill_tw_dispatch_g(const PrefillTwParams& pw, int G, int device, cudaStream_t st) {
+  switch (G) {
+    case 1: return prefill_tw_launch<C, 1, KIND>(pw, device, st);
+    case 2: return prefill_tw_launch<C, 2, KIND>(pw, device, st);
+    case 4: return prefill_tw_launch<C, 4, KIND>(pw, device, st);
+    case 8: return prefill_tw_launch<C, 8, KIND>(pw, device, st);
+    default: return KVB_BAD_SHAPE;
+  }
+}
+
+static int prefill_tw_run(const PrefillTwParams& pw, int C, int G, int kind, int device, cudaStream_t st) {
+  if (kind == 0) {
+    if (C == 32) return prefill_tw_dispatch_g<32, 0>(pw, G, device, st);
+    if (C == 64) return prefill_tw_dispatch_g<64, 0>(pw, G, device, st);
+    if (C == 128) return prefill_tw_dispatch_g<128, 0>(pw, G, device, st);
+  } else {
+    if (C == 32) return prefill_tw_dispatch_g<32, 1>(pw, G, device, st);
+    if (C == 64) return prefill_tw_dispatch_g<64, 1>(pw, G, device, st);
+    if (C == 128) return prefill_tw_dispatch_g<128, 1>(pw, G, device, st);
+  }
+  return KVB_BAD_SHAPE;
+}
+
+// bytes of one widened operand tile (128 tokens)
+static size_t prefill_operand_tile_bytes(int C, int kind) { return (size_t)TC_NTILE * C * (kind == 0 ? 1 : 2); }
+
+template <int C, int KIND>
+static int prefill_widen_launch(const uint8_t* packed, int64_t sb, int64_t sh, int B, int Hkv, int Tk, int cap_tiles,
+                                int first_tile, uint8_t* operands, cudaStream_t st) {
+  const int ntiles = ceil_div(Tk, TC_NTILE);
+  if (first_tile >= ntiles) return KVB_OK;
+  dim3 grid(ntiles - first_tile, B * Hkv);
+  prefill_widen_kernel<C, KIND><<<grid, TC_NTILE, 0, st>>>(packed, sb, sh, Hkv, Tk, cap_tiles, first_tile, operands);
+  KVB_CHECK_CUDA(cudaGetLastError());
+  return KVB_OK;
+}
+
+static int prefill_widen_run(const uint8_t* packed, int64_t sb, int64_t sh, int B, int Hkv, int Tk, int C, int kind,
+                             int cap_tiles, int first_tile, uint8_t* operands, cudaStream_t st) {
+  if (kind == 0) {
+    if (C == 32) return prefill_widen_launch<32, 0>(packed, sb, sh, B, Hkv, Tk, cap_tiles, first_tile, operands, st);
+    if (C == 64) return prefill_widen_launch<64, 0>(packed, sb, sh, B, Hkv, Tk, cap_tiles, first_tile, operands, st);
+    if (C == 128) return prefill_widen_launch<128, 0>(packed, sb, sh, B, Hkv, Tk, cap_tiles, first_tile, operands, st);
+  } else {
+    if (C == 32) return prefill_widen_launch<32, 1>(packed, sb, sh, B, Hkv, Tk, cap_tiles, first_tile, operands, st);
+    if (C == 64) return prefill_widen_launch<64, 1>(packed, sb, sh, B, Hkv, Tk, cap_tiles, first_tile, operands, st);
+    if (C == 128) return prefill_widen_launch<128, 1>(packed, sb, sh, B, Hkv, Tk, cap_tiles, first_tile, operands, st);
   }
   return KVB_BAD_SHAPE;
 }

@@ -645,13 +645,46 @@ def quantize_query_tokens(query: torch.Tensor, channel_idx: torch.Tensor) -> tup
 PREFILL_ENGINES = {"auto": 0, "mma": 1, "i8": 2, "f16": 3}
 
 
+class WidenedKeys:
+    """The int4 key codes of a side cache widened once to tensor-core operands (fp16 values or int8 bytes of the
+    same integers) in the core-matrix tile layout the prefill scorer reads: ``[B*Hkv, capacity/128, tile]``
+    bytes. A chunked prefill scores every chunk of queries against the same keys, so the widening is paid once
+    per cache (or once per appended range: ``update`` re-widens from ``first_token`` on), not once per CTA."""
+
+    def __init__(self, packed: torch.Tensor, key_count: Optional[int] = None, engine: str = "f16",
+                 capacity: Optional[int] = None):
+        if engine not in ("f16", "i8"):
+            raise ValueError("engine must be 'f16' or 'i8'")
+        B, Hkv, cap_rows, half_c = packed.shape
+        self.engine, self.B, self.Hkv, self.C = engine, B, Hkv, 2 * half_c
+        self.capacity = int(capacity if capacity is not None else cap_rows)
+        nbytes = _native.lib().kvb_prefill_operand_bytes(B, Hkv, self.capacity, self.C, PREFILL_ENGINES[engine])
+        if nbytes == 0:
+            raise ValueError("unsupported shape for widened prefill operands")
+        self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=packed.device)
+        self.key_count = 0
+        self.update(packed, packed.shape[2] if key_count is None else int(key_count), 0)
+
+    def update(self, packed: torch.Tensor, key_count: int, first_token: int) -> None:
+        """(Re-)widens the tokens ``first_token .. key_count-1`` (whole tiles of 128 from the tile of ``first_token``)."""
+        if key_count > self.capacity:
+            raise ValueError("key_count exceeds the capacity of the widened buffer")
+        check(_native.lib().kvb_widen_keys(
+            packed.data_ptr(), packed.stride(0), packed.stride(1), self.B, self.Hkv, int(key_count), self.capacity,
+            self.C, PREFILL_ENGINES[self.engine], int(first_token), self.buffer.data_ptr(), self.buffer.numel(),
+            _dev(packed), _stream(packed.device)), "kvb_widen_keys")
+        self.key_count = int(key_count)
+
+
 def score_prefill_blocks(qcode: torch.Tensor, qscale: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                         key_count: Optional[int] = None, engine: str = "auto") -> torch.Tensor:
+                         key_count: Optional[int] = None, engine: str = "auto",
+                         widened: Optional[WidenedKeys] = None) -> torch.Tensor:
     """Block scores fp32 ``[B,Hkv,Tq,ceil(Tk/64)]``: max over the GQA group and the 64 tokens of each
     key block of the dequantised int8 x int4 partial score; every query sees all ``key_count`` keys.
-    ``engine``: ``auto`` (tensor-memory path), ``mma`` (warp-level int8 MMA), ``i8`` / ``f16`` (tcgen05 with
-    int8 operands and int32 accumulators / the same integers as fp16 operands with fp32 accumulators);
-    all produce identical bits."""
+    ``engine``: ``auto`` (tensor-memory path on pre-widened operands: ``widened`` if given, else widened here
+    for this call), ``mma`` (warp-level int8 MMA), ``i8`` / ``f16`` (tcgen05, codes widened inside every CTA;
+    int8 operands and int32 accumulators / the same integers as fp16 operands with fp32 accumulators),
+    ``i8w`` / ``f16w`` (tcgen05 on pre-widened operands); all produce identical bits."""
     B, Hq, Tq, C_ = qcode.shape
     Hkv = packed.shape[1]
     _check_side_cache(packed, scale, C_)
@@ -659,6 +692,17 @@ def score_prefill_blocks(qcode: torch.Tensor, qscale: torch.Tensor, packed: torc
     dev = qcode.device
     nblk = (Tk + PREFILL_BLOCK - 1) // PREFILL_BLOCK
     out = torch.empty((B, Hkv, Tq, nblk), dtype=torch.float32, device=dev)
+    if engine in ("auto", "f16w", "i8w") or widened is not None:
+        if widened is None:
+            widened = WidenedKeys(packed, Tk, "i8" if engine == "i8w" else "f16", capacity=Tk)
+        if widened.key_count < Tk or widened.C != C_:
+            raise ValueError("the widened operands do not cover the keys asked for")
+        check(_native.lib().kvb_score_prefill_blocks_widened(
+            qcode.contiguous().data_ptr(), qscale.contiguous().data_ptr(), widened.buffer.data_ptr(),
+            widened.buffer.numel(), widened.capacity, scale.data_ptr(), scale.stride(0), scale.stride(1),
+            B, Hq, Hkv, Tq, Tk, C_, PREFILL_BLOCK, out.data_ptr(), PREFILL_ENGINES[widened.engine], _dev(qcode),
+            _stream(dev)), "kvb_score_prefill_blocks_widened")
+        return out
     check(_native.lib().kvb_score_prefill_blocks_engine(
         qcode.contiguous().data_ptr(), qscale.contiguous().data_ptr(),
         packed.data_ptr(), packed.stride(0), packed.stride(1),

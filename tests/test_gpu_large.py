@@ -116,7 +116,7 @@ def prefill_case(cuda_device):
                 want_idx=want_idx)
 
 
-@pytest.mark.parametrize("engine", ["mma", "i8", "f16"])
+@pytest.mark.parametrize("engine", ["mma", "i8", "f16", "i8w", "f16w"])
 def test_prefill_block_scores_at_full_key_length(prefill_case, engine):
     """The chunked-prefill configuration at its real size (4096 queries x 131072 keys, batch 2, 32 query
     heads over 8 KV heads): 64 seeded query rows per batch row are recomputed by the oracle over all

@@ -43,7 +43,7 @@ def test_block_scores_and_topk_bit_exact(cuda_device, B, Hq, Hkv, Tq, Tk, C):
     assert torch.equal(idx2, idx)
 
 
-@pytest.mark.parametrize("engine", ["mma", "i8", "f16"])
+@pytest.mark.parametrize("engine", ["mma", "i8", "f16", "i8w", "f16w"])
 @pytest.mark.parametrize("B,Hq,Hkv,Tq,Tk,C", [
     (1, 8, 2, 128, 4096, 64),       # 32 key tiles, two query tiles per CTA, G = 4
     (2, 4, 2, 150, 1000, 64),       # ragged query tile, short last block, odd number of blocks
@@ -62,7 +62,7 @@ def test_every_prefill_engine_gives_the_same_bits(cuda_device, engine, B, Hq, Hk
     assert torch.equal(bs.cpu().view(torch.int32), want.view(torch.int32))
 
 
-@pytest.mark.parametrize("engine", ["mma", "i8", "f16"])
+@pytest.mark.parametrize("engine", ["mma", "i8", "f16", "i8w", "f16w"])
 def test_prefill_engines_at_the_largest_accumulator(cuda_device, engine):
     """Every code at its extreme (|q| = 127, |k| = 7, C = 128): |acc| reaches 127 * 7 * 128 = 113792, the
     largest integer any accumulator of this path can hold; it must come out exact in every encoding."""
@@ -92,3 +92,24 @@ def test_block_topk_ties_and_short_rows(cuda_device):
     big = torch.randint(-3, 4, (70, 2048), generator=g, device=cuda_device).float()
     want, _ = oracle.select(big.cpu(), 32)
     assert torch.equal(ops.block_topk(big, 32).cpu().long(), want)
+
+
+@pytest.mark.parametrize("engine", ["i8", "f16"])
+def test_widened_keys_kept_across_chunks_and_grown(cuda_device, engine):
+    """One widened operand buffer with spare capacity serves several query chunks; keys appended later are
+    widened from the tile of the first new token on and the scores still equal the oracle's."""
+    B, Hq, Hkv, Tq, C = 1, 8, 2, 70, 64
+    T0, T1, cap = 1000, 1000 + 300, 2048
+    key, q = _case(cuda_device, B, Hq, Hkv, Tq, T1, C, seed=11)
+    ch = ops.choose_channels(key, C)
+    packed, scale = ops.quantize(key, ch)
+    qcode, qscale = ops.quantize_query_tokens(q, ch)
+    codes_o, _, kscale_o = oracle.quantize_pack(key.cpu(), ch.cpu())
+    wk = ops.WidenedKeys(packed, T0, engine, capacity=cap)
+    for Tk in (T0, T1):
+        if Tk > wk.key_count:
+            wk.update(packed, Tk, first_token=wk.key_count)
+        for _ in range(2):                              # two chunks against the same operands
+            bs = ops.score_prefill_blocks(qcode, qscale, packed, scale, Tk, widened=wk)
+            want = oracle.prefill_block_scores(qcode.cpu(), qscale.cpu(), codes_o[:, :, :Tk], kscale_o[:, :, :Tk])
+            assert torch.equal(bs.cpu().view(torch.int32), want.view(torch.int32))
