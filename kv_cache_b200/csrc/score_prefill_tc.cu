@@ -30,9 +30,6 @@
 #include "common.cuh"
 
 #include <cuda_fp16.h>
-#ifdef KVB_EXP_PROFILE
-#include <cstdio>
-#endif
 
 namespace kvb {
 
@@ -271,11 +268,7 @@ __device__ __forceinline__ float tc_chunk_max(const uint32_t* v, const float* ks
   float ma = m, mb = -INFINITY;
 #pragma unroll
   for (int c = 0; c < N; c += 4) {
-#ifdef KVB_EXP_NOKS
-    const float4 kk = *reinterpret_cast<const float4*>(ks);
-#else
     const float4 kk = *reinterpret_cast<const float4*>(ks + c);
-#endif
     float x0, x1, x2, x3;
     if constexpr (KIND == 0) {
       x0 = __uint_as_float(v[c] + 0x4B400000u) - 12582912.0f;
@@ -342,9 +335,6 @@ __device__ __forceinline__ void tc_issue_tiles(uint8_t* s_a, uint8_t* s_b, uint6
                                                uint64_t* acc_full, uint64_t* acc_empty, uint64_t* all_done,
                                                volatile uint32_t* s_dead, uint32_t tmem_base, int ntiles) {
   constexpr int BSTAGES = Cfg::BSTAGES;
-#ifdef KVB_EXP_PROFILE
-  long long g_prof_mma[2] = {0, 0};
-#endif
   {
     const uint32_t idesc = tc_instr_desc<KIND>(128, TC_NTILE);
     const uint64_t a_desc0 = tc_smem_desc(smem_u32(s_a), TC_LBO, Cfg::SBO);
@@ -363,18 +353,8 @@ __device__ __forceinline__ void tc_issue_tiles(uint8_t* s_a, uint8_t* s_b, uint6
         const int s = u % BSTAGES, a = u & 1;                          // constants after unrolling (U is even and a multiple of BSTAGES)
         const uint32_t use_b = round * (U / BSTAGES) + (uint32_t)(u / BSTAGES);   // n-th use of operand stage s
         const uint32_t use_a = round * (U / 2) + (uint32_t)(u / 2);               // n-th use of accumulator stage a
-#ifdef KVB_EXP_PROFILE
-        const long long c0 = clock64();
-#endif
         bool ok = mbar_wait_bounded(&b_full[s], use_b & 1u);
-#ifdef KVB_EXP_PROFILE
-        const long long c1 = clock64();
-#endif
         ok = ok && mbar_wait_bounded(&acc_empty[a], (use_a & 1u) ^ 1u);
-#ifdef KVB_EXP_PROFILE
-        const long long c2 = clock64();
-        g_prof_mma[0] += c1 - c0; g_prof_mma[1] += c2 - c1;
-#endif
         if (!ok) { *s_dead = 1; dead = true; break; }
         tc_fence_after();
 #pragma unroll
@@ -393,10 +373,6 @@ __device__ __forceinline__ void tc_issue_tiles(uint8_t* s_a, uint8_t* s_b, uint6
     }
     tc_commit(all_done);
     mbar_wait_bounded(all_done, 0);                 // nothing of this CTA is still in flight in the tensor core
-#ifdef KVB_EXP_PROFILE
-    if (blockIdx.x == 0 && blockIdx.y == 0)
-      printf("mma: wait b_full %lld wait acc_empty %lld per tile (ntiles %d)\n", g_prof_mma[0] / ntiles, g_prof_mma[1] / ntiles, ntiles);
-#endif
   }
 }
 
@@ -620,16 +596,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) score_prefill_tc_kernel(Prefill
 // ====================================================================================================
 // Second form: the key operands are widened ONCE into global memory (prefill_widen_kernel), already in the
 // core-matrix layout, one contiguous B_STAGE block per tile of 128 tokens, and every CTA fetches a tile with
-// one bulk copy issued by one thread. That frees the four conversion warps and their issue slots, and the
-// registers they held go to the epilogue: 18 warps, 16 of them epilogue warps that ALL drain every tile
-// (warp = TMEM lane quadrant x row tile x 64-column half = one block of one row tile), so an accumulator
-// stage is released after two 32-column loads per warp instead of eight 16-column loads, and the tensor
-// core is given the stage back four times sooner. The 64 CTAs of one (batch, KV head) read the same
+// one bulk copy issued by one thread. The four conversion warps and their issue slots are gone (18 warps
+// instead of 21), the registers they held go to the epilogue (32-column loads, two in flight), and the
+// operand ring is as deep as shared memory allows. The 64 CTAs of one (batch, KV head) read the same
 // operand stream at the same pace, so it comes from L2.
 constexpr int TW_EPI_WARPS = 16;
 constexpr int TW_WARPS = TW_EPI_WARPS + 2;        // + the bulk-copy thread's warp + the MMA warp
 constexpr int TW_THREADS = TW_WARPS * 32;
-constexpr int TW_CHW = 32;                        // accumulator columns per tensor-memory load
+constexpr int TW_CHW = 32;                        // accumulator columns per tensor-memory load (two loads alternate)
 
 template <int C, int KIND>
 struct TwCfg {
@@ -642,8 +616,8 @@ struct TwCfg {
   static constexpr int BSTAGES = FIT >= 8 ? 8 : (FIT & ~1);                 // even, at most 8
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + TC_QT * A_TILE;
-  static constexpr int OFF_KS = OFF_B + BSTAGES * B_STAGE;                  // [epilogue warps][2][64] key scales
-  static constexpr int OFF_BAR = OFF_KS + TW_EPI_WARPS * 2 * 64 * 4;
+  static constexpr int OFF_KS = OFF_B + BSTAGES * B_STAGE;                  // [epilogue warps][2][128] key scales
+  static constexpr int OFF_BAR = OFF_KS + TW_EPI_WARPS * 2 * TC_NTILE * 4;
   static constexpr int NBAR = 2 * BSTAGES + 2 * TC_ASTAGES + 1;
   static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;
   static constexpr int BYTES = OFF_MISC + 16;
@@ -697,7 +671,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) score_prefill_tw_kernel(Prefill
   uint64_t* b_full = bars;                          // [BSTAGES] bulk copy landed (transaction bytes)
   uint64_t* b_empty = bars + BSTAGES;               // [BSTAGES] MMA -> copy thread (commit)
   uint64_t* acc_full = bars + 2 * BSTAGES;          // [ASTAGES] MMA -> epilogue (commit)
-  uint64_t* acc_empty = acc_full + TC_ASTAGES;      // [ASTAGES] one arrival per epilogue warp
+  uint64_t* acc_empty = acc_full + TC_ASTAGES;      // [ASTAGES] one arrival per epilogue warp of the stage
   uint64_t* all_done = acc_empty + TC_ASTAGES;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tc_smem + Cfg::OFF_MISC);
   volatile uint32_t* s_dead = s_tmem + 1;
@@ -710,7 +684,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) score_prefill_tw_kernel(Prefill
 
   if (tid == 0) {
     for (int s = 0; s < BSTAGES; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
-    for (int a = 0; a < TC_ASTAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TW_EPI_WARPS); }
+    for (int a = 0; a < TC_ASTAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TW_EPI_WARPS / TC_ASTAGES); }
     mbar_init(all_done, 1);
     *s_dead = 0;
     fence_mbar_init();
@@ -729,102 +703,87 @@ __global__ void __launch_bounds__(TW_THREADS, 1) score_prefill_tw_kernel(Prefill
 
   if (warp < TW_EPI_WARPS) {
     // =============================== epilogue ===============================
-    // warp -> TMEM lane quadrant (warp % 4, fixed by the hardware), row tile qt, column half: the warp
-    // reads columns [64*half, 64*half + 64) of row tile qt of EVERY tile = block 2*i + half.
-    const int quad = warp & 3, qt = (warp >> 2) & 1, half = warp >> 3;
+    // warp -> TMEM lane quadrant (warp % 4, fixed by the hardware), row tile qt and accumulator stage `par`:
+    // the warp handles tiles par, par + 2, ... and reads all 128 columns (two blocks) of its row tile, so
+    // the per-visit costs (barrier, scale staging, group maximum, store) are paid once per 128 columns.
+    const int quad = warp & 3, qt = (warp >> 2) & 1, par = warp >> 3;
     const int row = quad * 32 + lane;
     const int qi = row / G, hd = row - qi * G;
     const int q = q0 + qt * QPT + qi;
     const float qs = q < p.Tq ? p.qscale[((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q] : 0.0f;
     float* out_row = p.out + (((int64_t)b * p.Hkv + kvh) * p.Tq + (q < p.Tq ? q : 0)) * p.nblk;
     const bool writer = hd == 0 && q < p.Tq;
-    float* my_ks = s_ks + warp * 2 * 64;
-    // Key scales of the warp's 64 tokens of a tile: lane l fetches tokens 2l, 2l+1; dead tokens get NaN,
-    // which never wins a max. Fetched two tiles ahead.
-    auto load_ks = [&](int tile) -> float2 {
+    float* my_ks = s_ks + warp * 2 * TC_NTILE;
+    // Key scales of a tile: lane l fetches tokens 4l .. 4l+3; dead tokens get NaN, which never wins a max.
+    // Fetched two of this warp's tiles ahead.
+    auto load_ks = [&](int tile) -> float4 {
       const float nan = __int_as_float(0x7fc00000);
-      float2 v = make_float2(nan, nan);
-      const int64_t t = (int64_t)tile * TC_NTILE + half * 64 + 2 * lane;
+      float4 v = make_float4(nan, nan, nan, nan);
+      const int64_t t = (int64_t)tile * TC_NTILE + 4 * lane;
       if (tile < ntiles) {
-        if (t + 1 < p.Tk) {
-          v = *reinterpret_cast<const float2*>(scale_row + t);
-        } else if (t < p.Tk) {
-          v.x = scale_row[t];
+        if (t + 3 < p.Tk) {
+          v = *reinterpret_cast<const float4*>(scale_row + t);
+        } else {
+          if (t < p.Tk) v.x = scale_row[t];
+          if (t + 1 < p.Tk) v.y = scale_row[t + 1];
+          if (t + 2 < p.Tk) v.z = scale_row[t + 2];
         }
-        if constexpr (KIND == 0) { v.x *= 0.0625f; v.y *= 0.0625f; }
+        if constexpr (KIND == 0) { v.x *= 0.0625f; v.y *= 0.0625f; v.z *= 0.0625f; v.w *= 0.0625f; }
       }
       return v;
     };
-    // TMEM address of the warp's columns in accumulator stage a
-    auto tcol = [&](int a) -> uint32_t {
-      return tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * TC_QT * TC_NTILE + qt * TC_NTILE + half * 64);
-    };
-    float2 k_cur = load_ks(0), k_next = load_ks(1);
-    uint32_t va[TW_CHW], vb[TW_CHW];
-    bool live = ntiles > 0;
-    if (live) {
-      if (!mbar_wait_bounded(&acc_full[0], 0u)) { *s_dead = 1; live = false; }
-    }
-    if (live) {
-      tc_fence_after();
-      TcLd<TW_CHW>::ld(tcol(0), va);
-    }
-#ifdef KVB_EXP_PROFILE
-    long long pf[5] = {0, 0, 0, 0, 0};
-    long long pc = clock64();
-#define PF_MARK(k) { const long long now = clock64(); pf[k] += now - pc; pc = now; }
-#else
-#define PF_MARK(k)
-#endif
-    for (int i = 0; live && i < ntiles; ++i) {
-      const int a = i & 1;
-      float* ksb = my_ks + a * 64;
-      *reinterpret_cast<float2*>(ksb + 2 * lane) = k_cur;
+    constexpr int NCH = TC_NTILE / TW_CHW;          // chunks per tile
+    constexpr int CPB = 64 / TW_CHW;                // chunks per 64-token block
+    const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(par * TC_QT * TC_NTILE + qt * TC_NTILE);
+    float4 k_cur = load_ks(par), k_next = load_ks(par + 2);
+    int buf = 0;
+    for (int i = par; i < ntiles; i += TC_ASTAGES, buf ^= 1) {
+      float* ksb = my_ks + buf * TC_NTILE;
+      *reinterpret_cast<float4*>(ksb + 4 * lane) = k_cur;
       k_cur = k_next;
-      k_next = load_ks(i + 2);
+      k_next = load_ks(i + 2 * TC_ASTAGES);
       __syncwarp();
-      PF_MARK(0)
-      TcLd<TW_CHW>::wait(va);
-      PF_MARK(1)
-      TcLd<TW_CHW>::ld(tcol(a) + TW_CHW, vb);
-      float m = tc_chunk_max<KIND, TW_CHW>(va, ksb, -INFINITY);
-      PF_MARK(2)
-      TcLd<TW_CHW>::wait(vb);
-      PF_MARK(1)
-      // the warp's 64 columns are in registers: its share of the stage may be refilled
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[a]);
-      if (i + 1 < ntiles) {                         // next tile's first half in flight while this one is finished
-        if (*s_dead || !mbar_wait_bounded(&acc_full[a ^ 1], (uint32_t)((i + 1) >> 1) & 1u)) {
-          *s_dead = 1;
-          live = false;
+      if (*s_dead) break;
+      if (!mbar_wait_bounded(&acc_full[par], (uint32_t)(i >> 1) & 1u)) { *s_dead = 1; break; }
+      tc_fence_after();
+      float m = -INFINITY, m0 = 0.0f;
+      uint32_t va[TW_CHW], vb[TW_CHW];
+      TcLd<TW_CHW>::ld(tbase, va);
+#pragma unroll
+      for (int ch = 0; ch < NCH; ++ch) {
+        uint32_t* cur = (ch & 1) ? vb : va;
+        uint32_t* nxt = (ch & 1) ? va : vb;
+        TcLd<TW_CHW>::wait(cur);
+        if (ch + 1 < NCH) {
+          TcLd<TW_CHW>::ld(tbase + (uint32_t)((ch + 1) * TW_CHW), nxt);
+        } else {                                    // the whole tile is in registers: the stage may be refilled
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[par]);
+        }
+        m = tc_chunk_max<KIND, TW_CHW>(cur, ksb + ch * TW_CHW, m);
+        if (ch == CPB - 1) { m0 = m; m = -INFINITY; }
+      }
+      // x -> fl(x * qscale) is monotone for qscale > 0: scale the block maxima only; then the group maximum
+      // over the G heads of the query, which are G neighbouring lanes
+      float r0 = __fmul_rn(m0, qs), r1 = __fmul_rn(m, qs);
+#pragma unroll
+      for (int off = 1; off < G; off <<= 1) {
+        r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, off));
+        r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, off));
+      }
+      if (writer) {
+        if (r0 == 0.0f) r0 = 0.0f;                  // -0 -> +0
+        if (r1 == 0.0f) r1 = 0.0f;
+        const int blk = 2 * i;
+        if (blk + 1 < p.nblk && (p.nblk & 1) == 0) {
+          *reinterpret_cast<float2*>(out_row + blk) = make_float2(r0, r1);
         } else {
-          tc_fence_after();
-          TcLd<TW_CHW>::ld(tcol(a ^ 1), va);
+          out_row[blk] = r0;
+          if (blk + 1 < p.nblk) out_row[blk + 1] = r1;
         }
       }
-      PF_MARK(3)
-      m = tc_chunk_max<KIND, TW_CHW>(vb, ksb + TW_CHW, m);
-      PF_MARK(2)
-      // x -> fl(x * qscale) is monotone for qscale > 0: scale the block maximum only; then the group
-      // maximum over the G heads of the query, which are G neighbouring lanes
-      float r0 = __fmul_rn(m, qs);
-#pragma unroll
-      for (int off = 1; off < G; off <<= 1) r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, off));
-      const int blk = 2 * i + half;
-      if (writer && blk < p.nblk) {
-        if (r0 == 0.0f) r0 = 0.0f;                  // -0 -> +0
-        out_row[blk] = r0;
-      }
-      PF_MARK(4)
     }
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#ifdef KVB_EXP_PROFILE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 5 || warp == 15))
-      printf("epi warp %d per tile: ks/sync %lld wait_ld %lld compute %lld arrive+acc_full %lld finalize %lld\n", warp,
-             pf[0] / ntiles, pf[1] / ntiles, pf[2] / ntiles, pf[3] / ntiles, pf[4] / ntiles);
-#endif
   } else if (warp == TW_EPI_WARPS) {
     // =============================== operand copies ===============================
     if (lane == 0) {
