@@ -59,6 +59,11 @@ __device__ __forceinline__ uint64_t qz_add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t qz_fma2(uint64_t a, uint64_t b, uint64_t c) {   // two fused multiply-adds
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 __device__ __forceinline__ uint64_t qz_sub2(uint64_t a, uint64_t b) {
   uint64_t r;
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
@@ -74,21 +79,41 @@ __device__ __forceinline__ float qz_div7(float a) {
   return fmaf(r, c, q);
 }
 
-// VPL = values (channels) per lane: 8 (C <= 32), 16 (C <= 64), 32 (C <= 128); a lane packs VPL / 2 bytes.
+// VPL = values (channels) per lane: 8 (C <= 32), 16 (C <= 64), 32 (C <= 128); a lane stores VPL / 2 bytes.
 // FULL: C == 4 * VPL, every lane value is a real channel.
 //
-// The kernel is bound by instruction issue, not by memory, unless the per-code work is a handful of
-// operations, so the codes are formed without a division: y = x * (1 / s) differs from the correctly rounded
-// quotient by less than 2e-6 (|x / s| <= 7; the roundings of the product and of the reciprocal), hence
-// rint(y) can differ from rint(x / s) only when y lies within that distance of a rounding boundary k + 0.5.
-// rint(y) + 8 comes from adding 1.5 * 2^23 + 8 and taking it off again (|x / s| <= 7 needs no clamp); the
-// offset codes 1..15 of four neighbours are summed as c0 + 16 c1 + 256 c2 + 4096 c3 in one exact fp32
-// accumulator, converted once, and flipping bit 3 of every nibble turns offset codes into two's complement.
-// A lane that meets a value within 1e-5 of a boundary (about one value in 10^5) redoes its codes with the
-// IEEE division. Products, sums and differences run two at a time (f32x2).
+// Which entries of the channel list a lane reads: entry e belongs to lane e % 4 of the token's team. The
+// list is ascending, so neighbouring entries are neighbouring channels (about two apart when half of the
+// channels are chosen): the four lanes of a team then read four neighbouring 32-bit words of the staged row,
+// and the eight teams of a warp, whose rows start four banks apart, cover all 32 banks — the gather runs
+// without bank conflicts for the typical list, where a blocked assignment (lane = e / VPL) put lanes 0 and 2,
+// and teams r and r + 4, on the same banks. The price is that the codes of one output byte now sit in two
+// lanes; they are brought together by a 4 x 4 exchange inside the team (below).
+//
+// The codes are formed without the division routine, exactly: with y = RN(1 / s) (the correctly rounded
+// reciprocal, computed once per token), q = RN(x y), the exact residual r = x - s q (one fused multiply-add)
+// and q' = RN(q + r y), q' is the correctly rounded quotient x / s (Markstein's theorem; it needs y
+// correctly rounded and no underflow, and tokens whose scale is outside [2^-100, 2^100] take the plain IEEE
+// division instead). rint(q') + 8 then comes from adding 1.5 * 2^23 + 8 and taking 1.5 * 2^23 off again —
+// the addition rounds half to even exactly like rint, and |x / s| <= 7 needs no clamp. Exact ties at k + 0.5
+// are COMMON for bf16 inputs (7 x / amax is a ratio of two 8-bit mantissas), which is why an approximate
+// quotient with a recheck near the boundaries was slow: most warps had a lane in the recheck. Products, sums
+// and fused multiply-adds run two at a time (f32x2). A test compares the codes of every (amax, x) pair of
+// bf16 values against IEEE division.
+//
+// The exchange: lane l' stores the entries [VPL l', VPL l' + VPL); of those, lane l holds e = 4 i + l for
+// VPL / 4 consecutive i, i.e. the nibbles 4 j + l (j = 0 .. VPL/4 - 1) of the destination's VPL / 8 words.
+// Lane l therefore builds, per destination, words that hold its offset codes (1..15) already at their final
+// bit positions 16 (j % 2) + 4 l of word j / 2 — two codes per word, placed by one exact fp32 multiply-add
+// with the lane's constants 2^(4 l) and 2^(16 + 4 l) and one conversion — and the destination ORs the four
+// contributions. Each lane orders its values by (destination XOR own lane), so that in exchange round r
+// every lane sends its r-th group with one xor-shuffle per word; flipping bit 3 of every nibble at the end
+// turns offset codes into two's complement.
 template <int VPL, bool FULL>
 __global__ void __launch_bounds__(QZ_THREADS) quantize_pack_kernel(QuantizeParams p) {
   extern __shared__ __align__(16) uint16_t qz_rows[];            // [QZ_STAGES][QZ_TOKENS_PER_PASS][D + QZ_PAD]
+  constexpr int GPL = VPL / 4;   // codes per (source lane, destination lane)
+  constexpr int NW = VPL / 8;    // packed words per lane
   const int tid = threadIdx.x;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
@@ -96,12 +121,17 @@ __global__ void __launch_bounds__(QZ_THREADS) quantize_pack_kernel(QuantizeParam
   const int l = tid & 3;         // lane inside the token's team
   const int nb = p.C >> 1;       // packed bytes per token
   const int byte0 = l * (VPL / 2);
-  // byte offsets, inside a staged row, of this lane's channels (VPL consecutive entries of the channel list)
+  // byte offsets, inside a staged row, of this lane's channels: value r * GPL + j is list entry
+  // 4 * ((l ^ r) * GPL + j) + l, destined to lane l ^ r
   uint32_t choff[VPL];
+  uint32_t live_mask = 0;        // (!FULL) values that are real channels
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int c = l * VPL + i;
-    choff[i] = (FULL || c < p.C) ? 2u * (uint32_t)p.channel_idx[(int64_t)h * p.C + c] : 0u;
+    const int r = i / GPL, j = i - r * GPL;
+    const int e = 4 * (((l ^ r) * GPL) + j) + l;
+    const bool real = FULL || e < p.C;
+    choff[i] = real ? 2u * (uint32_t)p.channel_idx[(int64_t)h * p.C + e] : 0u;
+    live_mask |= (real ? 1u : 0u) << i;
   }
   const __nv_bfloat16* key_row0 = p.key + (int64_t)b * p.key_sb + (int64_t)h * p.key_sh;
   uint8_t* packed_row0 = p.packed + (int64_t)b * p.packed_sb + (int64_t)h * p.packed_sh + (int64_t)p.t_dst * nb + byte0;
@@ -124,7 +154,8 @@ __global__ void __launch_bounds__(QZ_THREADS) quantize_pack_kernel(QuantizeParam
   };
   const uint64_t magic2 = qz_pack2(12582920.0f, 12582920.0f);      // 1.5 * 2^23 + 8
   const uint64_t base2 = qz_pack2(12582912.0f, 12582912.0f);       // 1.5 * 2^23
-  const uint64_t eight2 = qz_pack2(8.0f, 8.0f);
+  const float w_lo = (float)(1u << (4 * l));                         // the lane's nibble inside a 16-bit half
+  const float w_hi = w_lo * 65536.0f;
   // All teams of a warp run the same number of iterations (full-mask shuffles below). T < 2^31.
   int t0 = (int)blockIdx.x * QZ_TOKENS_PER_PASS;
   issue(t0, 0);
@@ -142,46 +173,51 @@ __global__ void __launch_bounds__(QZ_THREADS) quantize_pack_kernel(QuantizeParam
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       x[i] = qz_lds_bf16(row + choff[i]);
-      if (!FULL && l * VPL + i >= p.C) x[i] = 0.0f;
+      if (!FULL && !((live_mask >> i) & 1u)) x[i] = 0.0f;
       amax = fmaxf(amax, fabsf(x[i]));
     }
     if (!active) amax = 0.0f;                                       // stale bytes may hold NaN patterns: keep the shuffles clean
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const float sc = qz_div7(fmaxf(amax, 5.9604644775390625e-08f /* 2^-24 */));
-    float rcp;
-    asm("rcp.approx.f32 %0, %1;" : "=f"(rcp) : "f"(sc));
+    const bool plain = !(sc > 7.8886090522101181e-31f && sc < 1.2676506002282294e30f);   // 2^-100 .. 2^100 (NaN: plain)
+    const float rcp = __frcp_rn(sc);
     const uint64_t rcp2 = qz_pack2(rcp, rcp);
+    const uint64_t nsc2 = qz_pack2(-sc, -sc);
 
-    uint32_t words[VPL / 8];
-    float emax = 0.0f;
+    uint32_t grp[4][NW];                                            // grp[r]: this lane's contribution to lane l ^ r
+    if (!plain) {
 #pragma unroll
-    for (int w = 0; w < VPL / 8; ++w) {
-      float acc[2] = {0.0f, 0.0f};
-#pragma unroll
-      for (int j = 0; j < 8; j += 2) {
-        const uint64_t y2 = qz_mul2(qz_pack2(x[8 * w + j], x[8 * w + j + 1]), rcp2);
-        const uint64_t m2 = qz_add2(y2, magic2);                    // 1.5 * 2^23 + 8 + rint(y)
-        const uint64_t c2 = qz_sub2(m2, base2);                     // rint(y) + 8: the offset code, 1..15
-        const uint64_t e2 = qz_sub2(y2, qz_sub2(c2, eight2));       // y - rint(y)
-        float c0, c1, e0, e1;
+      for (int i = 0; i < VPL; i += 2) {
+        const uint64_t x2 = qz_pack2(x[i], x[i + 1]);
+        const uint64_t q2 = qz_mul2(x2, rcp2);
+        const uint64_t r2 = qz_fma2(nsc2, q2, x2);                  // x - s q, exact
+        const uint64_t y2 = qz_fma2(r2, rcp2, q2);                  // RN(x / s)
+        const uint64_t c2 = qz_sub2(qz_add2(y2, magic2), base2);    // rint(x / s) + 8: the offset code, 1..15
+        float c0, c1;
         qz_unpack2(c2, c0, c1);
-        qz_unpack2(e2, e0, e1);
-        emax = fmaxf(emax, fmaxf(fabsf(e0), fabsf(e1)));
-        const float sh = (j & 2) ? 256.0f : 1.0f;                   // nibble position inside the 16-bit half
-        acc[j >> 2] = fmaf(c0, sh, acc[j >> 2]);
-        acc[j >> 2] = fmaf(c1, 16.0f * sh, acc[j >> 2]);
+        // values i, i + 1 are codes j, j + 1 (j even) of group r: nibbles 4 j + l and 4 (j + 1) + l of the destination
+        grp[i / GPL][(i % GPL) >> 1] = __float2uint_rn(fmaf(c1, w_hi, c0 * w_lo));
       }
-      words[w] = (((uint32_t)__float2int_rn(acc[0])) | ((uint32_t)__float2int_rn(acc[1]) << 16)) ^ 0x88888888u;
+    } else {                                                        // scales near the ends of the fp32 range: IEEE division
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int w = 0; w < NW; ++w) grp[r][w] = 0;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const uint32_t u = (uint32_t)(quantize_code(x[i], sc) + 8);
+        grp[i / GPL][(i % GPL) >> 1] |= u << (4 * l + 16 * (i & 1));
+      }
     }
-    if (emax > 0.49999f) {                                          // rare: exact codes for this lane's values
+    uint32_t words[NW];
 #pragma unroll
-      for (int w = 0; w < VPL / 8; ++w) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) word |= (uint32_t)(quantize_code(x[8 * w + j], sc) & 0xF) << (4 * j);
-        words[w] = word;
-      }
+    for (int w = 0; w < NW; ++w) {
+      uint32_t v = grp[0][w];
+      v |= __shfl_xor_sync(0xffffffffu, grp[1][w], 1);
+      v |= __shfl_xor_sync(0xffffffffu, grp[2][w], 2);
+      v |= __shfl_xor_sync(0xffffffffu, grp[3][w], 3);
+      words[w] = v ^ 0x88888888u;
     }
     if (active) {
       uint8_t* dst = packed_row0 + (int64_t)t * nb;

@@ -71,3 +71,39 @@ def test_every_bf16_magnitude_as_the_row_maximum(cuda_device):
     _, packed_o, scale_o = oracle.quantize_pack(key, ch)
     assert torch.equal(scale.cpu(), scale_o)
     assert torch.equal(packed.cpu(), packed_o)
+
+
+def test_every_pair_of_bf16_magnitudes(cuda_device):
+    """The codes come from a reciprocal and two fused multiply-adds instead of the division routine; that is
+    exact by Markstein's theorem, and this test checks it on every pair (row maximum, value) of finite positive
+    bf16 magnitudes with value <= maximum (both signs of the value), against IEEE division, rint and clamp done
+    by torch in fp32 on the same device. (The oracle's numpy division is tied to the same arithmetic by the
+    other tests of this file.)"""
+    dev = cuda_device
+    mags = torch.arange(1, 0x7F80, dtype=torch.int32, device=dev).to(torch.int16).view(torch.bfloat16)   # 32639 values
+    n = mags.numel()
+    ch = torch.arange(64, dtype=torch.int32, device=dev).view(1, 64)
+    per_row = 62                                            # channel 0: the maximum, channel 1: its negative
+    rows_per_max = (n + per_row - 1) // per_row
+    pad = rows_per_max * per_row - n
+    xs = torch.cat([mags, mags[:1].expand(pad)]).view(rows_per_max, per_row)           # [rows_per_max, 62]
+    block = 256                                             # maxima per launch: 256 * 527 rows
+    for m0 in range(0, n, block):
+        mx = mags[m0:m0 + block]                            # [m]
+        m = mx.numel()
+        vals = torch.minimum(xs[None].expand(m, -1, -1), mx[:, None, None])            # value <= maximum
+        sign = torch.where((torch.arange(per_row, device=dev) & 1).bool(), -1.0, 1.0).to(torch.bfloat16)
+        key = torch.zeros((1, 1, m * rows_per_max, 128), dtype=torch.bfloat16, device=dev)
+        k3 = key.view(m, rows_per_max, 128)
+        k3[:, :, 0] = mx[:, None]
+        k3[:, :, 1] = -mx[:, None]
+        k3[:, :, 2:64] = vals * sign
+        packed, scale = ops.quantize(key, ch)
+        sel = key[..., :64].float()
+        amax = sel.abs().amax(-1).clamp_min(2.0 ** -24)
+        s_ref = amax / torch.full_like(amax, 7.0)          # a tensor divisor: true division, not a multiplication by 1/7
+        codes_ref = torch.round(sel / s_ref[..., None]).clamp(-7, 7).to(torch.int16)
+        u = codes_ref & 0xF
+        packed_ref = (u[..., 0::2] | (u[..., 1::2] << 4)).to(torch.uint8)
+        assert torch.equal(scale, s_ref), f"scales differ for maxima {m0}..{m0 + m}"
+        assert torch.equal(packed, packed_ref), f"codes differ for maxima {m0}..{m0 + m}"
