@@ -546,6 +546,82 @@ def measure_quantize(dev: torch.device) -> dict:
             "what": "kvb_quantize_pack over bf16 K [16,8,131072,128] -> int4 codes on 64 channels + fp32 scales"}
 
 
+def measure_model_decode(steps: int, dev: torch.device, batch: int = 8, context: int = 32768) -> dict:
+    """Config 1 as a whole model: the layer stack of Qwen3-0.6B (28 layers, 16 query / 8 KV heads of 128, hidden
+    1024, random weights, small vocabulary) decoding one token at a time with `batch` x `context` cached tokens
+    per layer. Two arms on the same GPU and the same weights: (a) the patched attention in mode
+    qabs32cand3p125attn (32 channels, top 1024 of 32768) over a PreallocatedCache, (b) dense attention over the
+    stock DynamicCache, which is what the reference's `baseline` mode runs (EVAL:6602-6604 fed by EVAL:7278).
+    The caches are filled with synthetic K/V directly (a 32768-token eager prefill does not fit memory and is
+    not what is measured); milliseconds per decoded token, CUDA events, host loop included."""
+    from transformers import DynamicCache, Qwen3Config, Qwen3ForCausalLM
+    from kv_cache_b200 import attention_patch as ap
+    from kv_cache_b200.cache import PreallocatedCache
+
+    torch.manual_seed(1)
+    L, Hkv, D = 28, 8, 128
+    cfg = Qwen3Config(vocab_size=1024, hidden_size=1024, intermediate_size=3072, num_hidden_layers=L,
+                      num_attention_heads=16, num_key_value_heads=Hkv, head_dim=D, max_position_embeddings=40960,
+                      rope_theta=1e6, rms_norm_eps=1e-6, attn_implementation="eager")
+    model = Qwen3ForCausalLM(cfg).to(dev, torch.bfloat16).eval()
+    g = torch.Generator(device=dev).manual_seed(1)
+    capacity = context + steps + 8
+
+    def filled_preallocated():
+        cache = PreallocatedCache(num_layers=L, capacity=capacity)
+        for layer in cache.layers:
+            k0 = torch.empty((batch, Hkv, 1, D), dtype=torch.bfloat16, device=dev)
+            layer.lazy_initialization(k0, k0)
+            layer.key_buffer[:, :, :context].normal_(generator=g)
+            layer.value_buffer[:, :, :context].normal_(generator=g)
+            layer.length = context
+            layer.keys, layer.values = layer.key_buffer[:, :, :context], layer.value_buffer[:, :, :context]
+        return cache
+
+    def filled_dynamic():
+        cache = DynamicCache(config=cfg)
+        for l in range(L):
+            k = torch.empty((batch, Hkv, context, D), dtype=torch.bfloat16, device=dev).normal_(generator=g)
+            v = torch.empty((batch, Hkv, context, D), dtype=torch.bfloat16, device=dev).normal_(generator=g)
+            cache.update(k, v, l)
+        return cache
+
+    toks = [torch.randint(0, 1024, (batch, 1), device=dev) for _ in range(steps + 3)]
+    pos0 = context
+
+    def run(cache, mode_args, state):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.inference_mode():
+            for i, tok in enumerate(toks):
+                if i == 3:
+                    e0.record()
+                position = torch.full((batch, 1), pos0 + i, device=dev, dtype=torch.long)
+                with ap.attention_mode(*mode_args, sparse_state=state):
+                    model(input_ids=tok, past_key_values=cache, use_cache=True, position_ids=position)
+            e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    ap.install_qwen3_attention_patch()
+    try:
+        state = ap.SparseDecodeState(capacity_hint=capacity)
+        cache = filled_preallocated()
+        sparse_ms = run(cache, ("qabs32cand3p125attn", 0.02, 3, True, 0, 0, None), state)
+        reallocs = cache.reallocations
+        del cache, state
+        torch.cuda.empty_cache()
+        dense_ms = run(filled_dynamic(), ("baseline",), ap.SparseDecodeState())
+    finally:
+        ap.uninstall_qwen3_attention_patch()
+    torch.cuda.empty_cache()
+    return {"workload": f"c1_model_qwen3-0.6b-shaped_28L_b{batch}_t{context}", "decoded_tokens": steps,
+            "sparse_ms_per_token": sparse_ms, "dense_dynamic_cache_ms_per_token": dense_ms,
+            "tokens_per_s_sparse": batch * 1e3 / sparse_ms, "tokens_per_s_dense": batch * 1e3 / dense_ms,
+            "cache_reallocations": reallocs,
+            "what": "whole-model decode, host loop and all 28 layers' MLPs included; the int4 side caches of the "
+                    "28 layers are built during the first (untimed) token"}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -563,6 +639,14 @@ def main() -> None:
     from kv_cache_b200 import inputs
 
     name = args.workload or ("c2" if args.gpus == 1 else "c4")
+    if name == "c1_model":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "whole-model decode is a secondary measurement; the reference arm times the layer step"}))
+            return
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        print(json.dumps(measure_model_decode(max(4, min(args.steps, 32)), dev, batch=args.batch or 8)), flush=True)
+        return
     if name == "c3":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference has no chunked-prefill scorer (query_count must be 1, EVAL:4413)"}))
