@@ -518,21 +518,21 @@ def run_prefill_gpu(args) -> None:
         "data": "synthetic",
         "config": {"workload": r["workload"], "batch": B, "q_heads": 32, "kv_heads": 8, "queries": args.queries,
                    "keys": 131072, "partial_channels": 64, "block": 64, "top_blocks": 32, "engine": r["engine"]},
-        "clocks": r["clocks"], "gpu_launches": 3 * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "score_prefill_tc_kernel (tcgen05)",
+        "clocks": r["clocks"], "gpu_launches": 4 * args.steps,      # query quantisation, key widening, scorer, block top-k
+        "roofline": {"bound": "tensor", "kernel": "score_prefill_tw_kernel (tcgen05, pre-widened operands)",
                      "achieved": max(r["kernel_tops"].values()), "peak": 4500.0, "unit": "TOPS",
                      "frac": r["frac_of_nominal_int8_peak"],
                      "peak_source": "nominal dense int8 (no measured int8 peak on this pool)", "kernel_ms": r["kernel_ms"],
-                     "note": "K = 64: every accumulator element is drained from tensor memory after only 64 MACs; the kernel is bound by that drain and the per-element scale+max, not by the MMAs"},
+                     "note": "K = 64: every accumulator element is drained from tensor memory after only 64 MACs; the kernel is bound by the per-element scale+max of the epilogue warps, not by the MMAs"},
     }
     print(json.dumps(line), flush=True)
 
 
-def measure_quantize(dev: torch.device) -> dict:
-    """Bulk quantize/pack of 4 GiB of bf16 K (config 2's cache of one layer), CUDA events."""
+def measure_quantize(dev: torch.device, batch: int = 16) -> dict:
+    """Bulk quantize/pack of 4 GiB of bf16 K (config 2's cache of one layer; `batch` scales it), CUDA events."""
     from kv_cache_b200 import ops
 
-    B, Hkv, T, D, C = 16, 8, 131072, 128, 64
+    B, Hkv, T, D, C = batch, 8, 131072, 128, 64
     key = torch.empty((B, Hkv, T, D), dtype=torch.bfloat16, device=dev).normal_()
     ch = torch.arange(0, 2 * C, 2, dtype=torch.int32, device=dev).repeat(Hkv, 1)
     packed, scale = ops.alloc_side_cache(B, Hkv, T, C, dev)
@@ -543,7 +543,7 @@ def measure_quantize(dev: torch.device) -> dict:
     nbytes = B * Hkv * T * (2 * D + C // 2 + 4)
     peak, _ = hbm_peak()
     return {"ms": ms, "bytes": nbytes, "gb_per_s": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak,
-            "what": "kvb_quantize_pack over bf16 K [16,8,131072,128] -> int4 codes on 64 channels + fp32 scales"}
+            "what": f"kvb_quantize_pack over bf16 K [{B},8,131072,128] -> int4 codes on 64 channels + fp32 scales"}
 
 
 def measure_model_decode(steps: int, dev: torch.device, batch: int = 8, context: int = 32768) -> dict:
@@ -639,6 +639,14 @@ def main() -> None:
     from kv_cache_b200 import inputs
 
     name = args.workload or ("c2" if args.gpus == 1 else "c4")
+    if name == "quantize":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no int4 quantizer (north-star stage 1)"}))
+            return
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        print(json.dumps(measure_quantize(dev, batch=args.batch or 16)), flush=True)
+        return
     if name == "c1_model":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "whole-model decode is a secondary measurement; the reference arm times the layer step"}))
