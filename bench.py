@@ -623,6 +623,9 @@ def measure_model_decode(steps: int, dev: torch.device, batch: int = 8, context:
 
 
 def main() -> None:
+    # the version banner NCCL prints at NCCL_DEBUG=VERSION goes to stdout, where only the JSON line belongs
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -18,18 +18,6 @@ namespace kvb {
 // count misses them (heavy ties, adversarial layouts) is re-scored into the group-max workspace by
 // the select kernel itself and selected by the exact refinement path, so the result is always the
 // exact top-k.
-constexpr int FS_THREADS = 512;
-constexpr int FS_RUNS = 32;                    // evenly spaced runs of sampled tokens per row
-constexpr int FS_PER_THREAD = 8;                // sampled tokens per thread for rows up to FS_LONG_ROW (4096 per row) ...
-constexpr int FS_PER_THREAD_LONG = 16;          // ... beyond it (8192 per row) ...
-constexpr int FS_PER_THREAD_MAX = 32;           // ... and beyond twice that (16384 per row); loaded four at a time
-constexpr int FS_LONG_ROW = 262144;
-// (the sample stays at least 1/64 of the row up to a million tokens, so the rank that sets the threshold stays
-// near 1.75 k / 64 and its relative spread near 10 %)
-__host__ __device__ inline int fs_per_thread(int T) {
-  return T > 2 * FS_LONG_ROW ? FS_PER_THREAD_MAX : (T > FS_LONG_ROW ? FS_PER_THREAD_LONG : FS_PER_THREAD);
-}
-
 struct SampleParams {
   ScoreParams sp;             // query / packed / scale / channels / shapes (outputs unused)
   float* tau;                 // [R]
@@ -45,6 +33,173 @@ struct SampleParams {
   __nv_bfloat16* value; int64_t v_sb, v_sh, v_st;
   uint32_t* step_counter = nullptr;   // optional: CTA 0 adds one (the step number of the sequence-sharded exchange)
 };
+
+// The rank-th largest of the sample values a CTA holds in registers (v[e], e < per, of every thread; NaN =
+// absent), as an order-preserving key — without a histogram: scores cluster in a few dozen exponent bins, and
+// the 8192 or 16384 shared-memory atomics of a long row's sample on those few words took 20 us.
+//   1. a lower bound L of the answer from the threads' largest keys: every warp sorts its 32 maxima and offers
+//      its ceil(rank / warps)-th largest; L is the smallest offer (at least rank sample values are >= L);
+//   2. the values >= L (about rank of them for well-spread scores) are compacted into a list with one
+//      ballot per step;
+//   3. the rank-th largest of the list, by counting: the entry that exactly rank - 1 others beat (ties by
+//      position) is the answer.
+// Returns false (and no key) when rank > NT or the list outgrows its room (heavy ties): the caller then takes
+// the histogram route. `s_work` needs NT + LIST + 4 words. Ends with a barrier.
+template <int NT, int VMAX, int LIST>
+__device__ __forceinline__ bool block_rank_select(const float (&v)[VMAX], int per, int rank, uint32_t* s_work,
+                                                  uint32_t& key_out) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  uint32_t* s_keys = s_work;
+  uint32_t* s_list = s_work + NT;
+  uint32_t* s_misc = s_list + LIST;             // [0] L, [1] list length, [2] answer, [3] found flag
+  if (rank > NT) return false;                  // (uniform)
+  uint32_t key[VMAX];
+  uint32_t kmax = 0;
+#pragma unroll
+  for (int e = 0; e < VMAX; ++e) {
+    key[e] = (e < per && v[e] == v[e]) ? float_to_key(v[e]) : 0u;
+    kmax = key[e] > kmax ? key[e] : kmax;
+  }
+  // every warp sorts its 32 maxima (bitonic network of shuffles, descending) and offers its r-th largest,
+  // r = ceil(rank / warps): the smallest offer L has at least warps * r >= rank sample values at or above it
+  {
+    uint32_t x = kmax;
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        const uint32_t y = __shfl_xor_sync(0xffffffffu, x, j);
+        const bool keep_max = ((lane & j) == 0) == ((lane & k) == 0);
+        x = keep_max ? (x > y ? x : y) : (x < y ? x : y);
+      }
+    }
+    constexpr int NW = NT / 32;
+    const int r = (rank + NW - 1) / NW;          // <= 32 because rank <= NT
+    const uint32_t offer = __shfl_sync(0xffffffffu, x, r - 1);
+    if (lane == 0) s_keys[tid >> 5] = offer;
+    if (tid == 0) { s_misc[1] = 0; s_misc[3] = 0; }
+    __syncthreads();
+    uint32_t lo = 0xFFFFFFFFu;
+#pragma unroll
+    for (int j = 0; j < NW; ++j) { const uint32_t o = s_keys[j]; lo = o < lo ? o : lo; }
+    if (tid == 0) s_misc[0] = lo;
+  }
+  __syncthreads();
+  const uint32_t L = s_misc[0];
+  if (L == 0) return false;                     // fewer than rank threads hold a value (uniform)
+#pragma unroll
+  for (int e = 0; e < VMAX; ++e) {
+    if (e >= per) break;
+    const bool take = key[e] >= L;
+    const uint32_t mask = __ballot_sync(0xffffffffu, take);
+    if (mask) {
+      uint32_t base = 0;
+      if (lane == 0) base = atomicAdd(&s_misc[1], (uint32_t)__popc(mask));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      const uint32_t pos = base + (uint32_t)__popc(mask & ((1u << lane) - 1u));
+      if (take && pos < (uint32_t)LIST) s_list[pos] = key[e];
+    }
+  }
+  __syncthreads();
+  const uint32_t n = s_misc[1];
+  if (n > (uint32_t)LIST) { __syncthreads(); return false; }
+  for (uint32_t i = tid; i < n; i += NT) {
+    const uint32_t ki = s_list[i];
+    int beat = 0;
+    for (uint32_t j = 0; j < n; ++j) {
+      const uint32_t kj = s_list[j];
+      beat += (kj > ki || (kj == ki && j < i)) ? 1 : 0;
+    }
+    if (beat == rank - 1) { s_misc[2] = ki; s_misc[3] = 1; }
+  }
+  __syncthreads();
+  const bool found = s_misc[3] != 0;
+  key_out = s_misc[2];
+  __syncthreads();
+  return found;
+}
+
+constexpr int FS_LIST = 2048;                   // room of block_rank_select's list
+
+// tau of a row from the key of the rank-th largest sample value
+__device__ __forceinline__ float fs_tau_from_key(uint32_t key) {
+  float t = key_to_float(key);
+  if (key <= 0x007FFFFFu || t != t) t = -INFINITY;            // NaN patterns: take everything
+  return t;
+}
+
+// The threshold of every row from sample values that the streaming scorer left at the start of the row's
+// workspace (score_sample_stream_run). Also does score_sample_kernel's side jobs (per-row counters, the
+// decoded token's K/V rows, the step number).
+__global__ void __launch_bounds__(FS_THREADS) sample_threshold_kernel(SampleParams q, const float* sample, int tile_tokens) {
+  __shared__ uint32_t s_hist[SEL_HIST_BINS];    // also the work area of block_rank_select (FS_THREADS + FS_LIST + 4 words)
+  __shared__ uint32_t s_tmp[80];
+  static_assert(FS_THREADS + FS_LIST + 4 <= SEL_HIST_BINS, "work area");
+  const ScoreParams& p = q.sp;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();                      // the scorer may become resident and prepare its query codes
+  pdl_wait();
+  if (q.step_counter && row == 0 && tid == 33) *q.step_counter += 1;
+  if (q.zero_count && tid == 0) q.zero_count[(int64_t)row * SC_COUNT_STRIDE] = 0;
+  if (q.zero_failed && tid == 32) q.zero_failed[row] = 0;
+  const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
+  if (q.new_k && tid >= 64 && tid < 96) {          // one warp: 16 lanes per row, 16 bytes per lane
+    const int l = tid - 64, rb = row / p.Hkv, rh = row - rb * p.Hkv;
+    if (l < 16) *reinterpret_cast<uint4*>(q.key + (int64_t)rb * q.k_sb + (int64_t)rh * q.k_sh + (int64_t)T * q.k_st + l * 8) = q.new_k[row * 16 + l];
+    else *reinterpret_cast<uint4*>(q.value + (int64_t)rb * q.v_sb + (int64_t)rh * q.v_sh + (int64_t)T * q.v_st + (l - 16) * 8) = q.new_v[row * 16 + l - 16];
+  }
+  if (T <= q.cap) {                             // short rows: every token is a candidate
+    if (tid == 0) q.tau[row] = -INFINITY;
+    return;
+  }
+  int grp, stride, n_sample;
+  fs_sample_geometry(T, tile_tokens, grp, stride, n_sample);
+  const float frac = (float)n_sample / (float)T;
+  const int kk = q.top_k < T ? q.top_k : T;
+  float expect = 1.75f * (float)kk;
+  if (expect * frac < 96.0f) expect = 96.0f / frac;
+  int rank = (int)(expect * frac + 0.999f);
+  if (rank < 1) rank = 1;
+  if (rank > n_sample) rank = n_sample;
+  // thread t holds the values t, t + NT, ... of the row's sample (scalar loads: the row pitch T need not be a
+  // multiple of four floats)
+  constexpr int VMAX = FS_PER_THREAD_MAX;       // n_sample <= FS_THREADS * VMAX
+  const int per = n_sample / FS_THREADS;        // 8, 16 or 32
+  const float* mine = sample + (int64_t)row * p.T;
+  float v[VMAX];
+#pragma unroll
+  for (int e = 0; e < VMAX; ++e) v[e] = e < per ? __ldcg(mine + tid + e * FS_THREADS) : __int_as_float(0x7fc00000);
+  uint32_t key;
+  if (block_rank_select<FS_THREADS, VMAX, FS_LIST>(v, per, rank, s_hist, key)) {
+    if (tid == 0) q.tau[row] = fs_tau_from_key(key);
+    return;
+  }
+  // heavy ties: two-level histogram of the keys
+  for (int i = tid; i < SEL_HIST_BINS; i += FS_THREADS) s_hist[i] = 0;
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < VMAX; ++e) {
+    if (e >= per) break;
+    if (v[e] == v[e]) atomicAdd(&s_hist[float_to_key(v[e]) >> (32 - SEL_HIST_BITS)], 1u);
+  }
+  __syncthreads();
+  uint32_t bin, above, inb;
+  find_threshold<FS_THREADS>(s_hist, SEL_HIST_BINS, (uint32_t)rank, s_tmp, bin, above, inb);
+  for (int i = tid; i < 2048; i += FS_THREADS) s_hist[i] = 0;
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < VMAX; ++e) {
+    if (e >= per) break;
+    if (v[e] == v[e]) {
+      const uint32_t k2 = float_to_key(v[e]);
+      if ((k2 >> (32 - SEL_HIST_BITS)) == bin) atomicAdd(&s_hist[(k2 >> 9) & 2047u], 1u);
+    }
+  }
+  __syncthreads();
+  uint32_t d, ab2, in2;
+  find_threshold<FS_THREADS>(s_hist, 2048, (uint32_t)rank - above, s_tmp, d, ab2, in2);
+  if (tid == 0) q.tau[row] = fs_tau_from_key((bin << (32 - SEL_HIST_BITS)) | (d << 9));
+}
 
 template <int C, int G>
 __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q) {
@@ -233,9 +388,13 @@ static void fill_score_params(ScoreParams& sp, const void* query, int64_t q_sb, 
   sp.units_per_row = 0; sp.full_tiles = 0; sp.total_units = 0;
 }
 
+// `sample_ws`: optional fp32 workspace [R, sp.T] (the group-max workspace of the caller). With it, long rows have
+// their sample scored by the streaming int8-MMA scorer and a small kernel derives the thresholds; otherwise one
+// kernel does both with dp4a.
 static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cudaStream_t st,
                       uint32_t* zero_count = nullptr, uint32_t* zero_failed = nullptr,
-                      const kvb_decode_step_params* rows = nullptr, uint32_t* step_counter = nullptr) {
+                      const kvb_decode_step_params* rows = nullptr, uint32_t* step_counter = nullptr,
+                      float* sample_ws = nullptr, int device = -1) {
   SampleParams sq;
   sq.sp = sp; sq.tau = tau; sq.top_k = top_k; sq.cap = cap;
   sq.zero_count = zero_count; sq.zero_failed = zero_failed;
@@ -251,6 +410,20 @@ static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cud
     sq.v_sb = rows->v_sb; sq.v_sh = rows->v_sh; sq.v_st = rows->v_st;
   }
   const int R = sp.B * sp.Hkv;
+  const int tile_tokens = score_stream_tile_tokens(sp.C, sp.G);
+  if (sample_ws && device >= 0 && tile_tokens > 0 && sp.T > FS_LONG_ROW) {
+    // (the single dp4a kernel is instruction-bound on the 8192- and 16384-token samples of long rows)
+    int grp, stride, n_sample;
+    fs_sample_geometry(sp.T, tile_tokens, grp, stride, n_sample);
+    if (n_sample <= FS_THREADS * FS_PER_THREAD_MAX && n_sample <= sp.T && (n_sample % FS_THREADS) == 0) {
+      const int rc = score_sample_stream_run(sp, sample_ws, cap, device, st);
+      if (rc != KVB_OK) return rc;
+      ChainLaunchScope early;                   // the threshold kernel starts early and waits inside
+      early.on();
+      KVB_CHECK_CUDA(launch_kernel(sample_threshold_kernel, dim3(R), dim3(FS_THREADS), 0, st, sq, (const float*)sample_ws, tile_tokens));
+      return KVB_OK;
+    }
+  }
   if (sp.C == 32) return sample_launch_g<32>(sq, R, st);
   if (sp.C == 64) return sample_launch_g<64>(sq, R, st);
   return sample_launch_g<128>(sq, R, st);
@@ -369,7 +542,8 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       ScoreParams base;
       fill_score_params(base, p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
                         p->scale_sh, p->channel_idx, p->B, p->Hq, p->Hkv, T, p->D, p->C, T_dev);
-      rc = sample_run(base, ftau, p->top_k, fcap, st, fcount, reinterpret_cast<uint32_t*>(ws + L.off_ffailed), p);
+      rc = sample_run(base, ftau, p->top_k, fcap, st, fcount, reinterpret_cast<uint32_t*>(ws + L.off_ffailed), p, nullptr,
+                      gmax, device);
       if (rc != KVB_OK) return rc;
       chain.on();                             // every later kernel of the step starts early and waits inside
 

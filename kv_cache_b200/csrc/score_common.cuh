@@ -13,7 +13,35 @@ constexpr int SC_MAX_G = 16;
 constexpr int SC_COUNT_STRIDE = 32;              // words between per-row counters (one 128-byte line each)
 constexpr int SC_EMIT_WARP_BUF = 512;            // composites a warp buffers per row segment before one global reservation
 constexpr int SC_EMIT_BUF = 8 * SC_EMIT_WARP_BUF; // per CTA (8 warps)
-enum { SC_MODE_PLAIN = 0, SC_MODE_HIST = 1, SC_MODE_EMIT = 2 };
+// SAMPLE: the plain mode over the sample tiles of every row only (see fs_sample_geometry); the group maxima go,
+// compacted, to the start of the row's gmax workspace.
+enum { SC_MODE_PLAIN = 0, SC_MODE_HIST = 1, SC_MODE_EMIT = 2, SC_MODE_SAMPLE = 3 };
+
+// ---- the sample that sets a row's candidate threshold ----------------------------------------
+constexpr int FS_THREADS = 512;
+constexpr int FS_RUNS = 32;                    // evenly spaced runs of sampled tokens per row
+constexpr int FS_PER_THREAD = 8;                // sampled tokens per thread for rows up to FS_LONG_ROW (4096 per row) ...
+constexpr int FS_PER_THREAD_LONG = 16;          // ... beyond it (8192 per row) ...
+constexpr int FS_PER_THREAD_MAX = 32;           // ... and beyond twice that (16384 per row); loaded four at a time
+constexpr int FS_LONG_ROW = 262144;
+// (the sample stays at least 1/64 of the row up to a million tokens, so the rank that sets the threshold stays
+// near 1.75 k / 64 and its relative spread near 10 %)
+__host__ __device__ inline int fs_per_thread(int T) {
+  return T > 2 * FS_LONG_ROW ? FS_PER_THREAD_MAX : (T > FS_LONG_ROW ? FS_PER_THREAD_LONG : FS_PER_THREAD);
+}
+
+// The sample as tiles of the streaming scorer (tile = TW tokens): FS_RUNS runs of `grp` consecutive tiles whose
+// starts are `stride` tiles apart; n_sample = FS_RUNS * grp * TW tokens (<= T whenever T >= FS_RUNS * run tokens,
+// which the fast path requires).
+__host__ __device__ inline void fs_sample_geometry(int T, int TW, int& grp, int& stride, int& n_sample) {
+  int run_tokens = fs_per_thread(T) * (FS_THREADS / FS_RUNS);     // 128, 256 or 512
+  if (run_tokens < TW) run_tokens = TW;
+  grp = run_tokens / TW;
+  stride = (T / FS_RUNS) / TW;
+  if (stride < grp) stride = grp;
+  n_sample = FS_RUNS * grp * TW;
+}
+
 
 struct ScoreParams {
   const __nv_bfloat16* query;

@@ -69,6 +69,7 @@ template <int C, int G, int NS, int MODE>
 __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_stream_kernel(ScoreParams p) {
   constexpr bool HIST = MODE == SC_MODE_HIST;
   constexpr bool EMIT = MODE == SC_MODE_EMIT;
+  constexpr bool SAMPLE = MODE == SC_MODE_SAMPLE;
   using Cfg = ScoreCfg<C, G>;
   constexpr int KS = Cfg::KS, TPA = Cfg::TPA, TW = Cfg::TW, IT = Cfg::IT;
   constexpr int WARPS = Cfg::WARPS, THREADS = Cfg::THREADS;
@@ -107,8 +108,15 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
   const uint64_t keep = l2_policy_evict_last();
   // work geometry from the history length (read from the device when it lives there)
   const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
-  const int full_tiles = T / TW;
-  const int units_per_row = full_tiles + ((T % TW) ? 1 : 0);
+  int full_tiles = T / TW;
+  int units_per_row = full_tiles + ((T % TW) ? 1 : 0);
+  // SAMPLE: logical tile lt of a row is physical tile (lt / grp) * grp_stride + lt % grp; outputs are compact
+  int grp = 1, grp_stride = 1;
+  if constexpr (SAMPLE) {
+    int n_sample;
+    fs_sample_geometry(T, TW, grp, grp_stride, n_sample);
+    full_tiles = units_per_row = (T > p.cand_cap) ? FS_RUNS * grp : 0;      // short rows need no threshold
+  }
   const int64_t total_units = (int64_t)p.B * p.Hkv * units_per_row;
   const int64_t u_begin = (int64_t)blockIdx.x * total_units / gridDim.x;
   const int64_t u_end = (int64_t)(blockIdx.x + 1) * total_units / gridDim.x;
@@ -142,7 +150,8 @@ __global__ void __launch_bounds__(ScoreCfg<C, G>::THREADS, 2) score_decode_strea
 
     auto issue = [&](int j, uint32_t slot) {
       // lane 0 only: tile j of this warp into ring slot `slot`
-      const int64_t t0 = (int64_t)(ta + warp + j * WARPS) * TW;
+      const int lt = ta + warp + j * WARPS;
+      const int64_t t0 = (int64_t)(SAMPLE ? (lt / grp) * grp_stride + lt % grp : lt) * TW;
       uint8_t* dst = my_stage + (slot % NS) * STAGE_BYTES;
       mbar_arrive_expect_tx(&my_bar[slot % NS], STAGE_BYTES);
       bulk_g2s_evict_first(dst, packed_row + t0 * TOKEN_BYTES, PACKED_BYTES, &my_bar[slot % NS], policy);
@@ -417,6 +426,11 @@ static int score_stream_launch(const ScoreParams& p0, int device, cudaStream_t s
   ScoreParams p = p0;
   p.full_tiles = p.T / Cfg::TW;
   p.units_per_row = p.full_tiles + ((p.T % Cfg::TW) ? 1 : 0);
+  if (MODE == SC_MODE_SAMPLE) {
+    int grp, stride, n_sample;
+    fs_sample_geometry(p.T, Cfg::TW, grp, stride, n_sample);
+    p.full_tiles = p.units_per_row = FS_RUNS * grp;
+  }
   p.total_units = (int64_t)p.B * p.Hkv * p.units_per_row;
   const size_t smem = score_stream_smem_bytes<C, G, NS, MODE>();
   auto kern = score_decode_stream_kernel<C, G, NS, MODE>;
@@ -451,6 +465,31 @@ static int score_stream_dispatch_g(const ScoreParams& p, int device, cudaStream_
     case 8: return score_stream_launch<C, 8, score_stages<C, 8>(), MODE>(p, device, st);
     default: return -1;
   }
+}
+
+// Tokens per tile of the streaming kernel for (C, G) (the unit of the sample geometry); 0 if unsupported.
+static int score_stream_tile_tokens(int C, int G) {
+  if (C != 32 && C != 64 && C != 128) return 0;
+  switch (G) {
+    case 1: return C == 32 ? ScoreCfg<32, 1>::TW : (C == 64 ? ScoreCfg<64, 1>::TW : ScoreCfg<128, 1>::TW);
+    case 2: return C == 32 ? ScoreCfg<32, 2>::TW : (C == 64 ? ScoreCfg<64, 2>::TW : ScoreCfg<128, 2>::TW);
+    case 4: return C == 32 ? ScoreCfg<32, 4>::TW : (C == 64 ? ScoreCfg<64, 4>::TW : ScoreCfg<128, 4>::TW);
+    case 8: return C == 32 ? ScoreCfg<32, 8>::TW : (C == 64 ? ScoreCfg<64, 8>::TW : ScoreCfg<128, 8>::TW);
+    default: return 0;
+  }
+}
+
+// The sample of every row scored by the streaming kernel: group maxima of the sample tiles, compacted, at
+// the start of row r of `sample` (row pitch base.T floats). Rows of at most `cap` tokens are skipped.
+static int score_sample_stream_run(const ScoreParams& base, float* sample, int cap, int device, cudaStream_t st) {
+  ScoreParams p = base;
+  p.gmax_out = sample; p.acc_out = nullptr; p.deq_out = nullptr; p.hist_out = nullptr;
+  p.tau = nullptr; p.cand = nullptr; p.cand_count = nullptr; p.cand_cap = cap;
+  int rc = -1;
+  if (p.C == 32) rc = score_stream_dispatch_g<32, SC_MODE_SAMPLE>(p, device, st);
+  else if (p.C == 64) rc = score_stream_dispatch_g<64, SC_MODE_SAMPLE>(p, device, st);
+  else if (p.C == 128) rc = score_stream_dispatch_g<128, SC_MODE_SAMPLE>(p, device, st);
+  return rc < 0 ? KVB_BAD_SHAPE : rc;
 }
 
 struct ScoreEmit {

@@ -96,7 +96,7 @@ static int shard_candidates_run(const void* query, int64_t q_sb, int64_t q_sh, c
   fill_score_params(base, query, q_sb, q_sh, packed, packed_sb, packed_sh, scale, scale_sb, scale_sh, channel_idx, B,
                     Hq, Hkv, T, D, C, nullptr);
   int rc = sample_run(base, tau, top_k, L.cap, st, count, reinterpret_cast<uint32_t*>(ws + L.off_failed), nullptr,
-                      step_counter);
+                      step_counter, gmax, device);
   if (rc != KVB_OK) return rc;
   if (chain) chain->on();                       // the kernels after the first start early and wait inside
   ScoreEmit emit{tau, cand, count, L.cap};

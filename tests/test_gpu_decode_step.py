@@ -71,7 +71,7 @@ def test_device_status_is_clean(cuda_device):
     assert st.value == 0
 
 
-@pytest.mark.parametrize("T,k", [(30000, 512), (12000, 4000)])
+@pytest.mark.parametrize("T,k", [(30000, 512), (12000, 4000), (300000, 1024)])      # the last: the long-row sampler
 def test_heavy_ties_take_the_rescue_path(cuda_device, T, k):
     """Keys quantised from a handful of distinct rows: scores tie massively, the sampled threshold
     admits far more candidates than fit, and the exact refinement over the re-scored row must take over."""
@@ -88,8 +88,9 @@ def test_heavy_ties_take_the_rescue_path(cuda_device, T, k):
     torch.testing.assert_close(out.float().cpu(), r["out"], rtol=RTOL, atol=ATOL)
 
 
-def test_all_zero_keys(cuda_device):
-    T, k = 10000, 256
+@pytest.mark.parametrize("T", [10000, 270000])          # the second: the long-row sampler, every sample value equal
+def test_all_zero_keys(cuda_device, T):
+    k = 256
     w, q, key, value = make_case(cuda_device, batch=1, q_heads=4, kv_heads=2, context=T, channels=32)
     key = torch.zeros_like(key)
     ch = torch.arange(32, dtype=torch.int32, device=cuda_device).repeat(2, 1)
