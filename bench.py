@@ -623,9 +623,9 @@ def measure_model_decode(steps: int, dev: torch.device, batch: int = 8, context:
 
 
 def main() -> None:
-    # the version banner NCCL prints at NCCL_DEBUG=VERSION goes to stdout, where only the JSON line belongs
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # NCCL writes its debug output (at NCCL_DEBUG=VERSION and above: a version banner) to stdout, where only the
+    # JSON line belongs
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
