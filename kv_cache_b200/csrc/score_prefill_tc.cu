@@ -43,6 +43,7 @@ constexpr int TC_ASTAGES = 2;                      // accumulator stages in tens
 constexpr int TC_TMEM_COLS = TC_ASTAGES * TC_QT * TC_NTILE;   // 512: all of it
 constexpr int TC_CHW = 16;                         // accumulator columns per tensor-memory load
 constexpr bool TC_DOUBLE_BUFFER = TC_CHW <= 32;    // two loads alternate in registers when they fit
+constexpr bool TC_PACKED_MUL = true;               // fp32 accumulators: scale two columns per instruction (mul.rn.f32x2)
 constexpr int TC_LBO = 128;                        // bytes between core matrices along K
 
 struct PrefillTcParams {
@@ -259,8 +260,8 @@ __device__ __forceinline__ void tc_widen_token(const uint32_t* words, uint8_t* d
 }
 
 // Maximum of N accumulator columns against their key scales, continued from m: one rounded fp32 multiply per
-// column (the scales come from shared memory four at a time, the same address for every lane) and one
-// 3-input maximum per two columns, on two independent chains. The accumulator registers of the
+// column (two per instruction for fp32 accumulators; the scales come from shared memory four at a time, the
+// same address for every lane) and one 3-input maximum per two columns, on two independent chains. The accumulator registers of the
 // tensor-memory load are used as they are; int32 accumulators are converted exactly (|acc| < 2^22) through
 // the bits of 1.5 * 2^23 + acc.
 template <int KIND, int N>
@@ -279,8 +280,23 @@ __device__ __forceinline__ float tc_chunk_max(const uint32_t* v, const float* ks
       x0 = __uint_as_float(v[c]); x1 = __uint_as_float(v[c + 1]);
       x2 = __uint_as_float(v[c + 2]); x3 = __uint_as_float(v[c + 3]);
     }
-    const float a0 = __fmul_rn(x0, kk.x), a1 = __fmul_rn(x1, kk.y);
-    const float a2 = __fmul_rn(x2, kk.z), a3 = __fmul_rn(x3, kk.w);
+    float a0, a1, a2, a3;
+    if constexpr (KIND == 1 && TC_PACKED_MUL) {
+      // two rounded products per instruction; the accumulator registers of a tensor-memory load and the
+      // halves of a 16-byte shared load are neighbouring registers, so the pairs need no moves
+      uint64_t p01, p23, k01, k23, r01, r23;
+      asm("mov.b64 %0, {%1, %2};" : "=l"(p01) : "f"(x0), "f"(x1));
+      asm("mov.b64 %0, {%1, %2};" : "=l"(p23) : "f"(x2), "f"(x3));
+      asm("mov.b64 %0, {%1, %2};" : "=l"(k01) : "f"(kk.x), "f"(kk.y));
+      asm("mov.b64 %0, {%1, %2};" : "=l"(k23) : "f"(kk.z), "f"(kk.w));
+      asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r01) : "l"(p01), "l"(k01));
+      asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r23) : "l"(p23), "l"(k23));
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(r01));
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(a2), "=f"(a3) : "l"(r23));
+    } else {
+      a0 = __fmul_rn(x0, kk.x); a1 = __fmul_rn(x1, kk.y);
+      a2 = __fmul_rn(x2, kk.z); a3 = __fmul_rn(x3, kk.w);
+    }
     asm("max.f32 %0, %0, %1, %2;" : "+f"(ma) : "f"(a0), "f"(a1));
     asm("max.f32 %0, %0, %1, %2;" : "+f"(mb) : "f"(a2), "f"(a3));
   }
