@@ -623,9 +623,13 @@ def measure_model_decode(steps: int, dev: torch.device, batch: int = 8, context:
 
 
 def main() -> None:
-    # NCCL writes its debug output (at NCCL_DEBUG=VERSION and above: a version banner) to stdout, where only the
-    # JSON line belongs
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # Only the JSON line belongs on stdout, but native libraries write there too (NCCL prints a version banner at
+    # NCCL_DEBUG=VERSION and above): file descriptor 1 is pointed at stderr for the whole run and Python's own
+    # sys.stdout keeps the original descriptor.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
