@@ -846,7 +846,11 @@ class GraphedDecode:
 
     def __init__(self, step: DecodeStep, key: torch.Tensor, value: torch.Tensor, packed: torch.Tensor,
                  scale: torch.Tensor, channel_idx: torch.Tensor, history: int, q_heads: int,
-                 advance: bool = True, scaling: Optional[float] = None):
+                 advance: bool = True, scaling: Optional[float] = None, zero_copy: bool = False):
+        """``zero_copy``: the step's kernels read the new K/V rows from, and write the output to, the pinned host
+        buffers themselves (pinned memory is addressable from the device), which takes the device-to-host copy node
+        and a third of the host-to-device one out of the graph; only the query, which three kernels read, is still
+        copied to the device first."""
         dev = key.device
         B, Hkv, rows, D = key.shape
         if history + 1 > rows:
@@ -871,7 +875,15 @@ class GraphedDecode:
         self.h_in.zero_()
         self.h_query.copy_(torch.randn((B, q_heads, D), generator=torch.Generator().manual_seed(0)).to(torch.bfloat16))
 
+        self.zero_copy = bool(zero_copy)
+
         def body():
+            if self.zero_copy:
+                self._in[:nq].copy_(self.h_in[:nq], non_blocking=True)
+                step(self._q, key, value, packed, scale, channel_idx, scaling=scaling, out=self.h_out,
+                     history_dev=self.history, advance_history=advance,
+                     new_rows=(self.h_key_row.view(B, Hkv, D), self.h_value_row.view(B, Hkv, D)))
+                return
             self._in.copy_(self.h_in, non_blocking=True)
             # the step itself stores the new rows at the device-side position
             step(self._q, key, value, packed, scale, channel_idx, scaling=scaling, out=self._out,

@@ -101,7 +101,8 @@ def test_all_zero_keys(cuda_device, T):
     assert torch.equal(sel.cpu(), torch.arange(k, dtype=torch.int32).expand(1, 2, k))     # all tie: lowest indices win
 
 
-def test_graphed_decode_loop_with_device_side_history(cuda_device):
+@pytest.mark.parametrize("zero_copy", [False, True])     # True: kernels read the new rows from / write the output to pinned host memory
+def test_graphed_decode_loop_with_device_side_history(cuda_device, zero_copy):
     """One captured graph replayed for consecutive tokens: the history length lives on the device and
     advances by one per replay; every replay must equal the oracle step at that length."""
     T0, k, steps = 12000, 256, 3
@@ -112,7 +113,7 @@ def test_graphed_decode_loop_with_device_side_history(cuda_device):
     cache_k[:, :, :T0], cache_v[:, :, :T0] = key[:, :, :T0], value[:, :, :T0]
     packed, scale = ops.alloc_side_cache(2, 2, T0 + steps + 4, 64, cuda_device)
     ops.quantize(key[:, :, :T0], ch, out=(packed, scale))
-    g = ops.GraphedDecode(ops.DecodeStep(k), cache_k, cache_v, packed, scale, ch, history=T0, q_heads=8)
+    g = ops.GraphedDecode(ops.DecodeStep(k), cache_k, cache_v, packed, scale, ch, history=T0, q_heads=8, zero_copy=zero_copy)
     for i in range(steps):
         T = T0 + i
         g.h_query.copy_(q)
