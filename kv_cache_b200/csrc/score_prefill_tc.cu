@@ -726,25 +726,24 @@ __global__ void __launch_bounds__(TW_THREADS, 1) score_prefill_tw_kernel(Prefill
     const int row = quad * 32 + lane;
     const int qi = row / G, hd = row - qi * G;
     const int q = q0 + qt * QPT + qi;
-    const float qs = q < p.Tq ? p.qscale[((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q] : 0.0f;
+    // (int8 operands carry 16 * code: the exact factor 1/16 goes into the query scale, a power of two)
+    const float qs = (q < p.Tq ? p.qscale[((int64_t)b * p.Hq + kvh * G + hd) * p.Tq + q] : 0.0f) * (KIND == 0 ? 0.0625f : 1.0f);
     float* out_row = p.out + (((int64_t)b * p.Hkv + kvh) * p.Tq + (q < p.Tq ? q : 0)) * p.nblk;
     const bool writer = hd == 0 && q < p.Tq;
     float* my_ks = s_ks + warp * 2 * TC_NTILE;
     // Key scales of a tile: lane l fetches tokens 4l .. 4l+3; dead tokens get NaN, which never wins a max.
     // Fetched two of this warp's tiles ahead.
     auto load_ks = [&](int tile) -> float4 {
+      const int64_t t = (int64_t)tile * TC_NTILE + 4 * lane;
+      if ((int64_t)(tile + 1) * TC_NTILE <= (int64_t)p.Tk)                 // interior tile (all but the last one or two)
+        return *reinterpret_cast<const float4*>(scale_row + t);
       const float nan = __int_as_float(0x7fc00000);
       float4 v = make_float4(nan, nan, nan, nan);
-      const int64_t t = (int64_t)tile * TC_NTILE + 4 * lane;
       if (tile < ntiles) {
-        if (t + 3 < p.Tk) {
-          v = *reinterpret_cast<const float4*>(scale_row + t);
-        } else {
-          if (t < p.Tk) v.x = scale_row[t];
-          if (t + 1 < p.Tk) v.y = scale_row[t + 1];
-          if (t + 2 < p.Tk) v.z = scale_row[t + 2];
-        }
-        if constexpr (KIND == 0) { v.x *= 0.0625f; v.y *= 0.0625f; v.z *= 0.0625f; v.w *= 0.0625f; }
+        if (t < p.Tk) v.x = scale_row[t];
+        if (t + 1 < p.Tk) v.y = scale_row[t + 1];
+        if (t + 2 < p.Tk) v.z = scale_row[t + 2];
+        if (t + 3 < p.Tk) v.w = scale_row[t + 3];
       }
       return v;
     };
@@ -759,7 +758,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) score_prefill_tw_kernel(Prefill
       k_cur = k_next;
       k_next = load_ks(i + 2 * TC_ASTAGES);
       __syncwarp();
-      if (*s_dead) break;
+      // (a role that gave up stops feeding the barriers, so this bounded wait ends every warp's loop)
       if (!mbar_wait_bounded(&acc_full[par], (uint32_t)(i >> 1) & 1u)) { *s_dead = 1; break; }
       tc_fence_after();
       float m = -INFINITY, m0 = 0.0f;
