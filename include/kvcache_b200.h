@@ -622,6 +622,16 @@ typedef struct kvb_decode_step_params {
    * step at config 2, but the order (and with it the last bits of the fp32 accumulation) varies from
    * run to run. */
   int selected_any_order;
+  /* Optional paged K/V. When kv_page_table is not NULL, `key` and `value` are page POOLS, bf16
+   * [num_pages, Hkv, kv_page_tokens, D] dense (D = 128), and token t of batch row b lives in page
+   * kv_page_table[b * kv_page_table_stride + t / kv_page_tokens] at row t % kv_page_tokens; the strides
+   * k_sb .. v_st are ignored. kv_page_tokens is a power of two; the table must cover row history_count (the
+   * decoded token's row, which the step reads and, with new_key_row, writes). A pool holds fewer than 2^31
+   * rows. The int4 side cache stays contiguous (36 bytes per token at C = 64 against 512 for K and V).
+   * No reference counterpart (the reference keeps HF's contiguous cache, EVAL:7278). */
+  const int32_t* kv_page_table;
+  int64_t kv_page_table_stride;
+  int kv_page_tokens;
 } kvb_decode_step_params;
 
 size_t kvb_decode_step_workspace_bytes(int B, int Hq, int Hkv, int history_count, int top_k,

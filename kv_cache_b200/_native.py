@@ -49,6 +49,9 @@ class DecodeStepParams(C.Structure):
         ("history_count_dev", _p), ("advance_history", _i),
         ("new_key_row", _p), ("new_value_row", _p),
         ("selected_any_order", _i),
+        ("kv_page_table", _p),
+        ("kv_page_table_stride", _i64),
+        ("kv_page_tokens", _i),
     ]
 
 

@@ -147,3 +147,70 @@ class PreallocatedCache(Cache):
     @property
     def reallocations(self) -> int:
         return sum(layer.reallocations for layer in self.layers)
+
+
+class PagedKV:
+    """K/V of a batch of equally long sequences in fixed-size pages of two shared pools: appended rows go into
+    the sequence's last page or into a page taken from the free list, and no stored row ever moves. The fused
+    decode step reads the pools through ``page_table`` (``ops.DecodeStep(...)(..., kv_pages=(table, history))``);
+    the int4 side cache stays contiguous (it is 7 % of the K/V bytes and is read as a stream).
+
+    ``key_pool`` / ``value_pool``: bf16 ``[num_pages, Hkv, page_tokens, D]``; ``page_table``: int32
+    ``[B, pages_per_sequence]`` (entries beyond the pages in use are 0, a valid page id that is never read)."""
+
+    def __init__(self, batch: int, kv_heads: int, head_dim: int, page_tokens: int, num_pages: int, device,
+                 pages_per_sequence: Optional[int] = None, dtype: torch.dtype = torch.bfloat16,
+                 free_order: Optional[torch.Tensor] = None):
+        if page_tokens < 1 or page_tokens & (page_tokens - 1):
+            raise ValueError("page_tokens must be a power of two")
+        self.B, self.Hkv, self.D, self.P = int(batch), int(kv_heads), int(head_dim), int(page_tokens)
+        self.key_pool = torch.zeros((num_pages, kv_heads, page_tokens, head_dim), dtype=dtype, device=device)
+        self.value_pool = torch.zeros_like(self.key_pool)
+        per_seq = pages_per_sequence if pages_per_sequence is not None else num_pages // max(1, batch)
+        self.page_table = torch.zeros((batch, per_seq), dtype=torch.int32, device=device)
+        order = list(range(num_pages)) if free_order is None else [int(i) for i in free_order.tolist()]
+        self.free = order[::-1]                           # pop() hands pages out in `order`
+        self.length = 0
+
+    def _ensure_pages(self, upto: int) -> None:
+        have = (self.length + self.P - 1) // self.P
+        need = (upto + self.P - 1) // self.P
+        if need > self.page_table.shape[1]:
+            raise RuntimeError("the page table has no room for that many tokens")
+        for page in range(have, need):
+            if len(self.free) < self.B:
+                raise RuntimeError("the pool has no free page left")
+            ids = [self.free.pop() for _ in range(self.B)]
+            self.page_table[:, page] = torch.tensor(ids, dtype=torch.int32, device=self.page_table.device)
+
+    def reserve(self, tokens: int) -> None:
+        """Makes sure pages exist for the next ``tokens`` rows (the fused step stores the decoded token's row itself)."""
+        self._ensure_pages(self.length + tokens)
+
+    def append(self, key_rows: torch.Tensor, value_rows: torch.Tensor) -> None:
+        """Stores rows ``[B,Hkv,n,D]`` behind the ``length`` rows already there."""
+        n = key_rows.shape[2]
+        self._ensure_pages(self.length + n)
+        done = 0
+        while done < n:
+            t = self.length + done
+            page, row = t // self.P, t % self.P
+            take = min(n - done, self.P - row)
+            ids = self.page_table[:, page].long()
+            self.key_pool[ids, :, row:row + take] = key_rows[:, :, done:done + take]
+            self.value_pool[ids, :, row:row + take] = value_rows[:, :, done:done + take]
+            done += take
+        self.length += n
+
+    def advance(self, tokens: int = 1) -> None:
+        """Counts rows that a kernel stored (``new_rows`` of the fused step)."""
+        self.length += tokens
+
+    def gather(self, upto: Optional[int] = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """The first ``upto`` (default: all) rows as contiguous ``[B,Hkv,T,D]`` tensors (a copy; for checks)."""
+        T = self.length if upto is None else int(upto)
+        pages = (T + self.P - 1) // self.P
+        ids = self.page_table[:, :pages].long()                                     # [B, pages]
+        k = self.key_pool[ids].permute(0, 2, 1, 3, 4).reshape(self.B, self.Hkv, pages * self.P, self.D)[:, :, :T]
+        v = self.value_pool[ids].permute(0, 2, 1, 3, 4).reshape(self.B, self.Hkv, pages * self.P, self.D)[:, :, :T]
+        return k.contiguous(), v.contiguous()

@@ -256,6 +256,18 @@ struct PartialWait {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- paged K/V: pools bf16 [num_pages, Hkv, page_tokens, D] addressed through a per-sequence page table ----
+struct KvPages {
+  const int32_t* table = nullptr;   // int32 [B, table_stride]: page id of logical page t >> shift of batch row b
+  int64_t table_stride = 0;
+  int shift = 0;                    // log2(page_tokens)
+};
+// Row of token t of (batch row b, KV head h) inside a pool, in units of one D-element row.
+__device__ __forceinline__ int64_t kv_paged_row(const KvPages& pg, int Hkv, int b, int h, int t) {
+  const int page = pg.table[(int64_t)b * pg.table_stride + (t >> pg.shift)];
+  return (((int64_t)page * Hkv + h) << pg.shift) + (int64_t)(t & ((1 << pg.shift) - 1));
+}
+
 // Whether launches made by this host thread ask for the early start (set only while a fused chain
 // whose kernels all begin with pdl_wait() is being enqueued).
 static thread_local bool t_chain_launch = false;

@@ -32,6 +32,7 @@ struct SampleParams {
   __nv_bfloat16* key; int64_t k_sb, k_sh, k_st;
   __nv_bfloat16* value; int64_t v_sb, v_sh, v_st;
   uint32_t* step_counter = nullptr;   // optional: CTA 0 adds one (the step number of the sequence-sharded exchange)
+  KvPages pages;                      // optional: key / value are page pools
 };
 
 // The rank-th largest of the sample values a CTA holds in registers (v[e], e < per, of every thread; NaN =
@@ -145,8 +146,11 @@ __global__ void __launch_bounds__(FS_THREADS) sample_threshold_kernel(SamplePara
   const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
   if (q.new_k && tid >= 64 && tid < 96) {          // one warp: 16 lanes per row, 16 bytes per lane
     const int l = tid - 64, rb = row / p.Hkv, rh = row - rb * p.Hkv;
-    if (l < 16) *reinterpret_cast<uint4*>(q.key + (int64_t)rb * q.k_sb + (int64_t)rh * q.k_sh + (int64_t)T * q.k_st + l * 8) = q.new_k[row * 16 + l];
-    else *reinterpret_cast<uint4*>(q.value + (int64_t)rb * q.v_sb + (int64_t)rh * q.v_sh + (int64_t)T * q.v_st + (l - 16) * 8) = q.new_v[row * 16 + l - 16];
+    int64_t ko = (int64_t)rb * q.k_sb + (int64_t)rh * q.k_sh + (int64_t)T * q.k_st;
+    int64_t vo = (int64_t)rb * q.v_sb + (int64_t)rh * q.v_sh + (int64_t)T * q.v_st;
+    if (q.pages.table) ko = vo = kv_paged_row(q.pages, p.Hkv, rb, rh, T) * 128;      // rows of D = 128 elements
+    if (l < 16) *reinterpret_cast<uint4*>(q.key + ko + l * 8) = q.new_k[row * 16 + l];
+    else *reinterpret_cast<uint4*>(q.value + vo + (l - 16) * 8) = q.new_v[row * 16 + l - 16];
   }
   if (T <= q.cap) {                             // short rows: every token is a candidate
     if (tid == 0) q.tau[row] = -INFINITY;
@@ -218,8 +222,11 @@ __global__ void __launch_bounds__(FS_THREADS) score_sample_kernel(SampleParams q
   const int T = p.T_dev ? min(*p.T_dev, p.T) : p.T;
   if (q.new_k && tid >= 64 && tid < 96) {          // one warp: 16 lanes per row, 16 bytes per lane
     const int l = tid - 64, rb = row / p.Hkv, rh = row - rb * p.Hkv;
-    if (l < 16) *reinterpret_cast<uint4*>(q.key + (int64_t)rb * q.k_sb + (int64_t)rh * q.k_sh + (int64_t)T * q.k_st + l * 8) = q.new_k[row * 16 + l];
-    else *reinterpret_cast<uint4*>(q.value + (int64_t)rb * q.v_sb + (int64_t)rh * q.v_sh + (int64_t)T * q.v_st + (l - 16) * 8) = q.new_v[row * 16 + l - 16];
+    int64_t ko = (int64_t)rb * q.k_sb + (int64_t)rh * q.k_sh + (int64_t)T * q.k_st;
+    int64_t vo = (int64_t)rb * q.v_sb + (int64_t)rh * q.v_sh + (int64_t)T * q.v_st;
+    if (q.pages.table) ko = vo = kv_paged_row(q.pages, p.Hkv, rb, rh, T) * 128;      // rows of D = 128 elements
+    if (l < 16) *reinterpret_cast<uint4*>(q.key + ko + l * 8) = q.new_k[row * 16 + l];
+    else *reinterpret_cast<uint4*>(q.value + vo + (l - 16) * 8) = q.new_v[row * 16 + l - 16];
   }
   if (T <= q.cap) {                             // short rows: every token is a candidate
     if (tid == 0) q.tau[row] = -INFINITY;
@@ -353,16 +360,19 @@ static int sample_launch_g(const SampleParams& q, int R, cudaStream_t st) {
 __global__ void __launch_bounds__(32) store_new_rows_kernel(const uint4* new_k, const uint4* new_v, __nv_bfloat16* key,
                                                             int64_t k_sb, int64_t k_sh, int64_t k_st,
                                                             __nv_bfloat16* value, int64_t v_sb, int64_t v_sh,
-                                                            int64_t v_st, int Hkv, int T, const int32_t* T_dev) {
+                                                            int64_t v_st, int Hkv, int T, const int32_t* T_dev,
+                                                            KvPages pages) {
   const int row = blockIdx.x, lane = threadIdx.x;
   const int b = row / Hkv, h = row - b * Hkv;
   const int t = T_dev ? min(*T_dev, T) : T;
   pdl_launch_dependents();
+  int64_t ko = (int64_t)b * k_sb + (int64_t)h * k_sh + (int64_t)t * k_st;
+  int64_t vo = (int64_t)b * v_sb + (int64_t)h * v_sh + (int64_t)t * v_st;
+  if (pages.table) ko = vo = kv_paged_row(pages, Hkv, b, h, t) * 128;
   if (lane < 16) {
-    *reinterpret_cast<uint4*>(key + (int64_t)b * k_sb + (int64_t)h * k_sh + (int64_t)t * k_st + lane * 8) = new_k[row * 16 + lane];
+    *reinterpret_cast<uint4*>(key + ko + lane * 8) = new_k[row * 16 + lane];
   } else {
-    *reinterpret_cast<uint4*>(value + (int64_t)b * v_sb + (int64_t)h * v_sh + (int64_t)t * v_st + (lane - 16) * 8) =
-        new_v[row * 16 + lane - 16];
+    *reinterpret_cast<uint4*>(value + vo + (lane - 16) * 8) = new_v[row * 16 + lane - 16];
   }
 }
 
@@ -391,6 +401,19 @@ static void fill_score_params(ScoreParams& sp, const void* query, int64_t q_sb, 
 // `sample_ws`: optional fp32 workspace [R, sp.T] (the group-max workspace of the caller). With it, long rows have
 // their sample scored by the streaming int8-MMA scorer and a small kernel derives the thresholds; otherwise one
 // kernel does both with dp4a.
+// The page table of a step's parameters (table == nullptr: contiguous caches); false if the fields are inconsistent.
+static bool step_kv_pages(const kvb_decode_step_params* p, KvPages& pg) {
+  pg = KvPages();
+  if (!p->kv_page_table) return true;
+  const int P = p->kv_page_tokens;
+  if (P < 1 || (P & (P - 1)) || p->D != 128) return false;                       // a power of two; rows of 128 elements
+  if (p->kv_page_table_stride * (int64_t)P < (int64_t)p->history_count + 1) return false;   // the table must cover row T
+  int shift = 0;
+  while ((1 << shift) < P) ++shift;
+  pg.table = p->kv_page_table; pg.table_stride = p->kv_page_table_stride; pg.shift = shift;
+  return true;
+}
+
 static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cudaStream_t st,
                       uint32_t* zero_count = nullptr, uint32_t* zero_failed = nullptr,
                       const kvb_decode_step_params* rows = nullptr, uint32_t* step_counter = nullptr,
@@ -408,6 +431,7 @@ static int sample_run(const ScoreParams& sp, float* tau, int top_k, int cap, cud
     sq.value = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(rows->value));
     sq.k_sb = rows->k_sb; sq.k_sh = rows->k_sh; sq.k_st = rows->k_st;
     sq.v_sb = rows->v_sb; sq.v_sh = rows->v_sh; sq.v_st = rows->v_st;
+    step_kv_pages(rows, sq.pages);                 // (validated by the caller)
   }
   const int R = sp.B * sp.Hkv;
   const int tile_tokens = score_stream_tile_tokens(sp.C, sp.G);
@@ -519,6 +543,8 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
                     (all_candidates || (run_len >= per_thread && 1.7 * expect <= (double)fcap));
   const int32_t* T_dev = p->history_count_dev;
   if (T_dev && !fast) return KVB_BAD_SHAPE;
+  KvPages pages;
+  if (!step_kv_pages(p, pages)) return KVB_BAD_SHAPE;
   if ((p->new_key_row == nullptr) != (p->new_value_row == nullptr)) return KVB_BAD_ARG;
   if (p->new_key_row && (p->D != 128 || !aligned_to(p->new_key_row, 16) || !aligned_to(p->new_value_row, 16)))
     return KVB_BAD_ALIGN;
@@ -528,7 +554,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
     store_new_rows_kernel<<<p->B * p->Hkv, 32, 0, st>>>(
         reinterpret_cast<const uint4*>(p->new_key_row), reinterpret_cast<const uint4*>(p->new_value_row),
         reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p->key)), p->k_sb, p->k_sh, p->k_st,
-        reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p->value)), p->v_sb, p->v_sh, p->v_st, p->Hkv, T, T_dev);
+        reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p->value)), p->v_sb, p->v_sh, p->v_st, p->Hkv, T, T_dev, pages);
     KVB_CHECK_CUDA(cudaGetLastError());
   }
   if (fast) {
@@ -605,7 +631,8 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
   AttendDeviceLength adl{T_dev, p->top_k, p->protect_sink, p->protect_recent, p->keep_self, p->advance_history};
   rc = attend_run(p->query, p->q_sb, p->q_sh, p->key, p->k_sb, p->k_sh, p->k_st, p->value, p->v_sb, p->v_sh, p->v_st,
                   list, &ap, T_dev ? &adl : nullptr, p->mask, p->mask_sb, p->B, p->Hq, p->Hkv, p->Hkv, T + 1, p->D, L.S, p->scaling,
-                  p->out, nullptr, attcnt, attpart, /*counters_zeroed=*/true, device, st);
+                  p->out, nullptr, attcnt, attpart, /*counters_zeroed=*/true, device, st, nullptr, nullptr, nullptr,
+                  &pages);
   if (rc != KVB_OK) return rc;
   return KVB_OK;
 }

@@ -94,6 +94,7 @@ struct AttendParams {
   // optional mean-value blend (SparQ): out = mean + alpha * (attention - mean)
   const float* blend_alpha;   // fp32 [B*Hq] or NULL
   const float* blend_mean;    // fp32 [B,Hkv,D] dense
+  KvPages pages;              // optional: key / value are page pools (rows of D contiguous elements)
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -222,12 +223,16 @@ __global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendPara
   const int nrows = s_end - s_begin;                     // >= 1 by construction of nsplit unless the device-side length shrank the list
   const int ntile = nrows > 0 ? (nrows + AT_TILE - 1) / AT_TILE : 0;
 
-  const __nv_bfloat16* kbase = p.key + (int64_t)b * p.k_sb + (int64_t)kvh * p.k_sh;
-  const __nv_bfloat16* vbase = p.value + (int64_t)b * p.v_sb + (int64_t)kvh * p.v_sh;
+  // paged pools: rows are addressed by their row number inside the pool (see kv_paged_row), D elements apart
+  const bool paged = p.pages.table != nullptr;
+  const __nv_bfloat16* kbase = paged ? p.key : p.key + (int64_t)b * p.k_sb + (int64_t)kvh * p.k_sh;
+  const __nv_bfloat16* vbase = paged ? p.value : p.value + (int64_t)b * p.v_sb + (int64_t)kvh * p.v_sh;
+  const int64_t k_st = paged ? AT_D : p.k_st, v_st = paged ? AT_D : p.v_st;
 
   if (p.append.enabled && split == 0) {
     const AttendAppend& A = p.append;
-    quantize_row_warp(kbase + A.t_src * p.k_st, A.channel_idx + (int64_t)kvh * A.C, A.C,
+    const int64_t src_row = paged ? kv_paged_row(p.pages, p.Hkv, b, kvh, A.t_src) : (int64_t)A.t_src;
+    quantize_row_warp(kbase + src_row * k_st, A.channel_idx + (int64_t)kvh * A.C, A.C,
                       A.packed + (int64_t)b * A.packed_sb + (int64_t)kvh * A.packed_sh + A.t_dst * (A.C >> 1),
                       A.scale + (int64_t)b * A.scale_sb + (int64_t)kvh * A.scale_sh + A.t_dst, lane);
   }
@@ -248,14 +253,16 @@ __global__ void __launch_bounds__(AT_THREADS, 2) sparse_attend_kernel(AttendPara
       s_msk[stage * AT_TILE + lane] = mv;
     }
     if (tok < 0) tok = 0;                                 // weight is forced to zero later; any live row will do
+    int prow = tok;                                       // row number: the token itself, or its place in the pool (< 2^31)
+    if (paged) prow = (int)kv_paged_row(p.pages, p.Hkv, b, kvh, tok);
     const int c16 = lane & 15;
     const int r0 = lane >> 4;
 #pragma unroll
     for (int j = 0; j < AT_TILE / 2; ++j) {
       const int r = r0 + 2 * j;
-      const int tr = __shfl_sync(0xffffffffu, tok, r);
-      cp_async_16(sk + r * AT_PITCH + c16 * 16, kbase + (int64_t)tr * p.k_st + c16 * 8);
-      cp_async_16(sv + r * AT_PITCH + c16 * 16, vbase + (int64_t)tr * p.v_st + c16 * 8);
+      const int tr = __shfl_sync(0xffffffffu, prow, r);
+      cp_async_16(sk + r * AT_PITCH + c16 * 16, kbase + (int64_t)tr * k_st + c16 * 8);
+      cp_async_16(sv + r * AT_PITCH + c16 * 16, vbase + (int64_t)tr * v_st + c16 * 8);
     }
   };
 
@@ -607,7 +614,7 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
                       int B, int Hq, int Hkv, int Hi, int Tk, int D, int S, float scaling, void* out,
                       float* out_partial, uint32_t* ws_counter, float* ws_partial, bool counters_zeroed, int device,
                       cudaStream_t st, const PartialPush* ppush = nullptr, const float* blend_alpha = nullptr,
-                      const float* blend_mean = nullptr) {
+                      const float* blend_mean = nullptr, const KvPages* pages = nullptr) {
   if (!query || !key || !value || !ws_counter || !ws_partial) return KVB_BAD_ARG;
   if (list.implicit ? (!list.selected && list.kk > 0) : !list.indices) return KVB_BAD_ARG;
   if (!out && !out_partial && !ppush) return KVB_BAD_ARG;
@@ -617,8 +624,9 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
   if (GG != 1 && GG != 2 && GG != 4 && GG != 8) return KVB_BAD_SHAPE;
   if ((int64_t)B * Hi > 65535) return KVB_BAD_SHAPE;
   if (!aligned_to(query, 16) || !aligned_to(key, 16) || !aligned_to(value, 16)) return KVB_BAD_ALIGN;
-  if ((q_sb % 8) || (q_sh % 8) || (k_sb % 8) || (k_sh % 8) || (k_st % 8) || (v_sb % 8) || (v_sh % 8) || (v_st % 8))
-    return KVB_BAD_ALIGN;
+  const bool paged = pages && pages->table;
+  if ((q_sb % 8) || (q_sh % 8)) return KVB_BAD_ALIGN;
+  if (!paged && ((k_sb % 8) || (k_sh % 8) || (k_st % 8) || (v_sb % 8) || (v_sh % 8) || (v_st % 8))) return KVB_BAD_ALIGN;
   if (!list.implicit && !aligned_to(list.indices, list.idx_is_i64 ? 8 : 4)) return KVB_BAD_ALIGN;
   if (!aligned_to(ws_partial, 16)) return KVB_BAD_ALIGN;
   if (append && append->enabled && (append->C > 128 || (append->C & 1))) return KVB_BAD_SHAPE;
@@ -647,6 +655,7 @@ static int attend_run(const void* query, int64_t q_sb, int64_t q_sh, const void*
   p.nsplit = plan.nsplit; p.tiles_per_split = plan.tiles_per_split;
   if (ppush) p.ppush = *ppush;
   p.blend_alpha = blend_alpha; p.blend_mean = blend_mean;
+  if (paged) p.pages = *pages;
 
   (void)counters_zeroed;   // the chunk merge is its own launch: no arrival counters to clear
   switch (GG) {

@@ -773,7 +773,8 @@ class DecodeStep:
                  selected_out: Optional[torch.Tensor] = None, history_dev: Optional[torch.Tensor] = None,
                  advance_history: bool = False,
                  new_rows: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
-                 top_k: Optional[int] = None) -> torch.Tensor:
+                 top_k: Optional[int] = None,
+                 kv_pages: Optional[tuple[torch.Tensor, int]] = None) -> torch.Tensor:
         """``key``/``value`` hold history+1 rows (the last is the token being decoded); the side
         cache holds the history rows. Returns bf16 ``[B,1,Hq,D]``. ``top_k`` overrides the count given at
         construction for this call (a policy whose count follows the history length keeps ONE step object
@@ -783,10 +784,21 @@ class DecodeStep:
         the device and ``key``/``value`` are the whole cache (capacity rows): the same launch
         sequence then serves every step of a CUDA-graph replayed decode loop; ``advance_history``
         makes the step add one to it when it is done. ``new_rows = (k_row, v_row)`` (bf16 ``[B,Hkv,D]``
-        dense): the step first stores them as row ``history`` of ``key`` / ``value``."""
+        dense): the step first stores them as row ``history`` of ``key`` / ``value``.
+
+        ``kv_pages = (page_table, history)``: ``key`` / ``value`` are page pools ``[num_pages,Hkv,P,D]`` (P a power of
+        two) and ``page_table`` (int32 ``[B, pages_per_sequence]``) maps token t of batch row b to page
+        ``page_table[b, t // P]``; ``history`` is the history length (the decoded token is row ``history``)."""
         query = _query3(query)
         B, Hq, D = query.shape
         Hkv, key_count = key.shape[1], key.shape[2]
+        if kv_pages is not None:
+            page_table, paged_history = kv_pages
+            if page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.shape[0] != B or not page_table.is_contiguous():
+                raise RuntimeError("page_table must be a dense int32 [B, pages] tensor")
+            if not (key.is_contiguous() and value.is_contiguous() and key.shape == value.shape):
+                raise RuntimeError("paged K/V pools must be dense [num_pages,Hkv,P,D] tensors of one shape")
+            key_count = int(paged_history) + 1
         T = key_count - 1
         if T < 1:
             raise RuntimeError("the fused step needs at least one history token")
@@ -823,6 +835,9 @@ class DecodeStep:
         p.history_count_dev = _ptr(history_dev)
         p.advance_history = int(advance_history)
         p.selected_any_order = 0 if self.ordered_selection else 1
+        if kv_pages is not None:
+            p.kv_page_table, p.kv_page_table_stride = page_table.data_ptr(), page_table.stride(0)
+            p.kv_page_tokens = int(key.shape[2])
         if new_rows is not None:
             k_row, v_row = new_rows
             if not (k_row.is_contiguous() and v_row.is_contiguous() and k_row.dtype == v_row.dtype == torch.bfloat16

@@ -68,3 +68,27 @@ def test_tiny_qwen3_decodes_to_the_same_logits_as_with_dynamic_cache():
             assert out_b.past_key_values is cache
     assert cache.get_seq_length() == 16 and cache.reallocations == 0
     assert [layer.key_buffer.data_ptr() for layer in cache.layers] == ptrs
+
+
+def test_paged_kv_bookkeeping_on_cpu():
+    """Pages are handed out in the given order, rows never move, gather() returns what was appended."""
+    from kv_cache_b200.cache import PagedKV
+
+    g = torch.Generator().manual_seed(0)
+    B, H, D, P = 2, 2, 128, 8
+    order = torch.randperm(20, generator=g)
+    kv = PagedKV(B, H, D, P, 20, "cpu", pages_per_sequence=6, dtype=torch.float32, free_order=order)
+    k = torch.randn(B, H, 37, D, generator=g)
+    v = torch.randn(B, H, 37, D, generator=g)
+    kv.append(k[:, :, :5], v[:, :, :5])
+    first_pages = kv.page_table[:, 0].clone()
+    kv.append(k[:, :, 5:30], v[:, :, 5:30])
+    kv.append(k[:, :, 30:], v[:, :, 30:])
+    assert kv.length == 37 and torch.equal(kv.page_table[:, 0], first_pages)
+    gk, gv = kv.gather()
+    assert torch.equal(gk, k) and torch.equal(gv, v)
+    used = kv.page_table[:, :5].flatten().tolist()
+    assert len(set(used)) == 10 and used[:2] != used[2:4]                 # ten distinct pages for 2 x 5
+    assert sorted(used) == sorted(int(i) for i in order[:10].tolist())     # taken in the order given
+    with pytest.raises(RuntimeError):
+        kv.append(k[:, :, :20], v[:, :, :20])                             # 57 tokens need 8 pages per sequence, the table has 6

@@ -128,3 +128,38 @@ def test_graphed_decode_loop_with_device_side_history(cuda_device, zero_copy):
     _, packed_o, scale_o = oracle.quantize_pack(key[:, :, :T0 + steps].cpu(), ch.cpu())
     assert torch.equal(packed[:, :, :T0 + steps].cpu(), packed_o)
     assert torch.equal(scale[:, :, :T0 + steps].cpu(), scale_o)
+
+
+def test_paged_kv_pools_give_the_same_step(cuda_device):
+    """K and V in pages of 256 tokens scattered over a pool in a shuffled order: the fused step through the page
+    table returns the bits it returns on contiguous caches (same selection, same attention order), stores the
+    decoded token's rows at their paged place, and appends the same int4 row."""
+    from kv_cache_b200.cache import PagedKV
+
+    T, k, P = 20000, 512, 256
+    w, q, key, value = make_case(cuda_device, batch=2, q_heads=8, kv_heads=2, context=T, channels=64, seed=21)
+    ch = ops.choose_channels(key[:, :, :T], 64)
+    packed, scale = ops.alloc_side_cache(2, 2, T + 1, 64, cuda_device)
+    ops.quantize(key[:, :, :T], ch, out=(packed, scale))
+    packed2, scale2 = packed.clone(), scale.clone()
+    sel = torch.empty((2, 2, k), dtype=torch.int32, device=cuda_device)
+    want = ops.DecodeStep(k, protect_sink=4, protect_recent=8)(q, key, value, packed, scale, ch, selected_out=sel)
+
+    pages_per_seq = (T + 1 + P - 1) // P
+    order = torch.randperm(2 * pages_per_seq + 5, generator=torch.Generator().manual_seed(3))
+    kv = PagedKV(2, 2, 128, P, 2 * pages_per_seq + 5, cuda_device, pages_per_sequence=pages_per_seq, free_order=order)
+    kv.append(key[:, :, :T], value[:, :, :T])
+    gk, gv = kv.gather()
+    assert torch.equal(gk, key[:, :, :T]) and torch.equal(gv, value[:, :, :T])
+    kv.reserve(1)
+    sel2 = torch.empty_like(sel)
+    new_k, new_v = key[:, :, T].contiguous(), value[:, :, T].contiguous()
+    got = ops.DecodeStep(k, protect_sink=4, protect_recent=8)(
+        q, kv.key_pool, kv.value_pool, packed2, scale2, ch, selected_out=sel2, new_rows=(new_k, new_v),
+        kv_pages=(kv.page_table, T))
+    kv.advance(1)
+    assert torch.equal(sel2, sel)
+    assert torch.equal(got, want)
+    gk, gv = kv.gather()
+    assert torch.equal(gk, key[:, :, :T + 1]) and torch.equal(gv, value[:, :, :T + 1])
+    assert torch.equal(packed2[:, :, :T + 1], packed[:, :, :T + 1]) and torch.equal(scale2[:, :, :T + 1], scale[:, :, :T + 1])
