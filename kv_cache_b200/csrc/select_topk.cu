@@ -746,7 +746,7 @@ again:
           if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(c >> 32));
           const uint64_t cg = (c & 0xFFFFFFFF00000000ull) | (uint64_t)(0xFFFFFFFFu - idx);
           if (p.out_comp) p.out_comp[o] = cg;
-          if (p.push.n > 0 && pos < (uint32_t)p.push.prefix) {
+          if (p.push.n > 0 && !p.out_comp && pos < (uint32_t)p.push.prefix) {      // (no local list to copy from)
             const int64_t slot = ((int64_t)p.push.rank * p.R + row) * p.push.prefix + pos;
             for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot] = cg;
           }
@@ -760,6 +760,31 @@ again:
     if (own && p.out_owned_count) {
       __syncthreads();
       if (tid == 0) p.out_owned_count[row] = (int32_t)(s_count[2] < (uint32_t)rkk ? s_count[2] : (uint32_t)rkk);
+    }
+    if (p.push.n > 0 && p.out_comp) {
+      // The prefix goes to the ranks' inboxes from the row's finished local list, not entry by entry from the
+      // walk above: consecutive threads copy consecutive 16-byte pairs, so a rank receives full lines over
+      // NVLink instead of scattered 8-byte stores.
+      __syncthreads();                                   // the list of this row is complete (written by this CTA)
+      int npush = p.push.prefix < rkk ? p.push.prefix : rkk;
+      const uint64_t* mine = p.out_comp + (int64_t)row * out_pitch;
+      const int64_t slot0 = ((int64_t)p.push.rank * p.R + row) * p.push.prefix;
+      const bool pairs = ((reinterpret_cast<uintptr_t>(mine) | (uintptr_t)(slot0 * 8)) & 15) == 0 && (p.push.prefix & 1) == 0;
+      if (pairs) {
+        for (int j = tid; 2 * j + 1 < npush; j += SEL_FINAL_THREADS) {
+          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine) + j);
+          for (int q = 0; q < p.push.n; ++q) reinterpret_cast<uint4*>(p.push.inbox[q] + slot0)[j] = v;
+        }
+        if ((npush & 1) && tid == 0) {
+          const uint64_t v = __ldcg(mine + npush - 1);
+          for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot0 + npush - 1] = v;
+        }
+      } else {
+        for (int j = tid; j < npush; j += SEL_FINAL_THREADS) {
+          const uint64_t v = __ldcg(mine + j);
+          for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot0 + j] = v;
+        }
+      }
     }
     if (p.push.n > 0) {
       // every thread's stores (local list and the ranks' inboxes) precede the barrier; one thread per rank
