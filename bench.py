@@ -639,6 +639,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the config 4 / config 3 / quantizer block of the default run")
     ap.add_argument("--queries", type=int, default=4096, help="query chunk length of the prefill workload (c3)")
+    ap.add_argument("--context", type=int, default=None,
+                    help="override the workload's history length (e.g. the per-rank shard length of a sharded run)")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's batch (smaller device footprint for profiler captures)")
     args = ap.parse_args()
@@ -671,6 +673,8 @@ def main() -> None:
     w = inputs.WORKLOADS[name]
     if args.batch:
         w = dataclasses.replace(w, batch=args.batch, name=f"{w.name}_batch{args.batch}")
+    if args.context:
+        w = dataclasses.replace(w, context=args.context, name=f"{w.name}_context{args.context}")
     if args.impl == "reference":
         run_reference_arm(args, w)
         return
