@@ -593,7 +593,11 @@ extern "C" __attribute__((visibility("default"))) int kvb_decode_step(const kvb_
       size_t smem = (size_t)fcap * 8 + SEL_FINAL_FIXED_SMEM;
       sp.use_bitmap = (smem + bitmap_bytes <= SEL_SMEM_LIMIT) ? 1 : 0;
       if (sp.use_bitmap) smem += bitmap_bytes;
-      if (p->selected_any_order) { sp.order_by_index = 2; sp.use_bitmap = 0; }     // skip the ordering bitmap
+      if (p->selected_any_order) {                                                 // skip the ordering bitmap
+        if (sp.use_bitmap) smem -= bitmap_bytes;
+        sp.order_by_index = 2; sp.use_bitmap = 0;
+        if (smem + select_stage_bytes(L.kk) <= SEL_SMEM_LIMIT) { sp.stage = 1; smem += select_stage_bytes(L.kk); }
+      }
       { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
       KVB_CHECK_CUDA(launch_kernel(select_final_kernel, dim3(L.R), dim3(SEL_FINAL_THREADS), smem, st, sp));
     }
@@ -716,6 +720,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_merge_candidates(
     sp.order_by_index = 1; sp.use_bitmap = 1; smem += bitmap_bytes;      // ascending global ids (cheap bitmap only)
   } else {
     sp.order_by_index = 2; sp.use_bitmap = 0;                              // exact set, arbitrary order
+    if (smem + select_stage_bytes(sp.kk) <= SEL_SMEM_LIMIT) { sp.stage = 1; smem += select_stage_bytes(sp.kk); }
   }
   { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
   select_final_kernel<<<R, SEL_FINAL_THREADS, smem, reinterpret_cast<cudaStream_t>(stream)>>>(sp);

@@ -76,6 +76,7 @@ struct SelectParams {
   // rank's inbox (push.n > 0, unordered output with split_k == push.prefix or push.prefix >= kk); the merge
   // kernel WAITS for all ranks' flags (wait.n > 0) and then selects from its local inbox (`gather`, rows
   // gather_pitch apart), falling back to the ranks' whole lists (wait.full) for a row its prefixes cannot decide.
+  int stage = 0;              // unordered output: 12 * kk bytes of staging follow the fixed shared-memory areas
   int out_pitch = 0;          // row pitch of the outputs; 0 = kk
   int gather_pitch = 0;       // row pitch of a segment in `gather`; 0 = gather_len
   PeerPush push;
@@ -729,9 +730,50 @@ again:
     uint32_t pa, pb, pq = 0, ta, tb, tq = 0, unused_e, unused_t;
     block_exclusive_scan2<SEL_FINAL_THREADS>((uint32_t)__popc(m_first), (uint32_t)__popc(m_second), s_tmp, pa, pb, ta, tb);
     if (own) block_exclusive_scan2<SEL_FINAL_THREADS>((uint32_t)__popc(m_mine), 0u, s_tmp, pq, unused_e, tq, unused_t);
-    (void)ta; (void)tb; (void)unused_e; (void)unused_t;
+    (void)unused_e; (void)unused_t;
     if (tid == 0) s_count[2] = tq;
-    {
+    // With a staging area the winners are first compacted in shared memory (a scatter there costs nothing) and
+    // then written out by consecutive threads to consecutive addresses — the lists, and the prefix that goes to
+    // the ranks' inboxes over NVLink, leave as full lines. Written straight from the walk, a warp's stores land
+    // in 32 different sectors (a thread's winners are neighbours, the lanes' runs are not).
+    const bool staged = p.stage != 0 && (!split || ta == (uint32_t)p.split_k);
+    if (staged) {
+      uint64_t* s_stage = reinterpret_cast<uint64_t*>(s_bitmap);                 // [rkk] (no bitmap in this mode)
+      int32_t* s_own = reinterpret_cast<int32_t*>(s_stage + rkk);               // [rkk]
+      int j = 0;
+      for (int i = tid; i < n; i += SEL_FINAL_THREADS, ++j) {
+        const bool first = (m_first >> j) & 1u, second = (m_second >> j) & 1u, mine = (m_mine >> j) & 1u;
+        if (!(first || second)) continue;
+        const uint64_t c = s_cand[i];
+        const uint32_t idx = (0xFFFFFFFFu - (uint32_t)(c & 0xFFFFFFFFull)) - id_sub + id_add;
+        const uint32_t pos = first ? pa++ : (uint32_t)p.split_k + pb++;
+        if (pos < (uint32_t)rkk) s_stage[pos] = (c & 0xFFFFFFFF00000000ull) | (uint64_t)(0xFFFFFFFFu - idx);
+        if (mine) {
+          if (pq < (uint32_t)rkk) s_own[pq] = (int32_t)idx;
+          ++pq;
+        }
+      }
+      __syncthreads();
+      uint32_t filled = split ? (uint32_t)p.split_k + tb : ta;
+      if (filled > (uint32_t)rkk) filled = (uint32_t)rkk;
+      const uint32_t npush = p.push.n > 0 ? ((uint32_t)p.push.prefix < filled ? (uint32_t)p.push.prefix : filled) : 0u;
+      const int64_t slot0 = ((int64_t)p.push.rank * p.R + row) * p.push.prefix;
+      for (uint32_t t = tid; t < filled; t += SEL_FINAL_THREADS) {
+        const uint64_t cg = s_stage[t];
+        const uint32_t idx = 0xFFFFFFFFu - (uint32_t)(cg & 0xFFFFFFFFull);
+        const int64_t o = (int64_t)row * out_pitch + t;
+        if (p.out_idx32) p.out_idx32[o] = (int32_t)idx;
+        if (p.out_idx64) p.out_idx64[o] = (int64_t)idx;
+        if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(cg >> 32));
+        if (p.out_comp) p.out_comp[o] = cg;
+        if (t < npush)
+          for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot0 + t] = cg;
+      }
+      if (own) {
+        const uint32_t nown = tq < (uint32_t)rkk ? tq : (uint32_t)rkk;
+        for (uint32_t t = tid; t < nown; t += SEL_FINAL_THREADS) p.out_owned[(int64_t)row * out_pitch + t] = s_own[t];
+      }
+    } else {
       int j = 0;
       for (int i = tid; i < n; i += SEL_FINAL_THREADS, ++j) {
         const bool first = (m_first >> j) & 1u, second = (m_second >> j) & 1u, mine = (m_mine >> j) & 1u;
@@ -761,7 +803,7 @@ again:
       __syncthreads();
       if (tid == 0) p.out_owned_count[row] = (int32_t)(s_count[2] < (uint32_t)rkk ? s_count[2] : (uint32_t)rkk);
     }
-    if (p.push.n > 0 && p.out_comp) {
+    if (p.push.n > 0 && p.out_comp && !staged) {
       // The prefix goes to the ranks' inboxes from the row's finished local list, not entry by entry from the
       // walk above: consecutive threads copy consecutive 16-byte pairs, so a rank receives full lines over
       // NVLink instead of scattered 8-byte stores.
@@ -789,11 +831,10 @@ again:
     if (p.push.n > 0) {
       // every thread's stores (local list and the ranks' inboxes) precede the barrier; one thread per rank
       // then makes them visible system-wide and raises this row's flag there
+      // (the release is cumulative over the barrier: it orders every thread's stores before the flag, at system
+      // scope, without a separate fence)
       __syncthreads();
-      if (tid < p.push.n) {
-        __threadfence_system();
-        st_release_sys_u32(p.push.flags[tid] + (int64_t)p.push.rank * p.R + row, epoch);
-      }
+      if (tid < p.push.n) st_release_sys_u32(p.push.flags[tid] + (int64_t)p.push.rank * p.R + row, epoch);
     }
     return;
   }
@@ -880,6 +921,8 @@ static int select_cap(int k) {
 
 constexpr size_t SEL_FINAL_FIXED_SMEM = sizeof(uint32_t) * (2048 + SEL_FINAL_THREADS + 40 + 8) + 8 * SEL_MAX_SEGMENTS;
 constexpr size_t SEL_SMEM_LIMIT = 227 * 1024;
+// staging of the unordered output: kk composites + kk owned ids
+static inline size_t select_stage_bytes(int kk) { return (size_t)kk * 12; }
 
 // Opts select_final_kernel into its large dynamic shared memory once per device (the device must be
 // current). Safe to call from several host threads: the flag is atomic and the attribute call is idempotent.

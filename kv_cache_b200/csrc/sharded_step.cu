@@ -119,6 +119,8 @@ static int shard_candidates_run(const void* query, int64_t q_sb, int64_t q_sh, c
   const size_t bitmap_bytes = sizeof(uint32_t) * (size_t)((T + 31) / 32);
   if (ascending && !out_comp && smem + bitmap_bytes <= SEL_SMEM_LIMIT) {      // ids in ascending order (on-chip bitmap)
     sp.order_by_index = 1; sp.use_bitmap = 1; smem += bitmap_bytes;
+  } else if (sp.order_by_index == 2 && smem + select_stage_bytes(L.kk) <= SEL_SMEM_LIMIT) {
+    sp.stage = 1; smem += select_stage_bytes(L.kk);                             // coalesced output and pushes
   }
   { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
   KVB_CHECK_CUDA(launch_kernel(select_final_kernel, dim3(L.R), dim3(SEL_FINAL_THREADS), smem, st, sp));
@@ -290,7 +292,8 @@ extern "C" __attribute__((visibility("default"))) int kvb_sharded_decode_step(co
     for (int r = 0; r < N; ++r)
       sp.wait.full[r] = reinterpret_cast<const uint64_t*>(reinterpret_cast<uint8_t*>(p->exchange[r]) + X.off_full);
     if ((int64_t)N * X.prefix > (int64_t)sp.cap) return KVB_BAD_SHAPE;
-    const size_t smem = (size_t)sp.cap * 8 + SEL_FINAL_FIXED_SMEM;
+    size_t smem = (size_t)sp.cap * 8 + SEL_FINAL_FIXED_SMEM;
+    if (smem + select_stage_bytes(sp.kk) <= SEL_SMEM_LIMIT) { sp.stage = 1; smem += select_stage_bytes(sp.kk); }
     { const int prc = select_final_prepare(device); if (prc != KVB_OK) return prc; }
     KVB_CHECK_CUDA(launch_kernel(select_final_kernel, dim3(X.R), dim3(SEL_FINAL_THREADS), smem, st, sp));
     chain.on();

@@ -478,11 +478,8 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
         op[AT_D + 1] = L;
       }
     }
-    __syncthreads();
-    if (d < p.ppush.n) {
-      __threadfence_system();
-      st_release_sys_u32(p.ppush.flags[d] + (int64_t)p.ppush.rank * p.B * p.Hq + bh, epoch);
-    }
+    __syncthreads();                                 // (the release below is cumulative over this barrier)
+    if (d < p.ppush.n) st_release_sys_u32(p.ppush.flags[d] + (int64_t)p.ppush.rank * p.B * p.Hq + bh, epoch);
   }
 }
 
