@@ -234,16 +234,37 @@ struct PeerWait {
   const uint64_t* full[KVB_MAX_RANKS] = {};
   int full_len = 0;
 };
-// The same for the attention partials fp32 [n, B*Hq, D+2], one flag per (rank, batch, query head).
+// Flag-in-data pairs: a value travels as one naturally aligned 8-byte store {value bits, step number}; a reader
+// that sees the step number it expects has the value of that step, with no fence on either side and no
+// separate flag (an 8-byte store is delivered whole). A system-scope release after a CTA's stores costs about
+// 3.5 us here; this costs the flight time of the store.
+__device__ __forceinline__ void st_pair(uint2* p, uint32_t bits, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_pair(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// Polls (bounded) until the pair carries `tag`; false (status word set) when it gives up.
+__device__ __forceinline__ bool wait_pair(const uint2* p, uint32_t tag, uint32_t limit, uint32_t& bits) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    const uint2 v = ld_pair(p);
+    if (v.y == tag) { bits = v.x; return true; }
+    __nanosleep(64);
+  }
+  atomicExch(&g_device_status, (int)KVB_TIMEOUT);
+  return false;
+}
+
+// The attention partials of every (rank, batch, query head): D+2 pairs {fp32 bits, step number} [n, B*Hq, D+2].
 struct PartialPush {
   int n = 0, rank = 0;
-  float* inbox[KVB_MAX_RANKS] = {};
-  uint32_t* flags[KVB_MAX_RANKS] = {};
+  uint2* inbox[KVB_MAX_RANKS] = {};
   const uint32_t* epoch = nullptr;
 };
 struct PartialWait {
   int n = 0;
-  const uint32_t* flags = nullptr;        // local, uint32 [n, B*Hq]
   const uint32_t* epoch = nullptr;
   uint32_t limit = KVB_DEFAULT_WAIT_POLLS;
 };

@@ -34,7 +34,7 @@ static ExchangeLayout exchange_layout(int B, int Hq, int Hkv, int top_k, int wor
   L.off_full = off;   off += round_up(sizeof(uint64_t) * (size_t)L.R * L.kk, 256);
   L.off_inbox = off;  off += round_up(sizeof(uint64_t) * (size_t)world * L.R * L.prefix, 256);
   L.off_flags = off;  off += round_up(sizeof(uint32_t) * (size_t)world * L.R, 256);
-  L.off_part = off;   off += round_up(sizeof(float) * (size_t)world * L.BH * (AT_D + 2), 256);
+  L.off_part = off;   off += round_up(sizeof(uint2) * (size_t)world * L.BH * (AT_D + 2), 256);    // {bits, step} pairs
   L.off_pflags = off; off += round_up(sizeof(uint32_t) * (size_t)world * L.BH, 256);
   L.bytes = off;
   return L;
@@ -311,8 +311,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_sharded_decode_step(co
     pp.n = N; pp.rank = me; pp.epoch = epoch;
     for (int r = 0; r < N; ++r) {
       uint8_t* xr = reinterpret_cast<uint8_t*>(p->exchange[r]);
-      pp.inbox[r] = reinterpret_cast<float*>(xr + X.off_part);
-      pp.flags[r] = reinterpret_cast<uint32_t*>(xr + X.off_pflags);
+      pp.inbox[r] = reinterpret_cast<uint2*>(xr + X.off_part);
     }
     rc = attend_run(p->query, p->q_sb, p->q_sh, p->key, p->k_sb, p->k_sh, p->k_st, p->value, p->v_sb, p->v_sh, p->v_st,
                     list, nullptr, nullptr, nullptr, 0, B, Hq, Hkv, Hkv, keep_self ? T + 1 : T, p->D, f.S, p->scaling,
@@ -324,9 +323,9 @@ extern "C" __attribute__((visibility("default"))) int kvb_sharded_decode_step(co
     DeviceGuard guard(device);
     if (!guard.ok) return KVB_BAD_DEVICE;
     PartialWait pw;
-    pw.n = N; pw.flags = reinterpret_cast<const uint32_t*>(mine + X.off_pflags); pw.epoch = epoch; pw.limit = polls;
-    KVB_CHECK_CUDA(launch_kernel(lse_merge_kernel, dim3(X.BH), dim3(AT_THREADS), 0, st,
-                                 reinterpret_cast<const float*>(mine + X.off_part), N, X.BH,
+    pw.n = N; pw.epoch = epoch; pw.limit = polls;
+    KVB_CHECK_CUDA(launch_kernel(lse_merge_pairs_kernel, dim3(X.BH), dim3(AT_THREADS), 0, st,
+                                 reinterpret_cast<const uint2*>(mine + X.off_part), N, X.BH,
                                  reinterpret_cast<__nv_bfloat16*>(p->out), pw));
   }
   return KVB_OK;

@@ -467,19 +467,18 @@ __global__ void __launch_bounds__(AT_D) attend_merge_kernel(AttendParams p) {
     }
   }
   if (p.ppush.n > 0) {
+    // every value goes to every rank as a {bits, step number} pair: no barrier, fence or flag behind it
     const uint32_t epoch = *p.ppush.epoch;
     const int64_t bh = (int64_t)b * p.Hq + head;
     const int64_t o = ((int64_t)p.ppush.rank * p.B * p.Hq + bh) * PW;
     for (int q = 0; q < p.ppush.n; ++q) {
-      float* op = p.ppush.inbox[q] + o;
-      op[d] = O;
+      uint2* op = p.ppush.inbox[q] + o;
+      st_pair(op + d, __float_as_uint(O), epoch);
       if (d == 0) {
-        op[AT_D] = M;
-        op[AT_D + 1] = L;
+        st_pair(op + AT_D, __float_as_uint(M), epoch);
+        st_pair(op + AT_D + 1, __float_as_uint(L), epoch);
       }
     }
-    __syncthreads();                                 // (the release below is cumulative over this barrier)
-    if (d < p.ppush.n) st_release_sys_u32(p.ppush.flags[d] + (int64_t)p.ppush.rank * p.B * p.Hq + bh, epoch);
   }
 }
 
@@ -491,15 +490,7 @@ __global__ void __launch_bounds__(AT_THREADS) lse_merge_kernel(const float* part
   constexpr int PW = AT_D + 2;
   const int bh = blockIdx.x, d = threadIdx.x;
   pdl_wait();
-  if (wait.n > 0) {
-    __shared__ int s_arrived;
-    const uint32_t epoch = *wait.epoch;
-    if (d == 0) s_arrived = 1;
-    __syncthreads();
-    if (d < wait.n && !wait_flag_bounded(wait.flags + (int64_t)d * BH + bh, epoch, wait.limit)) s_arrived = 0;
-    __syncthreads();
-    if (!s_arrived) return;                             // gave up (status word set): the output keeps its old contents
-  }
+  (void)wait;
   float M = -INFINITY;
   for (int r = 0; r < N; ++r) {
     const float* ps = partials + ((int64_t)r * BH + bh) * PW;
@@ -514,6 +505,43 @@ __global__ void __launch_bounds__(AT_THREADS) lse_merge_kernel(const float* part
         const float w = __expf(__ldcg(ps + AT_D) - M);
         L += l * w;
         O += __ldcg(ps + d) * w;
+      }
+    }
+  }
+  out[(int64_t)bh * AT_D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+}
+
+// The same combine over pairs {fp32 bits, step number} that the ranks' chunk merges store into this rank's
+// inbox: every thread polls (bounded) the pairs it needs until they carry this step's number.
+__global__ void __launch_bounds__(AT_THREADS) lse_merge_pairs_kernel(const uint2* partials, int N, int BH,
+                                                                     __nv_bfloat16* out, PartialWait wait) {
+  constexpr int PW = AT_D + 2;
+  const int bh = blockIdx.x, d = threadIdx.x;
+  pdl_wait();
+  const uint32_t epoch = *wait.epoch;
+  float M = -INFINITY;
+  float m_r[KVB_MAX_RANKS], l_r[KVB_MAX_RANKS], o_r[KVB_MAX_RANKS];
+#pragma unroll
+  for (int r = 0; r < KVB_MAX_RANKS; ++r) {
+    m_r[r] = -INFINITY; l_r[r] = 0.0f; o_r[r] = 0.0f;
+    if (r < N) {
+      const uint2* ps = partials + ((int64_t)r * BH + bh) * PW;
+      uint32_t bm, bl, bo;
+      if (!wait_pair(ps + AT_D, epoch, wait.limit, bm) || !wait_pair(ps + AT_D + 1, epoch, wait.limit, bl) ||
+          !wait_pair(ps + d, epoch, wait.limit, bo))
+        return;                                         // gave up (status word set): the output keeps its old contents
+      m_r[r] = __uint_as_float(bm); l_r[r] = __uint_as_float(bl); o_r[r] = __uint_as_float(bo);
+      if (l_r[r] > 0.0f) M = fmaxf(M, m_r[r]);
+    }
+  }
+  float L = 0.0f, O = 0.0f;
+  if (M != -INFINITY) {
+#pragma unroll
+    for (int r = 0; r < KVB_MAX_RANKS; ++r) {
+      if (r < N && l_r[r] > 0.0f) {
+        const float w = __expf(m_r[r] - M);
+        L += l_r[r] * w;
+        O += o_r[r] * w;
       }
     }
   }
