@@ -219,15 +219,16 @@ struct PeerPush {
   int n = 0;                              // ranks; 0 = no exchange
   int rank = 0;
   int prefix = 0;                         // entries per (rank, row) slot
-  uint64_t* inbox[KVB_MAX_RANKS] = {};    // rank q's inbox  uint64 [n, R, prefix]
-  uint32_t* flags[KVB_MAX_RANKS] = {};    // rank q's flags  uint32 [n, R]
+  uint4* inbox[KVB_MAX_RANKS] = {};       // rank q's inbox  [n, R, prefix] composites as tagged pairs (st_pair2)
+  uint32_t* flags[KVB_MAX_RANKS] = {};    // rank q's flags  uint32 [n, R]: raised when the rank's WHOLE list may be read
   const uint32_t* epoch = nullptr;        // this rank's step counter
 };
-// Consumer side (global merge kernel): waits for flags [s, row] == epoch for every rank s, then reads the
-// local inbox; `full[s]` is rank s's whole local list uint64 [R, full_len] (peer memory, read only when the
-// prefixes cannot decide a row).
+// Consumer side (global merge kernel): polls the tagged pairs of the local inbox; `full[s]` is rank s's whole
+// local list uint64 [R, full_len] (peer memory, read only when the prefixes cannot decide a row, and then only
+// after flags [s, row] == epoch for every rank s).
 struct PeerWait {
   int n = 0;
+  const uint4* inbox = nullptr;           // local, [n, R, prefix]
   const uint32_t* flags = nullptr;        // local, uint32 [n, R]
   const uint32_t* epoch = nullptr;
   uint32_t limit = KVB_DEFAULT_WAIT_POLLS;
@@ -252,6 +253,30 @@ __device__ __forceinline__ bool wait_pair(const uint2* p, uint32_t tag, uint32_t
     const uint2 v = ld_pair(p);
     if (v.y == tag) { bits = v.x; return true; }
     __nanosleep(64);
+  }
+  atomicExch(&g_device_status, (int)KVB_TIMEOUT);
+  return false;
+}
+
+// A 64-bit value as two pairs in one 16-byte store {high word, step number, low word, step number}: each 8-byte
+// half carries its own tag, so the halves may arrive apart.
+__device__ __forceinline__ void st_pair2(uint4* p, uint64_t v, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"((uint32_t)(v >> 32)), "r"(tag),
+               "r"((uint32_t)v), "r"(tag)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_pair2(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// `first` is an earlier load of the same place; polls (bounded) until both halves carry `tag`.
+__device__ __forceinline__ bool wait_pair2(const uint4* p, uint4 first, uint32_t tag, uint32_t limit, uint64_t& v) {
+  uint4 w = first;
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (w.y == tag && w.w == tag) { v = ((uint64_t)w.x << 32) | w.z; return true; }
+    __nanosleep(64);
+    w = ld_pair2(p);
   }
   atomicExch(&g_device_status, (int)KVB_TIMEOUT);
   return false;

@@ -426,7 +426,11 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   const int out_pitch = pin.out_pitch > 0 ? pin.out_pitch : pin.kk;     // rows of the outputs stay kk_max apart
   int rT = pin.T, rkk = pin.kk;
   pdl_launch_dependents();
-  pdl_wait();
+  // The merge of the ranks' prefixes takes nothing from the kernel before it in the stream except what that
+  // kernel stores into the inbox as tagged pairs (and, for a row the prefixes cannot decide, lists guarded by
+  // flags): it does not wait for that kernel to end — its blocks poll the pairs while the local select still
+  // runs, so neither that kernel's tail (the release of its flags) nor a launch gap lies on the step's path.
+  if (pin.wait.n == 0) pdl_wait();
   if (p.T_dev) {
     const int t = *p.T_dev;
     rT = t < pin.T ? t : pin.T;
@@ -445,23 +449,25 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   const bool peer = p.wait.n > 0;
   uint32_t epoch = 0;
   if (p.push.n > 0) epoch = *p.push.epoch;
+  // (the arrival word lives in the dynamic area: this kernel may ask for all the shared memory there is, which
+  // leaves no room for a static variable)
+  volatile uint32_t* s_arrived = s_count + 7;
   if (peer) {
-    // every rank's best entries for this row must have landed in the local inbox
-    // (the arrival word lives in the dynamic area: this kernel may ask for all the shared memory there is,
-    // which leaves no room for a static variable)
     epoch = *p.wait.epoch;
-    volatile uint32_t* s_arrived = s_count + 7;
     if (tid == 0) *s_arrived = 1;
     __syncthreads();
+  }
+  // Every rank's flag for this row (its whole list may be read): bounded; false when one never came.
+  auto wait_for_lists = [&]() -> bool {
     if (tid < p.wait.n && !wait_flag_bounded(p.wait.flags + (int64_t)tid * p.R + row, epoch, p.wait.limit)) *s_arrived = 0;
     __syncthreads();
     const bool arrived = *s_arrived != 0;
     __syncthreads();
-    if (!arrived) {                                     // gave up (status word set): this row selects nothing
-      if (tid == 0 && p.out_owned_count) p.out_owned_count[row] = 0;
-      return;
-    }
-  }
+    return arrived;
+  };
+  auto give_up = [&]() {                                  // (status word set): this row selects nothing
+    if (tid == 0 && p.out_owned_count) p.out_owned_count[row] = 0;
+  };
   const float* src = p.scores ? p.scores + (int64_t)row * p.row_stride : nullptr;
   const bool gathered = p.gather_n > 0;
   const int gpitch = p.gather_pitch > 0 ? p.gather_pitch : p.gather_len;
@@ -497,11 +503,30 @@ again:
     n = p.gather_n * p.gather_prefix;
     for (int i0 = 0; i0 < n; i0 += SEL_FINAL_THREADS * 8) {          // eight loads of every thread in flight
       uint64_t v[8];
+      if (peer) {
+        // tagged pairs stored by the ranks' select kernels: all eight loads first, then whatever has not arrived
+        uint4 w[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = i0 + u * SEL_FINAL_THREADS + tid;
-        const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
-        v[u] = i < n ? __ldcg(p.gather + (int64_t)seg * p.gather_stride + (int64_t)row * gpitch + j) : 0ull;
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * SEL_FINAL_THREADS + tid;
+          const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
+          w[u] = i < n ? ld_pair2(p.wait.inbox + ((int64_t)seg * p.R + row) * p.gather_prefix + j) : make_uint4(0, epoch, 0, epoch);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * SEL_FINAL_THREADS + tid;
+          const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
+          v[u] = 0ull;
+          if (i < n && !wait_pair2(p.wait.inbox + ((int64_t)seg * p.R + row) * p.gather_prefix + j, w[u], epoch, p.wait.limit, v[u]))
+            *s_arrived = 0;
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * SEL_FINAL_THREADS + tid;
+          const int seg = i / p.gather_prefix, j = i - seg * p.gather_prefix;
+          v[u] = i < n ? __ldcg(p.gather + (int64_t)seg * p.gather_stride + (int64_t)row * gpitch + j) : 0ull;
+        }
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
@@ -513,9 +538,11 @@ again:
       }
     }
     __syncthreads();
+    if (peer && *s_arrived == 0) { give_up(); return; }  // a rank's entries never came (uniform: read after the barrier)
     prefix = 0; fixed = 0; need = (uint32_t)rkk; in_prefix = (uint32_t)n;
     have_candidates = true;
   } else if (gathered) {
+    if (peer && !wait_for_lists()) { give_up(); return; }  // the whole lists live in the ranks' memory
     // All-gathered shard lists: up to gather_n * gather_len composites, far more than fit on chip. The
     // refinement below narrows them with 11-bit histogram passes over global memory (two passes bring
     // i.i.d. shard lists under the capacity) and then collects the survivors.
@@ -767,7 +794,7 @@ again:
         if (p.out_scores) p.out_scores[o] = key_to_float((uint32_t)(cg >> 32));
         if (p.out_comp) p.out_comp[o] = cg;
         if (t < npush)
-          for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot0 + t] = cg;
+          for (int q = 0; q < p.push.n; ++q) st_pair2(p.push.inbox[q] + slot0 + t, cg, epoch);
       }
       if (own) {
         const uint32_t nown = tq < (uint32_t)rkk ? tq : (uint32_t)rkk;
@@ -790,7 +817,7 @@ again:
           if (p.out_comp) p.out_comp[o] = cg;
           if (p.push.n > 0 && !p.out_comp && pos < (uint32_t)p.push.prefix) {      // (no local list to copy from)
             const int64_t slot = ((int64_t)p.push.rank * p.R + row) * p.push.prefix + pos;
-            for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot] = cg;
+            for (int q = 0; q < p.push.n; ++q) st_pair2(p.push.inbox[q] + slot, cg, epoch);
           }
         }
         if (mine) {
@@ -804,33 +831,22 @@ again:
       if (tid == 0) p.out_owned_count[row] = (int32_t)(s_count[2] < (uint32_t)rkk ? s_count[2] : (uint32_t)rkk);
     }
     if (p.push.n > 0 && p.out_comp && !staged) {
-      // The prefix goes to the ranks' inboxes from the row's finished local list, not entry by entry from the
-      // walk above: consecutive threads copy consecutive 16-byte pairs, so a rank receives full lines over
-      // NVLink instead of scattered 8-byte stores.
+      // (no staging area) The prefix goes to the ranks' inboxes from the row's finished local list, not entry by
+      // entry from the walk above: consecutive threads store consecutive entries, so a rank receives full lines
+      // over NVLink instead of scattered stores.
       __syncthreads();                                   // the list of this row is complete (written by this CTA)
       int npush = p.push.prefix < rkk ? p.push.prefix : rkk;
       const uint64_t* mine = p.out_comp + (int64_t)row * out_pitch;
       const int64_t slot0 = ((int64_t)p.push.rank * p.R + row) * p.push.prefix;
-      const bool pairs = ((reinterpret_cast<uintptr_t>(mine) | (uintptr_t)(slot0 * 8)) & 15) == 0 && (p.push.prefix & 1) == 0;
-      if (pairs) {
-        for (int j = tid; 2 * j + 1 < npush; j += SEL_FINAL_THREADS) {
-          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine) + j);
-          for (int q = 0; q < p.push.n; ++q) reinterpret_cast<uint4*>(p.push.inbox[q] + slot0)[j] = v;
-        }
-        if ((npush & 1) && tid == 0) {
-          const uint64_t v = __ldcg(mine + npush - 1);
-          for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot0 + npush - 1] = v;
-        }
-      } else {
-        for (int j = tid; j < npush; j += SEL_FINAL_THREADS) {
-          const uint64_t v = __ldcg(mine + j);
-          for (int q = 0; q < p.push.n; ++q) p.push.inbox[q][slot0 + j] = v;
-        }
+      for (int j = tid; j < npush; j += SEL_FINAL_THREADS) {
+        const uint64_t v = __ldcg(mine + j);
+        for (int q = 0; q < p.push.n; ++q) st_pair2(p.push.inbox[q] + slot0 + j, v, epoch);
       }
     }
     if (p.push.n > 0) {
-      // every thread's stores (local list and the ranks' inboxes) precede the barrier; one thread per rank
-      // then makes them visible system-wide and raises this row's flag there
+      // The prefix entries are tagged pairs and need nothing more. The flag tells a rank that this row's WHOLE
+      // local list may be read (the merge does that only when the prefixes cannot decide the row): every
+      // thread's stores precede the barrier, one thread per rank then releases the flag there
       // (the release is cumulative over the barrier: it orders every thread's stores before the flag, at system
       // scope, without a separate fence)
       __syncthreads();

@@ -32,7 +32,7 @@ static ExchangeLayout exchange_layout(int B, int Hq, int Hkv, int top_k, int wor
   size_t off = 0;
   L.off_epoch = off;  off += 256;
   L.off_full = off;   off += round_up(sizeof(uint64_t) * (size_t)L.R * L.kk, 256);
-  L.off_inbox = off;  off += round_up(sizeof(uint64_t) * (size_t)world * L.R * L.prefix, 256);
+  L.off_inbox = off;  off += round_up(sizeof(uint4) * (size_t)world * L.R * L.prefix, 256);      // tagged pairs (st_pair2)
   L.off_flags = off;  off += round_up(sizeof(uint32_t) * (size_t)world * L.R, 256);
   L.off_part = off;   off += round_up(sizeof(uint2) * (size_t)world * L.BH * (AT_D + 2), 256);    // {bits, step} pairs
   L.off_pflags = off; off += round_up(sizeof(uint32_t) * (size_t)world * L.BH, 256);
@@ -261,7 +261,7 @@ extern "C" __attribute__((visibility("default"))) int kvb_sharded_decode_step(co
     push.n = N; push.rank = me; push.prefix = X.prefix; push.epoch = epoch;
     for (int r = 0; r < N; ++r) {
       uint8_t* xr = reinterpret_cast<uint8_t*>(p->exchange[r]);
-      push.inbox[r] = reinterpret_cast<uint64_t*>(xr + X.off_inbox);
+      push.inbox[r] = reinterpret_cast<uint4*>(xr + X.off_inbox);
       push.flags[r] = reinterpret_cast<uint32_t*>(xr + X.off_flags);
     }
     rc = shard_candidates_run(p->query, p->q_sb, p->q_sh, p->packed, p->packed_sb, p->packed_sh, p->scale, p->scale_sb,
@@ -280,7 +280,8 @@ extern "C" __attribute__((visibility("default"))) int kvb_sharded_decode_step(co
     sp.hist = nullptr; sp.cand = nullptr; sp.cand_count = nullptr; sp.cap = select_cap(k);
     sp.tokens_per_cta = 0; sp.thresholds = nullptr;
     sp.from_candidates = 0; sp.row_failed = nullptr; sp.T_dev = nullptr;
-    sp.gather = reinterpret_cast<const uint64_t*>(mine + X.off_inbox);
+    sp.gather = nullptr;                                    // (the prefixes are read from wait.inbox)
+    sp.wait.inbox = reinterpret_cast<const uint4*>(mine + X.off_inbox);
     sp.gather_n = N; sp.gather_len = X.kk; sp.gather_stride = (int64_t)X.R * X.prefix; sp.gather_pitch = X.prefix;
     sp.gather_prefix = X.prefix;
     sp.rescue = 0;

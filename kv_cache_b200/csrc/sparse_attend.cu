@@ -517,7 +517,7 @@ __global__ void __launch_bounds__(AT_THREADS) lse_merge_pairs_kernel(const uint2
                                                                      __nv_bfloat16* out, PartialWait wait) {
   constexpr int PW = AT_D + 2;
   const int bh = blockIdx.x, d = threadIdx.x;
-  pdl_wait();
+  // (no wait for the kernel before it: everything this kernel reads arrives as tagged pairs)
   const uint32_t epoch = *wait.epoch;
   float M = -INFINITY;
   float m_r[KVB_MAX_RANKS], l_r[KVB_MAX_RANKS], o_r[KVB_MAX_RANKS];
