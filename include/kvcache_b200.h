@@ -415,20 +415,22 @@ int kvb_attend_selected_blend(const void* query, int64_t q_sb, int64_t q_sh,
  * token's K/V row are replicated. One call enqueues the whole step on `stream`:
  *   phase 1  sample -> candidate scorer -> exact local top-k; the last kernel stores its
  *            min(top_k, 8192/world) best (score, global id) composites per (batch, KV head) into
- *            EVERY rank's exchange buffer with ordinary 8-byte stores over NVLink and then raises a
- *            per-(source rank, row) flag there (st.release.sys);
- *   phase 2  global merge: waits for the `world` flags of its row (bounded polling), selects the
- *            global top-k from its LOCAL buffer with the acceptance test of kvb_merge_candidates
- *            (a row that fails it reads the ranks' whole lists with plain loads from their
- *            memory), compacts the winners this rank owns; attention over those rows; the chunk
- *            merge stores the un-normalised (o, m, l) of every (batch, head) into every rank's
- *            buffer and raises a second flag;
- *   phase 3  waits for the `world` partial flags and combines them by log-sum-exp into `out`
- *            (the same bits on every rank).
- * The flags carry a step number kept in the exchange buffer, so the same call sequence can be
+ *            EVERY rank's exchange buffer over NVLink as tagged pairs — each 32-bit half of a composite
+ *            beside the step number in one aligned 8-byte store, so a reader that finds the step number
+ *            has the half, without a fence or a flag — and then raises a per-(source rank, row) flag
+ *            there (st.release.sys), which says that the row's WHOLE local list may be read;
+ *   phase 2  global merge: polls the pairs of the `world` prefixes of its row in its LOCAL buffer (bounded),
+ *            selects the global top-k from them with the acceptance test of kvb_merge_candidates (a
+ *            row that fails it waits for the `world` flags and reads the ranks' whole lists with plain
+ *            loads from their memory), compacts the winners this rank owns; attention over those rows;
+ *            the chunk merge stores the un-normalised (o, m, l) of every (batch, head) into every rank's
+ *            buffer, again as tagged pairs;
+ *   phase 3  polls the `world` partials' pairs and combines them by log-sum-exp into `out` (the same
+ *            bits on every rank).
+ * Pairs and flags carry a step number kept in the exchange buffer, so the same call sequence can be
  * captured once in a CUDA graph and replayed. Every wait gives up after wait_polls polls (0 = a few
- * seconds' worth), sets KVB_TIMEOUT in the device status word and lets the kernel return. Only plain
- * loads and stores touch peer memory.
+ * seconds' worth), sets KVB_TIMEOUT in the device status word and lets the kernel return. Only plain and
+ * volatile loads and stores and the flags' release/acquire operations touch peer memory.
  *
  * All ranks must call with the same B, Hq, Hkv, top_k, world and take the same number of steps.
  * Needs the streaming scorer configuration (C in {32,64,128}, G in {1,2,4,8}, aligned side cache),
