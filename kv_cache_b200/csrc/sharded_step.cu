@@ -19,7 +19,7 @@ namespace kvb {
 
 struct ExchangeLayout {
   int R, BH, kk, prefix;
-  size_t off_epoch, off_full, off_inbox, off_flags, off_part, off_pflags, bytes;
+  size_t off_epoch, off_full, off_inbox, off_flags, off_part, bytes;
 };
 
 // Identical on every rank (it depends on the problem shape and the world size only).
@@ -35,7 +35,6 @@ static ExchangeLayout exchange_layout(int B, int Hq, int Hkv, int top_k, int wor
   L.off_inbox = off;  off += round_up(sizeof(uint4) * (size_t)world * L.R * L.prefix, 256);      // tagged pairs (st_pair2)
   L.off_flags = off;  off += round_up(sizeof(uint32_t) * (size_t)world * L.R, 256);
   L.off_part = off;   off += round_up(sizeof(uint2) * (size_t)world * L.BH * (AT_D + 2), 256);    // {bits, step} pairs
-  L.off_pflags = off; off += round_up(sizeof(uint32_t) * (size_t)world * L.BH, 256);
   L.bytes = off;
   return L;
 }

@@ -49,6 +49,22 @@ def test_size_queries_need_no_gpu():
     assert lib.kvb_decode_step_workspace_bytes(16, 32, 8, 131072, 2048, 0, 0, 1) > 16 * 8 * 131072 * 4
 
 
+def test_exchange_buffer_size_follows_the_documented_layout():
+    """step counter | full candidate lists [R, k] of 8-byte composites | inbox [N, R, prefix] of 16-byte tagged
+    pairs | flags [N, R] | partial inbox [N, B*Hq, D+2] of 8-byte tagged pairs, each area rounded to 256 bytes."""
+    lib = _native.lib()
+    D = 128
+    for B, Hq, Hkv, k, N in [(4, 32, 8, 4096, 1), (4, 32, 8, 4096, 2), (4, 32, 8, 4096, 8), (2, 8, 2, 64, 3),
+                             (16, 32, 8, 2048, 4)]:
+        R = B * Hkv
+        prefix = min(k, 8192 // N)
+        assert N * prefix >= k                                    # the prefixes alone can hold a full answer
+        areas = [4, 8 * R * k, 16 * N * R * prefix, 4 * N * R, 8 * N * B * Hq * (D + 2)]
+        got = lib.kvb_sharded_exchange_bytes(B, Hq, Hkv, k, N)
+        assert sum(areas) <= got <= sum(areas) + 256 * len(areas)
+        assert got % 256 == 0
+
+
 def test_bad_arguments_are_rejected_before_any_launch():
     lib = _native.lib()
     # null pointers / impossible shapes return a status without touching a device
