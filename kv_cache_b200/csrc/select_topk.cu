@@ -425,12 +425,16 @@ __global__ void __launch_bounds__(SEL_FINAL_THREADS) select_final_kernel(SelectP
   const SelectParams& p = pin;
   const int out_pitch = pin.out_pitch > 0 ? pin.out_pitch : pin.kk;     // rows of the outputs stay kk_max apart
   int rT = pin.T, rkk = pin.kk;
-  pdl_launch_dependents();
+  // A kernel that pushes its winners to the ranks is followed by a merge that reads the step number WITHOUT
+  // waiting for its predecessors: that merge may become resident only after this kernel's own wait has
+  // returned, i.e. after the first kernel of the step — which increments the step number — has completed.
+  if (pin.push.n == 0) pdl_launch_dependents();
   // The merge of the ranks' prefixes takes nothing from the kernel before it in the stream except what that
   // kernel stores into the inbox as tagged pairs (and, for a row the prefixes cannot decide, lists guarded by
   // flags): it does not wait for that kernel to end — its blocks poll the pairs while the local select still
   // runs, so neither that kernel's tail (the release of its flags) nor a launch gap lies on the step's path.
   if (pin.wait.n == 0) pdl_wait();
+  if (pin.push.n > 0) pdl_launch_dependents();
   if (p.T_dev) {
     const int t = *p.T_dev;
     rT = t < pin.T ? t : pin.T;
